@@ -1,0 +1,87 @@
+// Shared helpers of the sm_100a kernels: element types, warp and block reductions, launch checks.
+//
+// Every kernel file exports plain C functions (`extern "C" int tb_*`) that take raw device
+// pointers, sizes and a stream, launch, and return the CUDA error code of the launch (0 = ok).
+// The element type of activations and caches is chosen at run time by `dtype` (TB_F32 / TB_BF16);
+// arithmetic inside the kernels is float32 whatever the storage type.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TB_F32 0
+#define TB_BF16 1
+
+#define TB_ERR_BAD_DTYPE 10001
+#define TB_ERR_BAD_SIZE 10002
+
+namespace tb {
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+inline int launch_status() { return (int)cudaGetLastError(); }
+
+}  // namespace tb
+
+// Run `call<T>(...)` with T picked by a run-time dtype code.
+#define TB_DISPATCH_DTYPE(dtype, ...)                         \
+  do {                                                        \
+    if ((dtype) == TB_F32) {                                  \
+      using T = float;                                        \
+      __VA_ARGS__;                                            \
+    } else if ((dtype) == TB_BF16) {                          \
+      using T = __nv_bfloat16;                                \
+      __VA_ARGS__;                                            \
+    } else {                                                  \
+      return TB_ERR_BAD_DTYPE;                                \
+    }                                                         \
+  } while (0)

@@ -1,0 +1,193 @@
+// Per-token kernels: embedding gather, residual-add + RMSNorm, q/k-norm + rotary + cache write,
+// SiLU-and-multiply.  All arithmetic is float32; T is the storage type of activations and caches.
+//
+// Formulas: 12vivi/tandem python/tandem/layers/ops.py:29-61 (norm, fused add+norm, silu_and_mul,
+// rotate_half), python/tandem/layers/triton_ops.py:21-113 (the fused prologue and the fused
+// add+norm, which add in float32 and round once, as these kernels do).
+#include "common.cuh"
+
+namespace tb {
+
+// ---------------------------------------------------------------------------------------------
+// Embedding: out[t, :] = float(table[ids[t], :]).  The residual stream is float32 in both modes.
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ out, int H, int V) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* o = out + (size_t)t * H;
+  if (id < 0 || id >= V) {  // the host checks ids; never read outside the table
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+    return;
+  }
+  const T* row = table + (size_t)id * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// residual[src] += x[src] (if x); y[r] = residual[src] * rsqrt(mean(residual[src]^2) + eps) * w
+// with src = rows ? rows[r] : r.  One block per output row.
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ residual,
+                                   const float* __restrict__ weight, T* __restrict__ y,
+                                   const int* __restrict__ rows, int H, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * H;
+  const T* xr = x ? x + (size_t)src * H : nullptr;
+  float ss = 0.f;
+  if ((H & 3) == 0) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 s = *reinterpret_cast<const float4*>(res + i);
+      if (xr) {
+        s.x += to_float(xr[i]); s.y += to_float(xr[i + 1]); s.z += to_float(xr[i + 2]); s.w += to_float(xr[i + 3]);
+        *reinterpret_cast<float4*>(res + i) = s;
+      }
+      ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float s = res[i];
+      if (xr) { s += to_float(xr[i]); res[i] = s; }
+      ss += s * s;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  T* yr = y + (size_t)r * H;
+  // each thread re-reads only what it wrote itself above
+  if ((H & 3) == 0) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      const float4 s = *reinterpret_cast<const float4*>(res + i);
+      const float4 w = *reinterpret_cast<const float4*>(weight + i);
+      yr[i] = from_float<T>(s.x * inv * w.x);
+      yr[i + 1] = from_float<T>(s.y * inv * w.y);
+      yr[i + 2] = from_float<T>(s.z * inv * w.z);
+      yr[i + 3] = from_float<T>(s.w * inv * w.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_float<T>(res[i] * inv * weight[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// One warp per (token, head) of the fused projection qkv [T, (nh + 2 nkv) * hd]:
+//   q heads: optional RMSNorm over hd, rotary, written back in place;
+//   k heads: optional RMSNorm, rotary, written to the key cache at the token's slot;
+//   v heads: copied to the value cache.
+// Cache layout [page][kv head][offset in page][hd]; slot = page * page_size + offset; a negative
+// slot (padding row) or write_kv == 0 (the run reads another run's cache) writes nothing.
+// Rotary: pairs (j, j + rd/2), j < rd/2, angle table cs[pos][0..rd/2) = cos, [rd/2..rd) = sin.
+template <typename T>
+__global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                       const int* __restrict__ slots, const float* __restrict__ q_w,
+                                       const float* __restrict__ k_w, const float* __restrict__ cos_sin,
+                                       T* __restrict__ k_cache, T* __restrict__ v_cache, int T_tokens, int nh,
+                                       int nkv, int hd, int rd, int page_size, float eps, int write_kv,
+                                       int max_pos) {
+  const int lane = threadIdx.x & 31;
+  const int heads = nh + 2 * nkv;
+  const long long g = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (g >= (long long)T_tokens * heads) return;
+  const int t = (int)(g / heads), h = (int)(g % heads);
+  T* x = qkv + (size_t)t * heads * hd + (size_t)h * hd;
+  const int slot = slots ? slots[t] : -1;
+  const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+  if (!is_q && (slot < 0 || !write_kv)) return;
+
+  T* dst = x;
+  if (!is_q) {
+    const int kvh = is_k ? h - nh : h - nh - nkv;
+    const size_t page = slot / page_size, off = slot % page_size;
+    dst = (is_k ? k_cache : v_cache) + ((page * nkv + kvh) * page_size + off) * hd;
+  }
+  if (!is_q && !is_k) {  // v: plain copy
+    for (int d = lane; d < hd; d += 32) dst[d] = x[d];
+    return;
+  }
+  const float* w = is_q ? q_w : k_w;
+  float inv = 1.f;
+  if (w) {
+    float ss = 0.f;
+    for (int d = lane; d < hd; d += 32) { const float v = to_float(x[d]); ss += v * v; }
+    ss = warp_sum(ss);
+    inv = rsqrtf(ss / (float)hd + eps);
+  }
+  int pos = positions[t];
+  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);  // the host checks positions
+  const int half = rd >> 1;
+  const float* cs = cos_sin + (size_t)pos * rd;
+  for (int j = lane; j < half; j += 32) {
+    float a = to_float(x[j]) * inv, b = to_float(x[j + half]) * inv;
+    if (w) { a *= w[j]; b *= w[j + half]; }
+    const float c = cs[j], s = cs[half + j];
+    dst[j] = from_float<T>(a * c - b * s);
+    dst[j + half] = from_float<T>(b * c + a * s);
+  }
+  for (int d = rd + lane; d < hd; d += 32) {  // dims beyond the rotary part pass through
+    float a = to_float(x[d]) * inv;
+    if (w) a *= w[d];
+    dst[d] = from_float<T>(a);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i]
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I) {
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (long long)gridDim.x * blockDim.x) {
+    const long long t = e / I;
+    const int i = (int)(e % I);
+    const float g = to_float(gu[t * 2 * I + i]);
+    const float u = to_float(gu[t * 2 * I + I + i]);
+    out[e] = from_float<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+}  // namespace tb
+
+extern "C" {
+
+int tb_embedding(void* stream, const int* ids, const void* table, float* out, int T_tokens, int H, int V,
+                 int dtype) {
+  if (T_tokens <= 0) return 0;
+  TB_DISPATCH_DTYPE(dtype, tb::embedding_kernel<T><<<T_tokens, 256, 0, (cudaStream_t)stream>>>(
+                               ids, (const T*)table, out, H, V));
+  return tb::launch_status();
+}
+
+int tb_add_rmsnorm(void* stream, const void* x, float* residual, const float* weight, void* y, const int* rows,
+                   int num_rows, int H, float eps, int dtype) {
+  if (num_rows <= 0) return 0;
+  const int threads = H >= 4096 ? 512 : 256;
+  TB_DISPATCH_DTYPE(dtype, tb::add_rmsnorm_kernel<T><<<num_rows, threads, 0, (cudaStream_t)stream>>>(
+                               (const T*)x, residual, weight, (T*)y, rows, H, eps));
+  return tb::launch_status();
+}
+
+int tb_qk_norm_rope_kv(void* stream, void* qkv, const int* positions, const int* slots, const float* q_w,
+                       const float* k_w, const float* cos_sin, void* k_cache, void* v_cache, int T_tokens, int nh,
+                       int nkv, int hd, int rd, int page_size, float eps, int write_kv, int max_pos, int dtype) {
+  if (T_tokens <= 0) return 0;
+  if (rd < 0 || rd > hd || (rd & 1) || page_size <= 0) return TB_ERR_BAD_SIZE;
+  const long long warps = (long long)T_tokens * (nh + 2 * nkv);
+  const int blocks = (int)((warps + 3) / 4);
+  TB_DISPATCH_DTYPE(dtype, tb::qk_norm_rope_kv_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(
+                               (T*)qkv, positions, slots, q_w, k_w, cos_sin, (T*)k_cache, (T*)v_cache, T_tokens, nh,
+                               nkv, hd, rd, page_size, eps, write_kv, max_pos));
+  return tb::launch_status();
+}
+
+int tb_silu_mul(void* stream, const void* gu, void* out, int T_tokens, int I, int dtype) {
+  const long long total = (long long)T_tokens * I;
+  if (total <= 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  TB_DISPATCH_DTYPE(dtype, tb::silu_mul_kernel<T><<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
+                               (const T*)gu, (T*)out, total, I));
+  return tb::launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,145 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``run`` takes any mix of prompt portions and single decoded tokens, cut anywhere, flattens them
+into one batch, runs exactly those tokens from the cache that earlier steps left, and returns
+float32 logits at the wanted places only.  It samples nothing.  12vivi/tandem's counterpart is
+``ModelRunner.launch`` (python/tandem/executor/model_runner.py:83-163), which also samples;
+its batch description is python/tandem/layers/flashinfer_attention.py:39-67.
+
+``step`` is ``run`` with the cache bookkeeping around it (admit, take pages, commit, end), for
+callers that drive the engine without the scheduler: trace replay and tests.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from tandem_b200.cache.manager import CacheManager, OutOfPages
+from tandem_b200.cache.storage import CacheStorage
+from tandem_b200.models.decoder import Decoder
+from tandem_b200.parts.base import StepContext
+
+
+@dataclass
+class StepEntry:
+    request_id: str
+    tokens: Sequence[int]  # the request's next tokens
+    want: Sequence[int] = field(default_factory=list)  # places among ``tokens`` whose logits are returned
+
+
+class Executor:
+    def __init__(self, decoder: Decoder, manager: CacheManager, storage: CacheStorage) -> None:
+        self.decoder, self.manager, self.storage = decoder, manager, storage
+        self.device = decoder.device
+        self.vocab_size = decoder.plan.embedding.vocab_size
+        self.max_position = decoder.plan.max_position
+        self.num_steps = 0
+
+    # ------------------------------------------------------------------ batch description
+    def build_context(self, entries: Sequence[StepEntry]) -> tuple[StepContext, list]:
+        """Flatten the entries: token ids, positions, the request of each token, slots and block
+        tables per cache group.  All integers travel to the device in one copy."""
+        m, ps = self.manager, self.manager.page_size
+        ids, positions, seq_of_token, cu, starts, lens, slots_host, rows = [], [], [], [0], [], [], [], []
+        for b, e in enumerate(entries):
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.request_id!r} brings no tokens")
+            start = m.num_tokens(e.request_id)
+            if start + n > self.max_position:
+                raise ValueError(f"request {e.request_id!r} would reach position {start + n - 1}; "
+                                 f"the model's position table ends at {self.max_position - 1}")
+            for tok in e.tokens:
+                if not 0 <= int(tok) < self.vocab_size:
+                    raise ValueError(f"token id {tok} of request {e.request_id!r} is outside the vocabulary "
+                                     f"[0, {self.vocab_size})")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.request_id!r} wants logits at place {w} of {n} tokens")
+                rows.append(cu[-1] + w)
+            ids.extend(int(t) for t in e.tokens)
+            positions.extend(range(start, start + n))
+            seq_of_token.extend([b] * n)
+            cu.append(cu[-1] + n)
+            starts.append(start)
+            lens.append(n)
+            slots_host.append(m.slot(e.request_id))
+        T, B = len(ids), len(entries)
+        max_total = max((s + n for s, n in zip(starts, lens)), default=0)
+        width = max(1, -(-max_total // ps))
+        per_group = []
+        for g in range(len(m.groups)):
+            table = []
+            slot_list = []
+            for e, start, n in zip(entries, starts, lens):
+                t = m.table(g, e.request_id)
+                if len(t) * ps < start + n:
+                    raise OutOfPages(f"request {e.request_id!r} holds {len(t)} pages, {start + n} tokens need more")
+                table.extend(t[:width] + [-1] * (width - len(t[:width])))
+                slot_list.extend(m.slot_index(g, e.request_id, p) for p in range(start, start + n))
+            per_group.append((table, slot_list))
+
+        parts = [ids, positions, seq_of_token, cu, starts, slots_host, rows]
+        for table, slot_list in per_group:
+            parts += [table, slot_list]
+        flat = torch.tensor([x for p in parts for x in p], dtype=torch.int32).pin_memory() \
+            if self.device.type == "cuda" else torch.tensor([x for p in parts for x in p], dtype=torch.int32)
+        dev = flat.to(self.device, non_blocking=True)
+        views, off = [], 0
+        for p in parts:
+            views.append(dev[off: off + len(p)])
+            off += len(p)
+        ctx = StepContext(
+            dtype=self.decoder.dtype, device=self.device, num_tokens=T, num_seqs=B,
+            token_ids=views[0], positions=views[1], seq_of_token=views[2], cu_seqlens=views[3],
+            seq_starts=views[4], state_slots=views[5], host_starts=starts, host_lens=lens, host_slots=slots_host,
+            max_new=max(lens, default=0), max_total=max_total, storage=self.storage,
+        )
+        for g in range(len(m.groups)):
+            ctx.tables[g] = (views[7 + 2 * g].view(B, width), views[8 + 2 * g])
+        logit_rows = views[6]
+        return ctx, logit_rows
+
+    # ------------------------------------------------------------------ the step
+    @torch.inference_mode()
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Logits float32 [R, vocab] at the wanted places, in the order of the entries and of
+        their ``want``.  The requests must be live and hold the pages for their new tokens."""
+        if not entries:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        for e in entries:
+            if self.manager.num_tokens(e.request_id) == 0:  # new, or recomputed from the start
+                self.storage.reset_state(self.manager.slot(e.request_id))
+        ctx, logit_rows = self.build_context(entries)
+        logits = self.decoder.forward(ctx, logit_rows)
+        self.num_steps += 1
+        return logits
+
+    def step(self, entries: Sequence[StepEntry], end: Sequence[str] = ()) -> torch.Tensor:
+        """``run`` plus the bookkeeping: unknown requests are admitted, pages are taken for the new
+        tokens (OutOfPages if the pool cannot give them: nothing has run then), the tokens are
+        committed, and the requests in ``end`` give back what they hold afterwards."""
+        m = self.manager
+        begun = []
+        try:
+            for e in entries:
+                if not m.has(e.request_id):
+                    m.begin(e.request_id)
+                    begun.append(e.request_id)
+                if not m.grow(e.request_id, m.num_tokens(e.request_id) + len(e.tokens)):
+                    raise OutOfPages(f"no pages left for request {e.request_id!r} "
+                                     f"({m.num_tokens(e.request_id)} + {len(e.tokens)} tokens)")
+        except OutOfPages:
+            for rid in begun:
+                m.end(rid)
+            raise
+        logits = self.run(entries)
+        for e in entries:
+            m.commit(e.request_id, len(e.tokens))
+        for rid in end:
+            if m.has(rid):
+                m.end(rid)
+        return logits

@@ -1,0 +1,192 @@
+"""The engine a user holds: requests in, tokens out.
+
+``LLMEngine`` wires configuration, model, cache manager, scheduler, step function and sampler
+(12vivi/tandem python/tandem/engine/llm_engine.py:38-175), with the same calls: ``add_request``,
+``step``, ``generate``, ``abort_request``, ``stats``.  Prompts are lists of token ids; text
+prompts need a tokenizer, which this engine loads only when the model folder has one.
+``LLM`` is the short spelling: ``LLM(model=...).generate(prompts, sampling_params)``.
+"""
+
+from __future__ import annotations
+
+import itertools
+import os
+import time
+from typing import Optional, Sequence, Union
+
+import torch
+
+from tandem_b200.config.engine_config import EngineConfig
+from tandem_b200.engine.core import build_executor, load_model
+from tandem_b200.engine.executor import StepEntry
+from tandem_b200.engine.request import Request, RequestOutput, RequestStatus
+from tandem_b200.engine.scheduler import Scheduler, StepPlan
+from tandem_b200.sampling.params import SamplingParams
+from tandem_b200.sampling.sampler import sample
+
+PromptType = Union[str, Sequence[int]]
+
+
+class LLMEngine:
+    def __init__(self, config: EngineConfig, decoder=None, model_config=None, tokenizer=None,
+                 load_tokenizer: bool = True) -> None:
+        """``decoder`` / ``model_config``: a model that is already built (random weights made on
+        the device, tests); otherwise ``config.model`` is a folder read through the registry."""
+        self.config = config
+        if decoder is None:
+            decoder, model_config = load_model(config.model, config.resolved_dtype, config.device)
+        self.decoder, self.model_config = decoder, model_config
+        plan = decoder.plan
+        self.max_model_len = config.max_model_len or min(plan.max_position, 32768)  # llm_engine.py:55
+        if self.max_model_len > plan.max_position:
+            raise ValueError(f"max_model_len {self.max_model_len} exceeds the model's {plan.max_position} positions")
+        self.executor = build_executor(decoder, config.block_size, config.num_kv_blocks, config.kv_cache_memory_gb,
+                                       config.max_num_seqs)
+        self.cache = self.executor.manager
+        self.scheduler = Scheduler(self.cache, config.max_num_seqs, config.max_num_batched_tokens,
+                                   self.max_model_len, config.schedule_policy)
+        self.eos_token_ids = list(plan.eos_token_ids)
+        self.tokenizer = tokenizer
+        if tokenizer is None and load_tokenizer and config.model and \
+                os.path.isfile(os.path.join(config.model, "tokenizer.json")):
+            from transformers import AutoTokenizer  # text in and out only; no model code
+
+            self.tokenizer = AutoTokenizer.from_pretrained(config.model)
+        self.requests: dict = {}
+        self._ids = itertools.count()
+        self.num_steps = 0
+        self.graphs = None
+        if config.cuda_graph and decoder.dtype == torch.bfloat16:
+            from tandem_b200.engine.cuda_graph import DecodeGraphs
+
+            self.graphs = DecodeGraphs.maybe(self.executor, config.cuda_graph_max_bs, self.max_model_len)
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt: Optional[PromptType] = None, sampling_params: Optional[SamplingParams] = None,
+                    request_id: Optional[str] = None, prompt_token_ids: Optional[Sequence[int]] = None) -> str:
+        sp = sampling_params or SamplingParams()
+        if prompt_token_ids is None:
+            if isinstance(prompt, str):
+                if self.tokenizer is None:
+                    raise ValueError("text prompts need a tokenizer; pass token ids")
+                prompt_token_ids = self.tokenizer.encode(prompt)
+            elif prompt is not None:
+                prompt_token_ids = list(prompt)
+            else:
+                raise ValueError("either prompt or prompt_token_ids is required")
+        if not prompt_token_ids:
+            raise ValueError("empty prompt")
+        vocab = self.decoder.plan.embedding.vocab_size
+        for t in prompt_token_ids:
+            if not 0 <= int(t) < vocab:
+                raise ValueError(f"token id {t} is outside the vocabulary [0, {vocab})")
+        if len(prompt_token_ids) >= self.max_model_len:
+            raise ValueError(f"prompt has {len(prompt_token_ids)} tokens; max_model_len is {self.max_model_len}")
+        index = next(self._ids)
+        rid = request_id or f"req-{index}"
+        if rid in self.requests:
+            raise ValueError(f"duplicate request id {rid}")
+        # a request without a seed draws from the engine's seed and its own arrival number
+        seed = sp.seed if sp.seed is not None else (self.config.seed * 1_000_003 + index + 1)
+        req = Request(rid, list(prompt_token_ids), sp, self.eos_token_ids, sample_seed=seed)
+        self.scheduler.add_request(req)
+        self.requests[rid] = req
+        return rid
+
+    def abort_request(self, request_id: str) -> None:
+        req = self.requests.pop(request_id, None)
+        if req is not None and not req.finished:
+            self.scheduler.finish_request(req, RequestStatus.FINISHED_ABORTED)
+
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    # ------------------------------------------------------------------ step
+    def step(self) -> list:
+        """schedule -> run -> sample -> update (llm_engine.py:284-296 of 12vivi/tandem)."""
+        plan = self.scheduler.schedule()
+        if plan.is_empty:
+            if self.scheduler.has_unfinished() and not plan.preempted:
+                raise RuntimeError("the scheduler could place no request: the cache pool is too small")
+            return []
+        sampled = self._execute(plan)
+        updated = self.scheduler.update_from_output(plan, sampled)
+        self.num_steps += 1
+        outputs = []
+        for req in updated:
+            outputs.append(self._make_output(req))
+            if req.finished:
+                self.requests.pop(req.request_id, None)
+        return outputs
+
+    def _execute(self, plan: StepPlan) -> dict:
+        entries, sampling = [], []
+        for s in plan.scheduled:
+            req, n = s.request, s.num_tokens
+            start = req.num_computed_tokens
+            reaches_end = start + n >= req.num_tokens  # model_runner.py:102-105: only then logits
+            entries.append(StepEntry(req.request_id, req.token_ids_in_range(start, start + n),
+                                     [n - 1] if reaches_end else []))
+            if reaches_end:
+                sampling.append(req)
+        if self.graphs is not None and self.graphs.takes(entries):
+            logits = self.graphs.run(entries)
+        else:
+            logits = self.executor.run(entries)
+        tokens = sample(logits, [r.sampling_params for r in sampling], [r.sample_seed for r in sampling],
+                        [r.num_output_tokens for r in sampling])
+        return {r.request_id: t for r, t in zip(sampling, tokens)}
+
+    def _make_output(self, req: Request) -> RequestOutput:
+        metrics = {}
+        if req.first_token_time is not None:
+            metrics["ttft"] = req.first_token_time - req.arrival_time
+        if req.finished and req.finish_time is not None:
+            metrics["latency"] = req.finish_time - req.arrival_time
+            metrics["preemptions"] = req.num_preemptions
+        text = ""
+        if self.tokenizer is not None and req.finished:
+            text = self.tokenizer.decode(req.output_token_ids, skip_special_tokens=req.sampling_params.skip_special_tokens)
+        return RequestOutput(req.request_id, req.prompt_token_ids,
+                             list(req.output_token_ids) if req.finished else [], text, list(req.new_token_ids),
+                             req.finished, req.finish_reason, metrics, req.num_output_tokens)
+
+    # ------------------------------------------------------------------ offline API
+    def generate(self, prompts: Sequence[PromptType],
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> list:
+        """Run the prompts to completion; outputs in the order of the prompts (llm_engine.py:411-426)."""
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            params = [sampling_params or SamplingParams()] * len(prompts)
+        else:
+            params = list(sampling_params)
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        final = {}
+        while self.has_unfinished_requests():
+            for out in self.step():
+                if out.finished:
+                    final[out.request_id] = out
+        return [final[i] for i in ids]
+
+    def stats(self) -> dict:
+        return {
+            "steps": self.num_steps,
+            "free_kv_blocks": self.cache.free_pages(0) if self.cache.groups else 0,
+            "total_kv_blocks": self.cache.num_pages,
+            "running": len(self.scheduler.running),
+            "waiting": len(self.scheduler.waiting),
+            "preemptions": self.scheduler.num_preemptions,
+        }
+
+
+class LLM:
+    """``LLM(model=folder, dtype=..., **engine options).generate(prompts, sampling_params)``."""
+
+    def __init__(self, model: str, **options) -> None:
+        self.engine = LLMEngine(EngineConfig(model=model, **options))
+
+    def generate(self, prompts: Sequence[PromptType],
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> list:
+        return self.engine.generate(prompts, sampling_params)
+
+    def stats(self) -> dict:
+        return self.engine.stats()

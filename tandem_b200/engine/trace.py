@@ -1,0 +1,74 @@
+"""Trace replay: feed given token ids through a model step by step and write logits.
+
+Reads one JSON object per line,
+``{"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}``,
+runs every line as one step of the engine's own step function (the model, cache manager and
+kernels that generation uses), writes the float32 logits at the wanted places to
+``<out>/<step>.f32`` ([wanted, vocab], little-endian, entries in order, ``want`` in order) and
+prints ``done <step>``.  It samples nothing and keeps no model, cache or loader of its own.
+
+12vivi/tandem has no such tool; its nearest pieces are the direct forward of
+tests/test_model_equivalence.py:22-26 and the step trace of python/tandem/executor/step_timer.py:57-68.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+from tandem_b200.cache.manager import cdiv
+
+
+def replay(model: str, dtype: str, out_dir: str, max_tokens: int, lines, device: str = "cuda:0",
+           page_size: int = 16, echo=None) -> int:
+    """Run the steps read from ``lines``.  The cache pool holds ``max_tokens`` tokens (each
+    request's count rounded up to 64, which whole pages of ``page_size`` divide), so pages are
+    used again as requests end.  Returns the number of steps run."""
+    import numpy as np
+
+    from tandem_b200.engine.core import build_executor, load_model
+    from tandem_b200.engine.executor import StepEntry
+
+    if 64 % page_size:
+        raise ValueError("page_size must divide 64")
+    os.makedirs(out_dir, exist_ok=True)
+    decoder, _ = load_model(model, dtype, device)
+    executor = build_executor(decoder, page_size=page_size, num_pages=max(1, cdiv(max_tokens, page_size)),
+                              max_requests=64)
+    steps = 0
+    for line in lines:
+        line = line.strip()
+        if not line:
+            continue
+        rec = json.loads(line)
+        entries = [StepEntry(str(e["id"]), list(e["tokens"]), list(e.get("want", []))) for e in rec.get("entries", [])]
+        logits = executor.step(entries, end=[str(r) for r in rec.get("end", [])])
+        if logits.shape[0]:
+            arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+            tmp = os.path.join(out_dir, f".{rec['step']}.f32.tmp")
+            arr.tofile(tmp)
+            os.replace(tmp, os.path.join(out_dir, f"{rec['step']}.f32"))
+        steps += 1
+        if echo is not None:
+            echo(f"done {rec['step']}")
+    return steps
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(prog="trace_run", description="replay a trace of steps and write logits")
+    p.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    p.add_argument("--out", required=True, help="folder for <step>.f32 files")
+    p.add_argument("--max-tokens", type=int, required=True, help="tokens the cache pool holds")
+    p.add_argument("--device", default="cuda:0")
+    p.add_argument("--block-size", type=int, default=16, help="tokens per cache page (divides 64)")
+    args = p.parse_args(argv)
+
+    def echo(text: str) -> None:
+        sys.stdout.write(text + "\n")
+        sys.stdout.flush()
+
+    replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, args.device, args.block_size, echo)
+    return 0

@@ -1,0 +1,227 @@
+"""Tensor-level entry points of the CUDA kernels.
+
+Each function checks what it is given (device, dtype, layout, sizes), refuses what the kernel
+does not take with a clear error, and launches on the current CUDA stream.  There is no CPU
+path and no library stand-in for these operations: a tensor that is not on a CUDA device, or a
+library that cannot be built, raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from tandem_b200.kernels.build import load_library
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dtype}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be on a CUDA device (there is no CPU path), got {t.device}")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        detail = {10001: "unsupported dtype", 10002: "unsupported size"}.get(status, f"CUDA error {status}")
+        raise KernelError(f"{what}: {detail}")
+
+
+# ----------------------------------------------------------------------------- token-wise
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """ids [T] int32, table [V, H] -> float32 [T, H] (the start of the residual stream)."""
+    _need(ids, "ids", torch.int32)
+    _need(table, "embedding table")
+    T, (V, H) = ids.numel(), table.shape
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    lib = load_library("tokenwise")
+    _check(lib.tb_embedding(_stream(), _ptr(ids), _ptr(table), _ptr(out), T, H, V, _code(table.dtype)), "embedding")
+    return out
+
+
+def add_rmsnorm(x: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual += x (in place, float32; skipped when x is None); returns RMSNorm(residual) * weight
+    in ``out_dtype``.  With ``rows`` [R] int32 only those rows are updated and returned, in that order."""
+    _need(residual, "residual", torch.float32)
+    _need(weight, "norm weight", torch.float32)
+    T, H = residual.shape
+    if weight.numel() != H:
+        raise KernelError(f"norm weight has {weight.numel()} elements, rows have {H}")
+    if x is not None:
+        _need(x, "x", out_dtype)
+        if x.shape != residual.shape:
+            raise KernelError(f"x {tuple(x.shape)} and residual {tuple(residual.shape)} differ")
+    n = T
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n = rows.numel()
+    y = torch.empty((n, H), dtype=out_dtype, device=residual.device)
+    lib = load_library("tokenwise")
+    _check(lib.tb_add_rmsnorm(_stream(), _ptr(x), _ptr(residual), _ptr(weight), _ptr(y), _ptr(rows), n, H,
+                              ctypes.c_float(eps), _code(out_dtype)), "add_rmsnorm")
+    return y
+
+
+def qk_norm_rope_kv(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor],
+                    q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
+                    k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], num_heads: int,
+                    num_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int, eps: float,
+                    write_kv: bool = True) -> None:
+    """In place on qkv [T, (nh + 2 nkv) hd]: per-head RMSNorm (if weights) and rotary encoding of q
+    and k; k and v of every token are stored at ``slots[t]`` of the caches
+    [pages, nkv, page_size, hd] (unless ``write_kv`` is false or the slot is negative)."""
+    _need(qkv, "qkv")
+    T = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected {(num_heads + 2 * num_kv_heads) * head_dim}")
+    _need(positions, "positions", torch.int32)
+    if rotary_dim % 2 or rotary_dim > head_dim:
+        raise KernelError(f"rotary_dim {rotary_dim} must be even and at most head_dim {head_dim}")
+    max_pos = 1
+    if rotary_dim:
+        _need(cos_sin, "cos_sin", torch.float32)
+        if cos_sin.shape[1] != rotary_dim:
+            raise KernelError(f"cos_sin has {cos_sin.shape[1]} columns, rotary_dim is {rotary_dim}")
+        max_pos = cos_sin.shape[0]
+    for w, n in ((q_weight, "q_norm weight"), (k_weight, "k_norm weight")):
+        if w is not None:
+            _need(w, n, torch.float32)
+            if w.numel() != head_dim:
+                raise KernelError(f"{n} has {w.numel()} elements, head_dim is {head_dim}")
+    if write_kv:
+        _need(slots, "slots", torch.int32)
+        for c, n in ((k_cache, "k_cache"), (v_cache, "v_cache")):
+            _need(c, n, qkv.dtype)
+            if tuple(c.shape[1:]) != (num_kv_heads, page_size, head_dim):
+                raise KernelError(f"{n} has shape {tuple(c.shape)}, expected [pages, {num_kv_heads}, {page_size}, {head_dim}]")
+    lib = load_library("tokenwise")
+    _check(lib.tb_qk_norm_rope_kv(_stream(), _ptr(qkv), _ptr(positions), _ptr(slots), _ptr(q_weight), _ptr(k_weight),
+                                  _ptr(cos_sin), _ptr(k_cache), _ptr(v_cache), T, num_heads, num_kv_heads, head_dim,
+                                  rotary_dim, page_size, ctypes.c_float(eps), int(bool(write_kv)), max_pos,
+                                  _code(qkv.dtype)), "qk_norm_rope_kv")
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """[T, 2I] = [gate | up] -> silu(gate) * up, [T, I]."""
+    _need(gate_up, "gate_up")
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("gate_up must have an even number of columns")
+    out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    lib = load_library("tokenwise")
+    _check(lib.tb_silu_mul(_stream(), _ptr(gate_up), _ptr(out), T, two_i // 2, _code(gate_up.dtype)), "silu_mul")
+    return out
+
+
+# ----------------------------------------------------------------------------- matrix products
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [M, K] @ weight [N, K]^T -> [M, N].  float32 operands run the CUDA-core kernel (true
+    32-bit arithmetic); bfloat16 operands run on the tensor cores with float32 accumulation."""
+    _need(x, "x")
+    _need(weight, "weight")
+    if x.dtype != weight.dtype:
+        raise KernelError(f"x is {x.dtype} but the weight is {weight.dtype}")
+    M, K = x.shape
+    N, K2 = weight.shape
+    if K != K2:
+        raise KernelError(f"x has {K} columns, the weight has {K2}")
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.float32:
+        if out_dtype != torch.float32:
+            raise KernelError("the 32-bit product returns float32")
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        lib = load_library("gemm_f32")
+        _check(lib.tb_gemm_f32(_stream(), _ptr(x), _ptr(weight), _ptr(out), M, N, K, K, N), "gemm_f32")
+        return out
+    from tandem_b200.kernels import gemm_bf16
+
+    return gemm_bf16.linear(x, weight, out_dtype)
+
+
+# ----------------------------------------------------------------------------- attention
+def paged_attention_simt(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                         seq_of_token: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int,
+                         head_dim: int, page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
+    """Causal attention of every token of the step over its request's pages, on the CUDA cores.
+    ``qkv`` [T, >= nh*hd]: the query heads are the first nh*hd columns of each row."""
+    _need(qkv, "qkv")
+    for c, n in ((k_cache, "k_cache"), (v_cache, "v_cache")):
+        _need(c, n, qkv.dtype)
+    _need(block_table, "block_table", torch.int32)
+    _need(seq_of_token, "seq_of_token", torch.int32)
+    _need(positions, "positions", torch.int32)
+    T = qkv.shape[0]
+    if num_heads % num_kv_heads:
+        raise KernelError(f"{num_heads} query heads cannot share {num_kv_heads} kv heads")
+    if head_dim > 512:
+        raise KernelError(f"head_dim {head_dim} is larger than the 512 this kernel takes")
+    out = torch.empty((T, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    lib = load_library("attention_simt")
+    _check(lib.tb_attention_simt(_stream(), _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+                                 block_table.stride(0), _ptr(seq_of_token), _ptr(positions), _ptr(out), T, num_heads,
+                                 num_kv_heads, head_dim, page_size, int(window or 0), ctypes.c_float(scale),
+                                 _code(qkv.dtype)), "attention_simt")
+    return out
+
+
+# ----------------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """[R, V] float32 -> int32 [R], the lowest index among equal maxima."""
+    _need(logits, "logits", torch.float32)
+    R, V = logits.shape
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    lib = load_library("sampling")
+    _check(lib.tb_argmax(_stream(), _ptr(logits), _ptr(out), R, V), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, uniform: torch.Tensor, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of logits [R, V] float32.  Per-row options as tensors [R]: temperature
+    (< 1e-5: argmax), top_k (<= 0: off), top_p (>= 1: off), min_p (<= 0: off) and the uniform
+    number in [0, 1) that decides the draw.  ``scratch`` [R, V] float32 holds the filtered
+    probabilities while the kernel runs."""
+    _need(logits, "logits", torch.float32)
+    R, V = logits.shape
+    for t, n, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
+                     (top_p, "top_p", torch.float32), (min_p, "min_p", torch.float32),
+                     (uniform, "uniform", torch.float32)):
+        _need(t, n, dt)
+        if t.numel() != R:
+            raise KernelError(f"{n} has {t.numel()} entries for {R} rows")
+    if scratch is None:
+        scratch = torch.empty((R, V), dtype=torch.float32, device=logits.device)
+    _need(scratch, "scratch", torch.float32)
+    if scratch.numel() < R * V:
+        raise KernelError("scratch is smaller than the logits")
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    lib = load_library("sampling")
+    _check(lib.tb_sample(_stream(), _ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p),
+                         _ptr(uniform), _ptr(scratch), _ptr(out), R, V), "sample")
+    return out

@@ -1,0 +1,60 @@
+"""Grouped-query attention over the paged cache.
+
+One fused projection (rows [q | k | v], python/tandem/layers/attention.py:69-74 of
+12vivi/tandem), optional per-head RMSNorm of q and k before the rotary encoding
+(attention.py:75-78,101-104), keys and values written to the token's slot before the scores are
+taken, so a portion attends to itself through the cache (attention.py:43-48), causal softmax
+attention with scale and an optional window, then the output projection (attention.py:106).
+Every size is a parameter of the spec; the mixer does not know which model it serves.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from tandem_b200.cache.manager import KVNeed
+from tandem_b200.config.plan import AttentionSpec, ParamSpec, WeightSource
+from tandem_b200.kernels import attention as attention_kernels
+from tandem_b200.kernels import ops
+from tandem_b200.parts.base import Mixer, StepContext
+from tandem_b200.parts.shared import position_encoding
+
+
+class PagedAttention(Mixer):
+    @staticmethod
+    def params(spec: AttentionSpec) -> dict:
+        q, kv, H, p = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim, spec.hidden_size, spec.prefix
+        out = {
+            "qkv": ParamSpec((q + 2 * kv, H), (WeightSource(f"{p}.q_proj.weight", 0, q),
+                                               WeightSource(f"{p}.k_proj.weight", q, kv),
+                                               WeightSource(f"{p}.v_proj.weight", q + kv, kv))),
+            "o": ParamSpec((H, q), (WeightSource(f"{p}.o_proj.weight"),)),
+        }
+        if spec.qk_norm:
+            out["q_norm"] = ParamSpec((spec.head_dim,), (WeightSource(f"{p}.q_norm.weight"),), role="vector")
+            out["k_norm"] = ParamSpec((spec.head_dim,), (WeightSource(f"{p}.k_norm.weight"),), role="vector")
+        return out
+
+    @staticmethod
+    def kv_need(spec: AttentionSpec) -> KVNeed:
+        return KVNeed(spec.num_kv_heads, spec.head_dim, spec.window)
+
+    def __init__(self, spec: AttentionSpec, weights: dict, dtype: torch.dtype, device) -> None:
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"{spec.num_heads} query heads cannot share {spec.num_kv_heads} kv heads")
+        self.spec = spec
+        self.qkv = weights["qkv"]
+        self.o = weights["o"]
+        self.q_norm = weights.get("q_norm")
+        self.k_norm = weights.get("k_norm")
+        self.position = position_encoding(spec.position, device)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        s = self.spec
+        qkv = ops.linear(x, self.qkv)
+        kv = ctx.kv()
+        ops.qk_norm_rope_kv(qkv, ctx.positions, kv.slots, self.q_norm, self.k_norm, self.position.cos_sin,
+                            kv.k, kv.v, s.num_heads, s.num_kv_heads, s.head_dim, self.position.rotary_dim,
+                            kv.page_size, s.qk_norm_eps, write_kv=kv.writable)
+        o = attention_kernels.paged_attention(qkv, kv, ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
+        return ops.linear(o, self.o)

@@ -1,0 +1,158 @@
+"""The scheduler's decisions, driven by fake tokens without a model (CPU), in the manner of
+tests/test_scheduler.py:20-81 of 12vivi/tandem."""
+
+import pytest
+
+from tandem_b200.cache.manager import CacheManager, KVNeed
+from tandem_b200.engine.request import Request, RequestStatus
+from tandem_b200.engine.scheduler import Scheduler
+from tandem_b200.sampling.params import SamplingParams
+
+
+def make(policy="prefill_first", pages=64, page_size=4, budget=8, max_seqs=8, max_len=256, window=None):
+    cache = CacheManager([KVNeed(2, 16, window)], page_size, pages, max_seqs)
+    return Scheduler(cache, max_seqs, budget, max_len, policy), cache
+
+
+def req(rid, n, max_tokens=4, **kw):
+    return Request(rid, list(range(1, n + 1)), SamplingParams(max_tokens=max_tokens, temperature=0.0, **kw),
+                   eos_token_ids=[0])
+
+
+def run_step(s, token=7):
+    plan = s.schedule()
+    sampled = {x.request.request_id: token for x in plan.scheduled
+               if x.request.num_computed_tokens + x.num_tokens >= x.request.num_tokens}
+    s.update_from_output(plan, sampled)
+    return plan
+
+
+def sizes(plan):
+    return [(x.request.request_id, x.num_tokens) for x in plan.scheduled]
+
+
+def test_prompt_is_cut_by_the_budget():
+    s, cache = make(budget=8)
+    s.add_request(req("a", 20))
+    assert [sizes(run_step(s)) for _ in range(3)] == [[("a", 8)], [("a", 8)], [("a", 4)]]
+    assert sizes(run_step(s)) == [("a", 1)]  # decoding now
+    cache.check()
+
+
+def test_budget_is_shared_in_arrival_order():
+    s, _ = make(budget=8)
+    for rid, n in (("a", 5), ("b", 5), ("c", 2)):
+        s.add_request(req(rid, n))
+    assert sizes(run_step(s)) == [("a", 5), ("b", 3)]
+    assert sizes(run_step(s)) == [("b", 2), ("c", 2)]  # prefill_first: a (decoding) waits
+
+
+def test_decode_first_mixes_and_prefill_first_does_not():
+    for policy, expect in (("decode_first", [("a", 1), ("b", 7)]), ("prefill_first", [("b", 8)])):
+        s, _ = make(policy=policy, budget=8)
+        s.add_request(req("a", 3, max_tokens=10))
+        run_step(s)
+        s.add_request(req("b", 12))
+        assert sizes(run_step(s)) == expect
+
+
+def test_prefill_first_falls_back_to_decoding_when_nothing_fits():
+    s, _ = make(pages=4, page_size=4, budget=16)
+    s.add_request(req("a", 10, max_tokens=3))  # 3 pages
+    run_step(s)
+    s.add_request(req("b", 8))  # needs 2 pages, 1 free: stays waiting at the head
+    plan = run_step(s)
+    assert sizes(plan) == [("a", 1)] and [r.request_id for r in s.waiting] == ["b"]
+
+
+def test_max_num_seqs_limits_admission():
+    s, _ = make(max_seqs=2, budget=64)
+    for rid in "abc":
+        s.add_request(req(rid, 3))
+    assert sizes(run_step(s)) == [("a", 3), ("b", 3)] and len(s.waiting) == 1
+
+
+def test_finishing_by_length_eos_and_stop_token():
+    s, cache = make(budget=64)
+    s.add_request(req("a", 3, max_tokens=2))
+    run_step(s), run_step(s)
+    assert not s.has_unfinished() and cache.all_free()
+    s.add_request(r := req("b", 3, max_tokens=9))
+    run_step(s, token=0)  # eos
+    assert r.status is RequestStatus.FINISHED_STOPPED and r.finish_reason == "stop"
+    s.add_request(r := req("c", 3, max_tokens=9, ignore_eos=True, stop_token_ids=[5]))
+    run_step(s, token=0)
+    assert not r.finished
+    run_step(s, token=5)
+    assert r.finish_reason == "stop" and r.output_token_ids == [0, 5] and cache.all_free()
+
+
+def test_max_model_len_ends_a_request():
+    s, _ = make(max_len=6, budget=64)
+    s.add_request(r := req("a", 4, max_tokens=50))
+    while s.has_unfinished():
+        run_step(s)
+    assert r.finish_reason == "length" and r.num_tokens == 6
+    with pytest.raises(ValueError):
+        s.add_request(req("b", 6))
+
+
+def test_pages_run_out_youngest_is_preempted_and_recomputed():
+    # 6 pages of 4 tokens; two requests of 8 + up to 10 tokens cannot both grow to the end
+    s, cache = make(policy="decode_first", pages=6, page_size=4, budget=32)
+    a, b = req("a", 8, max_tokens=10), req("b", 8, max_tokens=10)
+    s.add_request(a), s.add_request(b)
+    preempted = []
+    steps = 0
+    while s.has_unfinished():
+        plan = run_step(s)
+        preempted += [r.request_id for r in plan.preempted]
+        cache.check()
+        steps += 1
+        assert steps < 200
+    assert preempted and set(preempted) == {"b"}  # the oldest request is never the victim
+    assert s.num_preemptions == len(preempted) and b.num_preemptions == len(preempted)
+    assert a.num_output_tokens == 10 and b.num_output_tokens == 10  # generated tokens survive recompute
+    assert cache.all_free()
+
+
+def test_preempted_request_goes_to_the_front_and_no_admission_in_that_step():
+    s, cache = make(policy="decode_first", pages=4, page_size=4, budget=32)
+    a, b = req("a", 8, max_tokens=20), req("b", 8, max_tokens=20)
+    s.add_request(a), s.add_request(b)
+    run_step(s)  # both admitted: 2 + 2 pages, all full
+    s.add_request(req("c", 2))
+    plan = run_step(s)  # both need a third page: b, the youngest, is preempted for a
+    assert [r.request_id for r in plan.preempted] == ["b"] and sizes(plan) == [("a", 1)]
+    assert [r.request_id for r in s.waiting] == ["b", "c"]
+    assert b.num_computed_tokens == 0 and b.num_output_tokens == 1 and not cache.has("b")
+
+
+def test_a_request_alone_always_fits():
+    s, cache = make(pages=3, page_size=4, budget=64, max_len=100)
+    assert s.max_model_len == 12  # the pool caps the length of a request
+    s.add_request(r := req("a", 5, max_tokens=50))
+    while s.has_unfinished():
+        run_step(s)
+    assert r.finish_reason == "length" and r.num_tokens == 12 and cache.all_free()
+    with pytest.raises(ValueError):
+        s.add_request(req("b", 12))
+
+
+def test_abort_releases_pages():
+    s, cache = make()
+    s.add_request(a := req("a", 6))
+    s.add_request(b := req("b", 6))
+    run_step(s)
+    s.finish_request(a, RequestStatus.FINISHED_ABORTED)
+    s.finish_request(b, RequestStatus.FINISHED_ABORTED)
+    assert a.finish_reason == "abort" and not s.has_unfinished() and cache.all_free()
+
+
+def test_windowed_request_outlives_the_pool():
+    s, cache = make(pages=4, page_size=4, budget=8, window=6, max_len=16)
+    s.add_request(r := req("a", 5, max_tokens=11))
+    while s.has_unfinished():
+        run_step(s)
+        cache.check()
+    assert r.num_tokens == 16 and cache.all_free()
