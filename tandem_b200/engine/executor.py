@@ -39,16 +39,18 @@ class Executor:
         self.num_steps = 0
 
     # ------------------------------------------------------------------ batch description
-    def build_context(self, entries: Sequence[StepEntry]) -> tuple[StepContext, list]:
-        """Flatten the entries: token ids, positions, the request of each token, slots and block
-        tables per cache group.  All integers travel to the device in one copy."""
-        m, ps = self.manager, self.manager.page_size
-        ids, positions, seq_of_token, cu, starts, lens, slots_host, rows = [], [], [], [0], [], [], [], []
-        for b, e in enumerate(entries):
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        """Refuse a step that cannot run, before it touches the cache: an empty portion, a token
+        outside the vocabulary, a position beyond the model's table, a wanted place that is not there."""
+        seen = set()
+        for e in entries:
             n = len(e.tokens)
             if n == 0:
                 raise ValueError(f"request {e.request_id!r} brings no tokens")
-            start = m.num_tokens(e.request_id)
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            start = self.manager.num_tokens(e.request_id) if self.manager.has(e.request_id) else 0
             if start + n > self.max_position:
                 raise ValueError(f"request {e.request_id!r} would reach position {start + n - 1}; "
                                  f"the model's position table ends at {self.max_position - 1}")
@@ -59,7 +61,17 @@ class Executor:
             for w in e.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.request_id!r} wants logits at place {w} of {n} tokens")
-                rows.append(cu[-1] + w)
+
+    def build_context(self, entries: Sequence[StepEntry]) -> tuple[StepContext, list]:
+        """Flatten the entries: token ids, positions, the request of each token, slots and block
+        tables per cache group.  All integers travel to the device in one copy."""
+        m, ps = self.manager, self.manager.page_size
+        self.validate(entries)
+        ids, positions, seq_of_token, cu, starts, lens, slots_host, rows = [], [], [], [0], [], [], [], []
+        for b, e in enumerate(entries):
+            n = len(e.tokens)
+            start = m.num_tokens(e.request_id)
+            rows.extend(cu[-1] + w for w in e.want)
             ids.extend(int(t) for t in e.tokens)
             positions.extend(range(start, start + n))
             seq_of_token.extend([b] * n)
@@ -123,6 +135,7 @@ class Executor:
         tokens (OutOfPages if the pool cannot give them: nothing has run then), the tokens are
         committed, and the requests in ``end`` give back what they hold afterwards."""
         m = self.manager
+        self.validate(entries)
         begun = []
         try:
             for e in entries:

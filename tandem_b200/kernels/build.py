@@ -27,7 +27,7 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC"]
 
-_lock = threading.Lock()
+_lock = threading.RLock()
 _loaded: dict[str, ctypes.CDLL] = {}
 
 
@@ -43,18 +43,25 @@ def _nvcc() -> str:
                            "the CUDA kernels cannot be built and there is no other path")
 
 
+_build_dir = None
+
+
 def build_dir() -> str:
-    d = os.path.join(CSRC, "_build")
-    try:
-        os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
-        open(probe, "w").close()
-        os.remove(probe)
-        return d
-    except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"tandem_b200_build_{os.getuid()}")
-        os.makedirs(d, exist_ok=True)
-        return d
+    """In the tree when it can be written, else a per-user folder in the temporary directory."""
+    global _build_dir
+    with _lock:
+        if _build_dir is None:
+            d = os.path.join(CSRC, "_build")
+            try:
+                os.makedirs(d, exist_ok=True)
+                fd, probe = tempfile.mkstemp(dir=d)
+                os.close(fd)
+                os.remove(probe)
+            except OSError:
+                d = os.path.join(tempfile.gettempdir(), f"tandem_b200_build_{os.getuid()}")
+                os.makedirs(d, exist_ok=True)
+            _build_dir = d
+        return _build_dir
 
 
 def _headers() -> list[str]:
@@ -65,7 +72,7 @@ def _digest(source: str, defines: tuple) -> str:
     h = hashlib.sha256()
     for path in [source] + _headers():
         with open(path, "rb") as f:
-            h.update(path.encode() + b"\0" + f.read())
+            h.update(os.path.basename(path).encode() + b"\0" + f.read())
     h.update(repr((ARCH_FLAGS, BASE_FLAGS, defines)).encode())
     return h.hexdigest()[:16]
 
@@ -114,7 +121,9 @@ def compile_many(jobs: list, verbose: bool = True) -> list[str]:
 
 def load_library(stem: str, defines: tuple = ()) -> ctypes.CDLL:
     key = stem + "|" + ",".join(defines)
-    with _lock:
-        if key not in _loaded:
-            _loaded[key] = ctypes.CDLL(compile_library(stem, defines))
-        return _loaded[key]
+    lib = _loaded.get(key)
+    if lib is None:
+        path = compile_library(stem, defines)
+        with _lock:
+            lib = _loaded.setdefault(key, ctypes.CDLL(path))
+    return lib

@@ -1,0 +1,17 @@
+"""Every CUDA library the package can ask for, so that all of them can be built ahead of time."""
+
+from __future__ import annotations
+
+from tandem_b200.kernels.build import compile_many
+
+# (source stem, defines)
+LIBRARIES = [
+    ("tokenwise", ()),
+    ("gemm_f32", ()),
+    ("attention_simt", ()),
+    ("sampling", ()),
+]
+
+
+def build_all(verbose: bool = True) -> list:
+    return compile_many(LIBRARIES, verbose)

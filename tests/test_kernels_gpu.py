@@ -1,0 +1,326 @@
+"""Each CUDA kernel alone against plain PyTorch float32 math, at sizes other than the engine's
+(odd widths, head sizes in steps of 16, group sizes 1..5, vocabularies that are no power of two)."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return dict(atol=(2e-5 if dtype == torch.float32 else 1.6e-2) * scale, rtol=1e-5 if dtype == torch.float32 else 1.6e-2)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tandem_b200.kernels import ops as o
+
+    return o
+
+
+def dev(t):
+    return t.to("cuda")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,V", [(1, 64, 50), (7, 100, 1000), (33, 4096, 777)])
+def test_embedding(ops, dtype, T, H, V):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(V, H, generator=g).to(dtype)
+    ids = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    out = ops.embedding(dev(ids), dev(table))
+    assert out.dtype == torch.float32
+    torch.testing.assert_close(out.cpu(), table[ids.long()].float(), atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,eps", [(1, 64, 1e-6), (5, 100, 1e-5), (19, 4096, 1e-6), (3, 5120, 3e-6), (2, 7, 1e-2)])
+def test_add_rmsnorm(ops, dtype, T, H, eps):
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(T, H, generator=g).to(dtype)
+    res = torch.randn(T, H, generator=g) * 3
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    s = x.float() + res
+    want = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + eps) * w
+    res_d = dev(res.clone())
+    y = ops.add_rmsnorm(dev(x), res_d, dev(w), eps, dtype)
+    torch.testing.assert_close(res_d.cpu(), s, atol=1e-6, rtol=1e-6)  # the residual sum is float32
+    torch.testing.assert_close(y.cpu().float(), want, **tol(dtype))
+    # without x: plain norm, the residual untouched; with rows: only those rows, in that order
+    res_d = dev(res.clone())
+    y = ops.add_rmsnorm(None, res_d, dev(w), eps, dtype)
+    torch.testing.assert_close(res_d.cpu(), res, atol=0, rtol=0)
+    torch.testing.assert_close(y.cpu().float(), res * torch.rsqrt(res.pow(2).mean(-1, keepdim=True) + eps) * w, **tol(dtype))
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32)[: min(2, T)]
+    res_d = dev(res.clone())
+    y = ops.add_rmsnorm(dev(x), res_d, dev(w), eps, dtype, rows=dev(rows))
+    torch.testing.assert_close(y.cpu().float(), want[rows.long()], **tol(dtype))
+
+
+def _rope_reference(x, pos, theta, rd):
+    half = rd // 2
+    inv = 1.0 / (theta ** (torch.arange(0, rd, 2, dtype=torch.int64).float() / rd))
+    ang = pos.float()[:, None] * inv[None]
+    c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    a, b, rest = x[..., :half], x[..., half:rd], x[..., rd:]
+    return torch.cat([a * c - b * s, b * c + a * s, rest], -1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rd,ps,norm", [(4, 2, 16, 16, 4, True), (6, 2, 32, 32, 8, True), (5, 5, 48, 48, 16, True),
+                                                 (8, 2, 128, 128, 16, True), (3, 1, 80, 32, 8, False), (2, 1, 256, 256, 16, True)])
+def test_qk_norm_rope_kv(ops, dtype, nh, nkv, hd, rd, ps, norm):
+    from tandem_b200.config.plan import PositionSpec
+    from tandem_b200.parts.rope import RotaryTable
+
+    g = torch.Generator().manual_seed(2)
+    T, pages, eps, theta = 13, 9, 1e-5, 12345.0
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype)
+    pos = torch.randint(0, 300, (T,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * ps, generator=g)[:T].to(torch.int32)
+    slots[3] = -1  # a padding row writes nothing
+    qw = (1 + 0.1 * torch.randn(hd, generator=g)) if norm else None
+    kw = (1 + 0.1 * torch.randn(hd, generator=g)) if norm else None
+    table = RotaryTable(PositionSpec("rope", rotary_dim=rd, theta=theta, max_position=300), "cuda")
+    kc = torch.full((pages, nkv, ps, hd), 7.0, dtype=dtype, device="cuda")
+    vc = torch.full((pages, nkv, ps, hd), 7.0, dtype=dtype, device="cuda")
+    qkv_d = dev(qkv.clone())
+    ops.qk_norm_rope_kv(qkv_d, dev(pos), dev(slots), dev(qw) if norm else None, dev(kw) if norm else None, table.cos_sin,
+                        kc, vc, nh, nkv, hd, rd, ps, eps)
+    x = qkv.float().view(T, nh + 2 * nkv, hd)
+    q, k, v = x[:, :nh], x[:, nh:nh + nkv], x[:, nh + nkv:]
+    if norm:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * qw
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * kw
+    q, k = _rope_reference(q, pos, theta, rd), _rope_reference(k, pos, theta, rd)
+    out = qkv_d.cpu().float().view(T, nh + 2 * nkv, hd)
+    torch.testing.assert_close(out[:, :nh], q, **tol(dtype, 4))
+    torch.testing.assert_close(out[:, nh:], x[:, nh:], atol=0, rtol=0)  # k and v columns of qkv stay as they were
+    kc, vc = kc.cpu().float(), vc.cpu().float()
+    written = torch.zeros(pages, ps, dtype=torch.bool)
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        written[s // ps, s % ps] = True
+        torch.testing.assert_close(kc[s // ps, :, s % ps], k[t], **tol(dtype, 4))
+        torch.testing.assert_close(vc[s // ps, :, s % ps], v[t], atol=0, rtol=0)
+    assert bool((kc.permute(0, 2, 1, 3)[~written] == 7.0).all()) and bool((vc.permute(0, 2, 1, 3)[~written] == 7.0).all())
+    # a run that reads another run's cache writes nothing
+    kc2 = torch.zeros((pages, nkv, ps, hd), dtype=dtype, device="cuda")
+    ops.qk_norm_rope_kv(dev(qkv.clone()), dev(pos), None, dev(qw) if norm else None, dev(kw) if norm else None,
+                        table.cos_sin, None, None, nh, nkv, hd, rd, ps, eps, write_kv=False)
+    assert float(kc2.abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(1, 192), (9, 250), (4, 12288), (3, 7)])
+def test_silu_mul(ops, dtype, T, I):
+    g = torch.Generator().manual_seed(3)
+    gu = (torch.randn(T, 2 * I, generator=g) * 2).to(dtype)
+    a, b = gu.float()[:, :I], gu.float()[:, I:]
+    torch.testing.assert_close(ops.silu_mul(dev(gu)).cpu().float(), a * torch.sigmoid(a) * b, **tol(dtype, 4))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 1000, 96), (33, 192, 100), (70, 130, 257), (128, 512, 64), (2, 3, 5)])
+def test_gemm_f32_is_true_float32_and_batch_invariant(ops, M, N, K):
+    g = torch.Generator().manual_seed(4)
+    x, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    y = ops.linear(dev(x), dev(w))
+    want = (x.double() @ w.double().T)
+    assert (y.cpu().double() - want).abs().max() < 1e-5 * math.sqrt(K) * 4
+    # TF32 would be off by ~1e-3 here; and a row alone gives bit-identical results
+    one = ops.linear(dev(x[M - 1:]), dev(w))
+    assert torch.equal(one[0], y[M - 1])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (3, 1000, 96), (8, 6144, 4096), (17, 320, 192), (64, 130, 264),
+                                   (100, 512, 1024), (300, 1000, 96), (2, 24, 8)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_bf16(ops, M, N, K, out_dtype):
+    g = torch.Generator().manual_seed(5)
+    x, w = torch.randn(M, K, generator=g).bfloat16(), (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16()
+    y = ops.linear(dev(x), dev(w), out_dtype=out_dtype)
+    assert y.dtype == out_dtype and y.shape == (M, N)
+    want = x.double() @ w.double().T
+    err = (y.cpu().double() - want).abs().max()
+    assert err < (2e-2 if out_dtype == torch.bfloat16 else 2e-4 * math.sqrt(K) / 8 + 1e-4), err
+
+
+# ----------------------------------------------------------------------------- attention
+def _paged_case(g, dtype, seqs, nh, nkv, hd, ps, extra_pages=5):
+    """seqs: [(start, n)] -> (qkv rows for the new tokens, caches with shuffled pages holding keys 0..start+n-1, ...)."""
+    total_pages = sum(-(-(s + n) // ps) for s, n in seqs) + extra_pages
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    kc = torch.full((total_pages, nkv, ps, hd), float("nan")).to(dtype)  # unwritten slots must never be read
+    vc = torch.full((total_pages, nkv, ps, hd), float("nan")).to(dtype)
+    width = max(-(-(s + n) // ps) for s, n in seqs)
+    table = torch.full((len(seqs), width), -1, dtype=torch.int32)
+    K, V, Q, positions, seq_of = [], [], [], [], []
+    for b, (start, n) in enumerate(seqs):
+        L = start + n
+        k = torch.randn(L, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(L, nkv, hd, generator=g).to(dtype)
+        q = torch.randn(n, nh, hd, generator=g).to(dtype)
+        for j in range(-(-L // ps)):
+            page = perm.pop()
+            table[b, j] = page
+            rows = slice(j * ps, min(L, (j + 1) * ps))
+            kc[page, :, : rows.stop - rows.start] = k[rows].transpose(0, 1)
+            vc[page, :, : rows.stop - rows.start] = v[rows].transpose(0, 1)
+        K.append(k), V.append(v), Q.append(q)
+        positions += list(range(start, L))
+        seq_of += [b] * n
+    # the query heads sit in the first nh*hd columns of a wider row, as in the fused projection
+    qrows = torch.cat(Q).reshape(len(positions), nh * hd)
+    qkv = torch.cat([qrows, torch.zeros(len(positions), 2 * nkv * hd, dtype=dtype)], 1).contiguous()
+    return qkv, kc, vc, table, torch.tensor(seq_of, dtype=torch.int32), torch.tensor(positions, dtype=torch.int32), Q, K, V
+
+
+def _attention_reference(Q, K, V, seqs, scale, window):
+    outs = []
+    for (start, n), q, k, v in zip(seqs, Q, K, V):
+        q, k, v = q.double(), k.double(), v.double()
+        g = q.shape[1] // k.shape[1]
+        k, v = k.repeat_interleave(g, 1), v.repeat_interleave(g, 1)
+        s = torch.einsum("qhd,khd->hqk", q, k) * scale
+        qpos = torch.arange(start, start + n)[:, None]
+        kpos = torch.arange(start + n)[None, :]
+        ok = kpos <= qpos
+        if window:
+            ok &= kpos > qpos - window
+        s = s.masked_fill(~ok[None], float("-inf"))
+        outs.append(torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(n, -1))
+    return torch.cat(outs)
+
+
+ATTN_SHAPES = [(4, 2, 16, 4), (6, 2, 32, 8), (5, 5, 48, 16), (8, 2, 128, 16), (3, 1, 80, 8), (10, 2, 64, 16),
+               (7, 7, 96, 16), (4, 1, 256, 16), (32, 8, 128, 16)]
+ATTN_BATCHES = [[(0, 1)], [(0, 37)], [(40, 1), (3, 1), (129, 1)], [(5, 2), (0, 19), (63, 1), (17, 40)], [(300, 3), (0, 130)]]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,ps", ATTN_SHAPES)
+@pytest.mark.parametrize("batch", range(len(ATTN_BATCHES)))
+@pytest.mark.parametrize("window", [None, 9])
+def test_paged_attention_simt(ops, dtype, nh, nkv, hd, ps, batch, window):
+    if (batch + (window or 0) + hd) % 2 and hd not in (16, 128):  # thin the product out
+        pytest.skip("covered by the neighbouring cases")
+    g = torch.Generator().manual_seed(6 + batch)
+    seqs = ATTN_BATCHES[batch]
+    qkv, kc, vc, table, seq_of, pos, Q, K, V = _paged_case(g, dtype, seqs, nh, nkv, hd, ps)
+    scale = hd ** -0.5
+    if window:  # pages wholly behind every query's window may be gone: the kernel must not touch them
+        for b, (start, n) in enumerate(seqs):
+            for j in range(max(0, start - window + 1) // ps):
+                kc[table[b, j]] = float("nan")
+                table[b, j] = -1
+    out = ops.paged_attention_simt(dev(qkv), dev(kc), dev(vc), dev(table), dev(seq_of), dev(pos), nh, nkv, hd, ps, window, scale)
+    want = _attention_reference(Q, K, V, seqs, scale, window)
+    torch.testing.assert_close(out.cpu().double(), want, atol=2e-5 if dtype == torch.float32 else 2e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_and_respects_edges(ops, dtype):
+    """Random weights hide a wrong key: make one score stand out.  The query at position p is
+    aligned with key j only, so the output must be v[j]; j is placed at a page's first and last
+    slot, at the far start, at the causal edge and at the window's edge."""
+    nh, nkv, hd, ps = 4, 2, 64, 16
+    g = torch.Generator().manual_seed(7)
+    L = 403
+    for j, window in [(0, None), (15, None), (16, None), (399, None), (402, None), (402 - 49, 50), (402 - 50, 50), (387, 100)]:
+        seqs = [(L - 1, 1)]
+        qkv, kc, vc, table, seq_of, pos, Q, K, V = _paged_case(g, dtype, seqs, nh, nkv, hd, ps)
+        direction = torch.randn(hd, generator=g)
+        direction /= direction.norm()
+        K[0][:] = (0.01 * torch.randn(L, nkv, hd, generator=g)).to(dtype)
+        K[0][j] = (8.0 * direction).to(dtype)
+        Q[0][:] = (8.0 * direction).to(dtype)
+        for p in range(-(-L // ps)):
+            rows = slice(p * ps, min(L, (p + 1) * ps))
+            kc[table[0, p], :, : rows.stop - rows.start] = K[0][rows].transpose(0, 1)
+        qkv[:, : nh * hd] = Q[0].reshape(1, -1)
+        out = ops.paged_attention_simt(dev(qkv), dev(kc), dev(vc), dev(table), dev(seq_of), dev(pos), nh, nkv, hd, ps,
+                                       window, 1.0).cpu().float().view(nh, hd)
+        inside = window is None or j > L - 1 - window
+        want = V[0][j].float().repeat_interleave(nh // nkv, 0)
+        if inside:
+            torch.testing.assert_close(out, want, atol=2e-2, rtol=2e-2)
+        else:  # the key lies just outside the window: it must not be seen
+            assert (out - want).abs().max() > 0.1
+
+
+# ----------------------------------------------------------------------------- sampling
+@pytest.mark.parametrize("R,V", [(1, 10), (3, 1000), (5, 151936), (2, 777)])
+def test_argmax(ops, R, V):
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(R, V, generator=g)
+    x[0, V // 2] = x[0, V - 1] = 99.0  # equal maxima: the lowest index
+    got = ops.argmax(dev(x)).cpu()
+    assert got.dtype == torch.int32 and got.tolist() == x.argmax(-1).tolist() and got[0] == V // 2
+
+
+def _sample_reference(logits, temperature, top_k, top_p, min_p, u):
+    import plain_qwen3 as plain
+
+    p = plain.filtered_probs(logits, temperature, top_k, top_p, min_p)
+    return plain.inverse_cdf_draw(p, u), p
+
+
+@pytest.mark.parametrize("V", [50, 1000, 151936])
+def test_sample_matches_the_plain_sampler(ops, V):
+    g = torch.Generator().manual_seed(9)
+    rows = [dict(t=1.0, k=-1, p=1.0, m=0.0), dict(t=0.7, k=5, p=1.0, m=0.0), dict(t=1.3, k=-1, p=0.8, m=0.0),
+            dict(t=0.9, k=-1, p=1.0, m=0.2), dict(t=0.8, k=40, p=0.9, m=0.05), dict(t=0.0, k=3, p=0.5, m=0.1),
+            dict(t=2.0, k=1, p=1.0, m=0.0)]
+    for trial in range(4):
+        R = len(rows)
+        logits = torch.randn(R, V, generator=g) * 3
+        u = torch.rand(R, generator=g)
+        got = ops.sample(dev(logits), dev(torch.tensor([r["t"] for r in rows])),
+                         dev(torch.tensor([r["k"] for r in rows], dtype=torch.int32)),
+                         dev(torch.tensor([r["p"] for r in rows])), dev(torch.tensor([r["m"] for r in rows])),
+                         dev(u)).cpu().tolist()
+        for i, r in enumerate(rows):
+            if r["t"] < 1e-5:
+                assert got[i] == int(logits[i].argmax())
+                continue
+            want, p = _sample_reference(logits[i], r["t"], r["k"], r["p"], r["m"], float(u[i]))
+            if got[i] != want:  # only where u * total falls within rounding of a boundary of the CDF
+                cum = p.cumsum(-1)
+                target = float(u[i]) * float(cum[-1])
+                lo = float(cum[got[i]] - p[got[i]])
+                assert p[got[i]] > 0 and lo - 1e-5 <= target <= float(cum[got[i]]) + 1e-5, (i, trial, got[i], want)
+
+
+def test_sample_keeps_only_filtered_tokens_and_follows_u(ops):
+    V = 4
+    logits = torch.log(torch.tensor([[0.5, 0.3, 0.15, 0.05]])).repeat(6, 1)
+    one, none = torch.ones(6), torch.zeros(6)
+    k = torch.tensor([2, 2, -1, -1, -1, -1], dtype=torch.int32)
+    p = torch.tensor([1.0, 1.0, 0.7, 0.7, 1.0, 1.0])
+    m = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.5, 0.5])
+    u = torch.tensor([0.62, 0.63, 0.62, 0.63, 0.62, 0.999])
+    got = ops.sample(dev(logits), dev(one), dev(k), dev(p), dev(m), dev(u)).cpu().tolist()
+    assert got == [0, 1, 0, 1, 0, 1]  # every filter leaves [.625, .375, 0, 0]
+    u = torch.tensor([0.0, 0.49, 0.51, 0.79, 0.81, 0.96])
+    got = ops.sample(dev(logits), dev(one), dev(torch.full((6,), -1, dtype=torch.int32)), dev(one), dev(none), dev(u))
+    assert got.cpu().tolist() == [0, 0, 1, 1, 2, 3]
+
+
+def test_refusals(ops):
+    x = torch.zeros(2, 8)
+    with pytest.raises(ops.KernelError, match="CUDA"):
+        ops.silu_mul(x)  # no CPU path
+    with pytest.raises(ops.KernelError, match="float32 or bfloat16"):
+        ops.silu_mul(dev(x.half()))
+    with pytest.raises(ops.KernelError):
+        ops.linear(dev(x), dev(torch.zeros(4, 7)))
+    with pytest.raises(ops.KernelError, match="share"):
+        ops.paged_attention_simt(dev(torch.zeros(1, 96)), dev(torch.zeros(1, 2, 4, 16)), dev(torch.zeros(1, 2, 4, 16)),
+                                 dev(torch.zeros(1, 1, dtype=torch.int32)), dev(torch.zeros(1, dtype=torch.int32)),
+                                 dev(torch.zeros(1, dtype=torch.int32)), 3, 2, 16, 4, None, 1.0)
