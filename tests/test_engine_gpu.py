@@ -1,0 +1,370 @@
+"""The engine on the GPU: generation through the entry point, long decoding, the first tokens of a
+sequence, preemption, temperature sampling, each part alone, and parts defined outside the package."""
+
+import subprocess
+import sys
+from dataclasses import dataclass, replace
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import ROOT, TINY, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+GREEDY = dict(temperature=0.0, ignore_eos=True)
+
+
+def near_tie(cfg, w, prompt, got, want, gap=0.05):
+    """bfloat16 greedy may leave the float32 path only where the plain logits nearly tie
+    (tests/test_gpu_fastpath.py:81-92 of 12vivi/tandem)."""
+    for i, (x, y) in enumerate(zip(got, want)):
+        if x != y:
+            logits = plain.forward(cfg, w, prompt + want[:i])[-1]
+            return abs(float(logits[x] - logits[y])) < gap
+    return True
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,lengths,budget,policy,new", [("A", [5, 17, 33], 16, "prefill_first", 8),
+                                                            ("B", [1, 9, 40, 70], 16, "decode_first", 12),
+                                                            ("C", [30, 3, 61], 24, "decode_first", 40)])
+def test_greedy_generation_through_the_entry_point(tiny_folder, name, lengths, budget, policy, new, dtype):
+    from tandem_b200 import LLM, SamplingParams
+
+    folder = tiny_folder(name, 0.1)
+    cfg, w = plain.read_folder(folder)
+    prompts = [random_tokens(7 + i, n, TINY[name]["vocab_size"]) for i, n in enumerate(lengths)]
+    llm = LLM(model=folder, dtype=dtype, block_size=8, num_kv_blocks=64, max_num_batched_tokens=budget,
+              schedule_policy=policy, max_num_seqs=4)
+    outs = llm.generate(prompts, SamplingParams(max_tokens=new, **GREEDY))
+    for p, o in zip(prompts, outs):
+        want = plain.greedy(cfg, w, p, new)
+        assert o.finish_reason == "length" and len(o.output_token_ids) == new
+        if dtype == "float32":
+            assert o.output_token_ids == want
+        else:
+            assert near_tie(cfg, w, p, o.output_token_ids, want)
+    assert llm.engine.cache.all_free()  # every page and slot given back
+    assert llm.stats()["free_kv_blocks"] == llm.stats()["total_kv_blocks"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_recomputes_exactly(tiny_folder, dtype):
+    """12 pages of 4 tokens cannot hold four requests of 10 + 14 tokens: some are preempted and
+    recomputed, and the outputs stay those of the plain implementation
+    (tests/test_model_equivalence.py:55-64 of 12vivi/tandem)."""
+    from tandem_b200 import EngineConfig, LLMEngine, SamplingParams
+
+    folder = tiny_folder("A", 0.1)
+    cfg, w = plain.read_folder(folder)
+    eng = LLMEngine(EngineConfig(model=folder, dtype=dtype, block_size=4, num_kv_blocks=12, max_num_batched_tokens=16,
+                                 schedule_policy="decode_first"))
+    prompts = [random_tokens(40 + i, 10, 512) for i in range(4)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=14, **GREEDY))
+    assert eng.scheduler.num_preemptions > 0
+    for p, o in zip(prompts, outs):
+        want = plain.greedy(cfg, w, p, 14)
+        assert o.output_token_ids == want if dtype == "float32" else near_tie(cfg, w, p, o.output_token_ids, want)
+    eng.cache.check()
+    assert eng.cache.all_free()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(tiny_folder, dtype):
+    """One token at a time from position 0 to 300 (the first tokens of a sequence: a single key,
+    a page's first slot) and on through many pages; logits against the plain implementation."""
+    from tandem_b200.engine.core import build_executor, load_model
+    from tandem_b200.engine.executor import StepEntry
+
+    folder = tiny_folder("B")
+    cfg, w = plain.read_folder(folder, torch.float64)
+    tokens = random_tokens(3, 300, 1000)
+    ref = plain.forward(cfg, w, tokens, torch.float64)
+    decoder, _ = load_model(folder, dtype, "cuda:0")
+    ex = build_executor(decoder, page_size=16, num_pages=20, max_requests=2)
+    rows = [ex.step([StepEntry("a", [t], [0])]) for t in tokens]
+    got = torch.cat(rows).cpu().double()
+    err = (got - ref).abs().max(-1).values
+    assert err[:4].max() < (1e-4 if dtype == "float32" else 0.05)
+    assert err.max() < (1e-4 if dtype == "float32" else 0.08), int(err.argmax())
+
+
+def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tiny_folder):
+    from tandem_b200 import EngineConfig, LLMEngine, SamplingParams
+
+    folder = tiny_folder("B", 0.1)
+    prompts = [random_tokens(60 + i, n, 1000) for i, n in enumerate([1, 9, 40, 70])]
+    sp = [SamplingParams(max_tokens=12, temperature=0.8, top_p=0.9, seed=42 + i, ignore_eos=True) for i in range(4)]
+
+    def run(which, budget, policy):
+        eng = LLMEngine(EngineConfig(model=folder, dtype="float32", block_size=8, num_kv_blocks=64,
+                                     max_num_batched_tokens=budget, schedule_policy=policy))
+        return [o.output_token_ids for o in eng.generate([prompts[i] for i in which], [sp[i] for i in which])]
+
+    together = run([0, 1, 2, 3], 16, "decode_first")
+    assert together == run([0, 1, 2, 3], 16, "decode_first")  # reproducible (tests/test_spec_and_sampling.py:82-88)
+    alone = [run([i], 64, "prefill_first")[0] for i in range(4)]
+    assert together == alone  # a draw depends on (seed, index of the token) only
+    assert len({tuple(t) for t in together}) == 4
+    # and the draws follow the plain sampler on the plain logits
+    cfg, w = plain.read_folder(folder)
+    from tandem_b200.sampling.rng import uniform
+
+    ids = list(prompts[1])
+    for k, tok in enumerate(alone[1][:4]):
+        p = plain.filtered_probs(plain.forward(cfg, w, ids)[-1], 0.8, top_p=0.9)
+        want = plain.inverse_cdf_draw(p, uniform(43, k))
+        assert tok == want
+        ids.append(tok)
+
+
+def test_command_line(tiny_folder):
+    out = subprocess.run([sys.executable, f"{ROOT}/bin/tandem", "generate", "--model", tiny_folder("A", 0.1), "--dtype", "float32",
+                          "--prompt-ids", "5 17 3 99", "--max-tokens", "5", "--temperature", "0", "--ignore-eos",
+                          "--block-size", "4", "--kv-cache-gb", "0.001"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    cfg, w = plain.read_folder(tiny_folder("A", 0.1))
+    assert [int(t) for t in out.stdout.split()] == plain.greedy(cfg, w, [5, 17, 3, 99], 5)
+    assert "tok/s" in out.stderr and "free_kv_blocks" in out.stderr
+
+
+# ----------------------------------------------------------------------------- parts alone
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_each_part_alone(dtype):
+    """Norm, feed-forward, position table and attention mixer built from specs with sizes of
+    their own (no model around them) against the plain functions."""
+    from tandem_b200.cache.manager import CacheManager
+    from tandem_b200.cache.storage import CacheStorage
+    from tandem_b200.config.plan import AttentionSpec, GatedMLPSpec, NormSpec, PositionSpec
+    from tandem_b200.engine.executor import Executor, StepEntry
+    from tandem_b200.parts.attention import PagedAttention
+    from tandem_b200.parts.mlp import GatedMLP
+    from tandem_b200.parts.norm import RMSNorm
+    from tandem_b200.parts.rope import RotaryTable
+
+    g = torch.Generator().manual_seed(0)
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+    H, I, nh, nkv, hd, T = 72, 100, 6, 3, 48, 21
+
+    def rnd(*shape, s=1.0):
+        return (torch.randn(*shape, generator=g) * s).to(dtype)
+
+    # norm
+    wn = 1 + 0.1 * torch.randn(H, generator=g)
+    norm = RMSNorm(NormSpec("rmsnorm", H, 1e-5, "n"), {"weight": wn.cuda()}, dtype, "cuda")
+    x, res = rnd(T, H), torch.randn(T, H, generator=g)
+    y = norm.forward(x.cuda(), res.clone().cuda(), dtype)
+    torch.testing.assert_close(y.cpu().float(), plain.rms_norm(x.float() + res, wn, 1e-5), **tol)
+
+    # feed-forward
+    wg, wu, wd = rnd(I, H, s=0.2), rnd(I, H, s=0.2), rnd(H, I, s=0.2)
+    mlp = GatedMLP(GatedMLPSpec("gated_mlp", "m", H, I), {"gate_up": torch.cat([wg, wu]).cuda(), "down": wd.cuda()}, dtype, "cuda")
+    wdict = {"m.gate_proj.weight": wg.float(), "m.up_proj.weight": wu.float(), "m.down_proj.weight": wd.float()}
+    torch.testing.assert_close(mlp.forward(x.cuda(), None).cpu().float(), plain.swiglu(x.float(), wdict, "m"), **tol)
+
+    # position table
+    table = RotaryTable(PositionSpec("rope", rotary_dim=hd, theta=777.0, max_position=64), "cuda")
+    cos, sin = plain.rope_tables(hd, 777.0, 64, torch.float32)
+    torch.testing.assert_close(table.cos_sin.cpu(), torch.cat([cos[:, : hd // 2], sin[:, : hd // 2]], 1), atol=0, rtol=0)
+
+    # attention mixer, two portions of one request through a cache of its own
+    spec = AttentionSpec("attention", prefix="a", hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                         scale=hd ** -0.5, qk_norm=True, qk_norm_eps=1e-5, window=None,
+                         position=PositionSpec("rope", rotary_dim=hd, theta=777.0, max_position=64))
+    wq, wk, wv, wo = rnd(nh * hd, H, s=0.2), rnd(nkv * hd, H, s=0.2), rnd(nkv * hd, H, s=0.2), rnd(H, nh * hd, s=0.2)
+    qn, kn = 1 + 0.1 * torch.randn(hd, generator=g), 1 + 0.1 * torch.randn(hd, generator=g)
+    mixer = PagedAttention(spec, {"qkv": torch.cat([wq, wk, wv]).cuda(), "o": wo.cuda(), "q_norm": qn.cuda(), "k_norm": kn.cuda()},
+                           dtype, "cuda")
+    need = PagedAttention.kv_need(spec)
+    manager = CacheManager([need], page_size=8, num_pages=4, max_requests=2)
+    storage = CacheStorage(manager, [need], [None], [None], dtype, "cuda")
+
+    class OneMixer:  # the smallest thing the executor's batch builder needs around a mixer
+        dtype, device = mixer.qkv.dtype, torch.device("cuda")
+
+        class plan:
+            max_position = 64
+
+            class embedding:
+                vocab_size = 10
+
+    ex = Executor(OneMixer, manager, storage)
+    outs = []
+    for start, n in ((0, 13), (13, 8)):
+        manager.begin("r") if start == 0 else None
+        assert manager.grow("r", start + n)
+        ctx, _ = ex.build_context([StepEntry("r", [0] * n, [])])
+        ctx.run = 0
+        outs.append(mixer.forward(x[start: start + n].cuda(), ctx))
+        manager.commit("r", n)
+    d = dict(nh=nh, nkv=nkv, hd=hd, eps=1e-5)
+    wdict = {"a.q_proj.weight": wq.float(), "a.k_proj.weight": wk.float(), "a.v_proj.weight": wv.float(),
+             "a.o_proj.weight": wo.float(), "a.q_norm.weight": qn, "a.k_norm.weight": kn}
+    cos, sin = plain.rope_tables(hd, 777.0, T, torch.float32)
+    want = plain.attention_block(x.float(), wdict, "a", d, cos, sin, None)
+    torch.testing.assert_close(torch.cat(outs).cpu().float(), want, atol=tol["atol"] * 4, rtol=tol["rtol"])
+
+
+# ----------------------------------------------------------------------------- parts from outside
+@dataclass(frozen=True)
+class DecaySpec:
+    """A toy mixer with state of its own: y_t = x_t + s_t, s_t = decay * s_{t-1} + x_t @ W,
+    s kept per request in a state slot of fixed size (hidden floats)."""
+
+    kind: str = "toy_decay"
+    prefix: str = ""
+    hidden_size: int = 0
+    decay: float = 0.5
+
+
+class DecayMixer:
+    @staticmethod
+    def params(spec):
+        from tandem_b200.config.plan import ParamSpec, WeightSource
+
+        return {"w": ParamSpec((spec.hidden_size, spec.hidden_size), (WeightSource(f"{spec.prefix}.w"),))}
+
+    @staticmethod
+    def kv_need(spec):
+        return None
+
+    @staticmethod
+    def state_need(spec):
+        from tandem_b200.parts.base import StateNeed
+
+        return StateNeed((spec.hidden_size,), torch.float32)
+
+    def __init__(self, spec, weights, dtype, device):
+        self.spec, self.w = spec, weights["w"]
+
+    def forward(self, x, ctx):
+        state = ctx.state()
+        u = (x.float() @ self.w.float().T)
+        out = torch.empty_like(u)
+        at = 0
+        for slot, n in zip(ctx.host_slots, ctx.host_lens):  # the step's requests, in order
+            s = state[slot]
+            for t in range(at, at + n):
+                s = self.spec.decay * s + u[t]
+                out[t] = x[t].float() + s
+            state[slot] = s
+            at += n
+        return out.to(x.dtype)
+
+
+def _toy_plan(vocab, H, layers):
+    from tandem_b200.config.plan import EmbeddingSpec, GatedMLPSpec, HeadSpec, LayerSpec, ModelPlan, NormSpec, RunStep
+
+    return ModelPlan(
+        embedding=EmbeddingSpec(vocab, H, "emb"),
+        layers=tuple(LayerSpec("prenorm", mixer=m, feed_forward=GatedMLPSpec("gated_mlp", f"l{i}.mlp", H, 2 * H),
+                               mixer_norm=NormSpec("rmsnorm", H, 1e-5, f"l{i}.n1"),
+                               feed_forward_norm=NormSpec("rmsnorm", H, 1e-5, f"l{i}.n2")) for i, m in enumerate(layers)),
+        order=tuple(RunStep(i) for i in range(len(layers))),
+        final_norm=NormSpec("rmsnorm", H, 1e-5, "fn"), head=HeadSpec(vocab, H, None), max_position=128)
+
+
+def _toy_weights(plan, extra, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    H, V = plan.embedding.hidden_size, plan.embedding.vocab_size
+    w = {"emb": torch.randn(V, H, generator=g) * 0.5, "fn": torch.ones(H)}
+    for i in range(len(plan.layers)):
+        w.update({f"l{i}.n1": 1 + 0.1 * torch.randn(H, generator=g), f"l{i}.n2": torch.ones(H),
+                  f"l{i}.mlp.gate_proj.weight": torch.randn(2 * H, H, generator=g) * 0.1,
+                  f"l{i}.mlp.up_proj.weight": torch.randn(2 * H, H, generator=g) * 0.1,
+                  f"l{i}.mlp.down_proj.weight": torch.randn(H, 2 * H, generator=g) * 0.1})
+    w.update(extra(g))
+    return w
+
+
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped():
+    """No file of the package changes: the test registers the kind, builds a plan that mixes the
+    toy mixer with the package's attention layer by layer, and steps it in portions.  Two
+    requests interleaved must not see each other's state; portions must carry the state on."""
+    from tandem_b200.config.plan import AttentionSpec, PositionSpec
+    from tandem_b200.engine.core import build_executor
+    from tandem_b200.engine.executor import StepEntry
+    from tandem_b200.models.decoder import Decoder
+    from tandem_b200.registry import register_part
+    from tandem_b200.weights.loader import TensorDict
+
+    register_part("mixer", "toy_decay", DecayMixer)
+    H, V = 32, 50
+    attn = AttentionSpec("attention", prefix="l1.attn", hidden_size=H, num_heads=2, num_kv_heads=1, head_dim=16,
+                         scale=0.25, qk_norm=False, position=PositionSpec("rope", rotary_dim=16, theta=100.0, max_position=128))
+    plan = _toy_plan(V, H, [DecaySpec(prefix="l0.mix", hidden_size=H, decay=0.7), attn, DecaySpec(prefix="l2.mix", hidden_size=H)])
+
+    def extra(g):
+        return {"l0.mix.w": torch.randn(H, H, generator=g) * 0.1, "l2.mix.w": torch.randn(H, H, generator=g) * 0.1,
+                "l1.attn.q_proj.weight": torch.randn(32, H, generator=g) * 0.2, "l1.attn.k_proj.weight": torch.randn(16, H, generator=g) * 0.2,
+                "l1.attn.v_proj.weight": torch.randn(16, H, generator=g) * 0.2, "l1.attn.o_proj.weight": torch.randn(H, 32, generator=g) * 0.2}
+
+    decoder = Decoder(plan, TensorDict(_toy_weights(plan, extra)), torch.float32, "cuda")
+    assert [n is not None for n in decoder.kv_needs()] == [False, True, False]
+    assert [n is not None for n in decoder.state_needs()] == [True, False, True]
+    ex = build_executor(decoder, page_size=8, num_pages=16, max_requests=3)
+    a, b = random_tokens(1, 40, V), random_tokens(2, 27, V)
+    whole_a = ex.step([StepEntry("a", a, list(range(40)))], end=["a"])
+    whole_b = ex.step([StepEntry("b", b, list(range(27)))], end=["b"])
+    # the same two requests in interleaved portions; a slot that is used again starts from zero state
+    got_a, got_b = [], []
+    ia = ib = 0
+    for na, nb in ((7, 2), (2, 13), (20, 1), (11, 11)):
+        entries = []
+        if na:
+            entries.append(StepEntry("a2", a[ia: ia + na], list(range(na))))
+        if nb:
+            entries.append(StepEntry("b2", b[ib: ib + nb], list(range(nb))))
+        out = ex.step(entries)
+        got_a.append(out[:na]), got_b.append(out[na:])
+        ia, ib = ia + na, ib + nb
+    assert ia == 40 and ib == 27
+    torch.testing.assert_close(torch.cat(got_a), whole_a, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(torch.cat(got_b), whole_b, atol=1e-5, rtol=1e-5)
+    ex.step([], end=["a2", "b2"])
+    assert ex.manager.all_free()
+
+
+def test_the_order_may_name_a_layer_twice_or_share_a_cache():
+    """order = [0, 1, 0, 1 reading the cache of run 1]: run 2 reuses layer 0's weights with a
+    cache of its own; run 3 reuses layer 1's weights and reads the keys run 1 stored."""
+    from tandem_b200.config.model_config import Qwen3Config
+    from tandem_b200.config.plan import RunStep
+    from tandem_b200.engine.core import build_executor
+    from tandem_b200.engine.executor import StepEntry
+    from tandem_b200.models.decoder import Decoder
+    from tandem_b200.models.qwen3 import build_plan, random_weights
+    from tandem_b200.weights.loader import TensorDict
+
+    cfg = Qwen3Config.from_dict(TINY["A"])
+    weights = dict(random_weights(cfg, 5, "cpu", torch.float32, std=0.1))
+    plan = replace(build_plan(cfg), order=(RunStep(0), RunStep(1), RunStep(0), RunStep(1, cache_of=1)))
+    decoder = Decoder(plan, TensorDict(dict(weights)), torch.float32, "cuda")
+    assert [n is not None for n in decoder.kv_needs()] == [True, True, True, False]
+    ex = build_executor(decoder, page_size=4, num_pages=32, max_requests=2)
+    assert sorted(ex.storage.k) == [0, 1, 2] and ex.storage.source_run[3] == 1
+    tokens = random_tokens(9, 30, 512)
+    whole = ex.step([StepEntry("w", tokens, list(range(30)))], end=["w"])
+    parts = [ex.step([StepEntry("p", tokens[i: i + n], list(range(n)))]) for i, n in ((0, 9), (9, 2), (11, 19))]
+    torch.testing.assert_close(torch.cat(parts), whole, atol=1e-5, rtol=1e-5)
+
+    # plain: layers 0, 1, 0, then layer 1's weights with its *own earlier* keys and values
+    w = {k: v.float() for k, v in weights.items()}
+    d = plain.derived(TINY["A"])
+    cos, sin = plain.rope_tables(d["hd"], d["theta"], 30, torch.float32)
+    h = w["model.embed_tokens.weight"][torch.tensor(tokens)]
+    h = plain.decoder_layer(h, w, 0, d, cos, sin)
+    x1 = plain.rms_norm(h, w["model.layers.1.input_layernorm.weight"], d["eps"])  # what run 1's k, v came from
+    h = plain.decoder_layer(h, w, 1, d, cos, sin)
+    h = plain.decoder_layer(h, w, 0, d, cos, sin)
+    p = "model.layers.1.self_attn"
+    x3 = plain.rms_norm(h, w["model.layers.1.input_layernorm.weight"], d["eps"])
+    q = plain.apply_rope(plain.rms_norm((x3 @ w[f"{p}.q_proj.weight"].T).view(30, d["nh"], d["hd"]), w[f"{p}.q_norm.weight"], d["eps"]), cos, sin)
+    k = plain.apply_rope(plain.rms_norm((x1 @ w[f"{p}.k_proj.weight"].T).view(30, d["nkv"], d["hd"]), w[f"{p}.k_norm.weight"], d["eps"]), cos, sin)
+    v = (x1 @ w[f"{p}.v_proj.weight"].T).view(30, d["nkv"], d["hd"])
+    h = h + plain.attention_scores(q, k, v, None).reshape(30, -1) @ w[f"{p}.o_proj.weight"].T
+    h = h + plain.swiglu(plain.rms_norm(h, w["model.layers.1.post_attention_layernorm.weight"], d["eps"]), w, "model.layers.1.mlp")
+    want = plain.rms_norm(h, w["model.norm.weight"], d["eps"]) @ w["model.embed_tokens.weight"].T
+    torch.testing.assert_close(whole.cpu(), want, atol=1e-4, rtol=1e-4)
