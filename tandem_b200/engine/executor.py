@@ -37,6 +37,7 @@ class Executor:
         self.vocab_size = decoder.plan.embedding.vocab_size
         self.max_position = decoder.plan.max_position
         self.num_steps = 0
+        self.h2d_bytes_last = 0  # bytes of the last step's batch description copied to the device
 
     # ------------------------------------------------------------------ batch description
     def validate(self, entries: Sequence[StepEntry]) -> None:
@@ -100,6 +101,7 @@ class Executor:
         flat = torch.tensor([x for p in parts for x in p], dtype=torch.int32).pin_memory() \
             if self.device.type == "cuda" else torch.tensor([x for p in parts for x in p], dtype=torch.int32)
         dev = flat.to(self.device, non_blocking=True)
+        self.h2d_bytes_last = flat.numel() * 4
         views, off = [], 0
         for p in parts:
             views.append(dev[off: off + len(p)])

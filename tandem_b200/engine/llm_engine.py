@@ -119,16 +119,20 @@ class LLMEngine:
                 self.requests.pop(req.request_id, None)
         return outputs
 
-    def _execute(self, plan: StepPlan) -> dict:
-        entries, sampling = [], []
+    def entries_of(self, plan: StepPlan) -> list:
+        """The plan as step entries: logits are wanted only at the last token of a portion that
+        reaches the request's newest token (python/tandem/executor/model_runner.py:102-105)."""
+        entries = []
         for s in plan.scheduled:
             req, n = s.request, s.num_tokens
             start = req.num_computed_tokens
-            reaches_end = start + n >= req.num_tokens  # model_runner.py:102-105: only then logits
             entries.append(StepEntry(req.request_id, req.token_ids_in_range(start, start + n),
-                                     [n - 1] if reaches_end else []))
-            if reaches_end:
-                sampling.append(req)
+                                     [n - 1] if start + n >= req.num_tokens else []))
+        return entries
+
+    def _execute(self, plan: StepPlan) -> dict:
+        entries = self.entries_of(plan)
+        sampling = [s.request for s, e in zip(plan.scheduled, entries) if e.want]
         if self.graphs is not None and self.graphs.takes(entries):
             logits = self.graphs.run(entries)
         else:

@@ -46,7 +46,12 @@ def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> No
         raise KernelError(f"{name} must be contiguous")
 
 
+launches = 0  # kernels of this package launched so far (CUDA-graph replays count what they captured)
+
+
 def _check(status: int, what: str) -> None:
+    global launches
+    launches += 1
     if status != 0:
         detail = {10001: "unsupported dtype", 10002: "unsupported size"}.get(status, f"CUDA error {status}")
         raise KernelError(f"{what}: {detail}")
