@@ -1,0 +1,333 @@
+// Paged attention for decoded tokens (one query token per request) in bfloat16, head size TB_HD
+// fixed at compile time: split-KV "flash decoding" on the tensor cores, fed by the TMA unit.
+//
+// Work is cut on the host into items (request, key range); one block runs one item for one kv
+// head and all the query heads that share it (rows of a 16-row MMA tile; more than 16 heads per kv
+// head take further blocks along grid.z).  A producer warp walks the request's block table and
+// issues 1-D bulk copies of cache tiles into a ring of shared-memory stages of 64 keys; the
+// cache's own tile layout (cache_layout.cuh) is the swizzled layout ldmatrix wants, so no thread
+// touches the data on its way in.  Four consumer warps take 16 keys of a stage each:
+// S = Q K^T with mma.sync (bf16 in, float32 out), masking, online softmax in float32 with exp2,
+// O += P V.  The warps' partial (max, sum, O) are merged through shared memory.  A request cut
+// into several items leaves its partials in scratch memory; the block that arrives last (an
+// atomic counter per request and kv head, reset by that block) merges them: nothing waits.
+//
+// It does what 12vivi/tandem's Triton split-KV kernel does
+// (python/tandem/layers/triton_decode_attn.py:28-129), and stands where it otherwise calls
+// FlashInfer's decode wrapper (python/tandem/layers/flashinfer_attention.py:138-157).
+#include "cache_layout.cuh"
+#include "common.cuh"
+#include "sm100_primitives.cuh"
+
+#ifndef TB_HD
+#error "compile with -DTB_HD=<head size, a multiple of 16>"
+#endif
+
+namespace tb {
+
+constexpr int HD = TB_HD;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
+constexpr bool SWZ = (HD % 64 == 0);
+constexpr int NB = SWZ ? HD / 64 : 1;  // column blocks of a cache tile
+constexpr int BW = SWZ ? 64 : HD;      // elements per row of a column block
+constexpr int WARPS = 4;               // consumer warps
+constexpr int TILE = 16;               // keys per warp tile
+constexpr int STAGE_KEYS = WARPS * TILE;
+constexpr int STAGES = HD <= 64 ? 4 : (HD <= 128 ? 3 : 2);
+constexpr int QS = HD + 8;             // padded row of the query tile in shared memory
+constexpr int OS = HD + 4;             // padded row of a warp's float32 output in the merge buffer
+constexpr int THREADS = (WARPS + 1) * 32;
+constexpr int ITEM_INTS = 6;           // token row, request, key begin, key end, first item of the request, its item count
+constexpr int STATUS_BAD_PAGE = 2;
+
+struct DecodeArgs {
+  const __nv_bfloat16* q;  // [T, q_stride], query heads first
+  int q_stride;
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;
+  const int* block_table;
+  int table_stride;
+  const int* items;
+  const int* num_items;  // device scalar: blocks beyond it return at once (fixed grids under CUDA graphs)
+  __nv_bfloat16* out;    // [T, nh * HD]
+  float* part_o;         // [items, nkv, G, HD] unnormalised outputs of split requests
+  float* part_ml;        // [items, nkv, G, 2] their running max (log2 domain) and sum
+  int* counters;         // [items * nkv * row tiles], zero between launches
+  int* status;
+  int nh, nkv, page_size;
+  float scale_log2;
+};
+
+__device__ __forceinline__ int tile_elem(int i, int d, int xmask) {  // inside one warp tile [NB][16][BW]
+  if (!SWZ) return i * HD + d;
+  const int blk = d >> 6, dd = d & 63;
+  return blk * TILE * 64 + i * 64 + ((((dd >> 3) ^ (i & xmask)) << 3) | (dd & 7));
+}
+
+__global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeArgs a) {
+  extern __shared__ unsigned char smem_unaligned[];
+  if ((int)blockIdx.x >= *a.num_items) return;
+  // 128-byte rows of the swizzled tiles must start on 128-byte boundaries
+  unsigned char* smem_raw = smem_unaligned + ((128u - (smem_u32(smem_unaligned) & 127u)) & 127u);
+  __nv_bfloat16* stage_mem = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [STAGES][K | V][STAGE_KEYS * HD]
+  constexpr int STAGE_ELEMS = 2 * STAGE_KEYS * HD;
+  __nv_bfloat16* q_s = stage_mem + STAGES * STAGE_ELEMS;  // [16][QS]
+  float* m_s = reinterpret_cast<float*>(q_s + 16 * QS);   // [WARPS][16]
+  float* l_s = m_s + WARPS * 16;
+  uint64_t* full = reinterpret_cast<uint64_t*>(l_s + WARPS * 16);
+  uint64_t* empty = full + STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + STAGES);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
+  const int t = item[0], req = item[1], kb = item[2], ke = item[3], first_item = item[4], nsplits = item[5];
+  const int kvh = blockIdx.y, G = a.nh / a.nkv, ps = a.page_size;
+  const int row0 = blockIdx.z * 16, rows = min(16, G - row0);  // query heads of this block: kvh*G + row0 + g
+  const int xmask = min(7, ps - 1);
+  const int s0 = (kb / STAGE_KEYS) * STAGE_KEYS;
+  const int num_stages = (ke - s0 + STAGE_KEYS - 1) / STAGE_KEYS;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, WARPS); }
+    *abort_flag = 0;
+    *last_flag = 0;
+    mbar_fence_init();
+  }
+  // value stages start from zero: rows of a stage that no copy fills are multiplied by zero weights,
+  // and must not hold NaN bit patterns left by an earlier kernel
+  for (int s = 0; s < STAGES; ++s) {
+    uint4* v4 = reinterpret_cast<uint4*>(stage_mem + s * STAGE_ELEMS + STAGE_KEYS * HD);
+    for (int i = tid; i < STAGE_KEYS * HD / 8; i += THREADS) v4[i] = make_uint4(0, 0, 0, 0);
+  }
+  for (int i = tid; i < 16 * (HD / 8); i += THREADS) {  // the query tile, 16 bytes at a time
+    const int g = i / (HD / 8), c = i % (HD / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (g < rows) v = *reinterpret_cast<const uint4*>(a.q + (size_t)t * a.q_stride + (size_t)(kvh * G + row0 + g) * HD + c * 8);
+    *reinterpret_cast<uint4*>(q_s + g * QS + c * 8) = v;
+  }
+  fence_proxy_async();
+  __syncthreads();
+
+  float o[HD / 8][4];
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+  if (warp == WARPS) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      const int* table = a.block_table + (size_t)req * a.table_stride;
+      const int piece = min(ps, TILE);  // rows one copy can bring: within one page, within one warp tile
+      for (int it = 0; it < num_stages; ++it) {
+        const int slot = it % STAGES;
+        if (it >= STAGES && !mbar_wait(empty + slot, ((it / STAGES) & 1) ^ 1, abort_flag, a.status)) break;
+        __nv_bfloat16* ks = stage_mem + slot * STAGE_ELEMS;
+        __nv_bfloat16* vs = ks + STAGE_KEYS * HD;
+        const int base = s0 + it * STAGE_KEYS;
+        uint32_t bytes = 0;
+        for (int kp = base; kp < base + STAGE_KEYS; kp += piece) {  // count first: the barrier must expect it
+          if (kp >= ke || kp + piece <= kb) continue;
+          if (table[kp / ps] >= 0) bytes += 2u * (uint32_t)min(piece, ke - kp) * HD * 2u;
+        }
+        mbar_arrive_expect_tx(full + slot, bytes);
+        for (int kp = base; kp < base + STAGE_KEYS; kp += piece) {
+          if (kp >= ke || kp + piece <= kb) continue;
+          const int page = table[kp / ps];
+          if (page < 0) { atomicExch(a.status, STATUS_BAD_PAGE); continue; }
+          const int n = min(piece, ke - kp), r0 = kp % ps, i0 = (kp - base) % TILE;
+          const int dst = ((kp - base) / TILE) * TILE * HD;  // the warp tile
+          const long long tile = cache_tile(page, kvh, a.nkv, ps, HD);
+          if (SWZ && ps == TILE && n == TILE) {  // a whole page tile is one contiguous block in both layouts
+            bulk_load(ks + dst, a.k_cache + tile, TILE * HD * 2, full + slot);
+            bulk_load(vs + dst, a.v_cache + tile, TILE * HD * 2, full + slot);
+            continue;
+          }
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            const long long src = tile + ((long long)b * ps + r0) * BW;
+            const int d = dst + (b * TILE + i0) * BW;
+            bulk_load(ks + d, a.k_cache + src, n * BW * 2, full + slot);
+            bulk_load(vs + d, a.v_cache + src, n * BW * 2, full + slot);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+      ldmatrix_x4(qf[ks], smem_u32(q_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * QS + ks * 16 + (lane >> 4) * 8));
+    for (int it = 0; it < num_stages; ++it) {
+      const int slot = it % STAGES;
+      if (!mbar_wait(full + slot, (it / STAGES) & 1, abort_flag, a.status)) break;
+      const int k0 = s0 + it * STAGE_KEYS + warp * TILE;
+      if (k0 < ke && k0 + TILE > kb) {
+        const __nv_bfloat16* kt = stage_mem + slot * STAGE_ELEMS + warp * TILE * HD;
+        const __nv_bfloat16* vt = kt + STAGE_KEYS * HD;
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          uint32_t b[4];
+          ldmatrix_x4(b, smem_u32(kt + tile_elem((lane & 7) + (lane >> 4) * 8, ks * 16 + ((lane >> 3) & 1) * 8, xmask)));
+          mma_bf16_16816(s[0], qf[ks], b[0], b[1]);
+          mma_bf16_16816(s[1], qf[ks], b[2], b[3]);
+        }
+        float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int key = k0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+            const float v = (key >= kb && key < ke) ? s[nt][e] * a.scale_log2 : -INFINITY;
+            s[nt][e] = v;
+            tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+          }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          float mx = tile_max[r];
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          const float m_new = fmaxf(m_run[r], mx);  // finite: the tile holds at least one visible key
+          corr[r] = exp2f(m_run[r] - m_new);
+          m_run[r] = m_new;
+          l_run[r] *= corr[r];
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            s[nt][e] = exp2f(s[nt][e] - m_run[e >> 1]);
+            l_run[e >> 1] += s[nt][e];
+          }
+        uint32_t pf[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]), pack_bf16(s[1][0], s[1][1]),
+                          pack_bf16(s[1][2], s[1][3])};
+#pragma unroll
+        for (int j = 0; j < HD / 8; j += 2) {
+          o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
+          o[j + 1][0] *= corr[0]; o[j + 1][1] *= corr[0]; o[j + 1][2] *= corr[1]; o[j + 1][3] *= corr[1];
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, smem_u32(vt + tile_elem((lane & 7) + ((lane >> 3) & 1) * 8, j * 8 + (lane >> 4) * 8, xmask)));
+          mma_bf16_16816(o[j], pf, b[0], b[1]);
+          mma_bf16_16816(o[j + 1], pf, b[2], b[3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty + slot);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+  }
+  __syncthreads();  // every stage has been read: the ring becomes the merge buffer
+  if (*abort_flag) {  // a wait gave up: let copies in flight land before the block leaves
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+    return;
+  }
+  float* o_s = reinterpret_cast<float*>(smem_raw);  // [WARPS][16][OS]
+  if (warp < WARPS) {
+    const int r = lane >> 2, c = (lane & 3) * 2;
+    if ((lane & 3) == 0) {
+      m_s[warp * 16 + r] = m_run[0]; m_s[warp * 16 + r + 8] = m_run[1];
+      l_s[warp * 16 + r] = l_run[0]; l_s[warp * 16 + r + 8] = l_run[1];
+    }
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) {
+      *reinterpret_cast<float2*>(o_s + (warp * 16 + r) * OS + j * 8 + c) = make_float2(o[j][0], o[j][1]);
+      *reinterpret_cast<float2*>(o_s + (warp * 16 + r + 8) * OS + j * 8 + c) = make_float2(o[j][2], o[j][3]);
+    }
+  }
+  __syncthreads();
+  const size_t part_row = ((size_t)blockIdx.x * a.nkv + kvh) * G + row0;  // + g
+  for (int idx = tid; idx < rows * HD; idx += THREADS) {
+    const int g = idx / HD, d = idx % HD;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, m_s[w * 16 + g]);
+    float acc = 0.f, sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float f = exp2f(m_s[w * 16 + g] - mx);  // a warp that saw no key has max -inf: weight 0
+      acc += o_s[(w * 16 + g) * OS + d] * f;
+      sum += l_s[w * 16 + g] * f;
+    }
+    if (nsplits == 1) {
+      a.out[(size_t)t * a.nh * HD + (size_t)(kvh * G + row0 + g) * HD + d] = __float2bfloat16_rn(acc / sum);
+    } else {
+      a.part_o[(part_row + g) * HD + d] = acc;
+      if (d == 0) { a.part_ml[(part_row + g) * 2] = mx; a.part_ml[(part_row + g) * 2 + 1] = sum; }
+    }
+  }
+  if (nsplits == 1) return;
+
+  // the block that arrives last for this (request, kv head, row tile) merges the request's items
+  __threadfence();
+  __syncthreads();
+  int* counter = a.counters + ((size_t)first_item * a.nkv + kvh) * gridDim.z + blockIdx.z;
+  if (tid == 0) *last_flag = (atomicAdd(counter, 1) == nsplits - 1);
+  __syncthreads();
+  if (!*last_flag) return;
+  __threadfence();
+  for (int idx = tid; idx < rows * HD; idx += THREADS) {
+    const int g = idx / HD, d = idx % HD;
+    float mx = -INFINITY;
+    for (int s = 0; s < nsplits; ++s)
+      mx = fmaxf(mx, __ldcg(a.part_ml + ((((size_t)(first_item + s) * a.nkv + kvh) * G + row0 + g) * 2)));
+    float acc = 0.f, sum = 0.f;
+    for (int s = 0; s < nsplits; ++s) {
+      const size_t pr = ((size_t)(first_item + s) * a.nkv + kvh) * G + row0 + g;
+      const float f = exp2f(__ldcg(a.part_ml + pr * 2) - mx);
+      acc += __ldcg(a.part_o + pr * HD + d) * f;
+      sum += __ldcg(a.part_ml + pr * 2 + 1) * f;
+    }
+    a.out[(size_t)t * a.nh * HD + (size_t)(kvh * G + row0 + g) * HD + d] = __float2bfloat16_rn(acc / sum);
+  }
+  if (tid == 0) *counter = 0;
+}
+
+constexpr size_t decode_smem_bytes() {
+  return 128 + (size_t)STAGES * 2 * STAGE_KEYS * HD * 2 + 16 * QS * 2 + 2 * WARPS * 16 * 4 + 2 * STAGES * 8 + 16;
+}
+static_assert((size_t)WARPS * 16 * OS * 4 <= (size_t)STAGES * 2 * STAGE_KEYS * HD * 2, "merge buffer must fit in the ring");
+
+}  // namespace tb
+
+extern "C" {
+
+int tb_attention_decode_head_dim() { return tb::HD; }
+
+// items: [max_items, 6] int32 on the device; grid = (max_items, nkv, ceil(G / 16)).
+int tb_attention_decode(void* stream, const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                        const int* block_table, int table_stride, const int* items, const int* num_items,
+                        int max_items, void* out, float* part_o, float* part_ml, int* counters, int* status, int nh,
+                        int nkv, int page_size, float scale) {
+  if (max_items <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || page_size <= 0) return TB_ERR_BAD_SIZE;
+  if (!(page_size == 1 || page_size == 2 || page_size == 4 || page_size == 8 || page_size % 16 == 0))
+    return TB_ERR_BAD_SIZE;
+  tb::DecodeArgs a;
+  a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride;
+  a.k_cache = (const __nv_bfloat16*)k_cache; a.v_cache = (const __nv_bfloat16*)v_cache;
+  a.block_table = block_table; a.table_stride = table_stride;
+  a.items = items; a.num_items = num_items;
+  a.out = (__nv_bfloat16*)out; a.part_o = part_o; a.part_ml = part_ml; a.counters = counters; a.status = status;
+  a.nh = nh; a.nkv = nkv; a.page_size = page_size;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  static bool configured = false;
+  const size_t smem = tb::decode_smem_bytes();
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(tb::attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int G = nh / nkv;
+  dim3 grid(max_items, nkv, (G + 15) / 16);
+  tb::attention_decode_kernel<<<grid, tb::THREADS, smem, (cudaStream_t)stream>>>(a);
+  return tb::launch_status();
+}
+
+}  // extern "C"

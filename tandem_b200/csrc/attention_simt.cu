@@ -6,10 +6,11 @@
 //
 // A query at position p of its request sees keys max(0, p - window + 1) .. p (window 0: all of
 // 0 .. p), read from the request's pages: key j lives in page table[j / page_size] at offset
-// j % page_size, cache layout [page][kv head][offset][hd].  Query head h reads kv head
+// j % page_size, tiles laid out as cache_layout.cuh says.  Query head h reads kv head
 // h / (nh / nkv).  Formula: 12vivi/tandem python/tandem/layers/attention.py:46-56,
 // python/tandem/executor/forward_context.py:70-74; online softmax as in
 // python/tandem/layers/triton_decode_attn.py:52-76 (with exp, not exp2).
+#include "cache_layout.cuh"
 #include "common.cuh"
 
 namespace tb {
@@ -46,15 +47,17 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
   for (int base = lo; base <= pos; base += 32) {
     const int key = base + lane;
     const bool valid = key <= pos;
-    long long row = -1;  // element offset of this lane's key row (same for K and V)
+    long long row = -1;  // element offset of the (page, kv head) tile of this lane's key, and its row in it
+    int r_in = 0;
     float s = -INFINITY;
     if (valid) {
       const int page = table[key / page_size];
       if (page >= 0) {
-        row = (((long long)page * nkv + kvh) * page_size + key % page_size) * hd;
+        row = cache_tile(page, kvh, nkv, page_size, hd);
+        r_in = key % page_size;
         const T* kr = k_cache + row;
         float dot = 0.f;
-        for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_float(kr[d]), dot);
+        for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_float(kr[cache_offset<T>(r_in, d, page_size, hd)]), dot);
         s = dot;
       }
     }
@@ -69,12 +72,13 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
     for (int j = 0; j < count; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const long long rj = __shfl_sync(0xffffffffu, row, j);
+      const int rin = __shfl_sync(0xffffffffu, r_in, j);
       if (rj < 0) continue;  // uniform across the warp
       const T* vr = v_cache + rj;
 #pragma unroll
       for (int i = 0; i < MAX_OWN; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) acc[i] = fmaf(pj, to_float(vr[d]), acc[i]);
+        if (d < hd) acc[i] = fmaf(pj, to_float(vr[cache_offset<T>(rin, d, page_size, hd)]), acc[i]);
       }
     }
   }

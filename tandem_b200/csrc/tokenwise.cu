@@ -4,6 +4,7 @@
 // Formulas: 12vivi/tandem python/tandem/layers/ops.py:29-61 (norm, fused add+norm, silu_and_mul,
 // rotate_half), python/tandem/layers/triton_ops.py:21-113 (the fused prologue and the fused
 // add+norm, which add in float32 and round once, as these kernels do).
+#include "cache_layout.cuh"
 #include "common.cuh"
 
 namespace tb {
@@ -76,8 +77,9 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
 //   q heads: optional RMSNorm over hd, rotary, written back in place;
 //   k heads: optional RMSNorm, rotary, written to the key cache at the token's slot;
 //   v heads: copied to the value cache.
-// Cache layout [page][kv head][offset in page][hd]; slot = page * page_size + offset; a negative
-// slot (padding row) or write_kv == 0 (the run reads another run's cache) writes nothing.
+// Cache tiles [page][kv head] of page_size x hd elements laid out as cache_layout.cuh says;
+// slot = page * page_size + offset; a negative slot (padding row) or write_kv == 0 (the run reads
+// another run's cache) writes nothing.
 // Rotary: pairs (j, j + rd/2), j < rd/2, angle table cs[pos][0..rd/2) = cos, [rd/2..rd) = sin.
 template <typename T>
 __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
@@ -96,14 +98,16 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
   const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
   if (!is_q && (slot < 0 || !write_kv)) return;
 
-  T* dst = x;
+  T* dst = x;   // q: in place.  k, v: the tile of (page, kv head); `row` is the token's row in it
+  int row = -1;
   if (!is_q) {
     const int kvh = is_k ? h - nh : h - nh - nkv;
-    const size_t page = slot / page_size, off = slot % page_size;
-    dst = (is_k ? k_cache : v_cache) + ((page * nkv + kvh) * page_size + off) * hd;
+    row = slot % page_size;
+    dst = (is_k ? k_cache : v_cache) + cache_tile(slot / page_size, kvh, nkv, page_size, hd);
   }
+  auto at = [&](int d) { return row < 0 ? d : cache_offset<T>(row, d, page_size, hd); };
   if (!is_q && !is_k) {  // v: plain copy
-    for (int d = lane; d < hd; d += 32) dst[d] = x[d];
+    for (int d = lane; d < hd; d += 32) dst[at(d)] = x[d];
     return;
   }
   const float* w = is_q ? q_w : k_w;
@@ -122,13 +126,13 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
     float a = to_float(x[j]) * inv, b = to_float(x[j + half]) * inv;
     if (w) { a *= w[j]; b *= w[j + half]; }
     const float c = cs[j], s = cs[half + j];
-    dst[j] = from_float<T>(a * c - b * s);
-    dst[j + half] = from_float<T>(b * c + a * s);
+    dst[at(j)] = from_float<T>(a * c - b * s);
+    dst[at(j + half)] = from_float<T>(b * c + a * s);
   }
   for (int d = rd + lane; d < hd; d += 32) {  // dims beyond the rotary part pass through
     float a = to_float(x[d]) * inv;
     if (w) a *= w[d];
-    dst[d] = from_float<T>(a);
+    dst[at(d)] = from_float<T>(a);
   }
 }
 

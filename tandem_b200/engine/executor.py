@@ -36,6 +36,7 @@ class Executor:
         self.device = decoder.device
         self.vocab_size = decoder.plan.embedding.vocab_size
         self.max_position = decoder.plan.max_position
+        self.mixers = [layer.mixer for layer in getattr(decoder, "layers", []) if hasattr(layer.mixer, "step_arrays")]
         self.num_steps = 0
         self.h2d_bytes_last = 0  # bytes of the last step's batch description copied to the device
 
@@ -83,7 +84,14 @@ class Executor:
         T, B = len(ids), len(entries)
         max_total = max((s + n for s, n in zip(starts, lens)), default=0)
         width = max(1, -(-max_total // ps))
-        per_group = []
+        ctx = StepContext(
+            dtype=self.decoder.dtype, device=self.device, num_tokens=T, num_seqs=B,
+            token_ids=None, positions=None, seq_of_token=None, cu_seqlens=None, seq_starts=None, state_slots=None,
+            host_starts=starts, host_lens=lens, host_slots=slots_host, max_new=max(lens, default=0),
+            max_total=max_total, storage=self.storage, page_size=ps,
+        )
+        arrays = {"ids": ids, "positions": positions, "seq_of_token": seq_of_token, "cu": cu, "starts": starts,
+                  "slots": slots_host, "rows": rows}
         for g in range(len(m.groups)):
             table = []
             slot_list = []
@@ -93,28 +101,35 @@ class Executor:
                     raise OutOfPages(f"request {e.request_id!r} holds {len(t)} pages, {start + n} tokens need more")
                 table.extend(t[:width] + [-1] * (width - len(t[:width])))
                 slot_list.extend(m.slot_index(g, e.request_id, p) for p in range(start, start + n))
-            per_group.append((table, slot_list))
+            arrays[("table", g)] = table
+            arrays[("kvslots", g)] = slot_list
+        extras: dict = {}
+        for layer in self.mixers:  # integer arrays that mixers want on the device for this step
+            layer.step_arrays(ctx, extras)
+        for key, value in extras.items():
+            arrays[("extra", key)] = value
 
-        parts = [ids, positions, seq_of_token, cu, starts, slots_host, rows]
-        for table, slot_list in per_group:
-            parts += [table, slot_list]
-        flat = torch.tensor([x for p in parts for x in p], dtype=torch.int32).pin_memory() \
-            if self.device.type == "cuda" else torch.tensor([x for p in parts for x in p], dtype=torch.int32)
-        dev = flat.to(self.device, non_blocking=True)
-        self.h2d_bytes_last = flat.numel() * 4
-        views, off = [], 0
-        for p in parts:
-            views.append(dev[off: off + len(p)])
-            off += len(p)
-        ctx = StepContext(
-            dtype=self.decoder.dtype, device=self.device, num_tokens=T, num_seqs=B,
-            token_ids=views[0], positions=views[1], seq_of_token=views[2], cu_seqlens=views[3],
-            seq_starts=views[4], state_slots=views[5], host_starts=starts, host_lens=lens, host_slots=slots_host,
-            max_new=max(lens, default=0), max_total=max_total, storage=self.storage,
-        )
+        sizes = {k: len(v) for k, v in arrays.items()}
+        flat = torch.empty(sum(sizes.values()) + 4 * len(sizes), dtype=torch.int32,
+                           pin_memory=self.device.type == "cuda")
+        offsets, off = {}, 0
+        for k, v in arrays.items():  # every array starts on a 16-byte boundary
+            flat[off: off + sizes[k]] = torch.as_tensor(v, dtype=torch.int32).reshape(-1)
+            offsets[k] = off
+            off += -(-sizes[k] // 4) * 4
+        dev = flat[:off].to(self.device, non_blocking=True)
+        self.h2d_bytes_last = off * 4
+
+        def view(k):
+            return dev[offsets[k]: offsets[k] + sizes[k]]
+
+        ctx.token_ids, ctx.positions, ctx.seq_of_token = view("ids"), view("positions"), view("seq_of_token")
+        ctx.cu_seqlens, ctx.seq_starts, ctx.state_slots = view("cu"), view("starts"), view("slots")
         for g in range(len(m.groups)):
-            ctx.tables[g] = (views[7 + 2 * g].view(B, width), views[8 + 2 * g])
-        logit_rows = views[6]
+            ctx.tables[g] = (view(("table", g)).view(B, width), view(("kvslots", g)))
+        for key in extras:
+            ctx.extras[key] = view(("extra", key))
+        logit_rows = view("rows")
         return ctx, logit_rows
 
     # ------------------------------------------------------------------ the step

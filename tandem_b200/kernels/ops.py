@@ -57,6 +57,27 @@ def _check(status: int, what: str) -> None:
         raise KernelError(f"{what}: {detail}")
 
 
+_status: dict = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """int32 [1] on the device where kernels record a fault they survived (0: none): a bounded
+    wait that gave up (1), a block table entry that should have held a page (2)."""
+    key = str(device)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device) -> None:
+    """Read the status word (this waits for the device) and raise if a kernel recorded a fault."""
+    code = int(status_word(device).item())
+    if code:
+        status_word(device).zero_()
+        what = {1: "a bounded wait inside a kernel gave up", 2: "a kernel met a missing page in a block table"}
+        raise KernelError(f"kernel status {code}: {what.get(code, 'unknown fault')}; results of this step are invalid")
+
+
 # ----------------------------------------------------------------------------- token-wise
 def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     """ids [T] int32, table [V, H] -> float32 [T, H] (the start of the residual stream)."""

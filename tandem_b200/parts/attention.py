@@ -49,6 +49,17 @@ class PagedAttention(Mixer):
         self.k_norm = weights.get("k_norm")
         self.position = position_encoding(spec.position, device)
 
+    def step_arrays(self, ctx: StepContext, out: dict) -> None:
+        """A step of single tokens runs the split-KV decode kernel: cut its items here."""
+        s = self.spec
+        key = ("decode", s.window, s.num_kv_heads)
+        if key in out or ctx.max_new != 1 or \
+                not attention_kernels.fast_decode_applies(ctx.dtype, s.head_dim, ctx.page_size):
+            return
+        items = attention_kernels.plan_decode(ctx.host_starts, s.window, s.num_kv_heads)
+        out[key] = [x for it in items for x in it]
+        out[key + ("count",)] = [len(items)]
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         s = self.spec
         qkv = ops.linear(x, self.qkv)

@@ -7,7 +7,8 @@ cache of the run in flight.
 
 Interfaces (duck-typed; these base classes only document them and give the defaults):
 
-``Mixer``         ``params(spec)``, ``kv_need(spec)``, ``state_need(spec)``, ``forward(x, ctx) -> y``
+``Mixer``         ``params(spec)``, ``kv_need(spec)``, ``state_need(spec)``, ``forward(x, ctx) -> y``,
+                  optionally ``step_arrays(ctx, out)``
 ``FeedForward``   ``params(spec)``, ``forward(x, ctx) -> y``
 ``Norm``          ``params(spec)``, ``forward(x, residual, out_dtype, rows=None) -> y`` (adds x into
                   the float32 residual in place, then normalises it)
@@ -67,6 +68,8 @@ class StepContext:
     max_new: int  # longest portion in the step
     max_total: int  # longest request after the step (start + new)
     storage: Any = None  # CacheStorage
+    page_size: int = 0
+    extras: dict = field(default_factory=dict)  # key -> int32 device array a mixer asked for (Mixer.step_arrays)
     tables: dict = field(default_factory=dict)  # group -> (block_table, slots)
     run: int = 0  # position in ModelPlan.order of the run in flight
     scratch: dict = field(default_factory=dict)  # per-step values parts may share (keyed by them)
@@ -94,6 +97,11 @@ class Mixer:
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
+
+    # Optional: ``step_arrays(self, ctx, out)`` is called once per step, before anything runs, with
+    # the host side of the batch (ctx.host_starts, ctx.host_lens, ...).  It may add integer arrays
+    # to ``out`` under keys of its own (skipping keys that are already there); they travel to the
+    # device with the batch description and appear as ``ctx.extras[key]`` in ``forward``.
 
 
 class FeedForward:

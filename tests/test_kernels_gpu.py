@@ -100,7 +100,9 @@ def test_qk_norm_rope_kv(ops, dtype, nh, nkv, hd, rd, ps, norm):
     out = qkv_d.cpu().float().view(T, nh + 2 * nkv, hd)
     torch.testing.assert_close(out[:, :nh], q, **tol(dtype, 4))
     torch.testing.assert_close(out[:, nh:], x[:, nh:], atol=0, rtol=0)  # k and v columns of qkv stay as they were
-    kc, vc = kc.cpu().float(), vc.cpu().float()
+    from tandem_b200.cache.layout import to_logical
+
+    kc, vc = to_logical(kc.cpu()).float(), to_logical(vc.cpu()).float()  # undo the physical tile layout
     written = torch.zeros(pages, ps, dtype=torch.bool)
     for t in range(T):
         s = int(slots[t])
@@ -181,6 +183,13 @@ def _paged_case(g, dtype, seqs, nh, nkv, hd, ps, extra_pages=5):
     return qkv, kc, vc, table, torch.tensor(seq_of, dtype=torch.int32), torch.tensor(positions, dtype=torch.int32), Q, K, V
 
 
+def phys(cache):
+    """A cache filled in logical order -> on the device in the layout the kernels use."""
+    from tandem_b200.cache.layout import to_physical
+
+    return to_physical(cache).to("cuda")
+
+
 def _attention_reference(Q, K, V, seqs, scale, window):
     outs = []
     for (start, n), q, k, v in zip(seqs, Q, K, V):
@@ -219,7 +228,7 @@ def test_paged_attention_simt(ops, dtype, nh, nkv, hd, ps, batch, window):
             for j in range(max(0, start - window + 1) // ps):
                 kc[table[b, j]] = float("nan")
                 table[b, j] = -1
-    out = ops.paged_attention_simt(dev(qkv), dev(kc), dev(vc), dev(table), dev(seq_of), dev(pos), nh, nkv, hd, ps, window, scale)
+    out = ops.paged_attention_simt(dev(qkv), phys(kc), phys(vc), dev(table), dev(seq_of), dev(pos), nh, nkv, hd, ps, window, scale)
     want = _attention_reference(Q, K, V, seqs, scale, window)
     torch.testing.assert_close(out.cpu().double(), want, atol=2e-5 if dtype == torch.float32 else 2e-2, rtol=1e-3)
 
@@ -244,7 +253,7 @@ def test_attention_finds_one_far_key_and_respects_edges(ops, dtype):
             rows = slice(p * ps, min(L, (p + 1) * ps))
             kc[table[0, p], :, : rows.stop - rows.start] = K[0][rows].transpose(0, 1)
         qkv[:, : nh * hd] = Q[0].reshape(1, -1)
-        out = ops.paged_attention_simt(dev(qkv), dev(kc), dev(vc), dev(table), dev(seq_of), dev(pos), nh, nkv, hd, ps,
+        out = ops.paged_attention_simt(dev(qkv), phys(kc), phys(vc), dev(table), dev(seq_of), dev(pos), nh, nkv, hd, ps,
                                        window, 1.0).cpu().float().view(nh, hd)
         inside = window is None or j > L - 1 - window
         want = V[0][j].float().repeat_interleave(nh // nkv, 0)
@@ -252,6 +261,76 @@ def test_attention_finds_one_far_key_and_respects_edges(ops, dtype):
             torch.testing.assert_close(out, want, atol=2e-2, rtol=2e-2)
         else:  # the key lies just outside the window: it must not be seen
             assert (out - want).abs().max() > 0.1
+
+
+
+# ----------------------------------------------------------------------------- decode attention (tensor cores)
+DECODE_SHAPES = [(4, 2, 16, 4), (6, 2, 32, 8), (5, 5, 48, 16), (32, 8, 128, 16), (3, 1, 80, 8), (10, 2, 64, 16),
+                 (8, 8, 64, 32), (4, 1, 256, 16), (20, 1, 64, 16), (6, 3, 128, 4), (2, 1, 112, 2), (12, 4, 96, 1)]
+DECODE_BATCHES = [[0], [15], [16], [63, 64, 65], [300, 5, 1000, 129, 0], [2047], [40] * 9]
+
+
+def _run_decode(qkv, kc, vc, table, nh, nkv, hd, ps, starts, window, scale, target_blocks):
+    from tandem_b200.kernels import attention as A
+    from tandem_b200.parts.base import KVView
+
+    items = A.plan_decode(starts, window, nkv, target_blocks)
+    flat = torch.tensor([x for it in items for x in it] + [0] * (A.ITEM_INTS * 3), dtype=torch.int32)  # spare capacity
+    count = torch.tensor([len(items)], dtype=torch.int32)
+    kv = KVView(phys(kc), phys(vc), dev(table), None, ps, True)
+    return A.paged_attention_decode(dev(qkv), kv, dev(flat), dev(count), nh, nkv, hd, scale), items
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", DECODE_SHAPES)
+@pytest.mark.parametrize("batch", range(len(DECODE_BATCHES)))
+@pytest.mark.parametrize("window,target", [(None, 592), (None, 8), (70, 4000)])
+def test_paged_attention_decode(ops, nh, nkv, hd, ps, batch, window, target):
+    if (batch + hd // 16 + (window or 0)) % 3 == 0 and hd not in (64, 128):
+        pytest.skip("covered by the neighbouring cases")
+    g = torch.Generator().manual_seed(20 + batch)
+    starts = DECODE_BATCHES[batch]
+    seqs = [(s, 1) for s in starts]
+    qkv, kc, vc, table, seq_of, pos, Q, K, V = _paged_case(g, torch.bfloat16, seqs, nh, nkv, hd, ps)
+    scale = hd ** -0.5
+    if window:
+        for b, (start, n) in enumerate(seqs):
+            for j in range(max(0, start - window + 1) // ps):
+                kc[table[b, j]] = float("nan")
+                vc[table[b, j]] = float("nan")
+                table[b, j] = -1
+    want = _attention_reference(Q, K, V, seqs, scale, window)
+    for attempt in range(2):  # twice: the arrival counters must have been put back to zero
+        out, items = _run_decode(qkv, kc, vc, table, nh, nkv, hd, ps, starts, window, scale, target)
+        torch.testing.assert_close(out.cpu().double(), want, atol=2e-2, rtol=2e-2)
+    ops.check_status("cuda")
+    if target == 4000 and max(starts) >= 300 and not window:
+        assert max(it[5] for it in items) > 1  # the long request was really split
+
+
+def test_decode_finds_one_far_key(ops):
+    nh, nkv, hd, ps = 8, 2, 128, 16
+    g = torch.Generator().manual_seed(21)
+    L = 1500
+    for j, window in [(0, None), (15, None), (16, None), (63, None), (64, None), (1499, None), (1498, None), (1000, 501),
+                      (999, 501)]:
+        seqs = [(L - 1, 1)]
+        qkv, kc, vc, table, seq_of, pos, Q, K, V = _paged_case(g, torch.bfloat16, seqs, nh, nkv, hd, ps)
+        direction = torch.randn(hd, generator=g)
+        direction /= direction.norm()
+        K[0][:] = (0.01 * torch.randn(L, nkv, hd, generator=g)).bfloat16()
+        K[0][j] = (8.0 * direction).bfloat16()
+        for p in range(-(-L // ps)):
+            rows = slice(p * ps, min(L, (p + 1) * ps))
+            kc[table[0, p], :, : rows.stop - rows.start] = K[0][rows].transpose(0, 1)
+        qkv[:, : nh * hd] = (8.0 * direction).bfloat16().repeat(nh)
+        out, _ = _run_decode(qkv, kc, vc, table, nh, nkv, hd, ps, [L - 1], window, 1.0, 4000)
+        out = out.cpu().float().view(nh, hd)
+        want = V[0][j].float().repeat_interleave(nh // nkv, 0)
+        if window is None or j > L - 1 - window:
+            torch.testing.assert_close(out, want, atol=2e-2, rtol=2e-2)
+        else:
+            assert (out - want).abs().max() > 0.1
+    ops.check_status("cuda")
 
 
 # ----------------------------------------------------------------------------- sampling
