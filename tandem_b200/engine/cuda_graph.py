@@ -1,9 +1,180 @@
-"""CUDA graphs for decode-only steps (placeholder until the graph runner is wired)."""
+"""CUDA graphs for decode-only steps.
+
+A step in which every request brings exactly one token launches a few hundred small kernels; at
+small batches their launch cost exceeds their run time.  Such steps are captured once per batch
+*bucket* (1, 2, 4, 8, 16, 24, 32, ... as python/tandem/executor/cuda_graph.py:34-38 of
+12vivi/tandem) and replayed: the batch description lives in one static int32 buffer on the
+device, refilled by a single copy before each replay.  Rows that pad a batch up to its bucket
+carry token 0 at position 0 with a negative cache slot (the cache-write kernel skips them) and no
+attention item; their outputs are never read.  Logits and sampling stay outside the graph
+(cuda_graph.py:10-11 of the reference).
+
+Only models whose mixers all declare ``capturable = True`` (everything they do in ``forward`` is
+kernel launches on the current stream, with no host-side reading of the batch) run under graphs.
+Mixers that asked for per-step arrays (``step_arrays``) say how large they can get for a bucket
+through ``step_array_capacity(bucket, max_model_len, page_size, out)``.
+"""
 
 from __future__ import annotations
 
+from typing import Sequence
+
+import torch
+
+from tandem_b200.engine.executor import Executor, StepEntry
+from tandem_b200.kernels import ops
+from tandem_b200.parts.base import StepContext
+
+
+def bucket_sizes(max_batch: int) -> list:
+    sizes = [b for b in (1, 2, 4, 8, 16) if b <= max_batch] + list(range(24, max_batch + 1, 8))
+    if max_batch not in sizes:
+        sizes.append(max_batch)
+    return sorted(set(sizes))
+
+
+class _Captured:
+    """One bucket: the static batch description, its graph and its logits."""
+
+    def __init__(self, executor: Executor, bucket: int, max_model_len: int) -> None:
+        self.executor, self.bucket = executor, bucket
+        m = executor.manager
+        self.width = -(-max_model_len // m.page_size)
+        self.sizes = {"ids": bucket, "positions": bucket, "seq_of_token": bucket, "cu": bucket + 1, "starts": bucket,
+                      "slots": bucket, "rows": bucket}
+        for g in range(len(m.groups)):
+            self.sizes[("table", g)] = bucket * self.width
+            self.sizes[("kvslots", g)] = bucket
+        capacity: dict = {}
+        for mixer in executor.mixers:
+            if hasattr(mixer, "step_array_capacity"):
+                mixer.step_array_capacity(bucket, max_model_len, m.page_size, capacity)
+        self.extra_keys = list(capacity)
+        for key, n in capacity.items():
+            self.sizes[("extra", key)] = n
+        self.offsets, off = {}, 0
+        for k, n in self.sizes.items():
+            self.offsets[k] = off
+            off += -(-n // 4) * 4
+        self.host = torch.zeros(off, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.device = torch.zeros(off, dtype=torch.int32, device=executor.device)
+        self.graph = None
+        self.logits = None
+        self.launches = 0
+
+    def view(self, k):
+        return self.device[self.offsets[k]: self.offsets[k] + self.sizes[k]]
+
+    def put(self, k, values) -> None:
+        o = self.offsets[k]
+        self.host_np[o: o + len(values)] = values
+
+    def fill(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Write this step's batch description into the pinned buffer and copy it to the device."""
+        ex, m, ps, Bk, B = self.executor, self.executor.manager, self.executor.manager.page_size, self.bucket, len(entries)
+        starts = [m.num_tokens(e.request_id) for e in entries]
+        pad = Bk - B
+        self.put("ids", [int(e.tokens[0]) for e in entries] + [0] * pad)
+        self.put("positions", starts + [0] * pad)
+        self.put("seq_of_token", list(range(Bk)))
+        self.put("cu", list(range(Bk + 1)))
+        self.put("starts", starts + [0] * pad)
+        slots = [m.slot(e.request_id) for e in entries]
+        self.put("slots", slots + [0] * pad)
+        self.put("rows", list(range(Bk)))
+        for g in range(len(m.groups)):
+            o = self.offsets[("table", g)]
+            block = self.host_np[o: o + Bk * self.width].reshape(Bk, self.width)
+            kvslots = []
+            for b, (e, s) in enumerate(zip(entries, starts)):
+                t = m.table(g, e.request_id)
+                block[b, : len(t)] = t
+                kvslots.append(m.slot_index(g, e.request_id, s))
+            self.put(("kvslots", g), kvslots + [-1] * pad)
+        ctx = StepContext(
+            dtype=ex.decoder.dtype, device=ex.device, num_tokens=Bk, num_seqs=Bk, token_ids=self.view("ids"),
+            positions=self.view("positions"), seq_of_token=self.view("seq_of_token"), cu_seqlens=self.view("cu"),
+            seq_starts=self.view("starts"), state_slots=self.view("slots"), host_starts=starts, host_lens=[1] * B,
+            host_slots=slots, max_new=1, max_total=max(starts) + 1, storage=ex.storage, page_size=ps,
+        )
+        extras: dict = {}
+        for mixer in ex.mixers:
+            mixer.step_arrays(ctx, extras)
+        for key in self.extra_keys:
+            values = extras.get(key, [])
+            if len(values) > self.sizes[("extra", key)]:
+                raise RuntimeError(f"step array {key} has {len(values)} entries, the graph was captured for "
+                                   f"{self.sizes[('extra', key)]}")
+            self.put(("extra", key), values)
+            ctx.extras[key] = self.view(("extra", key))
+        for g in range(len(m.groups)):
+            ctx.tables[g] = (self.view(("table", g)).view(Bk, self.width), self.view(("kvslots", g)))
+        self.device.copy_(self.host, non_blocking=True)
+        ex.h2d_bytes_last = self.host.numel() * 4
+        return ctx
+
+    def capture(self, entries: Sequence[StepEntry]) -> None:
+        ctx = self.fill(entries)
+        rows = self.view("rows")
+        torch.cuda.synchronize()
+        before = ops.launches
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = self.executor.decoder.forward(ctx, rows)
+        self.launches = ops.launches - before
+
 
 class DecodeGraphs:
+    def __init__(self, executor: Executor, max_batch: int, max_model_len: int) -> None:
+        self.executor, self.max_model_len = executor, max_model_len
+        self.buckets = bucket_sizes(max_batch)
+        self.captured: dict = {}
+
     @classmethod
-    def maybe(cls, executor, max_batch: int, max_model_len: int):
-        return None
+    def maybe(cls, executor: Executor, max_batch: int, max_model_len: int):
+        """Graphs need every mixer of the model to be capturable: no per-request state tensors
+        touched from the host, and array capacities known for those that plan on the host."""
+        if executor.storage.state:
+            return None
+        for layer in executor.decoder.layers:
+            if not getattr(layer.mixer, "capturable", False):
+                return None
+        for mixer in executor.mixers:
+            if not hasattr(mixer, "step_array_capacity"):
+                return None
+        return cls(executor, max_batch, max_model_len)
+
+    def takes(self, entries: Sequence[StepEntry]) -> bool:
+        return (0 < len(entries) <= self.buckets[-1]
+                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+                and all(self.executor.manager.num_tokens(e.request_id) < self.max_model_len for e in entries))
+
+    def bucket_of(self, n: int) -> int:
+        return next(b for b in self.buckets if b >= n)
+
+    def launches_per_replay(self, entries: Sequence[StepEntry]) -> int:
+        cap = self.captured.get(self.bucket_of(len(entries)))
+        return cap.launches if cap else 0
+
+    @torch.inference_mode()
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Same contract as ``Executor.run`` for a step of single tokens that all want logits."""
+        ex = self.executor
+        ex.validate(entries)
+        bucket = self.bucket_of(len(entries))
+        cap = self.captured.get(bucket)
+        if cap is None:
+            logits = ex.run(entries)  # the first step of a bucket runs eagerly (this also builds what is built lazily)
+            cap = _Captured(ex, bucket, self.max_model_len)
+            cap.capture(entries)
+            self.captured[bucket] = cap
+            return logits
+        for e in entries:
+            if ex.manager.num_tokens(e.request_id) == 0:
+                ex.storage.reset_state(ex.manager.slot(e.request_id))
+        cap.fill(entries)
+        cap.graph.replay()
+        ops.launches += cap.launches
+        ex.num_steps += 1
+        return cap.logits[: len(entries)]

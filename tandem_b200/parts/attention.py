@@ -21,6 +21,8 @@ from tandem_b200.parts.shared import position_encoding
 
 
 class PagedAttention(Mixer):
+    capturable = True  # forward only launches kernels: decode steps may be captured in CUDA graphs
+
     @staticmethod
     def params(spec: AttentionSpec) -> dict:
         q, kv, H, p = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim, spec.hidden_size, spec.prefix
@@ -59,6 +61,18 @@ class PagedAttention(Mixer):
         items = attention_kernels.plan_decode(ctx.host_starts, s.window, s.num_kv_heads)
         out[key] = [x for it in items for x in it]
         out[key + ("count",)] = [len(items)]
+
+    def step_array_capacity(self, bucket: int, max_model_len: int, page_size: int, out: dict) -> None:
+        """The most entries ``step_arrays`` can produce for a step of up to ``bucket`` single tokens
+        (CUDA graphs keep the arrays in static memory); also sizes the decode kernel's scratch."""
+        s = self.spec
+        key = ("decode", s.window, s.num_kv_heads)
+        if key in out or not attention_kernels.fast_decode_applies(self.qkv.dtype, s.head_dim, page_size):
+            return
+        items = attention_kernels.TARGET_BLOCKS // s.num_kv_heads + 2 * bucket + 8
+        out[key] = items * attention_kernels.ITEM_INTS
+        out[key + ("count",)] = 1
+        attention_kernels._workspace(self.qkv.device, items, s.num_kv_heads, s.num_heads // s.num_kv_heads, s.head_dim)
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         s = self.spec

@@ -91,6 +91,57 @@ def test_long_decoding_and_first_tokens(tiny_folder, dtype):
     assert err.max() < (1e-4 if dtype == "float32" else 0.08), int(err.argmax())
 
 
+def test_cuda_graph_decode_matches_eager(tiny_folder):
+    """Decode-only steps replayed from CUDA graphs (batches padded up to a bucket, static batch
+    description) give the logits of the eager step function, step after step, as requests come and go."""
+    from tandem_b200.engine.core import build_executor, load_model
+    from tandem_b200.engine.cuda_graph import DecodeGraphs, bucket_sizes
+    from tandem_b200.engine.executor import StepEntry
+
+    assert bucket_sizes(64) == [1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64] and bucket_sizes(5) == [1, 2, 4, 5]
+    decoder, _ = load_model(tiny_folder("B"), "bfloat16", "cuda:0")
+    eager = build_executor(decoder, page_size=16, num_pages=64, max_requests=8)
+    graph = build_executor(decoder, page_size=16, num_pages=64, max_requests=8)
+    graphs = DecodeGraphs.maybe(graph, 8, 512)
+    assert graphs is not None
+    prompts = {f"r{i}": random_tokens(80 + i, n, 1000) for i, n in enumerate([3, 70, 129, 17, 40])}
+    for ex in (eager, graph):
+        ex.step([StepEntry(rid, t, []) for rid, t in prompts.items()])
+    live = list(prompts)
+    for step in range(40):
+        if step in (7, 19, 30):  # a request ends: the batch shrinks, another bucket takes over
+            gone = live.pop(0)
+            eager.manager.end(gone), graph.manager.end(gone)
+        entries = [StepEntry(rid, [(step * 7 + i) % 1000], [0]) for i, rid in enumerate(live)]
+        assert graphs.takes(entries)
+        for ex in (eager, graph):
+            for e in entries:
+                assert ex.manager.grow(e.request_id, ex.manager.num_tokens(e.request_id) + 1)
+        a = eager.run(entries)
+        b = graphs.run(entries).clone()
+        for ex in (eager, graph):
+            for e in entries:
+                ex.manager.commit(e.request_id, 1)
+        assert (a - b).abs().max() < 0.06, step  # bfloat16 rounding only (the padded batch may pick other GEMM tiles)
+    assert len(graphs.captured) >= 3 and all(c.launches > 0 for c in graphs.captured.values())
+    assert not graphs.takes([StepEntry(live[0], [1, 2], [1])])
+
+
+def test_generation_with_cuda_graphs(tiny_folder):
+    from tandem_b200 import LLM, SamplingParams
+
+    folder = tiny_folder("A", 0.1)
+    cfg, w = plain.read_folder(folder)
+    prompts = [random_tokens(90 + i, n, 512) for i, n in enumerate([4, 30, 11])]
+    llm = LLM(model=folder, dtype="bfloat16", block_size=16, num_kv_blocks=32, max_num_seqs=4, cuda_graph=True)
+    assert llm.engine.graphs is not None
+    outs = llm.generate(prompts, SamplingParams(max_tokens=20, **GREEDY))
+    assert llm.engine.graphs.captured
+    for p, o in zip(prompts, outs):
+        assert near_tie(cfg, w, p, o.output_token_ids, plain.greedy(cfg, w, p, 20))
+    assert llm.engine.cache.all_free()
+
+
 def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tiny_folder):
     from tandem_b200 import EngineConfig, LLMEngine, SamplingParams
 
