@@ -94,12 +94,6 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
     *last_flag = 0;
     mbar_fence_init();
   }
-  // value stages start from zero: rows of a stage that no copy fills are multiplied by zero weights,
-  // and must not hold NaN bit patterns left by an earlier kernel
-  for (int s = 0; s < STAGES; ++s) {
-    uint4* v4 = reinterpret_cast<uint4*>(stage_mem + s * STAGE_ELEMS + STAGE_KEYS * HD);
-    for (int i = tid; i < STAGE_KEYS * HD / 8; i += THREADS) v4[i] = make_uint4(0, 0, 0, 0);
-  }
   for (int i = tid; i < 16 * (HD / 8); i += THREADS) {  // the query tile, 16 bytes at a time
     const int g = i / (HD / 8), c = i % (HD / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
@@ -116,39 +110,56 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
 
   if (warp == WARPS) {
     // ------------------------------------------------------------------ producer
-    if (lane == 0) {
-      const int* table = a.block_table + (size_t)req * a.table_stride;
-      const int piece = min(ps, TILE);  // rows one copy can bring: within one page, within one warp tile
-      for (int it = 0; it < num_stages; ++it) {
-        const int slot = it % STAGES;
-        if (it >= STAGES && !mbar_wait(empty + slot, ((it / STAGES) & 1) ^ 1, abort_flag, a.status)) break;
-        __nv_bfloat16* ks = stage_mem + slot * STAGE_ELEMS;
-        __nv_bfloat16* vs = ks + STAGE_KEYS * HD;
-        const int base = s0 + it * STAGE_KEYS;
-        uint32_t bytes = 0;
-        for (int kp = base; kp < base + STAGE_KEYS; kp += piece) {  // count first: the barrier must expect it
-          if (kp >= ke || kp + piece <= kb) continue;
-          if (table[kp / ps] >= 0) bytes += 2u * (uint32_t)min(piece, ke - kp) * HD * 2u;
+    // Lane i owns the i-th piece of a stage (a piece: the rows one copy can bring, inside one page
+    // and one warp tile): it looks the page up, the warp adds up the bytes, lane 0 tells the
+    // barrier, and every lane issues its own copies.
+    const int* table = a.block_table + (size_t)req * a.table_stride;
+    const int piece = min(ps, TILE);
+    const int pieces = STAGE_KEYS / piece;
+    bool alive = true;
+    for (int it = 0; it < num_stages && alive; ++it) {
+      const int slot = it % STAGES;
+      if (it >= STAGES) {
+        if (lane == 0) alive = mbar_wait(empty + slot, ((it / STAGES) & 1) ^ 1, abort_flag, a.status);
+        alive = __shfl_sync(0xffffffffu, alive, 0);
+        if (!alive) break;
+      }
+      __nv_bfloat16* ks = stage_mem + slot * STAGE_ELEMS;
+      __nv_bfloat16* vs = ks + STAGE_KEYS * HD;
+      const int base = s0 + it * STAGE_KEYS;
+      for (int p0 = 0; p0 < pieces; p0 += 32) {  // more than 32 pieces only for pages of one key
+        const int kp = base + (p0 + lane) * piece;
+        const bool mine = (p0 + lane) < pieces && kp < ke && kp + piece > kb;
+        int page = -1;
+        if (mine) {
+          page = table[kp / ps];
+          if (page < 0) atomicExch(a.status, STATUS_BAD_PAGE);
         }
-        mbar_arrive_expect_tx(full + slot, bytes);
-        for (int kp = base; kp < base + STAGE_KEYS; kp += piece) {
-          if (kp >= ke || kp + piece <= kb) continue;
-          const int page = table[kp / ps];
-          if (page < 0) { atomicExch(a.status, STATUS_BAD_PAGE); continue; }
-          const int n = min(piece, ke - kp), r0 = kp % ps, i0 = (kp - base) % TILE;
+        const int n = page >= 0 ? min(piece, ke - kp) : 0;
+        uint32_t bytes = 2u * (uint32_t)n * HD * 2u;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
+        const bool last_round = p0 + 32 >= pieces;
+        if (lane == 0) {  // one arrival per stage: the last round arrives, earlier rounds only add bytes
+          if (last_round) mbar_arrive_expect_tx(full + slot, bytes);
+          else if (bytes) asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(full + slot)), "r"(bytes) : "memory");
+        }
+        __syncwarp();
+        if (n > 0) {
+          const int r0 = kp % ps, i0 = (kp - base) % TILE;
           const int dst = ((kp - base) / TILE) * TILE * HD;  // the warp tile
           const long long tile = cache_tile(page, kvh, a.nkv, ps, HD);
           if (SWZ && ps == TILE && n == TILE) {  // a whole page tile is one contiguous block in both layouts
             bulk_load(ks + dst, a.k_cache + tile, TILE * HD * 2, full + slot);
             bulk_load(vs + dst, a.v_cache + tile, TILE * HD * 2, full + slot);
-            continue;
-          }
+          } else {
 #pragma unroll
-          for (int b = 0; b < NB; ++b) {
-            const long long src = tile + ((long long)b * ps + r0) * BW;
-            const int d = dst + (b * TILE + i0) * BW;
-            bulk_load(ks + d, a.k_cache + src, n * BW * 2, full + slot);
-            bulk_load(vs + d, a.v_cache + src, n * BW * 2, full + slot);
+            for (int b = 0; b < NB; ++b) {
+              const long long src = tile + ((long long)b * ps + r0) * BW;
+              const int d = dst + (b * TILE + i0) * BW;
+              bulk_load(ks + d, a.k_cache + src, n * BW * 2, full + slot);
+              bulk_load(vs + d, a.v_cache + src, n * BW * 2, full + slot);
+            }
           }
         }
       }
@@ -165,7 +176,18 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
       const int k0 = s0 + it * STAGE_KEYS + warp * TILE;
       if (k0 < ke && k0 + TILE > kb) {
         const __nv_bfloat16* kt = stage_mem + slot * STAGE_ELEMS + warp * TILE * HD;
-        const __nv_bfloat16* vt = kt + STAGE_KEYS * HD;
+        __nv_bfloat16* vt = stage_mem + slot * STAGE_ELEMS + STAGE_KEYS * HD + warp * TILE * HD;
+        if (k0 < kb || k0 + TILE > ke) {
+          // An edge tile: value rows of keys outside [kb, ke) get zero weights below, but may hold
+          // whatever shared memory held before (no copy filled them): make them zeros, not NaN.
+          for (int i = lane; i < TILE * (HD / 8); i += 32) {
+            const int row = i / (HD / 8), c = i % (HD / 8);
+            if (k0 + row < kb || k0 + row >= ke)
+              *reinterpret_cast<uint4*>(vt + (SWZ ? (c >> 3) * TILE * 64 + row * 64 + (c & 7) * 8 : row * HD + c * 8)) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async();  // these generic writes come before the next bulk copy into this stage
+          __syncwarp();
+        }
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {

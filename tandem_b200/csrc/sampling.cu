@@ -73,6 +73,42 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) argmax_kernel(const float* __r
   if (threadIdx.x == 0) out[r] = idx;
 }
 
+// Argmax of long rows with many blocks per row: every block folds its chunk into one 64-bit word
+// (ordered key of the value above, inverted index below, so the largest word is the largest value
+// at its lowest index), merges it into best[row] with atomicMax, and the block that arrives last
+// writes the index and puts best[row] and arrivals[row] back to zero for the next launch.
+__global__ void __launch_bounds__(256)
+argmax_split_kernel(const float* __restrict__ logits, int* __restrict__ out, unsigned long long* __restrict__ best,
+                    int* __restrict__ arrivals, int V, int chunks) {
+  __shared__ unsigned long long warp_best[8];
+  const int r = blockIdx.y, len = (V + chunks - 1) / chunks;
+  const int begin = blockIdx.x * len, end = min(V, begin + len);
+  const float* x = logits + (size_t)r * V;
+  unsigned long long mine = 0ull;
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const unsigned long long cand = ((unsigned long long)ordered_key(x[i]) << 32) | (0xFFFFFFFFu - (unsigned)i);
+    mine = cand > mine ? cand : mine;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
+    mine = other > mine ? other : mine;
+  }
+  if ((threadIdx.x & 31) == 0) warp_best[threadIdx.x >> 5] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) mine = warp_best[w] > mine ? warp_best[w] : mine;
+    if (mine) atomicMax(best + r, mine);
+    __threadfence();
+    if (atomicAdd(arrivals + r, 1) == chunks - 1) {
+      __threadfence();
+      const unsigned long long top = atomicExch(best + r, 0ull);
+      out[r] = (int)(0xFFFFFFFFu - (unsigned)(top & 0xFFFFFFFFull));
+      arrivals[r] = 0;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ min_p, const float* __restrict__ uniform,
@@ -203,6 +239,17 @@ int tb_argmax(void* stream, const float* logits, int* out, int R, int V) {
   if (R <= 0) return 0;
   if (V <= 0) return TB_ERR_BAD_SIZE;
   tb::argmax_kernel<<<R, tb::SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, out, V);
+  return tb::launch_status();
+}
+
+// The same result with `chunks` blocks per row; best [R] (64-bit) and arrivals [R] are scratch that
+// is zero before the call and zero again after it.
+int tb_argmax_split(void* stream, const float* logits, int* out, void* best, int* arrivals, int R, int V,
+                    int chunks) {
+  if (R <= 0) return 0;
+  if (V <= 0 || chunks <= 0 || R > 65535) return TB_ERR_BAD_SIZE;
+  tb::argmax_split_kernel<<<dim3(chunks, R), 256, 0, (cudaStream_t)stream>>>(
+      logits, out, (unsigned long long*)best, arrivals, V, chunks);
   return tb::launch_status();
 }
 

@@ -22,7 +22,7 @@ from tandem_b200.kernels.build import load_library
 
 ITEM_INTS = 6
 STAGE_KEYS = 64  # keys per shared-memory stage of the decode kernel: items are cut at multiples of it
-TARGET_BLOCKS = 148 * 4  # enough blocks for two waves at two blocks per SM
+TARGET_BLOCKS = 148 * 2  # one wave at two blocks per SM
 
 
 def decode_page_size_ok(page_size: int) -> bool:

@@ -217,13 +217,26 @@ def paged_attention_simt(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
 
 
 # ----------------------------------------------------------------------------- sampling
+_ARGMAX_ROWS = 4096
+_argmax_scratch: dict = {}
+
+
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     """[R, V] float32 -> int32 [R], the lowest index among equal maxima."""
     _need(logits, "logits", torch.float32)
     R, V = logits.shape
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     lib = load_library("sampling")
-    _check(lib.tb_argmax(_stream(), _ptr(logits), _ptr(out), R, V), "argmax")
+    chunks = min(64, 296 // max(1, R), V // 2048)
+    if chunks < 2 or R > _ARGMAX_ROWS:
+        _check(lib.tb_argmax(_stream(), _ptr(logits), _ptr(out), R, V), "argmax")
+        return out
+    key = str(logits.device)
+    if key not in _argmax_scratch:  # zero before and after every call: the kernel cleans up after itself
+        _argmax_scratch[key] = (torch.zeros(_ARGMAX_ROWS, dtype=torch.int64, device=logits.device),
+                                torch.zeros(_ARGMAX_ROWS, dtype=torch.int32, device=logits.device))
+    best, arrivals = _argmax_scratch[key]
+    _check(lib.tb_argmax_split(_stream(), _ptr(logits), _ptr(out), _ptr(best), _ptr(arrivals), R, V, chunks), "argmax")
     return out
 
 
