@@ -1,0 +1,115 @@
+// What the tensor-core attention kernels share: the compile-time head size and the tile geometry
+// that follows from it, addressing inside a shared-memory tile, and the producer warp that
+// streams a request's keys and values from its pages into a ring of shared-memory stages.
+//
+// A stage holds STAGE_KEYS = 64 keys as four sub-tiles of 16 keys, K then V, each sub-tile laid
+// out exactly like a 16-row cache tile (cache_layout.cuh): [column block][16 rows][block width],
+// 128-byte rows swizzled when the head size is a multiple of 64.  Copies are 1-D bulk copies
+// (the TMA unit) that complete on the stage's mbarrier.
+#pragma once
+
+#include "cache_layout.cuh"
+#include "common.cuh"
+#include "sm100_primitives.cuh"
+
+#ifndef TB_HD
+#error "compile with -DTB_HD=<head size, a multiple of 16>"
+#endif
+
+namespace tb {
+
+constexpr int HD = TB_HD;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
+constexpr bool SWZ = (HD % 64 == 0);
+constexpr int NB = SWZ ? HD / 64 : 1;  // column blocks of a cache tile
+constexpr int BW = SWZ ? 64 : HD;      // elements per row of a column block
+constexpr int TILE = 16;               // keys per sub-tile
+constexpr int STAGE_KEYS = 64;
+constexpr int STAGE_ELEMS = 2 * STAGE_KEYS * HD;  // K and V of one stage
+constexpr int STATUS_BAD_PAGE = 2;
+
+__device__ __forceinline__ int tile_elem(int i, int d, int xmask) {  // inside one sub-tile [NB][16][BW]
+  if (!SWZ) return i * HD + d;
+  const int blk = d >> 6, dd = d & 63;
+  return blk * TILE * 64 + i * 64 + ((((dd >> 3) ^ (i & xmask)) << 3) | (dd & 7));
+}
+
+__device__ __forceinline__ bool page_size_supported(int ps) {
+  return ps == 1 || ps == 2 || ps == 4 || ps == 8 || (ps & 15) == 0;
+}
+
+// The producer warp: fills stage after stage with keys [s0 + it*64, +64) of the request whose block
+// table is `table`, restricted to [kb, ke).  Lane i owns the i-th piece of a stage (a piece: the
+// rows one copy can bring, inside one page and one sub-tile): it looks the page up, the warp adds
+// up the bytes, lane 0 tells the barrier, and every lane issues its own copies.  Rows outside
+// [kb, ke) and pages that were given back are not copied.
+__device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache, const int* table,
+                                          int kvh, int nkv, int ps, int kb, int ke, int s0, int num_stages,
+                                          int stages, __nv_bfloat16* stage_mem, uint64_t* full, uint64_t* empty,
+                                          volatile int* abort_flag, int* status, int lane) {
+  const int piece = min(ps, TILE);
+  const int pieces = STAGE_KEYS / piece;
+  bool alive = true;
+  for (int it = 0; it < num_stages && alive; ++it) {
+    const int slot = it % stages;
+    if (it >= stages) {
+      if (lane == 0) alive = mbar_wait(empty + slot, ((it / stages) & 1) ^ 1, abort_flag, status);
+      alive = __shfl_sync(0xffffffffu, alive, 0);
+      if (!alive) break;
+    }
+    __nv_bfloat16* ks = stage_mem + slot * STAGE_ELEMS;
+    __nv_bfloat16* vs = ks + STAGE_KEYS * HD;
+    const int base = s0 + it * STAGE_KEYS;
+    for (int p0 = 0; p0 < pieces; p0 += 32) {  // more than 32 pieces only for pages of one key
+      const int kp = base + (p0 + lane) * piece;
+      const bool mine = (p0 + lane) < pieces && kp < ke && kp + piece > kb;
+      int page = -1;
+      if (mine) {
+        page = table[kp / ps];
+        if (page < 0) atomicExch(status, STATUS_BAD_PAGE);
+      }
+      const int n = page >= 0 ? min(piece, ke - kp) : 0;
+      uint32_t bytes = 2u * (uint32_t)n * HD * 2u;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
+      const bool last_round = p0 + 32 >= pieces;
+      if (lane == 0) {  // one arrival per stage: the last round arrives, earlier rounds only add bytes
+        if (last_round) mbar_arrive_expect_tx(full + slot, bytes);
+        else if (bytes) asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(full + slot)), "r"(bytes) : "memory");
+      }
+      __syncwarp();
+      if (n > 0) {
+        const int r0 = kp % ps, i0 = (kp - base) % TILE;
+        const int dst = ((kp - base) / TILE) * TILE * HD;  // the sub-tile
+        const long long tile = cache_tile(page, kvh, nkv, ps, HD);
+        if (SWZ && ps == TILE && n == TILE) {  // a whole page tile is one contiguous block in both layouts
+          bulk_load(ks + dst, k_cache + tile, TILE * HD * 2, full + slot);
+          bulk_load(vs + dst, v_cache + tile, TILE * HD * 2, full + slot);
+        } else {
+#pragma unroll
+          for (int b = 0; b < NB; ++b) {
+            const long long src = tile + ((long long)b * ps + r0) * BW;
+            const int d = dst + (b * TILE + i0) * BW;
+            bulk_load(ks + d, k_cache + src, n * BW * 2, full + slot);
+            bulk_load(vs + d, v_cache + src, n * BW * 2, full + slot);
+          }
+        }
+      }
+    }
+  }
+}
+
+// Value rows of the sub-tile at keys k0..k0+15 whose keys lie outside [kb, ke) get zero weights,
+// but may hold whatever shared memory held before (no copy filled them): make them zeros, not
+// NaN.  One warp; the generic writes are fenced against the next bulk copy into the stage.
+__device__ __forceinline__ void zero_value_rows(__nv_bfloat16* vt, int k0, int kb, int ke, int lane) {
+  for (int i = lane; i < TILE * (HD / 8); i += 32) {
+    const int row = i / (HD / 8), c = i % (HD / 8);
+    if (k0 + row < kb || k0 + row >= ke)
+      *reinterpret_cast<uint4*>(vt + (SWZ ? (c >> 3) * TILE * 64 + row * 64 + (c & 7) * 8 : row * HD + c * 8)) = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async();
+  __syncwarp();
+}
+
+}  // namespace tb

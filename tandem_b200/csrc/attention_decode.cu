@@ -15,30 +15,17 @@
 // It does what 12vivi/tandem's Triton split-KV kernel does
 // (python/tandem/layers/triton_decode_attn.py:28-129), and stands where it otherwise calls
 // FlashInfer's decode wrapper (python/tandem/layers/flashinfer_attention.py:138-157).
-#include "cache_layout.cuh"
-#include "common.cuh"
-#include "sm100_primitives.cuh"
-
-#ifndef TB_HD
-#error "compile with -DTB_HD=<head size, a multiple of 16>"
-#endif
+#include "attention_common.cuh"
 
 namespace tb {
 
-constexpr int HD = TB_HD;
-static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
-constexpr bool SWZ = (HD % 64 == 0);
-constexpr int NB = SWZ ? HD / 64 : 1;  // column blocks of a cache tile
-constexpr int BW = SWZ ? 64 : HD;      // elements per row of a column block
 constexpr int WARPS = 4;               // consumer warps
-constexpr int TILE = 16;               // keys per warp tile
-constexpr int STAGE_KEYS = WARPS * TILE;
+static_assert(WARPS * TILE == STAGE_KEYS, "one sub-tile of a stage per consumer warp");
 constexpr int STAGES = HD <= 64 ? 4 : (HD <= 128 ? 3 : 2);
 constexpr int QS = HD + 8;             // padded row of the query tile in shared memory
 constexpr int OS = HD + 4;             // padded row of a warp's float32 output in the merge buffer
 constexpr int THREADS = (WARPS + 1) * 32;
 constexpr int ITEM_INTS = 6;           // token row, request, key begin, key end, first item of the request, its item count
-constexpr int STATUS_BAD_PAGE = 2;
 
 struct DecodeArgs {
   const __nv_bfloat16* q;  // [T, q_stride], query heads first
@@ -58,19 +45,12 @@ struct DecodeArgs {
   float scale_log2;
 };
 
-__device__ __forceinline__ int tile_elem(int i, int d, int xmask) {  // inside one warp tile [NB][16][BW]
-  if (!SWZ) return i * HD + d;
-  const int blk = d >> 6, dd = d & 63;
-  return blk * TILE * 64 + i * 64 + ((((dd >> 3) ^ (i & xmask)) << 3) | (dd & 7));
-}
-
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeArgs a) {
   extern __shared__ unsigned char smem_unaligned[];
   if ((int)blockIdx.x >= *a.num_items) return;
   // 128-byte rows of the swizzled tiles must start on 128-byte boundaries
   unsigned char* smem_raw = smem_unaligned + ((128u - (smem_u32(smem_unaligned) & 127u)) & 127u);
   __nv_bfloat16* stage_mem = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [STAGES][K | V][STAGE_KEYS * HD]
-  constexpr int STAGE_ELEMS = 2 * STAGE_KEYS * HD;
   __nv_bfloat16* q_s = stage_mem + STAGES * STAGE_ELEMS;  // [16][QS]
   float* m_s = reinterpret_cast<float*>(q_s + 16 * QS);   // [WARPS][16]
   float* l_s = m_s + WARPS * 16;
@@ -110,60 +90,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
 
   if (warp == WARPS) {
     // ------------------------------------------------------------------ producer
-    // Lane i owns the i-th piece of a stage (a piece: the rows one copy can bring, inside one page
-    // and one warp tile): it looks the page up, the warp adds up the bytes, lane 0 tells the
-    // barrier, and every lane issues its own copies.
-    const int* table = a.block_table + (size_t)req * a.table_stride;
-    const int piece = min(ps, TILE);
-    const int pieces = STAGE_KEYS / piece;
-    bool alive = true;
-    for (int it = 0; it < num_stages && alive; ++it) {
-      const int slot = it % STAGES;
-      if (it >= STAGES) {
-        if (lane == 0) alive = mbar_wait(empty + slot, ((it / STAGES) & 1) ^ 1, abort_flag, a.status);
-        alive = __shfl_sync(0xffffffffu, alive, 0);
-        if (!alive) break;
-      }
-      __nv_bfloat16* ks = stage_mem + slot * STAGE_ELEMS;
-      __nv_bfloat16* vs = ks + STAGE_KEYS * HD;
-      const int base = s0 + it * STAGE_KEYS;
-      for (int p0 = 0; p0 < pieces; p0 += 32) {  // more than 32 pieces only for pages of one key
-        const int kp = base + (p0 + lane) * piece;
-        const bool mine = (p0 + lane) < pieces && kp < ke && kp + piece > kb;
-        int page = -1;
-        if (mine) {
-          page = table[kp / ps];
-          if (page < 0) atomicExch(a.status, STATUS_BAD_PAGE);
-        }
-        const int n = page >= 0 ? min(piece, ke - kp) : 0;
-        uint32_t bytes = 2u * (uint32_t)n * HD * 2u;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
-        const bool last_round = p0 + 32 >= pieces;
-        if (lane == 0) {  // one arrival per stage: the last round arrives, earlier rounds only add bytes
-          if (last_round) mbar_arrive_expect_tx(full + slot, bytes);
-          else if (bytes) asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(full + slot)), "r"(bytes) : "memory");
-        }
-        __syncwarp();
-        if (n > 0) {
-          const int r0 = kp % ps, i0 = (kp - base) % TILE;
-          const int dst = ((kp - base) / TILE) * TILE * HD;  // the warp tile
-          const long long tile = cache_tile(page, kvh, a.nkv, ps, HD);
-          if (SWZ && ps == TILE && n == TILE) {  // a whole page tile is one contiguous block in both layouts
-            bulk_load(ks + dst, a.k_cache + tile, TILE * HD * 2, full + slot);
-            bulk_load(vs + dst, a.v_cache + tile, TILE * HD * 2, full + slot);
-          } else {
-#pragma unroll
-            for (int b = 0; b < NB; ++b) {
-              const long long src = tile + ((long long)b * ps + r0) * BW;
-              const int d = dst + (b * TILE + i0) * BW;
-              bulk_load(ks + d, a.k_cache + src, n * BW * 2, full + slot);
-              bulk_load(vs + d, a.v_cache + src, n * BW * 2, full + slot);
-            }
-          }
-        }
-      }
-    }
+    stream_kv(a.k_cache, a.v_cache, a.block_table + (size_t)req * a.table_stride, kvh, a.nkv, ps, kb, ke, s0,
+              num_stages, STAGES, stage_mem, full, empty, abort_flag, a.status, lane);
   } else {
     // ------------------------------------------------------------------ consumers
     uint32_t qf[HD / 16][4];
@@ -177,17 +105,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
       if (k0 < ke && k0 + TILE > kb) {
         const __nv_bfloat16* kt = stage_mem + slot * STAGE_ELEMS + warp * TILE * HD;
         __nv_bfloat16* vt = stage_mem + slot * STAGE_ELEMS + STAGE_KEYS * HD + warp * TILE * HD;
-        if (k0 < kb || k0 + TILE > ke) {
-          // An edge tile: value rows of keys outside [kb, ke) get zero weights below, but may hold
-          // whatever shared memory held before (no copy filled them): make them zeros, not NaN.
-          for (int i = lane; i < TILE * (HD / 8); i += 32) {
-            const int row = i / (HD / 8), c = i % (HD / 8);
-            if (k0 + row < kb || k0 + row >= ke)
-              *reinterpret_cast<uint4*>(vt + (SWZ ? (c >> 3) * TILE * 64 + row * 64 + (c & 7) * 8 : row * HD + c * 8)) = make_uint4(0, 0, 0, 0);
-          }
-          fence_proxy_async();  // these generic writes come before the next bulk copy into this stage
-          __syncwarp();
-        }
+        if (k0 < kb || k0 + TILE > ke) zero_value_rows(vt, k0, kb, ke, lane);
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {

@@ -4,10 +4,11 @@ float32 always runs the CUDA-core kernel (true 32-bit arithmetic, batch-invarian
 bfloat16 runs the tensor-core kernels where they take the shape, and the CUDA-core kernel
 otherwise; all of them read the same cache layout.
 
-The decode kernel (every request of the step brings one token) works on *items*: a request's
-visible keys cut into ranges, so that few long requests still fill the GPU (split-KV, as
-12vivi/tandem's python/tandem/layers/triton_decode_attn.py:132-172 does).  ``plan_decode`` cuts
-them on the host; the items travel to the device with the batch description.
+The tensor-core path splits a step in two.  Requests that bring one token go to the decode kernel,
+which works on *items*: a request's visible keys cut into ranges, so that few long requests still
+fill the GPU (split-KV, as 12vivi/tandem's python/tandem/layers/triton_decode_attn.py:132-172
+does).  Requests that bring more go to the prefill kernel, which works on *tiles* of query tokens.
+Both plans are cut on the host and travel to the device with the batch description.
 """
 
 from __future__ import annotations
@@ -20,44 +21,58 @@ import torch
 from tandem_b200.kernels import ops
 from tandem_b200.kernels.build import load_library
 
-ITEM_INTS = 6
-STAGE_KEYS = 64  # keys per shared-memory stage of the decode kernel: items are cut at multiples of it
+ITEM_INTS = 6  # token row, request, key begin, key end, first item of the request, its item count
+TILE_INTS = 4  # first token row, request, first position, number of tokens
+STAGE_KEYS = 64  # keys per shared-memory stage: items are cut at multiples of it
+TILE_ROWS = 64  # rows (token x query head of the group) of a prefill tile
 TARGET_BLOCKS = 148 * 2  # one wave at two blocks per SM
 
 
-def decode_page_size_ok(page_size: int) -> bool:
+def page_size_ok(page_size: int) -> bool:
     return page_size in (1, 2, 4, 8) or page_size % 16 == 0
 
 
-def fast_decode_applies(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
-    return dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and decode_page_size_ok(page_size)
+def tensor_core_path_applies(dtype: torch.dtype, head_dim: int, page_size: int, groups: int) -> bool:
+    return (dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256 and page_size_ok(page_size)
+            and 1 <= groups <= TILE_ROWS)
 
 
-def plan_decode(starts, window: Optional[int], num_kv_heads: int, target_blocks: int = TARGET_BLOCKS) -> list:
-    """Items [token row, request, key begin, key end, first item of the request, its item count]
-    for a step in which request b brings one token at position starts[b]."""
-    lo = [max(0, s - window + 1) if window else 0 for s in starts]
-    longest = max(s + 1 - l for s, l in zip(starts, lo))
-    pieces = max(1, target_blocks // max(1, len(starts) * num_kv_heads))
+def plan_decode(rows, window: Optional[int], num_kv_heads: int, target_blocks: int = TARGET_BLOCKS) -> list:
+    """``rows``: (token row, request, position) of every request that brings one token.  Returns
+    the items [token row, request, key begin, key end, first item of the request, its item count]."""
+    if not rows:
+        return []
+    lo = [max(0, p - window + 1) if window else 0 for _, _, p in rows]
+    longest = max(p + 1 - l for (_, _, p), l in zip(rows, lo))
+    pieces = max(1, target_blocks // max(1, len(rows) * num_kv_heads))
     split = max(STAGE_KEYS, -(-(-(-longest // pieces)) // STAGE_KEYS) * STAGE_KEYS)
     items = []
-    for b, (s, l) in enumerate(zip(starts, lo)):
+    for (t, b, p), l in zip(rows, lo):
         first, k = len(items), l
-        while k <= s:
-            nxt = min(s + 1, (k // split + 1) * split)
-            items.append([b, b, k, nxt, first, 0])
+        while k <= p:
+            nxt = min(p + 1, (k // split + 1) * split)
+            items.append([t, b, k, nxt, first, 0])
             k = nxt
         for it in items[first:]:
             it[5] = len(items) - first
     return items
 
 
+def plan_prefill(seqs, groups: int) -> list:
+    """``seqs``: (first token row, request, first position, number of tokens) of every request that
+    brings several tokens.  Returns tiles of at most 64 // groups tokens, those with the most keys first."""
+    per_tile = TILE_ROWS // groups
+    tiles = [[t0 + off, b, p0 + off, min(per_tile, n - off)] for t0, b, p0, n in seqs for off in range(0, n, per_tile)]
+    tiles.sort(key=lambda x: -(x[2] + x[3]))
+    return tiles
+
+
 _workspaces: dict = {}
 
 
 def _workspace(device, items: int, num_kv_heads: int, groups: int, head_dim: int):
-    """Scratch of the decode kernel, kept and grown per device: partial outputs, their (max, sum),
-    arrival counters (zero between launches) and the status word."""
+    """Scratch of the decode kernel, kept and grown per device: partial outputs, their (max, sum)
+    and arrival counters (zero between launches)."""
     key = str(device)
     rows = items * num_kv_heads * groups
     ws = _workspaces.get(key)
@@ -73,13 +88,15 @@ def _workspace(device, items: int, num_kv_heads: int, groups: int, head_dim: int
 
 
 def paged_attention_decode(qkv: torch.Tensor, kv, items: torch.Tensor, count: torch.Tensor, num_heads: int,
-                           num_kv_heads: int, head_dim: int, scale: float) -> torch.Tensor:
+                           num_kv_heads: int, head_dim: int, scale: float,
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per request: ``items`` int32 [capacity * 6] and ``count`` int32 [1] (how many of
-    them are real) as ``plan_decode`` cut them."""
+    them are real) as ``plan_decode`` cut them.  Writes the rows of ``out`` that the items name."""
     T = qkv.shape[0]
     capacity = items.numel() // ITEM_INTS
     groups = num_heads // num_kv_heads
-    out = torch.empty((T, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    if out is None:
+        out = torch.empty((T, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     ws = _workspace(qkv.device, capacity, num_kv_heads, groups, head_dim)
     lib = load_library("attention_decode", (f"TB_HD={head_dim}",))
     ops._check(lib.tb_attention_decode(
@@ -90,12 +107,58 @@ def paged_attention_decode(qkv: torch.Tensor, kv, items: torch.Tensor, count: to
     return out
 
 
+def paged_attention_prefill(qkv: torch.Tensor, kv, tiles: torch.Tensor, num_heads: int, num_kv_heads: int,
+                            head_dim: int, window: Optional[int], scale: float,
+                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Several tokens per request: ``tiles`` int32 [n * 4] as ``plan_prefill`` cut them."""
+    T = qkv.shape[0]
+    if out is None:
+        out = torch.empty((T, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    lib = load_library("attention_prefill", (f"TB_HD={head_dim}",))
+    ops._check(lib.tb_attention_prefill(
+        ops._stream(), ops._ptr(qkv), qkv.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
+        kv.block_table.stride(0), ops._ptr(tiles), tiles.numel() // TILE_INTS, ops._ptr(out),
+        ops._ptr(ops.status_word(qkv.device)), num_heads, num_kv_heads, kv.page_size, int(window or 0),
+        ctypes.c_float(scale)), "attention_prefill")
+    return out
+
+
+def plan_key(window: Optional[int], num_heads: int, num_kv_heads: int) -> tuple:
+    return ("attention", window, num_heads, num_kv_heads)
+
+
+def plan_step(ctx, window: Optional[int], num_heads: int, num_kv_heads: int, head_dim: int, out: dict) -> None:
+    """Cut this step's attention work for the tensor-core kernels (if they apply) and put the
+    arrays into ``out``; what was planned is remembered in ``ctx.scratch`` for ``paged_attention``."""
+    key = plan_key(window, num_heads, num_kv_heads)
+    groups = num_heads // num_kv_heads
+    if key in ctx.scratch or not tensor_core_path_applies(ctx.dtype, head_dim, ctx.page_size, groups):
+        return
+    single, several, row = [], [], 0
+    for b, (start, n) in enumerate(zip(ctx.host_starts, ctx.host_lens)):
+        (single if n == 1 else several).append((row, b, start) if n == 1 else (row, b, start, n))
+        row += n
+    items = plan_decode(single, window, num_kv_heads)
+    tiles = plan_prefill(several, groups)
+    out[key + ("items",)] = [x for it in items for x in it]
+    out[key + ("count",)] = [len(items)]
+    out[key + ("tiles",)] = [x for t in tiles for x in t]
+    ctx.scratch[key] = (len(items), len(tiles))
+
+
 def paged_attention(qkv: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int, head_dim: int,
                     window: Optional[int], scale: float) -> torch.Tensor:
     """Attention output [T, nh * hd] for the query heads in the first nh*hd columns of qkv."""
-    key = ("decode", window, num_kv_heads)
-    if key in ctx.extras:
-        return paged_attention_decode(qkv, kv, ctx.extras[key], ctx.extras[key + ("count",)], num_heads, num_kv_heads,
-                                      head_dim, scale)
-    return ops.paged_attention_simt(qkv, kv.k, kv.v, kv.block_table, ctx.seq_of_token, ctx.positions, num_heads,
-                                    num_kv_heads, head_dim, kv.page_size, window, scale)
+    key = plan_key(window, num_heads, num_kv_heads)
+    planned = ctx.scratch.get(key)
+    if planned is None:
+        return ops.paged_attention_simt(qkv, kv.k, kv.v, kv.block_table, ctx.seq_of_token, ctx.positions, num_heads,
+                                        num_kv_heads, head_dim, kv.page_size, window, scale)
+    num_items, num_tiles = planned
+    out = torch.empty((qkv.shape[0], num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    if num_tiles:
+        paged_attention_prefill(qkv, kv, ctx.extras[key + ("tiles",)], num_heads, num_kv_heads, head_dim, window, scale, out)
+    if num_items:
+        paged_attention_decode(qkv, kv, ctx.extras[key + ("items",)], ctx.extras[key + ("count",)], num_heads,
+                               num_kv_heads, head_dim, scale, out)
+    return out

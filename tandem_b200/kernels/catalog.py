@@ -10,7 +10,7 @@ LIBRARIES = [
     ("gemm_f32", ()),
     ("attention_simt", ()),
     ("sampling", ()),
-] + [("attention_decode", (f"TB_HD={hd}",)) for hd in (16, 32, 48, 64, 128)]
+] + [(stem, (f"TB_HD={hd}",)) for hd in (16, 32, 48, 64, 128) for stem in ("attention_decode", "attention_prefill")]
 
 
 def build_all(verbose: bool = True) -> list:

@@ -52,27 +52,25 @@ class PagedAttention(Mixer):
         self.position = position_encoding(spec.position, device)
 
     def step_arrays(self, ctx: StepContext, out: dict) -> None:
-        """A step of single tokens runs the split-KV decode kernel: cut its items here."""
+        """Cut the step's attention work on the host: items for requests that bring one token
+        (split-KV decode kernel), tiles for those that bring more (prefill kernel)."""
         s = self.spec
-        key = ("decode", s.window, s.num_kv_heads)
-        if key in out or ctx.max_new != 1 or \
-                not attention_kernels.fast_decode_applies(ctx.dtype, s.head_dim, ctx.page_size):
-            return
-        items = attention_kernels.plan_decode(ctx.host_starts, s.window, s.num_kv_heads)
-        out[key] = [x for it in items for x in it]
-        out[key + ("count",)] = [len(items)]
+        attention_kernels.plan_step(ctx, s.window, s.num_heads, s.num_kv_heads, s.head_dim, out)
 
     def step_array_capacity(self, bucket: int, max_model_len: int, page_size: int, out: dict) -> None:
         """The most entries ``step_arrays`` can produce for a step of up to ``bucket`` single tokens
         (CUDA graphs keep the arrays in static memory); also sizes the decode kernel's scratch."""
         s = self.spec
-        key = ("decode", s.window, s.num_kv_heads)
-        if key in out or not attention_kernels.fast_decode_applies(self.qkv.dtype, s.head_dim, page_size):
+        key = attention_kernels.plan_key(s.window, s.num_heads, s.num_kv_heads)
+        groups = s.num_heads // s.num_kv_heads
+        if key + ("items",) in out or \
+                not attention_kernels.tensor_core_path_applies(self.qkv.dtype, s.head_dim, page_size, groups):
             return
         items = attention_kernels.TARGET_BLOCKS // s.num_kv_heads + 2 * bucket + 8
-        out[key] = items * attention_kernels.ITEM_INTS
+        out[key + ("items",)] = items * attention_kernels.ITEM_INTS
         out[key + ("count",)] = 1
-        attention_kernels._workspace(self.qkv.device, items, s.num_kv_heads, s.num_heads // s.num_kv_heads, s.head_dim)
+        out[key + ("tiles",)] = 0
+        attention_kernels._workspace(self.qkv.device, items, s.num_kv_heads, groups, s.head_dim)
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         s = self.spec

@@ -274,7 +274,7 @@ def _run_decode(qkv, kc, vc, table, nh, nkv, hd, ps, starts, window, scale, targ
     from tandem_b200.kernels import attention as A
     from tandem_b200.parts.base import KVView
 
-    items = A.plan_decode(starts, window, nkv, target_blocks)
+    items = A.plan_decode([(b, b, p) for b, p in enumerate(starts)], window, nkv, target_blocks)
     flat = torch.tensor([x for it in items for x in it] + [0] * (A.ITEM_INTS * 3), dtype=torch.int32)  # spare capacity
     count = torch.tensor([len(items)], dtype=torch.int32)
     kv = KVView(phys(kc), phys(vc), dev(table), None, ps, True)
@@ -330,6 +330,88 @@ def test_decode_finds_one_far_key(ops):
             torch.testing.assert_close(out, want, atol=2e-2, rtol=2e-2)
         else:
             assert (out - want).abs().max() > 0.1
+    ops.check_status("cuda")
+
+
+
+# ----------------------------------------------------------------------------- prefill attention (tensor cores)
+PREFILL_BATCHES = ATTN_BATCHES + [[(0, 64)], [(0, 65), (100, 31)], [(7, 200)], [(1000, 17), (0, 300), (63, 2)]]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,ps", DECODE_SHAPES)
+@pytest.mark.parametrize("batch", range(len(PREFILL_BATCHES)))
+@pytest.mark.parametrize("window", [None, 9, 70])
+def test_paged_attention_prefill(ops, nh, nkv, hd, ps, batch, window):
+    from tandem_b200.kernels import attention as A
+    from tandem_b200.parts.base import KVView
+
+    if (batch + hd // 16 + (window or 0)) % 3 == 0 and hd not in (64, 128):
+        pytest.skip("covered by the neighbouring cases")
+    g = torch.Generator().manual_seed(30 + batch)
+    seqs = PREFILL_BATCHES[batch]
+    qkv, kc, vc, table, seq_of, pos, Q, K, V = _paged_case(g, torch.bfloat16, seqs, nh, nkv, hd, ps)
+    scale = hd ** -0.5
+    if window:
+        for b, (start, n) in enumerate(seqs):
+            for j in range(max(0, start - window + 1) // ps):
+                kc[table[b, j]] = float("nan")
+                vc[table[b, j]] = float("nan")
+                table[b, j] = -1
+    rows, at = [], 0
+    for b, (start, n) in enumerate(seqs):
+        rows.append((at, b, start, n))
+        at += n
+    tiles = A.plan_prefill(rows, nh // nkv)
+    assert sum(t[3] for t in tiles) == at
+    flat = torch.tensor([x for t in tiles for x in t], dtype=torch.int32)
+    kv = KVView(phys(kc), phys(vc), dev(table), None, ps, True)
+    out = A.paged_attention_prefill(dev(qkv), kv, dev(flat), nh, nkv, hd, window, scale)
+    want = _attention_reference(Q, K, V, seqs, scale, window)
+    torch.testing.assert_close(out.cpu().double(), want, atol=2e-2, rtol=2e-2)
+    ops.check_status("cuda")
+
+
+def test_prefill_finds_one_far_key_per_row(ops):
+    """Every query row is aligned with one key of its own (far back, at a page edge, at the causal
+    edge, at the window's edge): its output must be that key's value."""
+    from tandem_b200.kernels import attention as A
+    from tandem_b200.parts.base import KVView
+
+    nh, nkv, hd, ps = 8, 2, 128, 16
+    g = torch.Generator().manual_seed(31)
+    start, n = 700, 90
+    L = start + n
+    for window in (None, 300):
+        seqs = [(start, n)]
+        qkv, kc, vc, table, seq_of, pos, Q, K, V = _paged_case(g, torch.bfloat16, seqs, nh, nkv, hd, ps)
+        dirs = torch.randn(n, hd, generator=g)
+        dirs /= dirs.norm(dim=-1, keepdim=True)
+        K[0][:] = (0.01 * torch.randn(L, nkv, hd, generator=g)).bfloat16()
+        target = []
+        for i in range(n):
+            q = start + i
+            lo = 0 if window is None else q - window + 1
+            j = [lo, q, (q // ps) * ps, max(lo, (q // ps) * ps - 1), lo + (q - lo) // 2][i % 5]
+            # keys already taken by an earlier row of this test would pull two rows: move on to a free one
+            while j in target and j < q:
+                j += 1
+            target.append(j)
+            K[0][j] = K[0][j] + (8.0 * dirs[i]).bfloat16()[None, :]
+            Q[0][i] = (8.0 * dirs[i]).bfloat16()[None, :].expand(nh, hd)
+        for p in range(-(-L // ps)):
+            rows = slice(p * ps, min(L, (p + 1) * ps))
+            kc[table[0, p], :, : rows.stop - rows.start] = K[0][rows].transpose(0, 1)
+        qkv[:, : nh * hd] = Q[0].reshape(n, -1)
+        tiles = A.plan_prefill([(0, 0, start, n)], nh // nkv)
+        kv = KVView(phys(kc), phys(vc), dev(table), None, ps, True)
+        out = A.paged_attention_prefill(dev(qkv), kv, dev(torch.tensor([x for t in tiles for x in t], dtype=torch.int32)),
+                                        nh, nkv, hd, window, 1.0).cpu().float().view(n, nh, hd)
+        ok = 0
+        for i, j in enumerate(target):
+            if target.count(j) == 1:
+                torch.testing.assert_close(out[i], V[0][j].float().repeat_interleave(nh // nkv, 0), atol=3e-2, rtol=3e-2)
+                ok += 1
+        assert ok > n // 2
     ops.check_status("cuda")
 
 
