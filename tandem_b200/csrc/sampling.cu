@@ -11,6 +11,7 @@
 //
 // The filtered probabilities of a row are built in `probs` [R, V], scratch memory that the caller
 // provides.
+#include "argmax_static.h"
 #include "common.cuh"
 
 namespace tb {
@@ -259,6 +260,41 @@ int tb_sample(void* stream, const float* logits, const float* temperature, const
   if (V <= 0) return TB_ERR_BAD_SIZE;
   tb::sample_kernel<<<R, tb::SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, temperature, top_k, top_p, min_p,
                                                                         uniform, probs_scratch, out, V);
+  return tb::launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// The variant of tb_argmax_split whose scratch lives in this library (argmax_static.h).
+// Layout of the array: best[MAX_ROWS] (64-bit words), then arrivals[MAX_ROWS] (32-bit).
+static __device__ __align__(256) unsigned char tb_argmax_static_scratch[TB_ARGMAX_STATIC_MAX_ROWS * 16];
+
+int tb_argmax_static(void* stream, const float* logits, int* out, int R, int V, int chunks) {
+  if (R <= 0) return 0;
+  if (V <= 0 || chunks <= 0) return TB_ERR_BAD_SIZE;
+  if (R > TB_ARGMAX_STATIC_MAX_ROWS) return TB_ERR_TOO_LARGE;
+  // In host code the array's name is only a handle: the kernel needs its device address, which
+  // differs from device to device.  Looked up once per device, with that device current.
+  static unsigned char* address[64] = {};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= 64) return TB_ERR_BAD_SIZE;
+  if (address[device] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, tb_argmax_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    address[device] = static_cast<unsigned char*>(p);
+  }
+  unsigned char* scratch = address[device];
+  // best and arrivals must be zero when the kernel starts; the kernel also leaves them zero, but a
+  // call does not rely on how the one before it ended
+  e = cudaMemsetAsync(scratch, 0, (size_t)R * 8, (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemsetAsync(scratch + (size_t)TB_ARGMAX_STATIC_MAX_ROWS * 8, 0, (size_t)R * 4, (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  tb::argmax_split_kernel<<<dim3(chunks, R), 256, 0, (cudaStream_t)stream>>>(
+      logits, out, reinterpret_cast<unsigned long long*>(scratch),
+      reinterpret_cast<int*>(scratch + (size_t)TB_ARGMAX_STATIC_MAX_ROWS * 8), V, chunks);
   return tb::launch_status();
 }
 
