@@ -10,6 +10,7 @@ LIBRARIES = [
     ("gemm_f32", ()),
     ("attention_simt", ()),
     ("sampling", ()),
+    ("gemm_skinny", ()),
 ] + [(stem, (f"TB_HD={hd}",)) for hd in (16, 32, 48, 64, 128) for stem in ("attention_decode", "attention_prefill")]
 
 
