@@ -25,13 +25,15 @@
 namespace tb {
 
 constexpr int BN = 128;  // rows of W per tile (the M of the MMA)
-constexpr int BK = 64;   // K elements per stage: 128 bytes, one swizzle row
+constexpr int BOX_K = 64;  // K elements per TMA box: 128 bytes, one swizzle row
+constexpr int BOXES = 2;   // boxes per stage, next to each other along K (256 contiguous bytes per row of W)
+constexpr int BK = BOX_K * BOXES;  // K elements per stage
 constexpr int SK_THREADS = 192;
 
 struct SkinnyArgs {
   void* y;         // [M, N] bf16 or f32
   float* partial;  // [grid][2][Mpad][BN] float32
-  int* counters;   // [tiles], zero between launches
+  int* counters;   // [tiles * 4], zero between launches
   int* status;
   int M, N, K, mpad, out_f32, stages;
 };
@@ -87,25 +89,38 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
   const int stages = a.stages, mpad = a.mpad;
-  const int stage_bytes = BN * BK * 2 + mpad * BK * 2;
+  const int stage_bytes = BN * BK * 2 + mpad * BK * 2;  // W boxes, then X boxes
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_bytes);
   uint64_t* empty = full + stages;
   uint64_t* acc_full = empty + stages;   // [2]
   uint64_t* acc_empty = acc_full + 2;    // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* last_flag = const_cast<int*>(abort_flag) + 1;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const long long KC = (a.K + BK - 1) / BK, NT = (a.N + BN - 1) / BN, total = KC * NT, blocks = gridDim.x;
   const long long c_begin = range_start(blockIdx.x, total, blocks), c_end = range_start(blockIdx.x + 1, total, blocks);
 
-  if (tid == 0) {
+  // The producer's first lane sets the barriers up and starts the first loads at once; everything
+  // else of the prologue (tensor memory, the block-wide sync) hides behind their latency.
+  int produced = 0;
+  if (warp == 4 && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     for (int s = 0; s < stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 4); }
     *abort_flag = 0;
-    *last_flag = 0;
     mbar_fence_init();
+    for (long long c = c_begin; c < c_end && produced < stages; ++c, ++produced) {
+      const int tile = (int)(c / KC), kc = (int)(c % KC);
+      unsigned char* ws = smem + (size_t)produced * stage_bytes;
+      mbar_arrive_expect_tx(full + produced, (uint32_t)stage_bytes);
+#pragma unroll
+      for (int b = 0; b < BOXES; ++b) {
+        tma_load_2d(ws + b * BN * BOX_K * 2, &map_w, kc * BK + b * BOX_K, tile * BN, full + produced);
+        tma_load_2d(ws + BN * BK * 2 + b * mpad * BOX_K * 2, &map_x, kc * BK + b * BOX_K, 0, full + produced);
+      }
+    }
   }
   if (warp == 0) {  // tensor memory for two accumulators of mpad columns (128 columns cover 2 x 64)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128) : "memory");
@@ -119,15 +134,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int it = 0;
-      for (long long c = c_begin; c < c_end; ++c, ++it) {
+      int it = produced;
+      for (long long c = c_begin + produced; c < c_end; ++c, ++it) {
         const int slot = it % stages;
-        if (it >= stages && !mbar_wait(empty + slot, ((it / stages) & 1) ^ 1, abort_flag, a.status)) break;
+        if (!mbar_wait(empty + slot, ((it / stages) & 1) ^ 1, abort_flag, a.status)) break;
         const int tile = (int)(c / KC), kc = (int)(c % KC);
         unsigned char* ws = smem + (size_t)slot * stage_bytes;
         mbar_arrive_expect_tx(full + slot, (uint32_t)stage_bytes);
-        tma_load_2d(ws, &map_w, kc * BK, tile * BN, full + slot);
-        tma_load_2d(ws + BN * BK * 2, &map_x, kc * BK, 0, full + slot);
+#pragma unroll
+        for (int b = 0; b < BOXES; ++b) {
+          tma_load_2d(ws + b * BN * BOX_K * 2, &map_w, kc * BK + b * BOX_K, tile * BN, full + slot);
+          tma_load_2d(ws + BN * BK * 2 + b * mpad * BOX_K * 2, &map_x, kc * BK + b * BOX_K, 0, full + slot);
+        }
       }
     }
   } else if (warp == 5) {
@@ -149,10 +167,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           if (!mbar_wait(full + slot, (it / stages) & 1, abort_flag, a.status)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const unsigned char* ws = smem + (size_t)slot * stage_bytes;
-          const uint64_t da = smem_desc_sw128(ws), db = smem_desc_sw128(ws + BN * BK * 2);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)  // 16 K elements = 32 bytes = 2 descriptor units further on
-            umma_bf16(d, da + 2 * k, db + 2 * k, idesc, (first && k == 0) ? 0u : 1u);
+          for (int b = 0; b < BOXES; ++b) {
+            const uint64_t da = smem_desc_sw128(ws + b * BN * BOX_K * 2);
+            const uint64_t db = smem_desc_sw128(ws + BN * BK * 2 + b * mpad * BOX_K * 2);
+#pragma unroll
+            for (int k = 0; k < BOX_K / 16; ++k)  // 16 K elements = 32 bytes = 2 descriptor units further on
+              umma_bf16(d, da + 2 * k, db + 2 * k, idesc, (first && b == 0 && k == 0) ? 0u : 1u);
+          }
           umma_commit(empty + slot);  // the stage is free once these MMAs have read it
         }
         if (!ok) break;
@@ -194,28 +216,41 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       if (lane == 0) mbar_arrive(acc_empty + buf);
       ++seg;
       if (whole) continue;
-      // a shared tile: the block that arrives last adds up the partials of all its blocks, in block order
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      // A shared tile: each warp owns 32 of the tile's columns in every block that works on the tile;
+      // the warp that arrives last for its quarter adds up that quarter's partials, in block order.
+      __syncwarp();
       const int p_lo = block_of_chunk(tile * KC, total, blocks), p_hi = block_of_chunk((tile + 1) * KC - 1, total, blocks);
-      if (tid == 0) *last_flag = (atomicAdd(a.counters + tile, 1) == p_hi - p_lo);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      const bool last = *last_flag != 0;
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // everyone has read the flag before it is written again
+      int last = 0;
+      if (lane == 0) {
+        __threadfence();
+        last = atomicAdd(a.counters + tile * 4 + warp, 1) == p_hi - p_lo;
+      }
+      last = __shfl_sync(0xffffffffu, last, 0);
       if (!last) continue;
       __threadfence();
-      for (int t = 0; t < a.M; ++t) {
-        float sum = 0.f;
+      // 16 tokens at a time, so that 16 loads are in flight per contributor
+      for (int t0 = 0; t0 < a.M; t0 += 16) {
+        float sum[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sum[j] = 0.f;
         for (int q = p_lo; q <= p_hi; ++q) {
           const int slot = range_start(q, total, blocks) >= tile * KC ? 0 : 1;
-          sum += __ldcg(a.partial + ((size_t)q * 2 + slot) * mpad * BN + (size_t)t * BN + col);
+          const float* src = a.partial + ((size_t)q * 2 + slot) * mpad * BN + (size_t)t0 * BN + col;
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = (t0 + j < a.M) ? __ldcg(src + (size_t)j * BN) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sum[j] += v[j];
         }
-        if (n < a.N) {
-          if (a.out_f32) reinterpret_cast<float*>(a.y)[(size_t)t * a.N + n] = sum;
-          else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)t * a.N + n] = __float2bfloat16_rn(sum);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = t0 + j;
+          if (t >= a.M || n >= a.N) continue;
+          if (a.out_f32) reinterpret_cast<float*>(a.y)[(size_t)t * a.N + n] = sum[j];
+          else reinterpret_cast<__nv_bfloat16*>(a.y)[(size_t)t * a.N + n] = __float2bfloat16_rn(sum[j]);
         }
       }
-      if (tid == 0) a.counters[tile] = 0;
+      if (lane == 0) a.counters[tile * 4 + warp] = 0;
     }
   }
   // ------------------------------------------------------------------ teardown
@@ -249,7 +284,7 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
   if (!enc) return TB_ERR_BAD_SIZE;
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t box[2] = {(cuuint32_t)BOX_K, (cuuint32_t)box_rows};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -261,7 +296,7 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 
 extern "C" {
 
-// Scratch the caller provides: partial >= blocks * 2 * 64 * 128 floats, counters >= ceil(N / 128)
+// Scratch the caller provides: partial >= blocks * 2 * 64 * 128 floats, counters >= 4 * ceil(N / 128)
 // ints that are zero (the kernel leaves them zero).  `blocks`: persistent blocks (one per SM).
 int tb_gemm_skinny(void* stream, const void* x, const void* w, void* y, float* partial, int* counters, int* status,
                    int M, int N, int K, int out_f32, int blocks) {
@@ -275,7 +310,7 @@ int tb_gemm_skinny(void* stream, const void* x, const void* w, void* y, float* p
   e = tb::make_map(&map_x, x, M, K, mpad);
   if (e) return e;
   const int stage_bytes = tb::BN * tb::BK * 2 + mpad * tb::BK * 2;
-  const int stages = mpad == 64 ? 8 : 10;
+  const int stages = mpad == 64 ? 4 : 5;
   const size_t smem = 1024 + (size_t)stages * stage_bytes + (2 * stages + 4) * 8 + 16;
   static size_t configured = 0;
   if (smem > configured) {

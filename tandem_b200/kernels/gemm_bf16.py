@@ -42,7 +42,16 @@ def skinny_scratch(device):
 
 
 def skinny_applies(M: int, N: int, K: int) -> bool:
-    return 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0 and N <= (1 << 16) * 128
+    """What the skinny kernel takes at all."""
+    return 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0 and N <= (1 << 14) * 128
+
+
+def skinny_preferred(M: int, N: int, K: int) -> bool:
+    """Where the skinny kernel is the faster one on a B200 (measured per shape inside CUDA graphs,
+    weights rotated through more than L2): up to 16 rows always; up to 64 rows for very tall
+    weights (the output head), where its stream-K split keeps every SM streaming to the end.
+    12vivi/tandem keeps such a table per shape as well (python/tandem/layers/triton_gemv.py:221-267)."""
+    return skinny_applies(M, N, K) and (M <= 16 or N >= 65536)
 
 
 def skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
@@ -60,6 +69,6 @@ def skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> tor
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise ops.KernelError(f"the bfloat16 product returns bfloat16 or float32, not {out_dtype}")
-    if skinny_applies(x.shape[0], weight.shape[0], x.shape[1]):
+    if skinny_preferred(x.shape[0], weight.shape[0], x.shape[1]):
         return skinny(x, weight, out_dtype)
     return _library(x, weight, out_dtype)

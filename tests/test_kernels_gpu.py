@@ -153,8 +153,16 @@ def test_gemm_bf16(ops, M, N, K, out_dtype):
     want = x.double() @ w.double().T
     xd, wd = dev(x), dev(w)
     first = None
+    from tandem_b200.kernels import gemm_bf16
+
+    def run():  # the kernel itself wherever it applies, whatever the dispatch would prefer
+        if gemm_bf16.skinny_applies(M, N, K):
+            return gemm_bf16.skinny(xd, wd, out_dtype)
+        return ops.linear(xd, wd, out_dtype=out_dtype)
+
+    torch.testing.assert_close(ops.linear(xd, wd, out_dtype=out_dtype).float(), run().float(), atol=2e-2, rtol=2e-2)
     for attempt in range(2):  # twice: the tile counters must be back at zero, and the sums the same bit for bit
-        y = ops.linear(xd, wd, out_dtype=out_dtype)
+        y = run()
         assert y.dtype == out_dtype and y.shape == (M, N)
         err = (y.cpu().double() - want).abs().max()
         assert err < (2e-2 if out_dtype == torch.bfloat16 else 2e-4 * math.sqrt(K) / 8 + 1e-4), err
