@@ -47,6 +47,8 @@ struct DecodeArgs {
 
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeArgs a) {
   extern __shared__ unsigned char smem_unaligned[];
+  pdl_launch_dependents();
+  pdl_wait();
   if ((int)blockIdx.x >= *a.num_items) return;
   // 128-byte rows of the swizzled tiles must start on 128-byte boundaries
   unsigned char* smem_raw = smem_unaligned + ((128u - (smem_u32(smem_unaligned) & 127u)) & 127u);
@@ -266,8 +268,7 @@ int tb_attention_decode(void* stream, const void* q, int q_stride, const void* k
   }
   const int G = nh / nkv;
   dim3 grid(max_items, nkv, (G + 15) / 16);
-  tb::attention_decode_kernel<<<grid, tb::THREADS, smem, (cudaStream_t)stream>>>(a);
-  return tb::launch_status();
+  return tb::launch(tb::attention_decode_kernel, grid, dim3(tb::THREADS), smem, stream, a);
 }
 
 }  // extern "C"

@@ -41,6 +41,8 @@ struct PrefillArgs {
 
 __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const PrefillArgs a) {
   extern __shared__ unsigned char smem_unaligned[];
+  pdl_launch_dependents();
+  pdl_wait();
   unsigned char* smem_raw = smem_unaligned + ((128u - (smem_u32(smem_unaligned) & 127u)) & 127u);
   __nv_bfloat16* stage_mem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* q_s = stage_mem + STAGES * STAGE_ELEMS;  // [BM][QS]
@@ -227,8 +229,7 @@ int tb_attention_prefill(void* stream, const void* q, int q_stride, const void* 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  tb::attention_prefill_kernel<<<dim3(num_tiles, nkv), tb::THREADS, smem, (cudaStream_t)stream>>>(a);
-  return tb::launch_status();
+  return tb::launch(tb::attention_prefill_kernel, dim3(num_tiles, nkv), dim3(tb::THREADS), smem, stream, a);
 }
 
 }  // extern "C"

@@ -25,6 +25,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
                       const int* __restrict__ seq_of_token, const int* __restrict__ positions, T* __restrict__ out,
                       int T_tokens, int nh, int nkv, int hd, int page_size, int window, float scale) {
   extern __shared__ float smem[];  // WARPS * hd floats: the scaled query of each warp
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long g = (long long)blockIdx.x * WARPS + warp;
   if (g >= (long long)T_tokens * nh) return;
@@ -102,9 +104,7 @@ extern "C" int tb_attention_simt(void* stream, const void* q, int q_stride, cons
   const long long warps = (long long)T_tokens * nh;
   const int blocks = (int)((warps + tb::WARPS - 1) / tb::WARPS);
   const size_t smem = (size_t)tb::WARPS * hd * sizeof(float);
-  TB_DISPATCH_DTYPE(dtype, tb::attention_simt_kernel<T><<<blocks, tb::WARPS * 32, smem, (cudaStream_t)stream>>>(
-                               (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table,
-                               table_stride, seq_of_token, positions, (T*)out, T_tokens, nh, nkv, hd, page_size,
-                               window, scale));
-  return tb::launch_status();
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::attention_simt_kernel<T>, dim3(blocks), dim3(tb::WARPS * 32), smem, stream, (const T*)q,
+                                      q_stride, (const T*)k_cache, (const T*)v_cache, block_table, table_stride, seq_of_token,
+                                      positions, (T*)out, T_tokens, nh, nkv, hd, page_size, window, scale));
 }

@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define TB_F32 0
 #define TB_BF16 1
@@ -70,17 +71,47 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 
 inline int launch_status() { return (int)cudaGetLastError(); }
 
+// Programmatic dependent launch.  Every kernel of this package is launched with the attribute that
+// lets it become resident while the kernel before it in the stream is still running, and calls
+// pdl_wait() before it reads anything an earlier kernel wrote and before it writes anything at
+// all; what it does before that (barrier set-up, tensor memory, prefetching weights, which no
+// kernel writes) overlaps the tail of its predecessor.  pdl_launch_dependents() tells the
+// scheduler that the kernel after this one may start to become resident.  TANDEM_PDL=0 turns
+// the attribute off (the two instructions are then no-ops).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("TANDEM_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void* stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace tb
 
-// Run `call<T>(...)` with T picked by a run-time dtype code.
+// `return <expression with T>` with T picked by a run-time dtype code.
 #define TB_DISPATCH_DTYPE(dtype, ...)                         \
   do {                                                        \
     if ((dtype) == TB_F32) {                                  \
       using T = float;                                        \
-      __VA_ARGS__;                                            \
+      return __VA_ARGS__;                                     \
     } else if ((dtype) == TB_BF16) {                          \
       using T = __nv_bfloat16;                                \
-      __VA_ARGS__;                                            \
+      return __VA_ARGS__;                                     \
     } else {                                                  \
       return TB_ERR_BAD_DTYPE;                                \
     }                                                         \

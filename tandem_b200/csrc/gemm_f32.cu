@@ -15,6 +15,8 @@ constexpr int BM = 64, BN = 64, BK = 16;
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W,
                                                         float* __restrict__ C, int M, int N, int K, int lda,
                                                         int ldc) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -62,6 +64,5 @@ extern "C" int tb_gemm_f32(void* stream, const float* A, const float* W, float* 
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || lda < K || ldc < N) return TB_ERR_BAD_SIZE;
   dim3 grid((N + tb::BN - 1) / tb::BN, (M + tb::BM - 1) / tb::BM);
-  tb::gemm_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(A, W, C, M, N, K, lda, ldc);
-  return tb::launch_status();
+  return tb::launch(tb::gemm_f32_kernel, grid, dim3(256), 0, stream, A, W, C, M, N, K, lda, ldc);
 }

@@ -111,15 +111,25 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 4); }
     *abort_flag = 0;
     mbar_fence_init();
+    // weights are written by no kernel: their first stages are on their way before the kernel in
+    // front of this one has finished; the activations follow once it has
     for (long long c = c_begin; c < c_end && produced < stages; ++c, ++produced) {
       const int tile = (int)(c / KC), kc = (int)(c % KC);
       unsigned char* ws = smem + (size_t)produced * stage_bytes;
       mbar_arrive_expect_tx(full + produced, (uint32_t)stage_bytes);
 #pragma unroll
-      for (int b = 0; b < BOXES; ++b) {
+      for (int b = 0; b < BOXES; ++b)
         tma_load_2d(ws + b * BN * BOX_K * 2, &map_w, kc * BK + b * BOX_K, tile * BN, full + produced);
-        tma_load_2d(ws + BN * BK * 2 + b * mpad * BOX_K * 2, &map_x, kc * BK + b * BOX_K, 0, full + produced);
-      }
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    int s = 0;
+    for (long long c = c_begin; s < produced; ++c, ++s) {
+      const int kc = (int)(c % KC);
+      unsigned char* ws = smem + (size_t)s * stage_bytes;
+#pragma unroll
+      for (int b = 0; b < BOXES; ++b)
+        tma_load_2d(ws + BN * BK * 2 + b * mpad * BOX_K * 2, &map_x, kc * BK + b * BOX_K, 0, full + s);
     }
   }
   if (warp == 0) {  // tensor memory for two accumulators of mpad columns (128 columns cover 2 x 64)
@@ -129,6 +139,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  pdl_wait();  // (the producer's first lane has waited already)
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 4) {
@@ -323,8 +334,7 @@ int tb_gemm_skinny(void* stream, const void* x, const void* w, void* y, float* p
   a.y = y; a.partial = partial; a.counters = counters; a.status = status;
   a.M = M; a.N = N; a.K = K; a.mpad = mpad; a.out_f32 = out_f32; a.stages = stages;
   const int grid = (int)(total < blocks ? total : blocks);
-  tb::gemm_skinny_kernel<<<grid, tb::SK_THREADS, smem, (cudaStream_t)stream>>>(map_w, map_x, a);
-  return tb::launch_status();
+  return tb::launch(tb::gemm_skinny_kernel, dim3(grid), dim3(tb::SK_THREADS), smem, stream, map_w, map_x, a);
 }
 
 }  // extern "C"

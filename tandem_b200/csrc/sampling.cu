@@ -69,6 +69,8 @@ __device__ int row_argmax(const float* __restrict__ x, int V, float* fscratch, i
 __global__ void __launch_bounds__(SAMPLE_THREADS) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
   __shared__ float fs[33];
   __shared__ int is[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int idx = row_argmax(logits + (size_t)r * V, V, fs, is);
   if (threadIdx.x == 0) out[r] = idx;
@@ -82,6 +84,8 @@ __global__ void __launch_bounds__(256)
 argmax_split_kernel(const float* __restrict__ logits, int* __restrict__ out, unsigned long long* __restrict__ best,
                     int* __restrict__ arrivals, int V, int chunks) {
   __shared__ unsigned long long warp_best[8];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.y, len = (V + chunks - 1) / chunks;
   const int begin = blockIdx.x * len, end = min(V, begin + len);
   const float* x = logits + (size_t)r * V;
@@ -118,6 +122,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   __shared__ int is[33];
   __shared__ float prefix[SAMPLE_THREADS];
   __shared__ int chosen;
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* x = logits + (size_t)r * V;
   float* p = probs + (size_t)r * V;
@@ -239,8 +245,7 @@ extern "C" {
 int tb_argmax(void* stream, const float* logits, int* out, int R, int V) {
   if (R <= 0) return 0;
   if (V <= 0) return TB_ERR_BAD_SIZE;
-  tb::argmax_kernel<<<R, tb::SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, out, V);
-  return tb::launch_status();
+  return tb::launch(tb::argmax_kernel, dim3(R), dim3(tb::SAMPLE_THREADS), 0, stream, logits, out, V);
 }
 
 // The same result with `chunks` blocks per row; best [R] (64-bit) and arrivals [R] are scratch that
@@ -249,18 +254,16 @@ int tb_argmax_split(void* stream, const float* logits, int* out, void* best, int
                     int chunks) {
   if (R <= 0) return 0;
   if (V <= 0 || chunks <= 0 || R > 65535) return TB_ERR_BAD_SIZE;
-  tb::argmax_split_kernel<<<dim3(chunks, R), 256, 0, (cudaStream_t)stream>>>(
-      logits, out, (unsigned long long*)best, arrivals, V, chunks);
-  return tb::launch_status();
+  return tb::launch(tb::argmax_split_kernel, dim3(chunks, R), dim3(256), 0, stream, logits, out, (unsigned long long*)best,
+                    arrivals, V, chunks);
 }
 
 int tb_sample(void* stream, const float* logits, const float* temperature, const int* top_k, const float* top_p,
               const float* min_p, const float* uniform, float* probs_scratch, int* out, int R, int V) {
   if (R <= 0) return 0;
   if (V <= 0) return TB_ERR_BAD_SIZE;
-  tb::sample_kernel<<<R, tb::SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, temperature, top_k, top_p, min_p,
-                                                                        uniform, probs_scratch, out, V);
-  return tb::launch_status();
+  return tb::launch(tb::sample_kernel, dim3(R), dim3(tb::SAMPLE_THREADS), 0, stream, logits, temperature, top_k, top_p, min_p,
+                    uniform, probs_scratch, out, V);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -14,6 +14,8 @@ namespace tb {
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int H, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * H;
@@ -33,6 +35,8 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
                                    const float* __restrict__ weight, T* __restrict__ y,
                                    const int* __restrict__ rows, int H, float eps) {
   __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* res = residual + (size_t)src * H;
@@ -88,6 +92,8 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
                                        T* __restrict__ k_cache, T* __restrict__ v_cache, int T_tokens, int nh,
                                        int nkv, int hd, int rd, int page_size, float eps, int write_kv,
                                        int max_pos) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int heads = nh + 2 * nkv;
   const long long g = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -140,6 +146,8 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
        e += (long long)gridDim.x * blockDim.x) {
     const long long t = e / I;
@@ -157,18 +165,15 @@ extern "C" {
 int tb_embedding(void* stream, const int* ids, const void* table, float* out, int T_tokens, int H, int V,
                  int dtype) {
   if (T_tokens <= 0) return 0;
-  TB_DISPATCH_DTYPE(dtype, tb::embedding_kernel<T><<<T_tokens, 256, 0, (cudaStream_t)stream>>>(
-                               ids, (const T*)table, out, H, V));
-  return tb::launch_status();
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::embedding_kernel<T>, dim3(T_tokens), dim3(256), 0, stream, ids, (const T*)table, out, H, V));
 }
 
 int tb_add_rmsnorm(void* stream, const void* x, float* residual, const float* weight, void* y, const int* rows,
                    int num_rows, int H, float eps, int dtype) {
   if (num_rows <= 0) return 0;
   const int threads = H >= 4096 ? 512 : 256;
-  TB_DISPATCH_DTYPE(dtype, tb::add_rmsnorm_kernel<T><<<num_rows, threads, 0, (cudaStream_t)stream>>>(
-                               (const T*)x, residual, weight, (T*)y, rows, H, eps));
-  return tb::launch_status();
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::add_rmsnorm_kernel<T>, dim3(num_rows), dim3(threads), 0, stream, (const T*)x, residual,
+                                      weight, (T*)y, rows, H, eps));
 }
 
 int tb_qk_norm_rope_kv(void* stream, void* qkv, const int* positions, const int* slots, const float* q_w,
@@ -178,10 +183,9 @@ int tb_qk_norm_rope_kv(void* stream, void* qkv, const int* positions, const int*
   if (rd < 0 || rd > hd || (rd & 1) || page_size <= 0) return TB_ERR_BAD_SIZE;
   const long long warps = (long long)T_tokens * (nh + 2 * nkv);
   const int blocks = (int)((warps + 3) / 4);
-  TB_DISPATCH_DTYPE(dtype, tb::qk_norm_rope_kv_kernel<T><<<blocks, 128, 0, (cudaStream_t)stream>>>(
-                               (T*)qkv, positions, slots, q_w, k_w, cos_sin, (T*)k_cache, (T*)v_cache, T_tokens, nh,
-                               nkv, hd, rd, page_size, eps, write_kv, max_pos));
-  return tb::launch_status();
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::qk_norm_rope_kv_kernel<T>, dim3(blocks), dim3(128), 0, stream, (T*)qkv, positions, slots,
+                                      q_w, k_w, cos_sin, (T*)k_cache, (T*)v_cache, T_tokens, nh, nkv, hd, rd, page_size, eps,
+                                      write_kv, max_pos));
 }
 
 int tb_silu_mul(void* stream, const void* gu, void* out, int T_tokens, int I, int dtype) {
@@ -189,9 +193,7 @@ int tb_silu_mul(void* stream, const void* gu, void* out, int T_tokens, int I, in
   if (total <= 0) return 0;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  TB_DISPATCH_DTYPE(dtype, tb::silu_mul_kernel<T><<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
-                               (const T*)gu, (T*)out, total, I));
-  return tb::launch_status();
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::silu_mul_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (const T*)gu, (T*)out, total, I));
 }
 
 }  // extern "C"
