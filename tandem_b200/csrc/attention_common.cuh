@@ -27,6 +27,7 @@ constexpr int TILE = 16;               // keys per sub-tile
 constexpr int STAGE_KEYS = 64;
 constexpr int STAGE_ELEMS = 2 * STAGE_KEYS * HD;  // K and V of one stage
 constexpr int STATUS_BAD_PAGE = 2;
+constexpr int TABLE_CACHE = 512;  // page numbers a block keeps in shared memory
 
 __device__ __forceinline__ int tile_elem(int i, int d, int xmask) {  // inside one sub-tile [NB][16][BW]
   if (!SWZ) return i * HD + d;
@@ -36,6 +37,17 @@ __device__ __forceinline__ int tile_elem(int i, int d, int xmask) {  // inside o
 
 __device__ __forceinline__ bool page_size_supported(int ps) {
   return ps == 1 || ps == 2 || ps == 4 || ps == 8 || (ps & 15) == 0;
+}
+
+// Copy the page numbers of keys [s0, ke) into shared memory (all threads; the caller synchronises
+// afterwards) and return a pointer that is indexed like the global table.  Ranges that do not fit
+// keep reading the global table.
+__device__ __forceinline__ const int* cache_table(const int* table, int* table_s, int s0, int ke, int ps, int tid,
+                                                  int threads) {
+  const int first = s0 / ps, count = (ke + ps - 1) / ps - first;
+  if (count > TABLE_CACHE) return table;
+  for (int i = tid; i < count; i += threads) table_s[i] = table[first + i];
+  return table_s - first;
 }
 
 // The producer warp: fills stage after stage with keys [s0 + it*64, +64) of the request whose block

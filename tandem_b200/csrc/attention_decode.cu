@@ -25,6 +25,7 @@ constexpr int STAGES = HD <= 64 ? 4 : (HD <= 128 ? 3 : 2);
 constexpr int QS = HD + 8;             // padded row of the query tile in shared memory
 constexpr int OS = HD + 4;             // padded row of a warp's float32 output in the merge buffer
 constexpr int THREADS = (WARPS + 1) * 32;
+constexpr int MAX_SPLITS = 64;         // items of one request the fast merge takes (48 floats of shared memory each)
 constexpr int ITEM_INTS = 6;           // token row, request, key begin, key end, first item of the request, its item count
 
 struct DecodeArgs {
@@ -60,6 +61,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   uint64_t* empty = full + STAGES;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + STAGES);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
+  int* table_s = last_flag + 1;  // [TABLE_CACHE] the request's page numbers for this block's keys
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
@@ -82,6 +84,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
     if (g < rows) v = *reinterpret_cast<const uint4*>(a.q + (size_t)t * a.q_stride + (size_t)(kvh * G + row0 + g) * HD + c * 8);
     *reinterpret_cast<uint4*>(q_s + g * QS + c * 8) = v;
   }
+  const int* table = cache_table(a.block_table + (size_t)req * a.table_stride, table_s, s0, ke, ps, tid, THREADS);
   fence_proxy_async();
   __syncthreads();
 
@@ -92,7 +95,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
 
   if (warp == WARPS) {
     // ------------------------------------------------------------------ producer
-    stream_kv(a.k_cache, a.v_cache, a.block_table + (size_t)req * a.table_stride, kvh, a.nkv, ps, kb, ke, s0,
+    stream_kv(a.k_cache, a.v_cache, table, kvh, a.nkv, ps, kb, ke, s0,
               num_stages, STAGES, stage_mem, full, empty, abort_flag, a.status, lane);
   } else {
     // ------------------------------------------------------------------ consumers
@@ -207,34 +210,69 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   if (nsplits == 1) return;
 
   // the block that arrives last for this (request, kv head, row tile) merges the request's items
-  __threadfence();
   __syncthreads();
   int* counter = a.counters + ((size_t)first_item * a.nkv + kvh) * gridDim.z + blockIdx.z;
-  if (tid == 0) *last_flag = (atomicAdd(counter, 1) == nsplits - 1);
+  if (tid == 0) *last_flag = (arrive_acq_rel(counter) == nsplits - 1);
   __syncthreads();
   if (!*last_flag) return;
-  __threadfence();
-  for (int idx = tid; idx < rows * HD; idx += THREADS) {
-    const int g = idx / HD, d = idx % HD;
-    float mx = -INFINITY;
-    for (int s = 0; s < nsplits; ++s)
-      mx = fmaxf(mx, __ldcg(a.part_ml + ((((size_t)(first_item + s) * a.nkv + kvh) * G + row0 + g) * 2)));
-    float acc = 0.f, sum = 0.f;
-    for (int s = 0; s < nsplits; ++s) {
+  if (nsplits <= MAX_SPLITS) {
+    // 1) every item's (max, sum) into shared memory, one load per thread at a time
+    float* ml = o_s;                       // [nsplits][16][2]
+    float* weight = o_s + MAX_SPLITS * 32;  // [nsplits][16]
+    for (int idx = tid; idx < nsplits * rows; idx += THREADS) {
+      const int s = idx / rows, g = idx % rows;
       const size_t pr = ((size_t)(first_item + s) * a.nkv + kvh) * G + row0 + g;
-      const float f = exp2f(__ldcg(a.part_ml + pr * 2) - mx);
-      acc += __ldcg(a.part_o + pr * HD + d) * f;
-      sum += __ldcg(a.part_ml + pr * 2 + 1) * f;
+      ml[(s * 16 + g) * 2] = __ldcg(a.part_ml + pr * 2);
+      ml[(s * 16 + g) * 2 + 1] = __ldcg(a.part_ml + pr * 2 + 1);
     }
-    a.out[(size_t)t * a.nh * HD + (size_t)(kvh * G + row0 + g) * HD + d] = __float2bfloat16_rn(acc / sum);
+    __syncthreads();
+    // 2) one thread per row turns them into the items' weights exp2(m_s - m) / sum
+    if (tid < rows) {
+      float mx = -INFINITY, sum = 0.f;
+      for (int s = 0; s < nsplits; ++s) mx = fmaxf(mx, ml[(s * 16 + tid) * 2]);
+      for (int s = 0; s < nsplits; ++s) sum += ml[(s * 16 + tid) * 2 + 1] * exp2f(ml[(s * 16 + tid) * 2] - mx);
+      const float inv = 1.f / sum;
+      for (int s = 0; s < nsplits; ++s) weight[s * 16 + tid] = exp2f(ml[(s * 16 + tid) * 2] - mx) * inv;
+    }
+    __syncthreads();
+    // 3) the weighted sum of the items' outputs, eight loads in flight per thread
+    for (int idx = tid; idx < rows * HD; idx += THREADS) {
+      const int g = idx / HD, d = idx % HD;
+      float acc = 0.f;
+      for (int s0 = 0; s0 < nsplits; s0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          v[j] = s0 + j < nsplits ? __ldcg(a.part_o + (((size_t)(first_item + s0 + j) * a.nkv + kvh) * G + row0 + g) * HD + d) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc += s0 + j < nsplits ? v[j] * weight[(s0 + j) * 16 + g] : 0.f;
+      }
+      a.out[(size_t)t * a.nh * HD + (size_t)(kvh * G + row0 + g) * HD + d] = __float2bfloat16_rn(acc);
+    }
+  } else {
+    for (int idx = tid; idx < rows * HD; idx += THREADS) {
+      const int g = idx / HD, d = idx % HD;
+      float mx = -INFINITY;
+      for (int s = 0; s < nsplits; ++s)
+        mx = fmaxf(mx, __ldcg(a.part_ml + ((((size_t)(first_item + s) * a.nkv + kvh) * G + row0 + g) * 2)));
+      float acc = 0.f, sum = 0.f;
+      for (int s = 0; s < nsplits; ++s) {
+        const size_t pr = ((size_t)(first_item + s) * a.nkv + kvh) * G + row0 + g;
+        const float f = exp2f(__ldcg(a.part_ml + pr * 2) - mx);
+        acc += __ldcg(a.part_o + pr * HD + d) * f;
+        sum += __ldcg(a.part_ml + pr * 2 + 1) * f;
+      }
+      a.out[(size_t)t * a.nh * HD + (size_t)(kvh * G + row0 + g) * HD + d] = __float2bfloat16_rn(acc / sum);
+    }
   }
   if (tid == 0) *counter = 0;
 }
 
 constexpr size_t decode_smem_bytes() {
-  return 128 + (size_t)STAGES * 2 * STAGE_KEYS * HD * 2 + 16 * QS * 2 + 2 * WARPS * 16 * 4 + 2 * STAGES * 8 + 16;
+  return 128 + (size_t)STAGES * 2 * STAGE_KEYS * HD * 2 + 16 * QS * 2 + 2 * WARPS * 16 * 4 + 2 * STAGES * 8 + 16 + TABLE_CACHE * 4;
 }
 static_assert((size_t)WARPS * 16 * OS * 4 <= (size_t)STAGES * 2 * STAGE_KEYS * HD * 2, "merge buffer must fit in the ring");
+static_assert((size_t)MAX_SPLITS * 48 * 4 <= (size_t)STAGES * 2 * STAGE_KEYS * HD * 2, "split weights must fit in the ring");
 
 }  // namespace tb
 

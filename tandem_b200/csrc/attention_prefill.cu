@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const Prefil
   uint64_t* full = reinterpret_cast<uint64_t*>(q_s + BM * QS);
   uint64_t* empty = full + STAGES;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + STAGES);
+  int* table_s = const_cast<int*>(abort_flag) + 2;  // [TABLE_CACHE] the request's page numbers for this tile's keys
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int* tile = a.tiles + (size_t)blockIdx.x * TILE_INTS;
@@ -72,11 +73,12 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const Prefil
       v = *reinterpret_cast<const uint4*>(a.q + (size_t)(t0 + tl) * a.q_stride + (size_t)(kvh * G + g) * HD + c * 8);
     *reinterpret_cast<uint4*>(q_s + row * QS + c * 8) = v;
   }
+  const int* table = cache_table(a.block_table + (size_t)req * a.table_stride, table_s, s0, ke, ps, tid, THREADS);
   fence_proxy_async();
   __syncthreads();
 
   if (warp == WARPS) {
-    stream_kv(a.k_cache, a.v_cache, a.block_table + (size_t)req * a.table_stride, kvh, a.nkv, ps, kb, ke, s0,
+    stream_kv(a.k_cache, a.v_cache, table, kvh, a.nkv, ps, kb, ke, s0,
               num_stages, STAGES, stage_mem, full, empty, abort_flag, a.status, lane);
     return;
   }
@@ -197,7 +199,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const Prefil
   }
 }
 
-constexpr size_t prefill_smem_bytes() { return 128 + (size_t)STAGES * STAGE_ELEMS * 2 + (size_t)BM * QS * 2 + 2 * STAGES * 8 + 16; }
+constexpr size_t prefill_smem_bytes() { return 128 + (size_t)STAGES * STAGE_ELEMS * 2 + (size_t)BM * QS * 2 + 2 * STAGES * 8 + 16 + TABLE_CACHE * 4; }
 
 }  // namespace tb
 

@@ -69,6 +69,15 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return scratch[32];
 }
 
+// Arrival on a counter that publishes what the arriving threads wrote before it and, for the thread
+// that turns out to be last, makes visible what the earlier arrivals published: one acquire-release
+// atomic instead of fence + atomic + fence (the caller synchronises its threads before and after).
+__device__ __forceinline__ int arrive_acq_rel(int* counter) {
+  int old;
+  asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
+  return old;
+}
+
 inline int launch_status() { return (int)cudaGetLastError(); }
 
 // Programmatic dependent launch.  Every kernel of this package is launched with the attribute that

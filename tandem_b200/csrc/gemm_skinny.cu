@@ -232,26 +232,28 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       __syncwarp();
       const int p_lo = block_of_chunk(tile * KC, total, blocks), p_hi = block_of_chunk((tile + 1) * KC - 1, total, blocks);
       int last = 0;
-      if (lane == 0) {
-        __threadfence();
-        last = atomicAdd(a.counters + tile * 4 + warp, 1) == p_hi - p_lo;
-      }
+      if (lane == 0) last = arrive_acq_rel(a.counters + tile * 4 + warp) == p_hi - p_lo;
       last = __shfl_sync(0xffffffffu, last, 0);
       if (!last) continue;
-      __threadfence();
       // 16 tokens at a time, so that 16 loads are in flight per contributor
       for (int t0 = 0; t0 < a.M; t0 += 16) {
         float sum[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) sum[j] = 0.f;
-        for (int q = p_lo; q <= p_hi; ++q) {
-          const int slot = range_start(q, total, blocks) >= tile * KC ? 0 : 1;
-          const float* src = a.partial + ((size_t)q * 2 + slot) * mpad * BN + (size_t)t0 * BN + col;
-          float v[16];
+        for (int q0 = p_lo; q0 <= p_hi; q0 += 4) {  // four contributors' loads in flight, summed in block order
+          float v[4][16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = (t0 + j < a.M) ? __ldcg(src + (size_t)j * BN) : 0.f;
+          for (int i = 0; i < 4; ++i) {
+            const int q = q0 + i;
+            const int slot = range_start(q, total, blocks) >= tile * KC ? 0 : 1;
+            const float* src = a.partial + ((size_t)q * 2 + slot) * mpad * BN + (size_t)t0 * BN + col;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) sum[j] += v[j];
+            for (int j = 0; j < 16; ++j) v[i][j] = (q <= p_hi && t0 + j < a.M) ? __ldcg(src + (size_t)j * BN) : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sum[j] += v[i][j];
         }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {

@@ -26,6 +26,7 @@ TILE_INTS = 4  # first token row, request, first position, number of tokens
 STAGE_KEYS = 64  # keys per shared-memory stage: items are cut at multiples of it
 TILE_ROWS = 64  # rows (token x query head of the group) of a prefill tile
 TARGET_BLOCKS = 148 * 2  # one wave at two blocks per SM
+MAX_SPLITS = 64  # items per request the kernel's fast merge takes
 
 
 def page_size_ok(page_size: int) -> bool:
@@ -44,7 +45,7 @@ def plan_decode(rows, window: Optional[int], num_kv_heads: int, target_blocks: i
         return []
     lo = [max(0, p - window + 1) if window else 0 for _, _, p in rows]
     longest = max(p + 1 - l for (_, _, p), l in zip(rows, lo))
-    pieces = max(1, target_blocks // max(1, len(rows) * num_kv_heads))
+    pieces = min(MAX_SPLITS - 1, max(1, target_blocks // max(1, len(rows) * num_kv_heads)))
     split = max(STAGE_KEYS, -(-(-(-longest // pieces)) // STAGE_KEYS) * STAGE_KEYS)
     items = []
     for (t, b, p), l in zip(rows, lo):
