@@ -103,6 +103,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   // The producer's first lane sets the barriers up and starts the first loads at once; everything
   // else of the prologue (tensor memory, the block-wide sync) hides behind their latency.
+  pdl_launch_dependents();  // by every thread: the kernel behind this one may become resident
   int produced = 0;
   if (warp == 4 && lane == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -121,7 +122,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       for (int b = 0; b < BOXES; ++b)
         tma_load_2d(ws + b * BN * BOX_K * 2, &map_w, kc * BK + b * BOX_K, tile * BN, full + produced);
     }
-    pdl_launch_dependents();
     pdl_wait();
     int s = 0;
     for (long long c = c_begin; s < produced; ++c, ++s) {
