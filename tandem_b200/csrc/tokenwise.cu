@@ -24,6 +24,16 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     return;
   }
   const T* row = table + (size_t)id * H;
+  if (sizeof(T) == 2 && (H & 7) == 0) {  // 16 bytes in, two 16-byte stores out
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(row + i);
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]), c = __bfloat1622float2(p[2]), d = __bfloat1622float2(p[3]);
+      *reinterpret_cast<float4*>(o + i) = make_float4(a.x, a.y, b.x, b.y);
+      *reinterpret_cast<float4*>(o + i + 4) = make_float4(c.x, c.y, d.x, d.y);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
 }
 
@@ -113,7 +123,11 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
   }
   auto at = [&](int d) { return row < 0 ? d : cache_offset<T>(row, d, page_size, hd); };
   if (!is_q && !is_k) {  // v: plain copy
-    for (int d = lane; d < hd; d += 32) dst[at(d)] = x[d];
+    if (sizeof(T) == 2) {
+      for (int d = lane * 2; d < hd; d += 64) *reinterpret_cast<uint32_t*>(dst + at(d)) = *reinterpret_cast<const uint32_t*>(x + d);
+    } else {
+      for (int d = lane; d < hd; d += 32) dst[at(d)] = x[d];
+    }
     return;
   }
   const float* w = is_q ? q_w : k_w;
@@ -128,6 +142,23 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
   pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);  // the host checks positions
   const int half = rd >> 1;
   const float* cs = cos_sin + (size_t)pos * rd;
+  if (sizeof(T) == 2 && (half & 1) == 0) {  // two neighbouring pairs per lane: 4-byte loads and stores
+    for (int j = lane * 2; j < half; j += 64) {
+      const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + j));
+      const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + j + half));
+      float a0 = lo.x * inv, a1 = lo.y * inv, b0 = hi.x * inv, b1 = hi.y * inv;
+      if (w) { a0 *= w[j]; a1 *= w[j + 1]; b0 *= w[j + half]; b1 *= w[j + half + 1]; }
+      const float2 c = *reinterpret_cast<const float2*>(cs + j), sn = *reinterpret_cast<const float2*>(cs + half + j);
+      *reinterpret_cast<__nv_bfloat162*>(dst + at(j)) = __floats2bfloat162_rn(a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
+      *reinterpret_cast<__nv_bfloat162*>(dst + at(j + half)) = __floats2bfloat162_rn(b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
+    }
+    for (int d = rd + lane; d < hd; d += 32) {
+      float a = to_float(x[d]) * inv;
+      if (w) a *= w[d];
+      dst[at(d)] = from_float<T>(a);
+    }
+    return;
+  }
   for (int j = lane; j < half; j += 32) {
     float a = to_float(x[j]) * inv, b = to_float(x[j + half]) * inv;
     if (w) { a *= w[j]; b *= w[j + half]; }
@@ -148,6 +179,26 @@ template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I) {
   pdl_launch_dependents();
   pdl_wait();
+  if (sizeof(T) == 2 && (I & 7) == 0) {  // eight elements per thread: 16-byte loads and stores
+    const long long groups = total / 8;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < groups; e += (long long)gridDim.x * blockDim.x) {
+      const long long t = (e * 8) / I;
+      const int i = (int)((e * 8) % I);
+      const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * I + i);
+      const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + i);
+      const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+      const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+      uint4 r;
+      __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+        r2[j] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+      }
+      *reinterpret_cast<uint4*>(out + e * 8) = r;
+    }
+    return;
+  }
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
        e += (long long)gridDim.x * blockDim.x) {
     const long long t = e / I;
