@@ -42,16 +42,18 @@ def load_model(folder: str, dtype: str = "bfloat16", device="cuda:0") -> tuple[D
 
 
 def random_model(config: dict, seed: int = 0, dtype: str = "bfloat16", device="cuda:0",
-                 num_layers: Optional[int] = None) -> tuple[Decoder, Any]:
+                 num_layers: Optional[int] = None, stored_dtype: Optional[str] = None) -> tuple[Decoder, Any]:
     """A model with seeded random weights made on the device, without a folder on disk (what
     ``write_random_model`` would store, drawn by the device's generator).  ``num_layers`` keeps
-    only the first layers of the configuration."""
+    only the first layers of the configuration.  ``stored_dtype``: the type the weights are drawn
+    in before they are cast to ``dtype`` ("bfloat16" gives a float32 model the very numbers a
+    bfloat16 model of the same seed has)."""
     arch = resolve_architecture(config)
     if num_layers is not None:
         config = dict(config, num_hidden_layers=num_layers)
     cfg = arch.config_class.from_dict(config)
     device = require_cuda(device)
-    source = _Lazy(arch.random_weights(cfg, seed, str(device), DTYPES[dtype]), "<random weights>")
+    source = _Lazy(arch.random_weights(cfg, seed, str(device), DTYPES[stored_dtype or dtype]), "<random weights>")
     return Decoder(arch.build_plan(cfg), source, DTYPES[dtype], device), cfg
 
 

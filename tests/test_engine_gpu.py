@@ -142,6 +142,48 @@ def test_generation_with_cuda_graphs(tiny_folder):
     assert llm.engine.cache.all_free()
 
 
+def test_qwen3_8b_widths_bfloat16_follows_float32_however_it_is_cut():
+    """The real layer sizes (hidden 4096, 32 query and 8 kv heads of 128, intermediate 12288,
+    vocabulary 151936, pages of 16), three layers of them with random weights made on the device:
+    a 330-token request whole, in portions with its last 30 tokens one by one, and beside another
+    request whose pages it later reuses.  The float32 path gives the same bits however it is cut;
+    bfloat16 stays within what its 8-bit mantissa allows (about 1 % of the logits' spread on
+    average; the bounds below leave a factor of two)."""
+    from bench import QWEN3_8B
+    from tandem_b200.engine.core import build_executor, random_model
+    from tandem_b200.engine.executor import StepEntry
+
+    tokens, other = random_tokens(1, 330, 151936), random_tokens(2, 200, 151936)
+    results = {}
+    for dtype in ("float32", "bfloat16"):
+        decoder, _ = random_model(QWEN3_8B, seed=3, dtype=dtype, num_layers=3, stored_dtype="bfloat16")
+        ex = build_executor(decoder, page_size=16, num_pages=30, max_requests=4)
+        whole = ex.step([StepEntry("w", tokens, list(range(300, 330)))], end=["w"])
+        cut, at = [], 0
+        for n in [130, 2, 61, 107] + [1] * 30:
+            out = ex.step([StepEntry("p", tokens[at: at + n], [i for i in range(n) if at + i >= 300])])
+            at += n
+            cut.append(out)
+        ex.step([], end=["p"])
+        # beside another request, in a pool of 30 pages that the two fill but for one: the end of the
+        # long request lands on pages the other one has given back
+        mixed = [ex.step([StepEntry("o", other, []), StepEntry("m", tokens[:200], [])])]
+        mixed.append(ex.step([StepEntry("o", [5], [0]), StepEntry("m", tokens[200:250], [])], end=["o"]))
+        assert ex.manager.free_pages(0) == 14
+        mixed = [ex.step([StepEntry("m", tokens[250:], list(range(50, 80)))], end=["m"])]
+        assert ex.manager.all_free()
+        results[dtype] = [whole.double().cpu(), torch.cat([c for c in cut if c.shape[0]]).double().cpu(), mixed[0].double().cpu()]
+        del decoder, ex
+        torch.cuda.empty_cache()
+    f32, b16 = results["float32"], results["bfloat16"]
+    assert torch.equal(f32[0], f32[1]) and torch.equal(f32[0], f32[2])
+    spread = f32[0].std().item()
+    assert spread > 0.5  # the logits are not degenerate
+    for got in b16:
+        err = (got - f32[0]).abs()
+        assert err.mean().item() < 0.025 * spread and err.max().item() < 0.15 * spread, (err.mean().item(), err.max().item(), spread)
+
+
 def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tiny_folder):
     from tandem_b200 import EngineConfig, LLMEngine, SamplingParams
 
