@@ -3,11 +3,11 @@
 // tensor cores, keys and values streamed from the pages by the TMA unit.
 //
 // The host cuts every request's new tokens into query tiles; one block runs one tile for one kv
-// head.  A tile's 64 rows are (token, query head of the group) pairs, token-major, so one pass
-// over the keys serves all the query heads that share the kv head.  Each of the four consumer
+// head.  A tile's 128 rows are (token, query head of the group) pairs, token-major, so one pass
+// over the keys serves all the query heads that share the kv head.  Each of the eight consumer
 // warps owns 16 rows; per stage of 64 keys it computes S = Q K^T with mma.sync, masks (causal
 // with the row's own position, optional window), runs the online softmax in float32 with exp2
-// and accumulates O += P V.  A fifth warp is the producer (attention_common.cuh).  Keys a portion
+// and accumulates O += P V.  A ninth warp is the producer (attention_common.cuh).  Keys a portion
 // needs from earlier steps and its own keys come from the cache alike: the step wrote them there
 // before this kernel runs.
 //
@@ -18,9 +18,15 @@
 
 namespace tb {
 
-constexpr int WARPS = 4;
+#ifndef TB_PF_WARPS
+#define TB_PF_WARPS 8  // consumer warps: a query tile of 128 rows shares every stage of keys and values
+#endif
+#ifndef TB_PF_STAGES
+#define TB_PF_STAGES (TB_HD <= 64 ? 4 : (TB_HD <= 192 ? 3 : 2))
+#endif
+constexpr int WARPS = TB_PF_WARPS;
 constexpr int BM = WARPS * 16;  // rows of a query tile
-constexpr int STAGES = HD <= 64 ? 4 : 2;
+constexpr int STAGES = TB_PF_STAGES;
 constexpr int QS = HD + 8;
 constexpr int THREADS = (WARPS + 1) * 32;
 constexpr int TILE_INTS = 4;  // first token row, request, first position, number of tokens
@@ -109,7 +115,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const Prefil
     __nv_bfloat16* kt = stage_mem + slot * STAGE_ELEMS;
     __nv_bfloat16* vt = kt + STAGE_KEYS * HD;
     if (base < kb || base + STAGE_KEYS > ke) {  // an edge stage: every warp cleans one sub-tile, then all read all
-      zero_value_rows(vt + warp * TILE * HD, base + warp * TILE, kb, ke, lane);
+      if (warp < 4) zero_value_rows(vt + warp * TILE * HD, base + warp * TILE, kb, ke, lane);
       asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory");
     }
     // keys of this stage that no row of the warp can see need no arithmetic at all
@@ -208,6 +214,7 @@ extern "C" {
 // How many tokens one query tile takes for `groups` query heads per kv head (0: the kernel does not
 // take that many heads per kv head).
 int tb_attention_prefill_tile_tokens(int groups) { return groups > 0 && groups <= tb::BM ? tb::BM / groups : 0; }
+int tb_attention_prefill_tile_rows() { return tb::BM; }
 
 // tiles: [num_tiles, 4] int32 on the device; grid = (num_tiles, nkv).
 int tb_attention_prefill(void* stream, const void* q, int q_stride, const void* k_cache, const void* v_cache,

@@ -157,7 +157,6 @@ class DecodeGraphs:
         cap = self.captured.get(self.bucket_of(len(entries)))
         return cap.launches if cap else 0
 
-    @torch.inference_mode()
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Same contract as ``Executor.run`` for a step of single tokens that all want logits."""
         ex = self.executor
@@ -167,7 +166,8 @@ class DecodeGraphs:
         if cap is None:
             logits = ex.run(entries)  # the first step of a bucket runs eagerly (this also builds what is built lazily)
             cap = _Captured(ex, bucket, self.max_model_len)
-            cap.capture(entries)
+            with torch.inference_mode():
+                cap.capture(entries)
             self.captured[bucket] = cap
             return logits
         for e in entries:

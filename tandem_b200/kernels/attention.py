@@ -14,6 +14,7 @@ Both plans are cut on the host and travel to the device with the batch descripti
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -24,7 +25,7 @@ from tandem_b200.kernels.build import load_library
 ITEM_INTS = 6  # token row, request, key begin, key end, first item of the request, its item count
 TILE_INTS = 4  # first token row, request, first position, number of tokens
 STAGE_KEYS = 64  # keys per shared-memory stage: items are cut at multiples of it
-TILE_ROWS = 64  # rows (token x query head of the group) of a prefill tile
+TILE_ROWS = 128  # rows (token x query head of the group) of a prefill tile
 TARGET_BLOCKS = 148 * 2  # one wave at two blocks per SM
 MAX_SPLITS = 64  # items per request the kernel's fast merge takes
 
@@ -59,10 +60,15 @@ def plan_decode(rows, window: Optional[int], num_kv_heads: int, target_blocks: i
     return items
 
 
-def plan_prefill(seqs, groups: int) -> list:
+def prefill_library(head_dim: int):
+    extra = tuple(d for d in os.environ.get("TANDEM_PREFILL_DEFS", "").split(",") if d)
+    return load_library("attention_prefill", (f"TB_HD={head_dim}",) + extra)
+
+
+def plan_prefill(seqs, groups: int, tile_rows: int = TILE_ROWS) -> list:
     """``seqs``: (first token row, request, first position, number of tokens) of every request that
-    brings several tokens.  Returns tiles of at most 64 // groups tokens, those with the most keys first."""
-    per_tile = TILE_ROWS // groups
+    brings several tokens.  Returns tiles of at most tile_rows // groups tokens, those with the most keys first."""
+    per_tile = tile_rows // groups
     tiles = [[t0 + off, b, p0 + off, min(per_tile, n - off)] for t0, b, p0, n in seqs for off in range(0, n, per_tile)]
     tiles.sort(key=lambda x: -(x[2] + x[3]))
     return tiles
@@ -115,7 +121,7 @@ def paged_attention_prefill(qkv: torch.Tensor, kv, tiles: torch.Tensor, num_head
     T = qkv.shape[0]
     if out is None:
         out = torch.empty((T, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    lib = load_library("attention_prefill", (f"TB_HD={head_dim}",))
+    lib = prefill_library(head_dim)
     ops._check(lib.tb_attention_prefill(
         ops._stream(), ops._ptr(qkv), qkv.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
         kv.block_table.stride(0), ops._ptr(tiles), tiles.numel() // TILE_INTS, ops._ptr(out),

@@ -1,0 +1,173 @@
+"""Kernel microbenchmarks: one kernel at a time, on shapes given on the command line.
+
+    python -m tandem_b200.kernels.microbench gemm --m 8 --n 24576 --k 4096
+    python -m tandem_b200.kernels.microbench decode-attention --batch 64 --context 2048
+    python -m tandem_b200.kernels.microbench prefill-attention --tokens 2048
+    python -m tandem_b200.kernels.microbench tokenwise --tokens 2048
+
+Timing follows 12vivi/tandem's kernel benchmarks (benchmarks/bench_gemv.py:3-6,35-56): the calls are
+captured in one CUDA graph so that launch cost does not count, and weights or caches are rotated
+through copies that together exceed L2, so every call streams from HBM.  ``--no-graph --iters N``
+runs N plain launches instead (what a profiler is pointed at).
+"""
+
+from __future__ import annotations
+
+import argparse
+import math
+
+import torch
+
+L2_BYTES = 126 << 20
+
+
+def time_calls(fn, iters: int, graph: bool) -> float:
+    """Microseconds per call of fn(i), i = 0 .. iters-1."""
+    for i in range(min(3, iters)):
+        fn(i)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        start.record()
+        g.replay()
+        stop.record()
+    else:
+        start.record()
+        for i in range(iters):
+            fn(i)
+        stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / iters * 1000.0
+
+
+def copies_for(nbytes: int) -> int:
+    return max(2, 3 * L2_BYTES // max(1, nbytes) + 1)
+
+
+def bench_gemm(args) -> None:
+    from tandem_b200.kernels import gemm_bf16
+
+    M, N, K = args.m, args.n, args.k
+    ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies_for(N * K * 2))]
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.float32 if args.f32_out else torch.bfloat16
+    rows = []
+    if gemm_bf16.skinny_applies(M, N, K) and args.impl in ("both", "skinny"):
+        rows.append(("tcgen05 skinny kernel", time_calls(lambda i: gemm_bf16.skinny(x, ws[i % len(ws)], out), args.iters, args.graph)))
+    if args.impl in ("both", "library"):
+        rows.append(("library (cuBLAS)", time_calls(lambda i: gemm_bf16._library(x, ws[i % len(ws)], out), args.iters, args.graph)))
+    for name, us in rows:
+        print(f"gemm M={M} N={N} K={K}  {name:24s} {us:8.1f} us  {N * K * 2 / us / 1e3:7.0f} GB/s weights  "
+              f"{2.0 * M * N * K / us / 1e6:7.1f} TFLOP/s")
+
+
+def _cache(pages: int, nkv: int, ps: int, hd: int):
+    return (torch.randn(pages, nkv, ps, hd, device="cuda", dtype=torch.bfloat16),
+            torch.randn(pages, nkv, ps, hd, device="cuda", dtype=torch.bfloat16))
+
+
+def bench_decode_attention(args) -> None:
+    from tandem_b200.kernels import attention as A
+    from tandem_b200.parts.base import KVView
+
+    B, L, nh, nkv, hd, ps = args.batch, args.context, args.heads, args.kv_heads, args.head_dim, args.page_size
+    pages_per_seq = -(-L // ps)
+    kv_bytes = B * L * nkv * hd * 2 * 2
+    copies = copies_for(kv_bytes)
+    views = []
+    for _ in range(copies):
+        k, v = _cache(B * pages_per_seq, nkv, ps, hd)
+        table = torch.randperm(B * pages_per_seq, device="cuda").to(torch.int32).view(B, pages_per_seq)
+        views.append(KVView(k, v, table, None, ps, True))
+    items = A.plan_decode([(b, b, L - 1) for b in range(B)], None, nkv)
+    flat = torch.tensor([x for it in items for x in it], dtype=torch.int32, device="cuda")
+    count = torch.tensor([len(items)], dtype=torch.int32, device="cuda")
+    qkv = torch.randn(B, (nh + 2 * nkv) * hd, device="cuda", dtype=torch.bfloat16)
+    us = time_calls(lambda i: A.paged_attention_decode(qkv, views[i % copies], flat, count, nh, nkv, hd, hd ** -0.5),
+                    args.iters, args.graph)
+    print(f"decode attention B={B} context={L} heads={nh}/{nkv} hd={hd} page={ps} items={len(items)}  {us:8.1f} us  "
+          f"{kv_bytes / us / 1e3:7.0f} GB/s of keys and values")
+
+
+def bench_prefill_attention(args) -> None:
+    from tandem_b200.kernels import attention as A
+    from tandem_b200.parts.base import KVView
+
+    T, start, nh, nkv, hd, ps = args.tokens, args.start, args.heads, args.kv_heads, args.head_dim, args.page_size
+    pages = -(-(start + T) // ps)
+    k, v = _cache(pages, nkv, ps, hd)
+    table = torch.randperm(pages, device="cuda").to(torch.int32).view(1, pages)
+    kv = KVView(k, v, table, None, ps, True)
+    tiles = A.plan_prefill([(0, 0, start, T)], nh // nkv, A.prefill_library(hd).tb_attention_prefill_tile_rows())
+    flat = torch.tensor([x for t in tiles for x in t], dtype=torch.int32, device="cuda")
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device="cuda", dtype=torch.bfloat16)
+    us = time_calls(lambda i: A.paged_attention_prefill(qkv, kv, flat, nh, nkv, hd, None, hd ** -0.5), args.iters, args.graph)
+    flops = 4.0 * nh * hd * (T * start + T * (T + 1) / 2)
+    print(f"prefill attention tokens={T} start={start} heads={nh}/{nkv} hd={hd} page={ps} tiles={len(tiles)}  {us:8.1f} us  "
+          f"{flops / us / 1e6:7.1f} TFLOP/s")
+
+
+def bench_tokenwise(args) -> None:
+    from tandem_b200.kernels import ops
+
+    T, H, I = args.tokens, args.hidden, args.intermediate
+    bf = torch.bfloat16
+    x, res, w = torch.randn(T, H, device="cuda", dtype=bf), torch.randn(T, H, device="cuda"), torch.ones(H, device="cuda")
+    us = time_calls(lambda i: ops.add_rmsnorm(x, res, w, 1e-6, bf), args.iters, args.graph)
+    print(f"add_rmsnorm T={T} H={H}  {us:8.1f} us  {T * H * 12 / us / 1e3:7.0f} GB/s")
+    gu = torch.randn(T, 2 * I, device="cuda", dtype=bf)
+    us = time_calls(lambda i: ops.silu_mul(gu), args.iters, args.graph)
+    print(f"silu_mul    T={T} I={I}  {us:8.1f} us  {T * I * 6 / us / 1e3:7.0f} GB/s")
+    table = torch.randn(32768, H, device="cuda", dtype=bf)
+    ids = torch.randint(0, 32768, (T,), device="cuda", dtype=torch.int32)
+    us = time_calls(lambda i: ops.embedding(ids, table), args.iters, args.graph)
+    print(f"embedding   T={T} H={H}  {us:8.1f} us  {T * H * 6 / us / 1e3:7.0f} GB/s")
+    logits = torch.randn(min(T, 64), 151936, device="cuda")
+    us = time_calls(lambda i: ops.argmax(logits), args.iters, args.graph)
+    print(f"argmax      R={logits.shape[0]} V=151936  {us:8.1f} us  {logits.numel() * 4 / us / 1e3:7.0f} GB/s")
+
+
+def main(argv=None) -> None:
+    p = argparse.ArgumentParser(prog="python -m tandem_b200.kernels.microbench")
+    sub = p.add_subparsers(dest="case", required=True)
+    common = argparse.ArgumentParser(add_help=False)
+    common.add_argument("--iters", type=int, default=20)
+    common.add_argument("--no-graph", dest="graph", action="store_false")
+    g = sub.add_parser("gemm", parents=[common])
+    g.add_argument("--m", type=int, default=8)
+    g.add_argument("--n", type=int, default=24576)
+    g.add_argument("--k", type=int, default=4096)
+    g.add_argument("--f32-out", action="store_true")
+    g.add_argument("--impl", choices=["both", "skinny", "library"], default="both")
+    g.set_defaults(fn=bench_gemm)
+    shape = argparse.ArgumentParser(add_help=False)
+    shape.add_argument("--heads", type=int, default=32)
+    shape.add_argument("--kv-heads", type=int, default=8)
+    shape.add_argument("--head-dim", type=int, default=128)
+    shape.add_argument("--page-size", type=int, default=16)
+    d = sub.add_parser("decode-attention", parents=[common, shape])
+    d.add_argument("--batch", type=int, default=64)
+    d.add_argument("--context", type=int, default=2048)
+    d.set_defaults(fn=bench_decode_attention)
+    f = sub.add_parser("prefill-attention", parents=[common, shape])
+    f.add_argument("--tokens", type=int, default=2048)
+    f.add_argument("--start", type=int, default=0)
+    f.set_defaults(fn=bench_prefill_attention)
+    t = sub.add_parser("tokenwise", parents=[common])
+    t.add_argument("--tokens", type=int, default=2048)
+    t.add_argument("--hidden", type=int, default=4096)
+    t.add_argument("--intermediate", type=int, default=12288)
+    t.set_defaults(fn=bench_tokenwise)
+    args = p.parse_args(argv)
+    with torch.inference_mode():
+        args.fn(args)
+
+
+if __name__ == "__main__":
+    main()
