@@ -14,5 +14,16 @@ LIBRARIES = [
 ] + [(stem, (f"TB_HD={hd}",)) for hd in (16, 32, 48, 64, 128) for stem in ("attention_decode", "attention_prefill")]
 
 
-def build_all(verbose: bool = True) -> list:
-    return compile_many(LIBRARIES, verbose)
+def build_all(verbose: bool = True, prune: bool = True) -> list:
+    """Build every library; with ``prune``, libraries in the build folder that none of them is
+    (older versions of the sources, head sizes built on demand) are removed."""
+    import glob
+    import os
+
+    from tandem_b200.kernels.build import build_dir
+
+    paths = compile_many(LIBRARIES, verbose)
+    if prune:
+        for stale in set(glob.glob(os.path.join(build_dir(), "tb_*.so"))) - set(paths):
+            os.remove(stale)
+    return paths
