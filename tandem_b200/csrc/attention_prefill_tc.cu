@@ -1,0 +1,417 @@
+// Paged causal attention for prompt portions on the fifth-generation tensor cores (tcgen05), head
+// size TB_HD (64 or 128) fixed at compile time.  Same contract as attention_prefill.cu (query tiles
+// of 128 rows = (token, query head of the group) pairs, one block per tile and kv head, keys and
+// values streamed from the request's pages by the TMA unit); what differs is who does the math:
+//
+//   warp 5   issues S = Q K^T (tcgen05.mma, M = 128 rows, N = 64 keys) into one of two score
+//            buffers in tensor memory, and O += P V (M = 128, N = head size) into the output
+//            accumulator, also in tensor memory;
+//   warps 0-3  own one query row per thread (a row of the MMA is a lane of tensor memory): they
+//            read a row of S with tcgen05.ld, mask it, keep the running maximum and sum in
+//            float32 (exp2), write the probabilities as bfloat16 into the swizzled shared-memory
+//            tile that is the A operand of the second MMA, and rescale O in tensor memory when
+//            the reference maximum has to move (only when a row's maximum grew by more than 2^8
+//            since the reference was set: the sum is kept against the same reference, so the
+//            result is exact);
+//   warp 4   is the producer (bulk copies of cache tiles, completing on mbarriers).
+//
+// While the softmax warps work on block j, the tensor cores already compute the scores of block
+// j + 1.  The cache's own tile layout is the 128-byte-swizzled layout that tcgen05 reads: K is a
+// K-major B operand as it lies, V an MN-major one.
+//
+// It stands where 12vivi/tandem calls FlashInfer's paged prefill wrapper
+// (python/tandem/layers/flashinfer_attention.py:167-171,194-209); the arithmetic is
+// python/tandem/layers/attention.py:46-56 of the reference.
+#include "cache_layout.cuh"
+#include "common.cuh"
+#include "sm100_primitives.cuh"
+
+#ifndef TB_HD
+#error "compile with -DTB_HD=64 or 128"
+#endif
+
+namespace tb {
+
+constexpr int HD = TB_HD;
+static_assert(HD == 64 || HD == 128, "the tcgen05 prefill kernel takes head sizes 64 and 128");
+constexpr int NB = HD / 64;        // 64-element column blocks of a row
+constexpr int BM = 128;            // rows of a query tile
+constexpr int BLOCK_KEYS = 64;     // keys per stage
+#ifndef TB_PF_STAGES
+#define TB_PF_STAGES (TB_HD == 128 ? 4 : 3)
+#endif
+constexpr int STAGES = TB_PF_STAGES;  // head size 128: one block per SM; 64: two
+constexpr int THREADS = 192;
+constexpr int TILE_INTS = 4;       // first token row, request, first position, number of tokens
+constexpr int K_BYTES = BLOCK_KEYS * HD * 2, STAGE_BYTES = 2 * K_BYTES;
+constexpr int Q_BYTES = BM * HD * 2, P_BYTES = BM * BLOCK_KEYS * 2;
+constexpr int TABLE_CACHE = 512;
+constexpr int STATUS_BAD_PAGE = 2;
+constexpr int TMEM_COLS = 256;     // S0 at 0, S1 at 64, O at 128
+constexpr float RESCALE_AT = 8.f;  // move a row's reference maximum when it has grown by 2^8
+
+struct PrefillArgs {
+  const __nv_bfloat16* q;
+  int q_stride;
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;
+  const int* block_table;
+  int table_stride;
+  const int* tiles;
+  __nv_bfloat16* out;
+  int* status;
+  int nh, nkv, page_size, window;
+  float scale_log2;
+};
+
+// ------------------------------------------------------------------------------------------- tcgen05
+__device__ __forceinline__ uint64_t desc_k_major(const void* p) {  // 128-byte rows, 8-row groups 1024 bytes apart
+  return (uint64_t)((smem_u32(p) & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ uint64_t desc_mn_major(const void* p, uint32_t block_stride_bytes) {
+  // rows of 64 contiguous N elements, 8 K-rows per 1024-byte group, 64-element N blocks block_stride apart
+  return (uint64_t)((smem_u32(p) & 0x3FFFFu) >> 4) | ((uint64_t)(block_stride_bytes >> 4) << 16) | (64ull << 32) |
+         (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+      "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};" ::"r"(__float_as_uint(v[0])),
+      "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])),
+      "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+      "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])),
+      "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+      "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+      "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])),
+      "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+      "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31])), "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------- producer
+// Stage layout: K then V, each [NB column blocks][64 key rows][64 elements], rows swizzled like the
+// cache tiles they come from (row index and row-in-page agree modulo 8: pages of 8 or 16k keys).
+__device__ __forceinline__ void stream_kv_blocks(const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache, const int* table,
+                                                 int kvh, int nkv, int ps, int kb, int ke, int s0, int num_blocks,
+                                                 unsigned char* stage_mem, uint64_t* full, uint64_t* empty,
+                                                 volatile int* abort_flag, int* status, int lane) {
+  const int piece = min(ps, 16);
+  const int pieces = BLOCK_KEYS / piece;  // at most 8
+  bool alive = true;
+  for (int it = 0; it < num_blocks && alive; ++it) {
+    const int slot = it % STAGES;
+    if (it >= STAGES) {
+      if (lane == 0) alive = mbar_wait(empty + slot, ((it / STAGES) & 1) ^ 1, abort_flag, status);
+      alive = __shfl_sync(0xffffffffu, alive, 0);
+      if (!alive) break;
+    }
+    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(stage_mem + (size_t)slot * STAGE_BYTES);
+    __nv_bfloat16* vs = ks + BLOCK_KEYS * HD;
+    const int base = s0 + it * BLOCK_KEYS;
+    const int kp = base + lane * piece;
+    const bool mine = lane < pieces && kp < ke && kp + piece > kb;
+    int page = -1;
+    if (mine) {
+      page = table[kp / ps];
+      if (page < 0) atomicExch(status, STATUS_BAD_PAGE);
+    }
+    const int n = page >= 0 ? min(piece, ke - kp) : 0;
+    uint32_t bytes = 2u * (uint32_t)n * HD * 2u;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
+    if (lane == 0) mbar_arrive_expect_tx(full + slot, bytes);
+    __syncwarp();
+    if (n > 0) {
+      const int r0 = kp % ps, i0 = kp - base;
+      const long long tile = cache_tile(page, kvh, nkv, ps, HD);
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        const long long src = tile + ((long long)b * ps + r0) * 64;
+        const int d = (b * BLOCK_KEYS + i0) * 64;
+        bulk_load(ks + d, k_cache + src, n * 128, full + slot);
+        bulk_load(vs + d, v_cache + src, n * 128, full + slot);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------- kernel
+__global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_tc_kernel(const PrefillArgs a) {
+  extern __shared__ unsigned char smem_unaligned[];
+  pdl_wait();
+  unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
+  unsigned char* q_s = smem;                       // [NB][128 rows][128 bytes]
+  unsigned char* p_s = q_s + Q_BYTES;              // [2][128 rows][128 bytes]
+  unsigned char* stage_mem = p_s + 2 * P_BYTES;    // [STAGES][K | V]
+  uint64_t* kv_full = reinterpret_cast<uint64_t*>(stage_mem + STAGES * STAGE_BYTES);
+  uint64_t* kv_empty = kv_full + STAGES;
+  uint64_t* s_full = kv_empty + STAGES;   // [2]
+  uint64_t* s_empty = s_full + 2;         // [2]
+  uint64_t* p_full = s_empty + 2;         // [2]
+  uint64_t* pv_done = p_full + 2;         // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* table_s = const_cast<int*>(abort_flag) + 1;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int* tile = a.tiles + (size_t)blockIdx.x * TILE_INTS;
+  const int t0 = tile[0], req = tile[1], p0 = tile[2], ntok = tile[3];
+  const int kvh = blockIdx.y, G = a.nh / a.nkv, ps = a.page_size, W = a.window;
+  const int kb = W > 0 ? max(0, p0 - W + 1) : 0, ke = p0 + ntok;
+  const int s0 = (kb / BLOCK_KEYS) * BLOCK_KEYS;
+  const int num_blocks = (ke - s0 + BLOCK_KEYS - 1) / BLOCK_KEYS;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(s_full + b, 1); mbar_init(s_empty + b, 4);
+      mbar_init(p_full + b, 4); mbar_init(pv_done + b, 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // the query tile, row = token * G + head of the group, in the swizzled K-major layout of an A operand
+  for (int i = tid; i < BM * (HD / 8); i += THREADS) {
+    const int row = i / (HD / 8), c = i % (HD / 8);
+    const int tl = row / G, g = row % G;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tl < ntok)
+      v = *reinterpret_cast<const uint4*>(a.q + (size_t)(t0 + tl) * a.q_stride + (size_t)(kvh * G + g) * HD + c * 8);
+    *reinterpret_cast<uint4*>(q_s + (c >> 3) * (BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
+  }
+  {  // the request's page numbers for this tile's keys
+    const int* table = a.block_table + (size_t)req * a.table_stride;
+    const int first = s0 / ps, count = (ke + ps - 1) / ps - first;
+    if (count <= TABLE_CACHE)
+      for (int i = tid; i < count; i += THREADS) table_s[i] = table[first + i];
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  // Only now may the kernel behind this one become resident: it may hold tensor memory while it
+  // waits for this grid to end, so every block of this grid must have its own columns first.
+  pdl_launch_dependents();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 128;
+
+  if (warp == 4) {
+    const int* table = a.block_table + (size_t)req * a.table_stride;
+    const int first = s0 / ps, count = (ke + ps - 1) / ps - first;
+    stream_kv_blocks(a.k_cache, a.v_cache, count <= TABLE_CACHE ? table_s - first : table, kvh, a.nkv, ps, kb, ke, s0,
+                     num_blocks, stage_mem, kv_full, kv_empty, abort_flag, a.status, lane);
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_KEYS >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      bool ok = true;
+      for (int j = 0; j <= num_blocks && ok; ++j) {
+        if (j < num_blocks) {  // S_j = Q K_j^T
+          const int slot = j % STAGES;
+          ok = mbar_wait(kv_full + slot, (j / STAGES) & 1, abort_flag, a.status);
+          if (ok && j >= 2) ok = mbar_wait(s_empty + (j & 1), ((j >> 1) & 1) ^ 1, abort_flag, a.status);
+          if (!ok) break;
+          tc_fence_after();
+          const unsigned char* ks = stage_mem + (size_t)slot * STAGE_BYTES;
+#pragma unroll
+          for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma(tmem_base + (uint32_t)((j & 1) * BLOCK_KEYS), desc_k_major(q_s + b * (BM * 128)) + 2 * k,
+                   desc_k_major(ks + b * (BLOCK_KEYS * 128)) + 2 * k, idesc_s, (b | k) ? 1u : 0u);
+          umma_commit(s_full + (j & 1));
+        }
+        if (j >= 1) {  // O += P_{j-1} V_{j-1}
+          const int i = j - 1, slot = i % STAGES;
+          ok = mbar_wait(p_full + (i & 1), (i >> 1) & 1, abort_flag, a.status);
+          if (!ok) break;
+          tc_fence_after();
+          const unsigned char* vs = stage_mem + (size_t)slot * STAGE_BYTES + K_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_KEYS / 16; ++k)  // 16 keys: 32 bytes along a row of P, 16 rows (2048 bytes) down V
+            umma(tmem_o, desc_k_major(p_s + (i & 1) * P_BYTES) + 2 * k, desc_mn_major(vs + k * 2048, BLOCK_KEYS * 128), idesc_o, (i | k) ? 1u : 0u);
+          umma_commit(kv_empty + slot);
+          umma_commit(pv_done + (i & 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax: one row per thread
+    const int row = tid;  // = lane of tensor memory
+    const int tl = row / G;
+    const bool live = tl < ntok;
+    const int qpos = p0 + min(tl, ntok - 1);
+    const int lo = W > 0 ? max(0, qpos - W + 1) : 0;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < num_blocks && ok; ++j) {
+      const int base = s0 + j * BLOCK_KEYS;
+      ok = mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_flag, a.status);
+      if (!ok) break;
+      tc_fence_after();
+      float s[64];
+      tmem_ld32(tmem_base + lane_base + (uint32_t)((j & 1) * BLOCK_KEYS), s);
+      tmem_ld32(tmem_base + lane_base + (uint32_t)((j & 1) * BLOCK_KEYS + 32), s + 32);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty + (j & 1));
+      const bool all_visible = base + BLOCK_KEYS - 1 <= qpos && base >= lo;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float v = s[c] * a.scale_log2;
+        if (!all_visible && (base + c > qpos || base + c < lo)) v = -INFINITY;
+        s[c] = v;
+        mx = fmaxf(mx, v);
+      }
+      // move the reference maximum only when it pays (any row of the warp: the tensor-memory
+      // instructions below are executed by whole warps)
+      const bool need = mx > m_ref + RESCALE_AT;
+      const bool warp_need = __any_sync(0xffffffffu, need);
+      float corr = 1.f;
+      if (warp_need) {
+        const float m_new = fmaxf(m_ref, mx);
+        corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_new);
+        m_ref = m_new;
+        l *= corr;
+      }
+      if (j >= 2) {  // this block's buffer of P is free once O += P V of the block before the last has completed
+        ok = mbar_wait(pv_done + (j & 1), ((j - 2) >> 1) & 1, abort_flag, a.status);
+        if (!ok) break;
+      }
+      if (j >= 1 && warp_need) {  // O is touched only between two of the tensor cores' updates
+        ok = mbar_wait(pv_done + ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, a.status);
+        if (!ok) break;
+        tc_fence_after();
+        {
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            float o[32];
+            tmem_ld32(tmem_o + lane_base + c0, o);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] *= corr;
+            tmem_st32(tmem_o + lane_base + c0, o);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
+      float sum = 0.f;
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8) {  // eight 16-byte chunks of the row of P
+        float p[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) { p[c] = exp2f(s[c8 * 8 + c] - m_safe); sum += p[c]; }
+        *reinterpret_cast<uint4*>(p_s + (j & 1) * P_BYTES + row * 128 + ((c8 ^ (row & 7)) << 4)) =
+            make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
+      }
+      l += sum;
+      if (base < kb || base + BLOCK_KEYS > ke) {
+        // an edge block: value rows of keys outside [kb, ke) were not copied and get zero weights,
+        // but must not hold NaN patterns: this warp clears its quarter of the stage's rows
+        unsigned char* vs = stage_mem + (size_t)(j % STAGES) * STAGE_BYTES + K_BYTES;
+        for (int i = lane; i < 16 * NB * 8; i += 32) {
+          const int r = warp * 16 + i / (NB * 8), bc = i % (NB * 8);
+          if (base + r < kb || base + r >= ke)
+            *reinterpret_cast<uint4*>(vs + (bc >> 3) * (BLOCK_KEYS * 128) + r * 128 + ((bc & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      fence_proxy_async();  // P (and the cleared rows) are read by the tensor cores through the async proxy
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full + (j & 1));
+    }
+    // ------------------------------------------------------------------ epilogue
+    if (ok) ok = mbar_wait(pv_done + ((num_blocks - 1) & 1), ((num_blocks - 1) >> 1) & 1, abort_flag, a.status);
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = a.out + (size_t)(t0 + tl) * a.nh * HD + (size_t)(kvh * G + row % G) * HD;
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        float o[32];
+        tmem_ld32(tmem_o + lane_base + c0, o);
+        if (live) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8)
+            *reinterpret_cast<uint4*>(dst + c0 + c) = make_uint4(pack_bf16(o[c] * inv, o[c + 1] * inv), pack_bf16(o[c + 2] * inv, o[c + 3] * inv),
+                                                                 pack_bf16(o[c + 4] * inv, o[c + 5] * inv), pack_bf16(o[c + 6] * inv, o[c + 7] * inv));
+        }
+      }
+    }
+  }
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+constexpr size_t smem_bytes() { return 1024 + Q_BYTES + 2 * P_BYTES + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 8) * 8 + 16 + TABLE_CACHE * 4; }
+
+}  // namespace tb
+
+extern "C" {
+
+int tb_attention_prefill_tc_tile_rows() { return tb::BM; }
+
+// tiles: [num_tiles, 4] int32 on the device; grid = (num_tiles, nkv).  Pages of 8 keys or a multiple of 16.
+int tb_attention_prefill_tc(void* stream, const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                            const int* block_table, int table_stride, const int* tiles, int num_tiles, void* out,
+                            int* status, int nh, int nkv, int page_size, int window, float scale) {
+  if (num_tiles <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > tb::BM) return TB_ERR_BAD_SIZE;
+  if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TB_ERR_BAD_SIZE;
+  tb::PrefillArgs a;
+  a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride;
+  a.k_cache = (const __nv_bfloat16*)k_cache; a.v_cache = (const __nv_bfloat16*)v_cache;
+  a.block_table = block_table; a.table_stride = table_stride;
+  a.tiles = tiles; a.out = (__nv_bfloat16*)out; a.status = status;
+  a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  static bool configured = false;
+  const size_t smem = tb::smem_bytes();
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(tb::attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return tb::launch(tb::attention_prefill_tc_kernel, dim3(num_tiles, nkv), dim3(tb::THREADS), smem, stream, a);
+}
+
+}  // extern "C"

@@ -65,6 +65,13 @@ def prefill_library(head_dim: int):
     return load_library("attention_prefill", (f"TB_HD={head_dim}",) + extra)
 
 
+def tcgen05_prefill_applies(head_dim: int, page_size: int) -> bool:
+    """The tcgen05 prefill kernel takes head sizes 64 and 128 and pages of 8 keys or a multiple of 16
+    (``TANDEM_PREFILL=mma`` keeps the mma.sync kernel)."""
+    return (head_dim in (64, 128) and (page_size == 8 or page_size % 16 == 0)
+            and os.environ.get("TANDEM_PREFILL", "tcgen05") != "mma")
+
+
 def plan_prefill(seqs, groups: int, tile_rows: int = TILE_ROWS) -> list:
     """``seqs``: (first token row, request, first position, number of tokens) of every request that
     brings several tokens.  Returns tiles of at most tile_rows // groups tokens, those with the most keys first."""
@@ -121,12 +128,14 @@ def paged_attention_prefill(qkv: torch.Tensor, kv, tiles: torch.Tensor, num_head
     T = qkv.shape[0]
     if out is None:
         out = torch.empty((T, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    lib = prefill_library(head_dim)
-    ops._check(lib.tb_attention_prefill(
-        ops._stream(), ops._ptr(qkv), qkv.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
-        kv.block_table.stride(0), ops._ptr(tiles), tiles.numel() // TILE_INTS, ops._ptr(out),
-        ops._ptr(ops.status_word(qkv.device)), num_heads, num_kv_heads, kv.page_size, int(window or 0),
-        ctypes.c_float(scale)), "attention_prefill")
+    if tcgen05_prefill_applies(head_dim, kv.page_size):
+        fn, what = load_library("attention_prefill_tc", (f"TB_HD={head_dim}",)).tb_attention_prefill_tc, "attention_prefill_tc"
+    else:
+        fn, what = prefill_library(head_dim).tb_attention_prefill, "attention_prefill"
+    ops._check(fn(ops._stream(), ops._ptr(qkv), qkv.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
+                  kv.block_table.stride(0), ops._ptr(tiles), tiles.numel() // TILE_INTS, ops._ptr(out),
+                  ops._ptr(ops.status_word(qkv.device)), num_heads, num_kv_heads, kv.page_size, int(window or 0),
+                  ctypes.c_float(scale)), what)
     return out
 
 

@@ -11,7 +11,8 @@ LIBRARIES = [
     ("attention_simt", ()),
     ("sampling", ()),
     ("gemm_skinny", ()),
-] + [(stem, (f"TB_HD={hd}",)) for hd in (16, 32, 48, 64, 128) for stem in ("attention_decode", "attention_prefill")]
+] + [(stem, (f"TB_HD={hd}",)) for hd in (16, 32, 48, 64, 128) for stem in ("attention_decode", "attention_prefill")] \
+    + [("attention_prefill_tc", (f"TB_HD={hd}",)) for hd in (64, 128)]
 
 
 def build_all(verbose: bool = True, prune: bool = True) -> list:

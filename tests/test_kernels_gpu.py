@@ -284,7 +284,8 @@ def test_attention_finds_one_far_key_and_respects_edges(ops, dtype):
 
 # ----------------------------------------------------------------------------- decode attention (tensor cores)
 DECODE_SHAPES = [(4, 2, 16, 4), (6, 2, 32, 8), (5, 5, 48, 16), (32, 8, 128, 16), (3, 1, 80, 8), (10, 2, 64, 16),
-                 (8, 8, 64, 32), (4, 1, 256, 16), (20, 1, 64, 16), (6, 3, 128, 4), (2, 1, 112, 2), (12, 4, 96, 1)]
+                 (8, 8, 64, 32), (4, 1, 256, 16), (20, 1, 64, 16), (6, 3, 128, 4), (2, 1, 112, 2), (12, 4, 96, 1),
+                 (14, 2, 128, 8), (9, 3, 64, 48)]
 DECODE_BATCHES = [[0], [15], [16], [63, 64, 65], [300, 5, 1000, 129, 0], [2047], [40] * 9]
 
 
@@ -359,12 +360,16 @@ PREFILL_BATCHES = ATTN_BATCHES + [[(0, 64)], [(0, 65), (100, 31)], [(7, 200)], [
 @pytest.mark.parametrize("nh,nkv,hd,ps", DECODE_SHAPES)
 @pytest.mark.parametrize("batch", range(len(PREFILL_BATCHES)))
 @pytest.mark.parametrize("window", [None, 9, 70])
-def test_paged_attention_prefill(ops, nh, nkv, hd, ps, batch, window):
+@pytest.mark.parametrize("impl", ["tcgen05", "mma"])
+def test_paged_attention_prefill(ops, monkeypatch, nh, nkv, hd, ps, batch, window, impl):
     from tandem_b200.kernels import attention as A
     from tandem_b200.parts.base import KVView
 
     if (batch + hd // 16 + (window or 0)) % 3 == 0 and hd not in (64, 128):
         pytest.skip("covered by the neighbouring cases")
+    monkeypatch.setenv("TANDEM_PREFILL", impl)
+    if impl == "tcgen05" and not A.tcgen05_prefill_applies(hd, ps):
+        pytest.skip("the tcgen05 kernel does not take this head size or page size")
     g = torch.Generator().manual_seed(30 + batch)
     seqs = PREFILL_BATCHES[batch]
     qkv, kc, vc, table, seq_of, pos, Q, K, V = _paged_case(g, torch.bfloat16, seqs, nh, nkv, hd, ps)
@@ -389,12 +394,14 @@ def test_paged_attention_prefill(ops, nh, nkv, hd, ps, batch, window):
     ops.check_status("cuda")
 
 
-def test_prefill_finds_one_far_key_per_row(ops):
+@pytest.mark.parametrize("impl", ["tcgen05", "mma"])
+def test_prefill_finds_one_far_key_per_row(ops, monkeypatch, impl):
     """Every query row is aligned with one key of its own (far back, at a page edge, at the causal
     edge, at the window's edge): its output must be that key's value."""
     from tandem_b200.kernels import attention as A
     from tandem_b200.parts.base import KVView
 
+    monkeypatch.setenv("TANDEM_PREFILL", impl)
     nh, nkv, hd, ps = 8, 2, 128, 16
     g = torch.Generator().manual_seed(31)
     start, n = 700, 90
