@@ -2,10 +2,11 @@
 // that follows from it, addressing inside a shared-memory tile, and the producer warp that
 // streams a request's keys and values from its pages into a ring of shared-memory stages.
 //
-// A stage holds STAGE_KEYS = 64 keys as four sub-tiles of 16 keys, K then V, each sub-tile laid
-// out exactly like a 16-row cache tile (cache_layout.cuh): [column block][16 rows][block width],
-// 128-byte rows swizzled when the head size is a multiple of 64.  Copies are 1-D bulk copies
-// (the TMA unit) that complete on the stage's mbarrier.
+// A stage holds STAGE_KEYS = 64 keys, K then V, each laid out like the rows of a cache tile
+// (cache_layout.cuh): when the head size is a multiple of 64, [8 row groups][column block][8 rows]
+// [64 elements] with 128-byte rows swizzled, else plain [64 rows][head size].  A sub-tile of 16 keys
+// is two row groups.  Copies are 1-D bulk copies (the TMA unit) that complete on the stage's
+// mbarrier; with pages of 8 keys or more one copy brings all rows that a page has in the stage.
 #pragma once
 
 #include "cache_layout.cuh"
@@ -29,10 +30,10 @@ constexpr int STAGE_ELEMS = 2 * STAGE_KEYS * HD;  // K and V of one stage
 constexpr int STATUS_BAD_PAGE = 2;
 constexpr int TABLE_CACHE = 512;  // page numbers a block keeps in shared memory
 
-__device__ __forceinline__ int tile_elem(int i, int d, int xmask) {  // inside one sub-tile [NB][16][BW]
+__device__ __forceinline__ int tile_elem(int i, int d, int xmask) {  // inside one sub-tile of 16 rows
   if (!SWZ) return i * HD + d;
   const int blk = d >> 6, dd = d & 63;
-  return blk * TILE * 64 + i * 64 + ((((dd >> 3) ^ (i & xmask)) << 3) | (dd & 7));
+  return (((i >> 3) * NB + blk) * 8 + (i & 7)) * 64 + ((((dd >> 3) ^ (i & xmask)) << 3) | (dd & 7));
 }
 
 __device__ __forceinline__ bool page_size_supported(int ps) {
@@ -52,15 +53,18 @@ __device__ __forceinline__ const int* cache_table(const int* table, int* table_s
 
 // The producer warp: fills stage after stage with keys [s0 + it*64, +64) of the request whose block
 // table is `table`, restricted to [kb, ke).  Lane i owns the i-th piece of a stage (a piece: the
-// rows one copy can bring, inside one page and one sub-tile): it looks the page up, the warp adds
-// up the bytes, lane 0 tells the barrier, and every lane issues its own copies.  Rows outside
-// [kb, ke) and pages that were given back are not copied.
+// rows of one page that fall into the stage): it looks the page up, the warp adds up the bytes,
+// lane 0 tells the barrier, and every lane issues its own copies.  With swizzled tiles and pages of
+// 8 keys or more a piece is copied in whole row groups (rows of a group that lie outside [kb, ke)
+// come along; the consumers mask them and clear their values), else row by row.  Pages that were
+// given back are not copied.
 __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache, const int* table,
                                           int kvh, int nkv, int ps, int kb, int ke, int s0, int num_stages,
                                           int stages, __nv_bfloat16* stage_mem, uint64_t* full, uint64_t* empty,
                                           volatile int* abort_flag, int* status, int lane) {
-  const int piece = min(ps, TILE);
+  const int piece = ps % 64 == 0 ? 64 : ps % 32 == 0 ? 32 : ps % 16 == 0 ? 16 : ps;  // divides the page and the stage
   const int pieces = STAGE_KEYS / piece;
+  const bool groups = SWZ && ps >= 8;
   bool alive = true;
   for (int it = 0; it < num_stages && alive; ++it) {
     const int slot = it % stages;
@@ -80,7 +84,14 @@ __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __
         page = table[kp / ps];
         if (page < 0) atomicExch(status, STATUS_BAD_PAGE);
       }
-      const int n = page >= 0 ? min(piece, ke - kp) : 0;
+      // rows [lo, hi) of the piece
+      int lo = 0, hi = 0;
+      if (page >= 0) {
+        lo = max(0, kb - kp);
+        hi = min(piece, ke - kp);
+        if (groups) { lo &= ~7; hi = (hi + 7) & ~7; }
+      }
+      const int n = hi - lo;
       uint32_t bytes = 2u * (uint32_t)n * HD * 2u;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
@@ -91,19 +102,18 @@ __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __
       }
       __syncwarp();
       if (n > 0) {
-        const int r0 = kp % ps, i0 = (kp - base) % TILE;
-        const int dst = ((kp - base) / TILE) * TILE * HD;  // the sub-tile
+        const int r0 = kp % ps + lo, i0 = kp - base + lo;  // first row in the page and in the stage
         const long long tile = cache_tile(page, kvh, nkv, ps, HD);
-        if (SWZ && ps == TILE && n == TILE) {  // a whole page tile is one contiguous block in both layouts
-          bulk_load(ks + dst, k_cache + tile, TILE * HD * 2, full + slot);
-          bulk_load(vs + dst, v_cache + tile, TILE * HD * 2, full + slot);
-        } else {
+        if (groups || !SWZ) {  // rows (or row groups) are contiguous in the page as in the stage
+          bulk_load(ks + i0 * HD, k_cache + tile + (long long)r0 * HD, n * HD * 2, full + slot);
+          bulk_load(vs + i0 * HD, v_cache + tile + (long long)r0 * HD, n * HD * 2, full + slot);
+        } else {  // a page of fewer than 8 rows is one short group: [column block][rows][64]
 #pragma unroll
           for (int b = 0; b < NB; ++b) {
-            const long long src = tile + ((long long)b * ps + r0) * BW;
-            const int d = dst + (b * TILE + i0) * BW;
-            bulk_load(ks + d, k_cache + src, n * BW * 2, full + slot);
-            bulk_load(vs + d, v_cache + src, n * BW * 2, full + slot);
+            const long long src = tile + ((long long)b * ps + r0) * 64;
+            const int d = (((i0 >> 3) * NB + b) * 8 + (i0 & 7)) * 64;
+            bulk_load(ks + d, k_cache + src, n * 128, full + slot);
+            bulk_load(vs + d, v_cache + src, n * 128, full + slot);
           }
         }
       }
@@ -118,7 +128,7 @@ __device__ __forceinline__ void zero_value_rows(__nv_bfloat16* vt, int k0, int k
   for (int i = lane; i < TILE * (HD / 8); i += 32) {
     const int row = i / (HD / 8), c = i % (HD / 8);
     if (k0 + row < kb || k0 + row >= ke)
-      *reinterpret_cast<uint4*>(vt + (SWZ ? (c >> 3) * TILE * 64 + row * 64 + (c & 7) * 8 : row * HD + c * 8)) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(vt + (SWZ ? (((row >> 3) * NB + (c >> 3)) * 8 + (row & 7)) * 64 + (c & 7) * 8 : row * HD + c * 8)) = make_uint4(0, 0, 0, 0);
   }
   fence_proxy_async();
   __syncwarp();

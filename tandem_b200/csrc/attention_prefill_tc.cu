@@ -3,50 +3,44 @@
 // of 128 rows = (token, query head of the group) pairs, one block per tile and kv head, keys and
 // values streamed from the request's pages by the TMA unit); what differs is who does the math:
 //
-//   warp 5   issues S = Q K^T (tcgen05.mma, M = 128 rows, N = 64 keys) into one of two score
+//   warp 9   issues S = Q K^T (tcgen05.mma, M = 128 rows, N = 64 keys) into one of two score
 //            buffers in tensor memory, and O += P V (M = 128, N = head size) into the output
 //            accumulator, also in tensor memory;
-//   warps 0-3  own one query row per thread (a row of the MMA is a lane of tensor memory): they
+//   warps 0-7  a row of the MMA is a lane of tensor memory, and a warp reaches the 32 lanes of its
+//            number modulo 4: warps w and w + 4 share 32 query rows, each thread taking half of a
+//            row's keys (and half of its output columns); the two exchange their row maxima through
+//            shared memory.  They
 //            read a row of S with tcgen05.ld, mask it, keep the running maximum and sum in
 //            float32 (exp2), write the probabilities as bfloat16 into the swizzled shared-memory
 //            tile that is the A operand of the second MMA, and rescale O in tensor memory when
 //            the reference maximum has to move (only when a row's maximum grew by more than 2^8
 //            since the reference was set: the sum is kept against the same reference, so the
 //            result is exact);
-//   warp 4   is the producer (bulk copies of cache tiles, completing on mbarriers).
+//   warp 8   is the producer (bulk copies of cache tiles, completing on mbarriers).
 //
 // While the softmax warps work on block j, the tensor cores already compute the scores of block
-// j + 1.  The cache's own tile layout is the 128-byte-swizzled layout that tcgen05 reads: K is a
-// K-major B operand as it lies, V an MN-major one.
+// j + 1.  The cache's own tile layout (cache_layout.cuh) is the 128-byte-swizzled layout that
+// tcgen05 reads: K is a K-major B operand as it lies, V an MN-major one.
 //
 // It stands where 12vivi/tandem calls FlashInfer's paged prefill wrapper
 // (python/tandem/layers/flashinfer_attention.py:167-171,194-209); the arithmetic is
 // python/tandem/layers/attention.py:46-56 of the reference.
-#include "cache_layout.cuh"
-#include "common.cuh"
-#include "sm100_primitives.cuh"
-
-#ifndef TB_HD
-#error "compile with -DTB_HD=64 or 128"
-#endif
+#include "attention_common.cuh"
 
 namespace tb {
 
-constexpr int HD = TB_HD;
 static_assert(HD == 64 || HD == 128, "the tcgen05 prefill kernel takes head sizes 64 and 128");
-constexpr int NB = HD / 64;        // 64-element column blocks of a row
 constexpr int BM = 128;            // rows of a query tile
 constexpr int BLOCK_KEYS = 64;     // keys per stage
 #ifndef TB_PF_STAGES
 #define TB_PF_STAGES (TB_HD == 128 ? 4 : 3)
 #endif
 constexpr int STAGES = TB_PF_STAGES;  // head size 128: one block per SM; 64: two
-constexpr int THREADS = 192;
+constexpr int SOFTMAX_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9;
+constexpr int THREADS = 320;
 constexpr int TILE_INTS = 4;       // first token row, request, first position, number of tokens
 constexpr int K_BYTES = BLOCK_KEYS * HD * 2, STAGE_BYTES = 2 * K_BYTES;
 constexpr int Q_BYTES = BM * HD * 2, P_BYTES = BM * BLOCK_KEYS * 2;
-constexpr int TABLE_CACHE = 512;
-constexpr int STATUS_BAD_PAGE = 2;
 constexpr int TMEM_COLS = 256;     // S0 at 0, S1 at 64, O at 128
 constexpr float RESCALE_AT = 8.f;  // move a row's reference maximum when it has grown by 2^8
 
@@ -65,13 +59,15 @@ struct PrefillArgs {
 };
 
 // ------------------------------------------------------------------------------------------- tcgen05
-__device__ __forceinline__ uint64_t desc_k_major(const void* p) {  // 128-byte rows, 8-row groups 1024 bytes apart
-  return (uint64_t)((smem_u32(p) & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+// Shared-memory operand descriptors, 128-byte swizzle: rows of 128 bytes in groups of eight.
+__device__ __forceinline__ uint64_t desc_k_major(const void* p, uint32_t group_stride_bytes) {  // 8-row groups that far apart
+  return (uint64_t)((smem_u32(p) & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(group_stride_bytes >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
 }
-__device__ __forceinline__ uint64_t desc_mn_major(const void* p, uint32_t block_stride_bytes) {
-  // rows of 64 contiguous N elements, 8 K-rows per 1024-byte group, 64-element N blocks block_stride apart
-  return (uint64_t)((smem_u32(p) & 0x3FFFFu) >> 4) | ((uint64_t)(block_stride_bytes >> 4) << 16) | (64ull << 32) |
-         (1ull << 46) | (2ull << 61);
+__device__ __forceinline__ uint64_t desc_mn_major(const void* p, uint32_t block_stride_bytes, uint32_t group_stride_bytes) {
+  // rows of 64 contiguous N elements; groups of 8 K-rows group_stride apart, 64-element N blocks block_stride apart
+  return (uint64_t)((smem_u32(p) & 0x3FFFFu) >> 4) | ((uint64_t)(block_stride_bytes >> 4) << 16) |
+         ((uint64_t)(group_stride_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 __device__ __forceinline__ void umma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -82,8 +78,8 @@ __device__ __forceinline__ void umma(uint32_t d, uint64_t a, uint64_t b, uint32_
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
-  uint32_t r[32];
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float* v) {  // tmem_ld_wait() before v is read
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
       "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -92,9 +88,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
         "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  tmem_ld32_issue(taddr, v);
+  tmem_ld_wait();
+}
+__device__ __forceinline__ float fast_exp2(float x) {  // 2^x, -inf -> 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
   asm volatile(
@@ -113,53 +116,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// ------------------------------------------------------------------------------------------- producer
-// Stage layout: K then V, each [NB column blocks][64 key rows][64 elements], rows swizzled like the
-// cache tiles they come from (row index and row-in-page agree modulo 8: pages of 8 or 16k keys).
-__device__ __forceinline__ void stream_kv_blocks(const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache, const int* table,
-                                                 int kvh, int nkv, int ps, int kb, int ke, int s0, int num_blocks,
-                                                 unsigned char* stage_mem, uint64_t* full, uint64_t* empty,
-                                                 volatile int* abort_flag, int* status, int lane) {
-  const int piece = min(ps, 16);
-  const int pieces = BLOCK_KEYS / piece;  // at most 8
-  bool alive = true;
-  for (int it = 0; it < num_blocks && alive; ++it) {
-    const int slot = it % STAGES;
-    if (it >= STAGES) {
-      if (lane == 0) alive = mbar_wait(empty + slot, ((it / STAGES) & 1) ^ 1, abort_flag, status);
-      alive = __shfl_sync(0xffffffffu, alive, 0);
-      if (!alive) break;
-    }
-    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(stage_mem + (size_t)slot * STAGE_BYTES);
-    __nv_bfloat16* vs = ks + BLOCK_KEYS * HD;
-    const int base = s0 + it * BLOCK_KEYS;
-    const int kp = base + lane * piece;
-    const bool mine = lane < pieces && kp < ke && kp + piece > kb;
-    int page = -1;
-    if (mine) {
-      page = table[kp / ps];
-      if (page < 0) atomicExch(status, STATUS_BAD_PAGE);
-    }
-    const int n = page >= 0 ? min(piece, ke - kp) : 0;
-    uint32_t bytes = 2u * (uint32_t)n * HD * 2u;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
-    if (lane == 0) mbar_arrive_expect_tx(full + slot, bytes);
-    __syncwarp();
-    if (n > 0) {
-      const int r0 = kp % ps, i0 = kp - base;
-      const long long tile = cache_tile(page, kvh, nkv, ps, HD);
-#pragma unroll
-      for (int b = 0; b < NB; ++b) {
-        const long long src = tile + ((long long)b * ps + r0) * 64;
-        const int d = (b * BLOCK_KEYS + i0) * 64;
-        bulk_load(ks + d, k_cache + src, n * 128, full + slot);
-        bulk_load(vs + d, v_cache + src, n * 128, full + slot);
-      }
-    }
-  }
-}
-
 // ------------------------------------------------------------------------------------------- kernel
 __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_tc_kernel(const PrefillArgs a) {
   extern __shared__ unsigned char smem_unaligned[];
@@ -174,9 +130,12 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
   uint64_t* s_empty = s_full + 2;         // [2]
   uint64_t* p_full = s_empty + 2;         // [2]
   uint64_t* pv_done = p_full + 2;         // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  uint64_t* pair_bar = pv_done + 2;       // [4]: the two warps that share 32 rows
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* table_s = const_cast<int*>(abort_flag) + 1;
+  float* mx_s = reinterpret_cast<float*>(const_cast<int*>(abort_flag) + 1);  // [2 blocks][2 halves][128 rows]
+  float* l_s = mx_s + 4 * BM;                                                // [2 halves][128 rows]
+  int* table_s = reinterpret_cast<int*>(l_s + 2 * BM);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int* tile = a.tiles + (size_t)blockIdx.x * TILE_INTS;
@@ -189,9 +148,10 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(s_full + b, 1); mbar_init(s_empty + b, 4);
-      mbar_init(p_full + b, 4); mbar_init(pv_done + b, 1);
+      mbar_init(s_full + b, 1); mbar_init(s_empty + b, SOFTMAX_WARPS);
+      mbar_init(p_full + b, SOFTMAX_WARPS); mbar_init(pv_done + b, 1);
     }
+    for (int q = 0; q < 4; ++q) mbar_init(pair_bar + q, 2);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -225,12 +185,12 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 128;
 
-  if (warp == 4) {
+  if (warp == PRODUCER_WARP) {
     const int* table = a.block_table + (size_t)req * a.table_stride;
     const int first = s0 / ps, count = (ke + ps - 1) / ps - first;
-    stream_kv_blocks(a.k_cache, a.v_cache, count <= TABLE_CACHE ? table_s - first : table, kvh, a.nkv, ps, kb, ke, s0,
-                     num_blocks, stage_mem, kv_full, kv_empty, abort_flag, a.status, lane);
-  } else if (warp == 5) {
+    stream_kv(a.k_cache, a.v_cache, count <= TABLE_CACHE ? table_s - first : table, kvh, a.nkv, ps, kb, ke, s0, num_blocks,
+              STAGES, reinterpret_cast<__nv_bfloat16*>(stage_mem), kv_full, kv_empty, abort_flag, a.status, lane);
+  } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_KEYS >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -248,8 +208,8 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
           for (int b = 0; b < NB; ++b)
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              umma(tmem_base + (uint32_t)((j & 1) * BLOCK_KEYS), desc_k_major(q_s + b * (BM * 128)) + 2 * k,
-                   desc_k_major(ks + b * (BLOCK_KEYS * 128)) + 2 * k, idesc_s, (b | k) ? 1u : 0u);
+              umma(tmem_base + (uint32_t)((j & 1) * BLOCK_KEYS), desc_k_major(q_s + b * (BM * 128), 1024) + 2 * k,
+                   desc_k_major(ks + b * 1024, NB * 1024) + 2 * k, idesc_s, (b | k) ? 1u : 0u);
           umma_commit(s_full + (j & 1));
         }
         if (j >= 1) {  // O += P_{j-1} V_{j-1}
@@ -259,45 +219,56 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
           tc_fence_after();
           const unsigned char* vs = stage_mem + (size_t)slot * STAGE_BYTES + K_BYTES;
 #pragma unroll
-          for (int k = 0; k < BLOCK_KEYS / 16; ++k)  // 16 keys: 32 bytes along a row of P, 16 rows (2048 bytes) down V
-            umma(tmem_o, desc_k_major(p_s + (i & 1) * P_BYTES) + 2 * k, desc_mn_major(vs + k * 2048, BLOCK_KEYS * 128), idesc_o, (i | k) ? 1u : 0u);
+          for (int k = 0; k < BLOCK_KEYS / 16; ++k)  // 16 keys: 32 bytes along a row of P, two row groups down V
+            umma(tmem_o, desc_k_major(p_s + (i & 1) * P_BYTES, 1024) + 2 * k, desc_mn_major(vs + k * (2 * NB * 1024), 1024, NB * 1024),
+                 idesc_o, (i | k) ? 1u : 0u);
           umma_commit(kv_empty + slot);
           umma_commit(pv_done + (i & 1));
         }
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax: one row per thread
-    const int row = tid;  // = lane of tensor memory
+    // ------------------------------------------------------------------ softmax: half a row per thread
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;  // = lane of tensor memory
     const int tl = row / G;
     const bool live = tl < ntok;
     const int qpos = p0 + min(tl, ntok - 1);
     const int lo = W > 0 ? max(0, qpos - W + 1) : 0;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    constexpr int OC = HD / 2;            // output columns of this thread
+    const uint32_t my_o = tmem_o + lane_base + (uint32_t)(half * OC);
+    uint64_t* pair = pair_bar + quarter;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < num_blocks && ok; ++j) {
-      const int base = s0 + j * BLOCK_KEYS;
+      const int base = s0 + j * BLOCK_KEYS, cbase = base + half * 32;
       ok = mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_flag, a.status);
       if (!ok) break;
       tc_fence_after();
-      float s[64];
-      tmem_ld32(tmem_base + lane_base + (uint32_t)((j & 1) * BLOCK_KEYS), s);
-      tmem_ld32(tmem_base + lane_base + (uint32_t)((j & 1) * BLOCK_KEYS + 32), s + 32);
+      float s[32];
+      tmem_ld32(tmem_base + lane_base + (uint32_t)((j & 1) * BLOCK_KEYS + half * 32), s);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty + (j & 1));
-      const bool all_visible = base + BLOCK_KEYS - 1 <= qpos && base >= lo;
-      float mx = -INFINITY;
+      if (cbase + 31 > qpos || cbase < lo) {  // a block at the causal or the window's edge
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float v = s[c] * a.scale_log2;
-        if (!all_visible && (base + c > qpos || base + c < lo)) v = -INFINITY;
-        s[c] = v;
-        mx = fmaxf(mx, v);
+        for (int c = 0; c < 32; ++c)
+          if (cbase + c > qpos || cbase + c < lo) s[c] = -INFINITY;
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // the row's maximum over both halves
+      mx_s[((j & 1) * 2 + half) * BM + row] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pair);
+      ok = mbar_wait(pair, j & 1, abort_flag, a.status);
+      if (!ok) break;
+      mx = fmaxf(mx, mx_s[((j & 1) * 2 + (half ^ 1)) * BM + row]) * a.scale_log2;  // the scale is positive
       // move the reference maximum only when it pays (any row of the warp: the tensor-memory
-      // instructions below are executed by whole warps)
+      // instructions below are executed by whole warps; both warps of a pair decide alike)
       const bool need = mx > m_ref + RESCALE_AT;
       const bool warp_need = __any_sync(0xffffffffu, need);
       float corr = 1.f;
@@ -315,37 +286,38 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
         ok = mbar_wait(pv_done + ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, a.status);
         if (!ok) break;
         tc_fence_after();
-        {
 #pragma unroll
-          for (int c0 = 0; c0 < HD; c0 += 32) {
-            float o[32];
-            tmem_ld32(tmem_o + lane_base + c0, o);
+        for (int c0 = 0; c0 < OC; c0 += 32) {
+          float o[32];
+          tmem_ld32(my_o + c0, o);
 #pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] *= corr;
-            tmem_st32(tmem_o + lane_base + c0, o);
-          }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          for (int c = 0; c < 32; ++c) o[c] *= corr;
+          tmem_st32(my_o + c0, o);
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-      const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
-      float sum = 0.f;
+      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {  // eight 16-byte chunks of the row of P
+      for (int c8 = 0; c8 < 4; ++c8) {  // four 16-byte chunks of the row of P
         float p[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) { p[c] = exp2f(s[c8 * 8 + c] - m_safe); sum += p[c]; }
-        *reinterpret_cast<uint4*>(p_s + (j & 1) * P_BYTES + row * 128 + ((c8 ^ (row & 7)) << 4)) =
+        for (int c = 0; c < 8; ++c) {
+          p[c] = fast_exp2(fmaf(s[c8 * 8 + c], a.scale_log2, neg_m));
+          sum4[c & 3] += p[c];
+        }
+        *reinterpret_cast<uint4*>(p_s + (j & 1) * P_BYTES + row * 128 + (((half * 4 + c8) ^ (row & 7)) << 4)) =
             make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
       }
-      l += sum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       if (base < kb || base + BLOCK_KEYS > ke) {
-        // an edge block: value rows of keys outside [kb, ke) were not copied and get zero weights,
-        // but must not hold NaN patterns: this warp clears its quarter of the stage's rows
+        // an edge block: value rows of keys outside [kb, ke) get zero weights, but must not hold NaN
+        // patterns (they were not copied, or came along with their row group): this warp clears its eighth of the stage's rows
         unsigned char* vs = stage_mem + (size_t)(j % STAGES) * STAGE_BYTES + K_BYTES;
-        for (int i = lane; i < 16 * NB * 8; i += 32) {
-          const int r = warp * 16 + i / (NB * 8), bc = i % (NB * 8);
+        for (int i = lane; i < 8 * NB * 8; i += 32) {
+          const int r = warp * 8 + i / (NB * 8), bc = i % (NB * 8);
           if (base + r < kb || base + r >= ke)
-            *reinterpret_cast<uint4*>(vs + (bc >> 3) * (BLOCK_KEYS * 128) + r * 128 + ((bc & 7) << 4)) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vs + ((r >> 3) * NB + (bc >> 3)) * 1024 + (r & 7) * 128 + ((bc & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
       }
       fence_proxy_async();  // P (and the cleared rows) are read by the tensor cores through the async proxy
@@ -354,15 +326,22 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
       if (lane == 0) mbar_arrive(p_full + (j & 1));
     }
     // ------------------------------------------------------------------ epilogue
+    if (ok) {  // the row's sum over both halves
+      l_s[half * BM + row] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pair);
+      ok = mbar_wait(pair, num_blocks & 1, abort_flag, a.status);
+    }
     if (ok) ok = mbar_wait(pv_done + ((num_blocks - 1) & 1), ((num_blocks - 1) >> 1) & 1, abort_flag, a.status);
     if (ok) {
       tc_fence_after();
+      l += l_s[(half ^ 1) * BM + row];
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = a.out + (size_t)(t0 + tl) * a.nh * HD + (size_t)(kvh * G + row % G) * HD;
+      __nv_bfloat16* dst = a.out + (size_t)(t0 + tl) * a.nh * HD + (size_t)(kvh * G + row % G) * HD + half * OC;
 #pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
+      for (int c0 = 0; c0 < OC; c0 += 32) {
         float o[32];
-        tmem_ld32(tmem_o + lane_base + c0, o);
+        tmem_ld32(my_o + c0, o);
         if (live) {
 #pragma unroll
           for (int c = 0; c < 32; c += 8)
@@ -382,7 +361,7 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
   }
 }
 
-constexpr size_t smem_bytes() { return 1024 + Q_BYTES + 2 * P_BYTES + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 8) * 8 + 16 + TABLE_CACHE * 4; }
+constexpr size_t smem_bytes() { return 1024 + Q_BYTES + 2 * P_BYTES + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 12) * 8 + 16 + 6 * BM * 4 + TABLE_CACHE * 4; }
 
 }  // namespace tb
 
@@ -395,7 +374,7 @@ int tb_attention_prefill_tc(void* stream, const void* q, int q_stride, const voi
                             const int* block_table, int table_stride, const int* tiles, int num_tiles, void* out,
                             int* status, int nh, int nkv, int page_size, int window, float scale) {
   if (num_tiles <= 0) return 0;
-  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > tb::BM) return TB_ERR_BAD_SIZE;
+  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > tb::BM || !(scale > 0.f)) return TB_ERR_BAD_SIZE;
   if (!(page_size == 8 || (page_size > 0 && page_size % 16 == 0))) return TB_ERR_BAD_SIZE;
   tb::PrefillArgs a;
   a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride;

@@ -1,7 +1,7 @@
 // Thin wrappers over the PTX this package uses on sm_100a: mbarriers with bounded waits, bulk
 // asynchronous copies (the TMA unit, 1-D form), ldmatrix and the bf16 mma.sync tile.
 //
-// Every wait has an iteration limit.  When a wait gives up it records a code in the kernel's status
+// Every wait has a time limit.  When a wait gives up it records a code in the kernel's status
 // word (device memory, read by the host) and raises the block's abort flag, after which every
 // further wait of the block returns at once: a kernel can then produce a wrong result that the
 // host is told about, but it cannot hang the GPU.
@@ -43,14 +43,20 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wait until the barrier's phase with the given parity has completed; at most ~`limit` polls.
+// Wait until the barrier's phase with the given parity has completed, for at most ~`limit` clock
+// cycles (two seconds or so).  try_wait suspends the thread in hardware for a while by itself, so
+// the loop neither sleeps (a sleep's granularity would add to every hand-off) nor burns issue slots.
 // Returns false (and raises *abort, records the status) if it gave up or the block had aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, int* status,
-                                          uint32_t limit = 4u << 20) {
-  for (uint32_t i = 0; i < limit; ++i) {
-    if (mbar_test(bar, parity)) return true;
+                                          long long limit = 4ll << 30) {
+  if (mbar_test(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i)
+      if (mbar_test(bar, parity)) return true;
     if (*abort) return false;
-    if (i > 64) __nanosleep(32);
+    if (clock64() - t0 > limit) break;
   }
   *abort = 1;
   if (status) atomicExch(status, STATUS_WAIT_TIMEOUT);
