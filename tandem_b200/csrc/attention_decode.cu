@@ -49,8 +49,13 @@ struct DecodeArgs {
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeArgs a) {
   extern __shared__ unsigned char smem_unaligned[];
   pdl_launch_dependents();
-  pdl_wait();
-  if ((int)blockIdx.x >= *a.num_items) return;
+  // The batch's description (items, their number, block tables) is written by the host before the
+  // step's first kernel: it is read, and the barriers are set up, while the kernel in front of
+  // this one still runs.  The queries and the newest cache rows are that kernel's output.
+  const int num_items = *a.num_items;
+  const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
+  const int t = item[0], req = item[1], kb = item[2], ke = item[3], first_item = item[4], nsplits = item[5];
+  if ((int)blockIdx.x >= num_items) return;
   // 128-byte rows of the swizzled tiles must start on 128-byte boundaries
   unsigned char* smem_raw = smem_unaligned + ((128u - (smem_u32(smem_unaligned) & 127u)) & 127u);
   __nv_bfloat16* stage_mem = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [STAGES][K | V][STAGE_KEYS * HD]
@@ -64,8 +69,6 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   int* table_s = last_flag + 1;  // [TABLE_CACHE] the request's page numbers for this block's keys
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
-  const int t = item[0], req = item[1], kb = item[2], ke = item[3], first_item = item[4], nsplits = item[5];
   const int kvh = blockIdx.y, G = a.nh / a.nkv, ps = a.page_size;
   const int row0 = blockIdx.z * 16, rows = min(16, G - row0);  // query heads of this block: kvh*G + row0 + g
   const int xmask = min(7, ps - 1);
@@ -78,13 +81,14 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
     *last_flag = 0;
     mbar_fence_init();
   }
+  const int* table = cache_table(a.block_table + (size_t)req * a.table_stride, table_s, s0, ke, ps, tid, THREADS);
+  pdl_wait();
   for (int i = tid; i < 16 * (HD / 8); i += THREADS) {  // the query tile, 16 bytes at a time
     const int g = i / (HD / 8), c = i % (HD / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (g < rows) v = *reinterpret_cast<const uint4*>(a.q + (size_t)t * a.q_stride + (size_t)(kvh * G + row0 + g) * HD + c * 8);
     *reinterpret_cast<uint4*>(q_s + g * QS + c * 8) = v;
   }
-  const int* table = cache_table(a.block_table + (size_t)req * a.table_stride, table_s, s0, ke, ps, tid, THREADS);
   fence_proxy_async();
   __syncthreads();
 
@@ -226,28 +230,45 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
       ml[(s * 16 + g) * 2 + 1] = __ldcg(a.part_ml + pr * 2 + 1);
     }
     __syncthreads();
-    // 2) one thread per row turns them into the items' weights exp2(m_s - m) / sum
-    if (tid < rows) {
+    // 2) eight lanes per row turn them into the items' weights exp2(m_s - m) / sum (whole warps
+    //    run the shuffles; lanes of rows that do not exist idle along)
+    if (warp < 4) {
+      const int g = tid >> 3, sub = tid & 7;
+      const int n = g < rows ? nsplits : 0;
       float mx = -INFINITY, sum = 0.f;
-      for (int s = 0; s < nsplits; ++s) mx = fmaxf(mx, ml[(s * 16 + tid) * 2]);
-      for (int s = 0; s < nsplits; ++s) sum += ml[(s * 16 + tid) * 2 + 1] * exp2f(ml[(s * 16 + tid) * 2] - mx);
+      for (int s = sub; s < n; s += 8) mx = fmaxf(mx, ml[(s * 16 + g) * 2]);
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      for (int s = sub; s < n; s += 8) {
+        const float w = exp2f(ml[(s * 16 + g) * 2] - mx);
+        weight[s * 16 + g] = w;
+        sum += ml[(s * 16 + g) * 2 + 1] * w;
+      }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       const float inv = 1.f / sum;
-      for (int s = 0; s < nsplits; ++s) weight[s * 16 + tid] = exp2f(ml[(s * 16 + tid) * 2] - mx) * inv;
+      for (int s = sub; s < n; s += 8) weight[s * 16 + g] *= inv;
     }
     __syncthreads();
-    // 3) the weighted sum of the items' outputs, eight loads in flight per thread
-    for (int idx = tid; idx < rows * HD; idx += THREADS) {
-      const int g = idx / HD, d = idx % HD;
-      float acc = 0.f;
+    // 3) the weighted sum of the items' outputs, four columns per thread, eight loads in flight
+    for (int idx = tid; idx < rows * (HD / 4); idx += THREADS) {
+      const int g = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int s0 = 0; s0 < nsplits; s0 += 8) {
-        float v[8];
+        float4 v[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          v[j] = s0 + j < nsplits ? __ldcg(a.part_o + (((size_t)(first_item + s0 + j) * a.nkv + kvh) * G + row0 + g) * HD + d) : 0.f;
+          v[j] = s0 + j < nsplits
+                     ? __ldcg(reinterpret_cast<const float4*>(a.part_o + (((size_t)(first_item + s0 + j) * a.nkv + kvh) * G + row0 + g) * HD + d))
+                     : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc += s0 + j < nsplits ? v[j] * weight[(s0 + j) * 16 + g] : 0.f;
+        for (int j = 0; j < 8; ++j) {
+          const float w = s0 + j < nsplits ? weight[(s0 + j) * 16 + g] : 0.f;
+          acc.x += v[j].x * w; acc.y += v[j].y * w; acc.z += v[j].z * w; acc.w += v[j].w * w;
+        }
       }
-      a.out[(size_t)t * a.nh * HD + (size_t)(kvh * G + row0 + g) * HD + d] = __float2bfloat16_rn(acc);
+      __nv_bfloat16* dst = a.out + (size_t)t * a.nh * HD + (size_t)(kvh * G + row0 + g) * HD + d;
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
     }
   } else {
     for (int idx = tid; idx < rows * HD; idx += THREADS) {

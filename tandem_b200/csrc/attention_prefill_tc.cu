@@ -4,8 +4,10 @@
 // values streamed from the request's pages by the TMA unit); what differs is who does the math:
 //
 //   warp 9   issues S = Q K^T (tcgen05.mma, M = 128 rows, N = 64 keys) into one of two score
-//            buffers in tensor memory, and O += P V (M = 128, N = head size) into the output
-//            accumulator, also in tensor memory;
+//            buffers in tensor memory;
+//   warp 10  issues O += P V (M = 128, N = head size) into the output accumulator, also in tensor
+//            memory (a thread of its own, so that the scores of the next block never queue behind
+//            a wait for this block's probabilities);
 //   warps 0-7  a row of the MMA is a lane of tensor memory, and a warp reaches the 32 lanes of its
 //            number modulo 4: warps w and w + 4 share 32 query rows, each thread taking half of a
 //            row's keys (and half of its output columns); the two exchange their row maxima through
@@ -36,8 +38,8 @@ constexpr int BLOCK_KEYS = 64;     // keys per stage
 #define TB_PF_STAGES (TB_HD == 128 ? 4 : 3)
 #endif
 constexpr int STAGES = TB_PF_STAGES;  // head size 128: one block per SM; 64: two
-constexpr int SOFTMAX_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9;
-constexpr int THREADS = 320;
+constexpr int SOFTMAX_WARPS = 8, PRODUCER_WARP = 8, SCORE_WARP = 9, OUTPUT_WARP = 10;
+constexpr int THREADS = 352;
 constexpr int TILE_INTS = 4;       // first token row, request, first position, number of tokens
 constexpr int K_BYTES = BLOCK_KEYS * HD * 2, STAGE_BYTES = 2 * K_BYTES;
 constexpr int Q_BYTES = BM * HD * 2, P_BYTES = BM * BLOCK_KEYS * 2;
@@ -190,44 +192,44 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
     const int first = s0 / ps, count = (ke + ps - 1) / ps - first;
     stream_kv(a.k_cache, a.v_cache, count <= TABLE_CACHE ? table_s - first : table, kvh, a.nkv, ps, kb, ke, s0, num_blocks,
               STAGES, reinterpret_cast<__nv_bfloat16*>(stage_mem), kv_full, kv_empty, abort_flag, a.status, lane);
-  } else if (warp == MMA_WARP) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == SCORE_WARP) {
+    // ------------------------------------------------------------------ S_j = Q K_j^T
     if (lane == 0) {
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_KEYS >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      bool ok = true;
-      for (int j = 0; j <= num_blocks && ok; ++j) {
-        if (j < num_blocks) {  // S_j = Q K_j^T
-          const int slot = j % STAGES;
-          ok = mbar_wait(kv_full + slot, (j / STAGES) & 1, abort_flag, a.status);
-          if (ok && j >= 2) ok = mbar_wait(s_empty + (j & 1), ((j >> 1) & 1) ^ 1, abort_flag, a.status);
-          if (!ok) break;
-          tc_fence_after();
-          const unsigned char* ks = stage_mem + (size_t)slot * STAGE_BYTES;
+      for (int j = 0; j < num_blocks; ++j) {
+        const int slot = j % STAGES;
+        if (!mbar_wait(kv_full + slot, (j / STAGES) & 1, abort_flag, a.status)) break;
+        if (j >= 2 && !mbar_wait(s_empty + (j & 1), ((j >> 1) & 1) ^ 1, abort_flag, a.status)) break;
+        tc_fence_after();
+        const unsigned char* ks = stage_mem + (size_t)slot * STAGE_BYTES;
 #pragma unroll
-          for (int b = 0; b < NB; ++b)
+        for (int b = 0; b < NB; ++b)
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma(tmem_base + (uint32_t)((j & 1) * BLOCK_KEYS), desc_k_major(q_s + b * (BM * 128), 1024) + 2 * k,
-                   desc_k_major(ks + b * 1024, NB * 1024) + 2 * k, idesc_s, (b | k) ? 1u : 0u);
-          umma_commit(s_full + (j & 1));
-        }
-        if (j >= 1) {  // O += P_{j-1} V_{j-1}
-          const int i = j - 1, slot = i % STAGES;
-          ok = mbar_wait(p_full + (i & 1), (i >> 1) & 1, abort_flag, a.status);
-          if (!ok) break;
-          tc_fence_after();
-          const unsigned char* vs = stage_mem + (size_t)slot * STAGE_BYTES + K_BYTES;
-#pragma unroll
-          for (int k = 0; k < BLOCK_KEYS / 16; ++k)  // 16 keys: 32 bytes along a row of P, two row groups down V
-            umma(tmem_o, desc_k_major(p_s + (i & 1) * P_BYTES, 1024) + 2 * k, desc_mn_major(vs + k * (2 * NB * 1024), 1024, NB * 1024),
-                 idesc_o, (i | k) ? 1u : 0u);
-          umma_commit(kv_empty + slot);
-          umma_commit(pv_done + (i & 1));
-        }
+          for (int k = 0; k < 4; ++k)
+            umma(tmem_base + (uint32_t)((j & 1) * BLOCK_KEYS), desc_k_major(q_s + b * (BM * 128), 1024) + 2 * k,
+                 desc_k_major(ks + b * 1024, NB * 1024) + 2 * k, idesc_s, (b | k) ? 1u : 0u);
+        umma_commit(s_full + (j & 1));
       }
     }
-  } else {
+  } else if (warp == OUTPUT_WARP) {
+    // ------------------------------------------------------------------ O += P_i V_i
+    if (lane == 0) {
+      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      for (int i = 0; i < num_blocks; ++i) {
+        const int slot = i % STAGES;
+        // the probabilities exist only after the scores, which needed the stage's keys: its values have landed too
+        if (!mbar_wait(p_full + (i & 1), (i >> 1) & 1, abort_flag, a.status)) break;
+        tc_fence_after();
+        const unsigned char* vs = stage_mem + (size_t)slot * STAGE_BYTES + K_BYTES;
+#pragma unroll
+        for (int k = 0; k < BLOCK_KEYS / 16; ++k)  // 16 keys: 32 bytes along a row of P, two row groups down V
+          umma(tmem_o, desc_k_major(p_s + (i & 1) * P_BYTES, 1024) + 2 * k, desc_mn_major(vs + k * (2 * NB * 1024), 1024, NB * 1024),
+               idesc_o, (i | k) ? 1u : 0u);
+        umma_commit(kv_empty + slot);  // the scores of this stage completed before its probabilities were made
+        umma_commit(pv_done + (i & 1));
+      }
+    }
+  } else if (warp < SOFTMAX_WARPS) {
     // ------------------------------------------------------------------ softmax: half a row per thread
     const int quarter = warp & 3, half = warp >> 2;
     const int row = quarter * 32 + lane;  // = lane of tensor memory

@@ -28,6 +28,7 @@ STAGE_KEYS = 64  # keys per shared-memory stage: items are cut at multiples of i
 TILE_ROWS = 128  # rows (token x query head of the group) of a prefill tile
 TARGET_BLOCKS = 148 * 2  # one wave at two blocks per SM
 MAX_SPLITS = 64  # items per request the kernel's fast merge takes
+MIN_ITEM_KEYS = 320  # a request is not cut into items shorter than this (measured: decode attention, batch 1 to 16)
 
 
 def page_size_ok(page_size: int) -> bool:
@@ -46,7 +47,9 @@ def plan_decode(rows, window: Optional[int], num_kv_heads: int, target_blocks: i
         return []
     lo = [max(0, p - window + 1) if window else 0 for _, _, p in rows]
     longest = max(p + 1 - l for (_, _, p), l in zip(rows, lo))
-    pieces = min(MAX_SPLITS - 1, max(1, target_blocks // max(1, len(rows) * num_kv_heads)))
+    # as many items as fill the GPU once, but none shorter than a few stages: every further item
+    # of a request costs the merging block a little
+    pieces = min(MAX_SPLITS - 1, max(1, target_blocks // max(1, len(rows) * num_kv_heads)), -(-longest // MIN_ITEM_KEYS))
     split = max(STAGE_KEYS, -(-(-(-longest // pieces)) // STAGE_KEYS) * STAGE_KEYS)
     items = []
     for (t, b, p), l in zip(rows, lo):
