@@ -1,7 +1,7 @@
 """Engine options, named as 12vivi/tandem names them (python/tandem/config.py:37-81).
 
 Options of tandem that belong to parts this engine does not have (prefix cache, host KV tier,
-attention backend choice, overlap scheduling, speculative decoding, hybrid MoE) are left out.
+attention backend choice, speculative decoding, hybrid MoE) are left out.
 """
 
 from __future__ import annotations
@@ -27,6 +27,7 @@ class EngineConfig:
     seed: int = 0
     cuda_graph: bool = True  # decode-only steps replay CUDA graphs
     cuda_graph_max_bs: int = 64
+    overlap_schedule: bool = True  # launch step N before step N-1's tokens reach the host (config.py:64 of the reference)
 
     def __post_init__(self) -> None:
         if self.dtype not in _DTYPES:

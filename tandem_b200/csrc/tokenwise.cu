@@ -38,6 +38,21 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 }
 
 // ---------------------------------------------------------------------------------------------
+// ids[i] = tokens[source[i]] where source[i] >= 0: token ids that the step before sampled and that
+// have not travelled to the host yet go straight into this step's batch.  It stands where
+// 12vivi/tandem gathers the in-flight step's tokens on the device
+// (python/tandem/executor/model_runner.py:118-126).
+__global__ void take_tokens_kernel(int* __restrict__ ids, const int* __restrict__ source, const int* __restrict__ tokens,
+                                   int n, int num_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int s = source[i];
+  if (s >= 0 && s < num_tokens) ids[i] = tokens[s];
+}
+
+// ---------------------------------------------------------------------------------------------
 // residual[src] += x[src] (if x); y[r] = residual[src] * rsqrt(mean(residual[src]^2) + eps) * w
 // with src = rows ? rows[r] : r.  One block per output row.
 template <typename T>
@@ -217,6 +232,11 @@ int tb_embedding(void* stream, const int* ids, const void* table, float* out, in
                  int dtype) {
   if (T_tokens <= 0) return 0;
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::embedding_kernel<T>, dim3(T_tokens), dim3(256), 0, stream, ids, (const T*)table, out, H, V));
+}
+
+int tb_take_tokens(void* stream, int* ids, const int* source, const int* tokens, int n, int num_tokens) {
+  if (n <= 0) return 0;
+  return tb::launch(tb::take_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, source, tokens, n, num_tokens);
 }
 
 int tb_add_rmsnorm(void* stream, const void* x, float* residual, const float* weight, void* y, const int* rows,

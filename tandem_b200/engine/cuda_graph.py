@@ -41,7 +41,7 @@ class _Captured:
         m = executor.manager
         self.width = -(-max_model_len // m.page_size)
         self.sizes = {"ids": bucket, "positions": bucket, "seq_of_token": bucket, "cu": bucket + 1, "starts": bucket,
-                      "slots": bucket, "rows": bucket}
+                      "slots": bucket, "rows": bucket, "pending": bucket}
         for g in range(len(m.groups)):
             self.sizes[("table", g)] = bucket * self.width
             self.sizes[("kvslots", g)] = bucket
@@ -75,7 +75,9 @@ class _Captured:
         ex, m, ps, Bk, B = self.executor, self.executor.manager, self.executor.manager.page_size, self.bucket, len(entries)
         starts = [m.num_tokens(e.request_id) for e in entries]
         pad = Bk - B
-        self.put("ids", [int(e.tokens[0]) for e in entries] + [0] * pad)
+        self.put("ids", [int(e.tokens[0]) if e.pending is None else 0 for e in entries] + [0] * pad)
+        any_pending = any(e.pending is not None for e in entries)
+        self.put("pending", [-1 if e.pending is None else e.pending for e in entries] + [-1] * pad)
         self.put("positions", starts + [0] * pad)
         self.put("seq_of_token", list(range(Bk)))
         self.put("cu", list(range(Bk + 1)))
@@ -112,6 +114,8 @@ class _Captured:
             ctx.tables[g] = (self.view(("table", g)).view(Bk, self.width), self.view(("kvslots", g)))
         self.device.copy_(self.host, non_blocking=True)
         ex.h2d_bytes_last = self.host.numel() * 4
+        if any_pending:  # tokens of the step in flight enter the batch on the device, before the graph reads it
+            ops.take_tokens(self.view("ids"), self.view("pending"), ex.pending_tokens)
         return ctx
 
     def capture(self, entries: Sequence[StepEntry]) -> None:

@@ -28,6 +28,9 @@ class StepEntry:
     request_id: str
     tokens: Sequence[int]  # the request's next tokens
     want: Sequence[int] = field(default_factory=list)  # places among ``tokens`` whose logits are returned
+    # The value of the last token is still on the device: row ``pending`` of ``Executor.pending_tokens``
+    # (what the step before sampled; python/tandem/executor/model_runner.py:88-111 of 12vivi/tandem).
+    pending: Optional[int] = None
 
 
 class Executor:
@@ -39,6 +42,7 @@ class Executor:
         self.mixers = [layer.mixer for layer in getattr(decoder, "layers", []) if hasattr(layer.mixer, "step_arrays")]
         self.num_steps = 0
         self.h2d_bytes_last = 0  # bytes of the last step's batch description copied to the device
+        self.pending_tokens: Optional[torch.Tensor] = None  # int32 on the device: tokens of the step in flight
 
     # ------------------------------------------------------------------ batch description
     def validate(self, entries: Sequence[StepEntry]) -> None:
@@ -56,7 +60,10 @@ class Executor:
             if start + n > self.max_position:
                 raise ValueError(f"request {e.request_id!r} would reach position {start + n - 1}; "
                                  f"the model's position table ends at {self.max_position - 1}")
-            for tok in e.tokens:
+            if e.pending is not None and (self.pending_tokens is None or not 0 <= e.pending < self.pending_tokens.numel()):
+                raise ValueError(f"request {e.request_id!r} takes its token from row {e.pending} of a step in flight "
+                                 "that has no such row")
+            for tok in (e.tokens if e.pending is None else e.tokens[:-1]):
                 if not 0 <= int(tok) < self.vocab_size:
                     raise ValueError(f"token id {tok} of request {e.request_id!r} is outside the vocabulary "
                                      f"[0, {self.vocab_size})")
@@ -70,11 +77,17 @@ class Executor:
         m, ps = self.manager, self.manager.page_size
         self.validate(entries)
         ids, positions, seq_of_token, cu, starts, lens, slots_host, rows = [], [], [], [0], [], [], [], []
+        pending = []  # (token row, row of pending_tokens)
         for b, e in enumerate(entries):
             n = len(e.tokens)
             start = m.num_tokens(e.request_id)
             rows.extend(cu[-1] + w for w in e.want)
-            ids.extend(int(t) for t in e.tokens)
+            if e.pending is None:
+                ids.extend(int(t) for t in e.tokens)
+            else:
+                ids.extend(int(t) for t in e.tokens[:-1])
+                ids.append(0)
+                pending.append((cu[-1] + n - 1, e.pending))
             positions.extend(range(start, start + n))
             seq_of_token.extend([b] * n)
             cu.append(cu[-1] + n)
@@ -92,6 +105,11 @@ class Executor:
         )
         arrays = {"ids": ids, "positions": positions, "seq_of_token": seq_of_token, "cu": cu, "starts": starts,
                   "slots": slots_host, "rows": rows}
+        if pending:
+            source = [-1] * T
+            for row, src in pending:
+                source[row] = src
+            arrays["pending"] = source
         for g in range(len(m.groups)):
             table = []
             slot_list = []
@@ -124,6 +142,10 @@ class Executor:
             return dev[offsets[k]: offsets[k] + sizes[k]]
 
         ctx.token_ids, ctx.positions, ctx.seq_of_token = view("ids"), view("positions"), view("seq_of_token")
+        if pending:
+            from tandem_b200.kernels import ops
+
+            ops.take_tokens(ctx.token_ids, view("pending"), self.pending_tokens)
         ctx.cu_seqlens, ctx.seq_starts, ctx.state_slots = view("cu"), view("starts"), view("slots")
         for g in range(len(m.groups)):
             ctx.tables[g] = (view(("table", g)).view(B, width), view(("kvslots", g)))

@@ -19,12 +19,36 @@ import torch
 from tandem_b200.config.engine_config import EngineConfig
 from tandem_b200.engine.core import build_executor, load_model
 from tandem_b200.engine.executor import StepEntry
-from tandem_b200.engine.request import Request, RequestOutput, RequestStatus
+from tandem_b200.engine.request import PLACEHOLDER, Request, RequestOutput, RequestStatus
 from tandem_b200.engine.scheduler import Scheduler, StepPlan
 from tandem_b200.sampling.params import SamplingParams
-from tandem_b200.sampling.sampler import sample
+from tandem_b200.sampling.sampler import sample_on_device
 
 PromptType = Union[str, Sequence[int]]
+
+
+class _InFlight:
+    """A launched step: its plan, the requests that get a token from it (in the order of the
+    rows of ``tokens``), the tokens on the device, and their copy to pinned host memory with the
+    event that says it has landed."""
+
+    def __init__(self, plan: StepPlan, requests: list, tokens: torch.Tensor) -> None:
+        self.plan, self.requests, self.tokens = plan, requests, tokens
+        self.host = None
+        self.event = None
+        if tokens.is_cuda:
+            self.host = torch.empty(tokens.shape, dtype=tokens.dtype, pin_memory=True)
+            self.host.copy_(tokens, non_blocking=True)
+            self.event = torch.cuda.Event()
+            self.event.record()
+
+    def resolve(self) -> dict:
+        if self.event is not None:
+            self.event.synchronize()
+            values = self.host.tolist()
+        else:
+            values = self.tokens.tolist()
+        return {r.request_id: t for r, t in zip(self.requests, values)}
 
 
 class LLMEngine:
@@ -52,6 +76,10 @@ class LLMEngine:
             from transformers import AutoTokenizer  # text in and out only; no model code
 
             self.tokenizer = AutoTokenizer.from_pretrained(config.model)
+        # Overlap scheduling (llm_engine.py:298-346 of the reference): step N is launched before the
+        # host has seen the tokens of step N-1, which enter N's batch on the device.
+        self.overlap = bool(config.overlap_schedule)
+        self.inflight: Optional[_InFlight] = None
         self.requests: dict = {}
         self._ids = itertools.count()
         self.num_steps = 0
@@ -99,19 +127,54 @@ class LLMEngine:
             self.scheduler.finish_request(req, RequestStatus.FINISHED_ABORTED)
 
     def has_unfinished_requests(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self.inflight is not None
 
     # ------------------------------------------------------------------ step
     def step(self) -> list:
-        """schedule -> run -> sample -> update (llm_engine.py:284-296 of 12vivi/tandem)."""
+        """schedule -> run -> sample -> update (llm_engine.py:284-296 of 12vivi/tandem).  With
+        overlap scheduling a call launches one step and returns the outputs of the step launched
+        by the call before, whose tokens the host reads while the new step runs."""
+        if self.overlap:
+            return self._step_overlap()
         plan = self.scheduler.schedule()
         if plan.is_empty:
             if self.scheduler.has_unfinished() and not plan.preempted:
                 raise RuntimeError("the scheduler could place no request: the cache pool is too small")
             return []
-        sampled = self._execute(plan)
-        updated = self.scheduler.update_from_output(plan, sampled)
+        launched = self._launch(plan)
+        updated = self.scheduler.update_from_output(plan, launched.resolve())
         self.num_steps += 1
+        return self._emit(updated)
+
+    def _step_overlap(self) -> list:
+        outputs = []
+        if self.inflight is not None and self.scheduler.may_preempt():
+            outputs = self.drain()  # pages are short: no request with a token in flight may be preempted
+        plan = self.scheduler.schedule()
+        launched = None
+        if not plan.is_empty:
+            launched = self._launch(plan)
+            self.scheduler.on_launch(plan)
+            for row, req in enumerate(launched.requests):
+                req.inflight_row = row
+            self.num_steps += 1
+        elif self.inflight is None and not outputs and self.scheduler.has_unfinished() and not plan.preempted:
+            raise RuntimeError("the scheduler could place no request: the cache pool is too small")
+        previous, self.inflight = self.inflight, launched
+        self.executor.pending_tokens = launched.tokens if launched is not None else None
+        if previous is not None:
+            outputs += self._emit(self.scheduler.update_resolved(previous.plan, previous.resolve()))
+        return outputs
+
+    def drain(self) -> list:
+        """Wait for the step in flight, if any, and apply its tokens."""
+        previous, self.inflight = self.inflight, None
+        self.executor.pending_tokens = None
+        if previous is None:
+            return []
+        return self._emit(self.scheduler.update_resolved(previous.plan, previous.resolve()))
+
+    def _emit(self, updated: list) -> list:
         outputs = []
         for req in updated:
             outputs.append(self._make_output(req))
@@ -126,20 +189,26 @@ class LLMEngine:
         for s in plan.scheduled:
             req, n = s.request, s.num_tokens
             start = req.num_computed_tokens
-            entries.append(StepEntry(req.request_id, req.token_ids_in_range(start, start + n),
-                                     [n - 1] if start + n >= req.num_tokens else []))
+            tokens = req.token_ids_in_range(start, start + n)
+            # only the newest token can still be on its way (model_runner.py:95-99 of the reference)
+            pending = req.inflight_row if tokens[-1] == PLACEHOLDER else None
+            entries.append(StepEntry(req.request_id, tokens, [n - 1] if start + n >= req.num_tokens else [], pending))
         return entries
 
-    def _execute(self, plan: StepPlan) -> dict:
+    def _launch(self, plan: StepPlan) -> _InFlight:
+        """Run the plan's step and its sampling on the device; nothing is read back here."""
         entries = self.entries_of(plan)
         sampling = [s.request for s, e in zip(plan.scheduled, entries) if e.want]
         if self.graphs is not None and self.graphs.takes(entries):
             logits = self.graphs.run(entries)
         else:
             logits = self.executor.run(entries)
-        tokens = sample(logits, [r.sampling_params for r in sampling], [r.sample_seed for r in sampling],
-                        [r.num_output_tokens for r in sampling])
-        return {r.request_id: t for r, t in zip(sampling, tokens)}
+        if sampling:
+            tokens = sample_on_device(logits, [r.sampling_params for r in sampling], [r.sample_seed for r in sampling],
+                                      [r.num_output_tokens for r in sampling])
+        else:
+            tokens = torch.empty(0, dtype=torch.int32, device=logits.device)
+        return _InFlight(plan, sampling, tokens)
 
     def _make_output(self, req: Request) -> RequestOutput:
         metrics = {}

@@ -1,5 +1,5 @@
 """One generation request and what comes back from it
-(python/tandem/engine/request.py:18-155, without the prefix-cache, speculative and overlap fields)."""
+(python/tandem/engine/request.py:18-155, without the prefix-cache and speculative fields)."""
 
 from __future__ import annotations
 
@@ -9,6 +9,9 @@ from dataclasses import dataclass, field
 from typing import Optional
 
 from tandem_b200.sampling.params import SamplingParams
+
+
+PLACEHOLDER = -1  # an output token that a launched step will produce and the host has not seen yet
 
 
 class RequestStatus(enum.Enum):
@@ -44,6 +47,12 @@ class Request:
         self.first_token_time: Optional[float] = None
         self.finish_time: Optional[float] = None
         self.num_preemptions = 0
+        self.num_resolved_outputs = 0  # output tokens whose values the host knows (overlap scheduling)
+        self.inflight_row = -1  # row of the launched step's token tensor that holds the placeholder's value
+
+    @property
+    def has_pending_token(self) -> bool:
+        return self.num_resolved_outputs < len(self.output_token_ids)
 
     @property
     def num_prompt_tokens(self) -> int:

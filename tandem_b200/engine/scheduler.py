@@ -1,7 +1,7 @@
 """Continuous batching with chunked prefill under a token budget.
 
 The state machine of python/tandem/scheduler/scheduler.py:216-288,364-407 without its prefix
-cache, host tier, short-prefill lane and overlap placeholders:
+cache, host tier and short-prefill lane:
 
 * two queues, ``waiting`` (first in, first out) and ``running``;
 * each step has ``max_num_batched_tokens`` tokens to give; a request takes
@@ -20,6 +20,15 @@ count returns to zero, and it goes to the *front* of the waiting queue to be rec
 its generated tokens included.  A step that preempted admits nobody.  Because no request may be
 longer than one group's whole pool (``token_capacity``), the oldest request can always finish,
 so the queue always drains.
+
+Overlap scheduling (scheduler.py:409-469 of the reference): the engine may launch step N before
+the tokens of step N-1 have reached the host.  ``on_launch`` books a launched step at once, with a
+placeholder for every token it will produce; ``update_resolved`` fills the placeholders in one
+step later.  A request that turns out to have ended (its token was an end token, or it was
+aborted) may already sit in the next launched step: that step's token for it is dropped.  A
+request whose token in flight is the last it may produce is not scheduled again.  The engine
+resolves the step in flight *before* it schedules whenever pages are so short that a preemption
+is possible (``may_preempt``), so a preempted request never carries a placeholder.
 """
 
 from __future__ import annotations
@@ -29,7 +38,7 @@ from collections import deque
 from dataclasses import dataclass, field
 
 from tandem_b200.cache.manager import CacheManager
-from tandem_b200.engine.request import Request, RequestStatus
+from tandem_b200.engine.request import PLACEHOLDER, Request, RequestStatus
 
 
 @dataclass
@@ -115,7 +124,7 @@ class Scheduler:
     def _schedule(self, decodes: bool) -> StepPlan:
         plan = StepPlan()
         budget = self.max_num_batched_tokens
-        order = ([r for r in self.running if r.is_decoding] if decodes else []) + \
+        order = ([r for r in self.running if r.is_decoding and not self._awaiting_last_token(r)] if decodes else []) + \
                 [r for r in self.running if not r.is_decoding]
 
         # 1) running requests: decoding ones first, then prompt portions
@@ -180,8 +189,69 @@ class Scheduler:
                 req.finish_time = now
         return updated
 
+    # ------------------------------------------------------------------ overlap scheduling
+    def _awaiting_last_token(self, req: Request) -> bool:
+        """The token it has in flight is the last one it may produce (scheduler.py:417-421)."""
+        return req.has_pending_token and (req.num_output_tokens >= req.sampling_params.max_tokens
+                                          or req.num_tokens >= self.max_model_len)
+
+    def may_preempt(self) -> bool:
+        """Could the next ``schedule`` run out of pages for a running request?  Every running
+        request may need one more page, and prompt portions at most a budget's worth."""
+        ps = self.cache.page_size
+        need = len(self.running) + -(-self.max_num_batched_tokens // ps) + 1
+        return any(self.cache.free_pages(g) < need for g in range(len(self.cache.groups)))
+
+    def on_launch(self, plan: StepPlan) -> None:
+        """Book a step that has been launched: its tokens count as computed, and every request
+        that reaches its newest token gets a placeholder for the token on its way."""
+        for s in plan.scheduled:
+            req = s.request
+            produces = req.num_computed_tokens + s.num_tokens >= req.num_tokens
+            req.num_computed_tokens += s.num_tokens
+            self.cache.commit(req.request_id, s.num_tokens)
+            if produces:
+                req.output_token_ids.append(PLACEHOLDER)
+
+    def update_resolved(self, plan: StepPlan, sampled: dict) -> list:
+        """The tokens of a launched step have arrived: fill the placeholders in, finish what ends."""
+        now = time.monotonic()
+        updated = []
+        for s in plan.scheduled:
+            req = s.request
+            token = sampled.get(req.request_id)
+            if token is None:
+                continue
+            req.new_token_ids = []
+            if req.finished:  # ended (or was aborted) while this step was in flight: its token is dropped
+                del req.output_token_ids[req.num_resolved_outputs:]
+                continue
+            token = int(token)
+            req.output_token_ids[req.num_resolved_outputs] = token
+            req.num_resolved_outputs += 1
+            req.new_token_ids.append(token)
+            if req.first_token_time is None:
+                req.first_token_time = now
+            updated.append(req)
+            if token in req.eos_token_ids or token in req.stop_token_ids:
+                status = RequestStatus.FINISHED_STOPPED
+            elif (req.num_resolved_outputs >= req.sampling_params.max_tokens
+                  or req.num_prompt_tokens + req.num_resolved_outputs >= self.max_model_len):
+                status = RequestStatus.FINISHED_LENGTH
+            else:
+                continue
+            del req.output_token_ids[req.num_resolved_outputs:]  # the next step's token, if launched, is dropped
+            req.num_computed_tokens = min(req.num_computed_tokens, req.num_tokens)
+            if req in self.running:
+                self.running.remove(req)
+            self._release(req)
+            req.status = status
+            req.finish_time = now
+        return updated
+
     def _append_token(self, req: Request, token: int) -> None:
         req.output_token_ids.append(token)
+        req.num_resolved_outputs = len(req.output_token_ids)
         req.new_token_ids.append(token)
         if token in req.eos_token_ids or token in req.stop_token_ids:
             req.status = RequestStatus.FINISHED_STOPPED

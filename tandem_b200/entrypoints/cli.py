@@ -27,6 +27,7 @@ def _engine_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--kv-cache-gb", type=float, default=1.0)
     p.add_argument("--num-kv-blocks", type=int, default=None)
     p.add_argument("--no-cuda-graph", action="store_true", help="run decode steps without CUDA graphs")
+    p.add_argument("--no-overlap", action="store_true", help="read every step's tokens before the next step is launched")
     p.add_argument("--cuda-graph-max-bs", type=int, default=64)
     p.add_argument("--engine-seed", type=int, default=0, help="seed of requests that carry none")
 
@@ -38,7 +39,7 @@ def _engine_config(args):
         model=args.model, device=args.device, dtype=args.dtype, max_num_seqs=args.max_num_seqs,
         max_num_batched_tokens=args.max_num_batched_tokens, schedule_policy=args.schedule_policy,
         max_model_len=args.max_model_len, block_size=args.block_size, kv_cache_memory_gb=args.kv_cache_gb,
-        num_kv_blocks=args.num_kv_blocks, seed=args.engine_seed, cuda_graph=not args.no_cuda_graph,
+        num_kv_blocks=args.num_kv_blocks, seed=args.engine_seed, cuda_graph=not args.no_cuda_graph, overlap_schedule=not args.no_overlap,
         cuda_graph_max_bs=args.cuda_graph_max_bs,
     )
 

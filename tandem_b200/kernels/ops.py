@@ -90,6 +90,18 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def take_tokens(ids: torch.Tensor, source: torch.Tensor, tokens: torch.Tensor) -> None:
+    """ids[i] = tokens[source[i]] wherever source[i] >= 0 (all int32, in place): tokens that the
+    step before sampled enter this step's batch without a trip to the host."""
+    _need(ids, "ids", torch.int32)
+    _need(source, "source", torch.int32)
+    _need(tokens, "tokens", torch.int32)
+    if source.numel() != ids.numel():
+        raise KernelError(f"source has {source.numel()} entries, ids {ids.numel()}")
+    lib = load_library("tokenwise")
+    _check(lib.tb_take_tokens(_stream(), _ptr(ids), _ptr(source), _ptr(tokens), ids.numel(), tokens.numel()), "take_tokens")
+
+
 def add_rmsnorm(x: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """residual += x (in place, float32; skipped when x is None); returns RMSNorm(residual) * weight

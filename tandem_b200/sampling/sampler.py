@@ -24,11 +24,17 @@ def sample(logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequen
            counters: Sequence[int]) -> list:
     """logits [R, V] float32 on the device -> R token ids on the host.  Row r is drawn with
     ``uniform(seeds[r], counters[r])``."""
-    R = logits.shape[0]
-    if R == 0:
+    if logits.shape[0] == 0:
         return []
+    return sample_on_device(logits, params, seeds, counters).tolist()
+
+
+def sample_on_device(logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+                     counters: Sequence[int]) -> torch.Tensor:
+    """As ``sample``, but the R token ids stay on the device (int32): the caller decides when
+    the host reads them."""
     if all(p.greedy for p in params):
-        return ops.argmax(logits).tolist()
+        return ops.argmax(logits)
     dev = logits.device
     host = torch.tensor(
         [[p.temperature for p in params], [p.top_p for p in params], [p.min_p for p in params],
@@ -36,4 +42,4 @@ def sample(logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequen
     ks = torch.tensor([p.top_k for p in params], dtype=torch.int32).pin_memory()
     f = host.to(dev, non_blocking=True)
     k = ks.to(dev, non_blocking=True)
-    return ops.sample(logits, f[0], k, f[1], f[2], f[3]).tolist()
+    return ops.sample(logits, f[0], k, f[1], f[2], f[3])

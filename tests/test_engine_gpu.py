@@ -461,3 +461,40 @@ def test_the_order_may_name_a_layer_twice_or_share_a_cache():
     h = h + plain.swiglu(plain.rms_norm(h, w["model.layers.1.post_attention_layernorm.weight"], d["eps"]), w, "model.layers.1.mlp")
     want = plain.rms_norm(h, w["model.norm.weight"], d["eps"]) @ w["model.embed_tokens.weight"].T
     torch.testing.assert_close(whole.cpu(), want, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlap_scheduling_changes_no_token(tiny_folder, dtype):
+    """Launching step N before the host has read step N-1's tokens gives the tokens of the
+    synchronous loop: greedy and seeded sampling, prompts cut by the budget, requests that end on a
+    stop token while their next token is already in flight, a pool so small that requests are
+    preempted, and a request of a single new token."""
+    from tandem_b200 import EngineConfig, LLMEngine, SamplingParams
+
+    folder = tiny_folder("B", 0.1)
+    prompts = [random_tokens(80 + i, n, 1000) for i, n in enumerate([1, 9, 40, 23, 5])]
+
+    def run(overlap, sps, **options):
+        eng = LLMEngine(EngineConfig(model=folder, dtype=dtype, block_size=8, max_num_batched_tokens=16,
+                                     schedule_policy="decode_first", overlap_schedule=overlap, **options))
+        outs = eng.generate(prompts, sps)
+        eng.cache.check()
+        assert eng.cache.all_free() and eng.inflight is None
+        return [(o.output_token_ids, o.finish_reason) for o in outs], eng
+
+    greedy = [SamplingParams(max_tokens=n, **GREEDY) for n in (12, 1, 20, 7, 2)]
+    sync, _ = run(False, greedy, num_kv_blocks=64)
+    over, eng = run(True, greedy, num_kv_blocks=64)
+    assert over == sync and eng.overlap
+    # stop tokens: take tokens that the greedy run produced in the middle of two requests
+    stops = [SamplingParams(max_tokens=20, temperature=0.0, ignore_eos=True, stop_token_ids=[sync[i][0][k]])
+             if i in (0, 2) else SamplingParams(max_tokens=6, **GREEDY) for i, k in zip(range(5), (5, 0, 9, 0, 0))]
+    sync_stop, _ = run(False, stops, num_kv_blocks=64)
+    over_stop, _ = run(True, stops, num_kv_blocks=64)
+    assert over_stop == sync_stop and sync_stop[0][1] == "stop" and sync_stop[2][1] == "stop"
+    # seeded sampling
+    drawn = [SamplingParams(max_tokens=10, temperature=0.9, top_k=50, seed=7 + i, ignore_eos=True) for i in range(5)]
+    assert run(True, drawn, num_kv_blocks=64)[0] == run(False, drawn, num_kv_blocks=64)[0]
+    # 10 pages of 8 tokens: five requests of up to 60 tokens do not fit, some are preempted
+    small, eng = run(True, greedy, num_kv_blocks=10, max_num_seqs=5)
+    assert small == sync and eng.scheduler.num_preemptions > 0

@@ -156,3 +156,53 @@ def test_windowed_request_outlives_the_pool():
         run_step(s)
         cache.check()
     assert r.num_tokens == 16 and cache.all_free()
+
+
+# ----------------------------------------------------------------------------- overlap scheduling
+def overlap_step(s, inflight, tokens):
+    """One call of the engine's overlap loop with fake tokens: schedule and book step N, then
+    resolve step N-1 (``tokens``: request id -> token for the step being resolved)."""
+    plan = s.schedule()
+    if not plan.is_empty:
+        s.on_launch(plan)
+    if inflight is not None:
+        s.update_resolved(inflight, {x.request.request_id: tokens.get(x.request.request_id, 7) for x in inflight.scheduled
+                                     if x.request.output_token_ids or x.request.finished})
+    return plan
+
+
+def test_overlap_books_a_placeholder_and_fills_it_one_step_later():
+    from tandem_b200.engine.request import PLACEHOLDER
+
+    s, cache = make(budget=8)
+    a = req("a", 5, max_tokens=3)
+    s.add_request(a)
+    p0 = overlap_step(s, None, {})
+    assert sizes(p0) == [("a", 5)] and a.output_token_ids == [PLACEHOLDER] and a.num_resolved_outputs == 0
+    p1 = overlap_step(s, p0, {"a": 11})  # decodes with its token still on the way, then learns it
+    assert sizes(p1) == [("a", 1)] and a.output_token_ids == [11, PLACEHOLDER] and a.num_resolved_outputs == 1
+    p2 = overlap_step(s, p1, {"a": 12})
+    assert sizes(p2) == [("a", 1)] and a.output_token_ids == [11, 12, PLACEHOLDER]
+    p3 = overlap_step(s, p2, {"a": 13})  # the third token is the last it may produce: not scheduled again
+    assert p3.is_empty and a.finished and a.finish_reason == "length" and a.output_token_ids == [11, 12, 13]
+    assert not s.has_unfinished() and cache.all_free()
+
+
+def test_overlap_drops_the_token_launched_after_an_end_token():
+    s, cache = make(budget=8)
+    a, b = req("a", 3, max_tokens=8), req("b", 4, max_tokens=8)
+    s.add_request(a)
+    s.add_request(b)
+    p0 = overlap_step(s, None, {})
+    p1 = overlap_step(s, p0, {"a": 0, "b": 5})  # a's first token is its end token (0), found after p1 was launched
+    assert ("a", 1) in sizes(p1) and a.finished and a.finish_reason == "stop" and a.output_token_ids == [0]
+    p2 = overlap_step(s, p1, {"a": 9, "b": 6})  # p1's token for a is dropped
+    assert sizes(p2) == [("b", 1)] and a.output_token_ids == [0] and b.output_token_ids[:2] == [5, 6]
+    cache.check()
+
+
+def test_overlap_resolves_first_when_pages_are_short():
+    s, _ = make(pages=2, page_size=4, budget=8)
+    assert s.may_preempt()  # fewer free pages than a budget's worth: the engine reads the step in flight before it schedules
+    s2, _ = make(pages=64, page_size=4, budget=8)
+    assert not s2.may_preempt()
