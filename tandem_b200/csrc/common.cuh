@@ -90,6 +90,11 @@ inline int launch_status() { return (int)cudaGetLastError(); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {  // two floats -> bfloat16 pair (lo in the low half)
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 inline bool pdl_enabled() {
   static const bool on = [] { const char* e = getenv("TANDEM_PDL"); return !(e && e[0] == '0'); }();
   return on;

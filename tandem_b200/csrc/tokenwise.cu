@@ -5,6 +5,7 @@
 // rotate_half), python/tandem/layers/triton_ops.py:21-113 (the fused prologue and the fused
 // add+norm, which add in float32 and round once, as these kernels do).
 #include "cache_layout.cuh"
+#include "split_output.cuh"
 #include "common.cuh"
 
 namespace tb {
@@ -55,18 +56,45 @@ __global__ void take_tokens_kernel(int* __restrict__ ids, const int* __restrict_
 // ---------------------------------------------------------------------------------------------
 // residual[src] += x[src] (if x); y[r] = residual[src] * rsqrt(mean(residual[src]^2) + eps) * w
 // with src = rows ? rows[r] : r.  One block per output row.
+// x may be a split output (bfloat16 only): the partials of its shared tiles are added on the way in.
 template <typename T>
 __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ residual,
                                    const float* __restrict__ weight, T* __restrict__ y,
-                                   const int* __restrict__ rows, int H, float eps) {
+                                   const int* __restrict__ rows, int H, float eps, const SplitView sv) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
+  const SplitTile first = split_tile(sv, min((int)threadIdx.x * 8, H - 1));  // this thread's first columns (host-written table)
   pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* res = residual + (size_t)src * H;
   const T* xr = x ? x + (size_t)src * H : nullptr;
   float ss = 0.f;
+  if (sizeof(T) == 2 && (H & 7) == 0) {  // eight elements per thread and turn: 16-byte loads and stores
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float4 s0 = *reinterpret_cast<const float4*>(res + i), s1 = *reinterpret_cast<const float4*>(res + i + 4);
+      if (xr) {
+        float v[8];
+        split_load8(reinterpret_cast<const __nv_bfloat16*>(xr), sv, i == (int)threadIdx.x * 8 ? first : split_tile(sv, i), src, i, v);
+        s0.x += v[0]; s0.y += v[1]; s0.z += v[2]; s0.w += v[3];
+        s1.x += v[4]; s1.y += v[5]; s1.z += v[6]; s1.w += v[7];
+        *reinterpret_cast<float4*>(res + i) = s0;
+        *reinterpret_cast<float4*>(res + i + 4) = s1;
+      }
+      ss += s0.x * s0.x + s0.y * s0.y + s0.z * s0.z + s0.w * s0.w + s1.x * s1.x + s1.y * s1.y + s1.z * s1.z + s1.w * s1.w;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    __nv_bfloat16* yr = reinterpret_cast<__nv_bfloat16*>(y) + (size_t)r * H;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {  // each thread re-reads only what it wrote itself
+      const float4 s0 = *reinterpret_cast<const float4*>(res + i), s1 = *reinterpret_cast<const float4*>(res + i + 4);
+      const float4 w0 = *reinterpret_cast<const float4*>(weight + i), w1 = *reinterpret_cast<const float4*>(weight + i + 4);
+      *reinterpret_cast<uint4*>(yr + i) =
+          make_uint4(pack2(s0.x * inv * w0.x, s0.y * inv * w0.y), pack2(s0.z * inv * w0.z, s0.w * inv * w0.w),
+                     pack2(s1.x * inv * w1.x, s1.y * inv * w1.y), pack2(s1.z * inv * w1.z, s1.w * inv * w1.w));
+    }
+    return;
+  }
   if ((H & 3) == 0) {
     for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
       float4 s = *reinterpret_cast<const float4*>(res + i);
@@ -116,7 +144,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
                                        const float* __restrict__ k_w, const float* __restrict__ cos_sin,
                                        T* __restrict__ k_cache, T* __restrict__ v_cache, int T_tokens, int nh,
                                        int nkv, int hd, int rd, int page_size, float eps, int write_kv,
-                                       int max_pos) {
+                                       int max_pos, const SplitView sv) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -128,6 +156,18 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
   const int slot = slots ? slots[t] : -1;
   const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
   if (!is_q && (slot < 0 || !write_kv)) return;
+  if (sizeof(T) == 2 && sv.partial) {  // a split output (hd is a multiple of 8): this head's columns are made whole first
+    __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(qkv) + (size_t)t * heads * hd;
+    for (int c = lane; c < hd / 8; c += 32) {
+      const int n0 = h * hd + c * 8;
+      const int* info = sv.tiles + 3 * (n0 / SPLIT_BN);
+      if (info[0] == info[1]) continue;
+      float v[8];
+      split_load8(row, sv, t, n0, v);
+      *reinterpret_cast<uint4*>(row + n0) = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+    }
+    __syncwarp();
+  }
 
   T* dst = x;   // q: in place.  k, v: the tile of (page, kv head); `row` is the token's row in it
   int row = -1;
@@ -191,7 +231,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
 // ---------------------------------------------------------------------------------------------
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I, const SplitView sv) {
   pdl_launch_dependents();
   pdl_wait();
   if (sizeof(T) == 2 && (I & 7) == 0) {  // eight elements per thread: 16-byte loads and stores
@@ -199,17 +239,15 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < groups; e += (long long)gridDim.x * blockDim.x) {
       const long long t = (e * 8) / I;
       const int i = (int)((e * 8) % I);
-      const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * I + i);
-      const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + i);
-      const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
-      const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+      const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(gu) + t * 2 * I;
+      float g[8], u[8];
+      split_load8(row, sv, (int)t, i, g);
+      split_load8(row, sv, (int)t, I + i, u);
       uint4 r;
-      __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&r);
+      uint32_t* r2 = reinterpret_cast<uint32_t*>(&r);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
-        r2[j] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
-      }
+      for (int j = 0; j < 4; ++j)
+        r2[j] = pack2(g[2 * j] / (1.f + expf(-g[2 * j])) * u[2 * j], g[2 * j + 1] / (1.f + expf(-g[2 * j + 1])) * u[2 * j + 1]);
       *reinterpret_cast<uint4*>(out + e * 8) = r;
     }
     return;
@@ -239,32 +277,41 @@ int tb_take_tokens(void* stream, int* ids, const int* source, const int* tokens,
   return tb::launch(tb::take_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, source, tokens, n, num_tokens);
 }
 
+// partial, tiles, mpad: x is a split output (split_output.cuh); null partial: a plain tensor.
 int tb_add_rmsnorm(void* stream, const void* x, float* residual, const float* weight, void* y, const int* rows,
-                   int num_rows, int H, float eps, int dtype) {
+                   int num_rows, int H, float eps, int dtype, const float* partial, const int* tiles, int mpad) {
   if (num_rows <= 0) return 0;
+  if (partial && (dtype != TB_BF16 || (H & 7))) return TB_ERR_BAD_SIZE;
   const int threads = H >= 4096 ? 512 : 256;
+  const tb::SplitView sv{partial, tiles, mpad};
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::add_rmsnorm_kernel<T>, dim3(num_rows), dim3(threads), 0, stream, (const T*)x, residual,
-                                      weight, (T*)y, rows, H, eps));
+                                      weight, (T*)y, rows, H, eps, sv));
 }
 
 int tb_qk_norm_rope_kv(void* stream, void* qkv, const int* positions, const int* slots, const float* q_w,
                        const float* k_w, const float* cos_sin, void* k_cache, void* v_cache, int T_tokens, int nh,
-                       int nkv, int hd, int rd, int page_size, float eps, int write_kv, int max_pos, int dtype) {
+                       int nkv, int hd, int rd, int page_size, float eps, int write_kv, int max_pos, int dtype,
+                       const float* partial, const int* tiles, int mpad) {
   if (T_tokens <= 0) return 0;
   if (rd < 0 || rd > hd || (rd & 1) || page_size <= 0) return TB_ERR_BAD_SIZE;
+  if (partial && (dtype != TB_BF16 || (hd & 7))) return TB_ERR_BAD_SIZE;
+  const tb::SplitView sv{partial, tiles, mpad};
   const long long warps = (long long)T_tokens * (nh + 2 * nkv);
   const int blocks = (int)((warps + 3) / 4);
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::qk_norm_rope_kv_kernel<T>, dim3(blocks), dim3(128), 0, stream, (T*)qkv, positions, slots,
                                       q_w, k_w, cos_sin, (T*)k_cache, (T*)v_cache, T_tokens, nh, nkv, hd, rd, page_size, eps,
-                                      write_kv, max_pos));
+                                      write_kv, max_pos, sv));
 }
 
-int tb_silu_mul(void* stream, const void* gu, void* out, int T_tokens, int I, int dtype) {
+int tb_silu_mul(void* stream, const void* gu, void* out, int T_tokens, int I, int dtype, const float* partial,
+                const int* tiles, int mpad) {
   const long long total = (long long)T_tokens * I;
   if (total <= 0) return 0;
+  if (partial && (dtype != TB_BF16 || (I & 7))) return TB_ERR_BAD_SIZE;
+  const tb::SplitView sv{partial, tiles, mpad};
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::silu_mul_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (const T*)gu, (T*)out, total, I));
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::silu_mul_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (const T*)gu, (T*)out, total, I, sv));
 }
 
 }  // extern "C"

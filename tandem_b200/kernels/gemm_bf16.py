@@ -7,6 +7,16 @@ kernels take over for the shapes on which they beat cuBLAS, by a table measured 
 this package's tcgen05 weight-streaming kernel (``csrc/gemm_skinny.cu``); which of the two is
 faster for a shape is measured once, the first time the shape is seen outside a stream capture.
 ``TANDEM_GEMM=skinny`` or ``=library`` forces one of them.
+
+A caller whose output goes to a kernel that takes split input (``ops.add_rmsnorm``,
+``ops.qk_norm_rope_kv``, ``ops.silu_mul``) may allow a ``SplitOutput``: the skinny kernel then
+leaves the partial sums of the tiles that several blocks share to that kernel, which adds them
+on its way in (``csrc/split_output.cuh``), and the product ends three trips to the L2 earlier.
+Measured on a B200 at Qwen3-8B sizes and 8 rows: the product alone gets 3 to 5 us shorter (o_proj
+14.1 -> 8.9 us, down_proj 23.3 -> 18.6 us), the reading kernel 2 to 5 us longer, product plus norm
+0.7 to 1.6 us shorter back to back, but a whole decode step came out 2 % slower (1,860 against
+1,896 tok/s).  So it is off unless ``TANDEM_SPLIT_OUTPUT=1``; the values are bit for bit the same
+either way.
 """
 
 from __future__ import annotations
@@ -19,6 +29,7 @@ from tandem_b200.kernels import ops
 from tandem_b200.kernels.build import load_library
 
 SKINNY_MAX_ROWS = 64
+SPLIT_MAX_ROWS = 32  # beyond this the partials are more than a reader should add up
 _mm_out_dtype = True  # torch.mm(..., out_dtype=) is tried once
 _sm_count: dict = {}
 _choice: dict = {}  # (padded rows, N, K, out dtype) -> True: the skinny kernel is the faster one
@@ -53,21 +64,73 @@ def skinny_scratch(device):
     return _sm_count[key]
 
 
+class SplitOutput:
+    """The output [M, N] of a skinny product whose shared tiles are still partial sums in the
+    kernel's scratch memory.  It lives until the next skinny product on the device; kernels that
+    take split input read it, anything else goes through ``ops.as_tensor``."""
+
+    __slots__ = ("y", "partial", "tiles", "mpad", "serial")
+
+    def __init__(self, y, partial, tiles, mpad, serial) -> None:
+        self.y, self.partial, self.tiles, self.mpad, self.serial = y, partial, tiles, mpad, serial
+
+    @property
+    def shape(self):
+        return self.y.shape
+
+    @property
+    def dtype(self):
+        return self.y.dtype
+
+    @property
+    def device(self):
+        return self.y.device
+
+    def check(self) -> None:
+        if _serial.get(str(self.y.device)) != self.serial:
+            raise ops.KernelError("a split output was read after another skinny product had reused its scratch memory")
+
+
+_serial: dict = {}  # device -> number of skinny products launched (their scratch is shared)
+_tiles: dict = {}
+
+
+def split_tiles(device, N: int, K: int):
+    """int32 [N tiles, 3] on the device: which blocks contribute to each tile of a skinny product of
+    this shape (first block, last block, slot of the first one's partial)."""
+    key = (str(device), N, K)
+    if key not in _tiles:
+        host = torch.zeros(3 * -(-N // 128), dtype=torch.int32)
+        load_library("gemm_skinny").tb_gemm_skinny_tiles(N, K, sm_count(device), ops._ptr(host))
+        _tiles[key] = host.to(device)
+    return _tiles[key]
+
+
+def split_enabled() -> bool:
+    return os.environ.get("TANDEM_SPLIT_OUTPUT", "0") == "1"
+
+
 def skinny_applies(M: int, N: int, K: int) -> bool:
     """What the skinny kernel takes at all."""
     return 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0 and N <= (1 << 14) * 128
 
 
-def skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+def skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, split: bool = False):
+    """The tcgen05 weight-streaming kernel.  ``split``: return a ``SplitOutput`` (bfloat16 only)."""
     M, K = x.shape
     N = weight.shape[0]
     y = torch.empty((M, N), dtype=out_dtype, device=x.device)
     partial, counters = skinny_scratch(x.device)
+    tiles = split_tiles(x.device, N, K) if split else None
     lib = load_library("gemm_skinny")
     ops._check(lib.tb_gemm_skinny(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(y), ops._ptr(partial),
                                   ops._ptr(counters), ops._ptr(ops.status_word(x.device)), M, N, K,
-                                  int(out_dtype == torch.float32), sm_count(x.device)), "gemm_skinny")
-    return y
+                                  int(out_dtype == torch.float32), sm_count(x.device), int(split)), "gemm_skinny")
+    dev = str(x.device)
+    _serial[dev] = _serial.get(dev, 0) + 1
+    if not split:
+        return y
+    return SplitOutput(y, partial, tiles, 16 if M <= 16 else (32 if M <= 32 else 64), _serial[dev])
 
 
 def _measure(fn, x, weight, out_dtype, flush) -> float:
@@ -85,7 +148,7 @@ def _measure(fn, x, weight, out_dtype, flush) -> float:
     return sorted(times)[len(times) // 2]
 
 
-def skinny_preferred(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> bool:
+def skinny_preferred(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, split: bool = False) -> bool:
     M, K = x.shape
     N = weight.shape[0]
     if not skinny_applies(M, N, K):
@@ -93,7 +156,7 @@ def skinny_preferred(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dty
     forced = os.environ.get("TANDEM_GEMM")
     if forced in ("skinny", "library"):
         return forced == "skinny"
-    key = (16 if M <= 16 else (32 if M <= 32 else 64), N, K, out_dtype)
+    key = (16 if M <= 16 else (32 if M <= 32 else 64), N, K, out_dtype, split)
     if key not in _choice:
         if torch.cuda.is_current_stream_capturing():
             return M <= 16  # nothing can be timed while a graph is being captured
@@ -101,7 +164,7 @@ def skinny_preferred(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dty
         with torch.inference_mode():
             if dev not in _flush:
                 _flush[dev] = torch.empty(192 << 20, dtype=torch.uint8, device=x.device)  # larger than L2
-            a = _measure(skinny, x, weight, out_dtype, _flush[dev])
+            a = _measure(lambda x_, w_, d_: skinny(x_, w_, d_, split), x, weight, out_dtype, _flush[dev])
             b = _measure(_library, x, weight, out_dtype, _flush[dev])
         _choice[key] = a <= b
     return _choice[key]
@@ -112,9 +175,13 @@ def choices() -> dict:
     return dict(_choice)
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, split_ok: bool = False):
+    """``split_ok``: the caller hands the result to a kernel that takes split input (or through
+    ``ops.as_tensor``), so a ``SplitOutput`` may come back instead of a tensor."""
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise ops.KernelError(f"the bfloat16 product returns bfloat16 or float32, not {out_dtype}")
-    if skinny_preferred(x, weight, out_dtype):
-        return skinny(x, weight, out_dtype)
+    split = (split_ok and out_dtype == torch.bfloat16 and x.shape[0] <= SPLIT_MAX_ROWS and weight.shape[0] % 8 == 0
+             and split_enabled())
+    if skinny_preferred(x, weight, out_dtype, split):
+        return skinny(x, weight, out_dtype, split)
     return _library(x, weight, out_dtype)

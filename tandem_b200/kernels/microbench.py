@@ -4,6 +4,7 @@
     python -m tandem_b200.kernels.microbench decode-attention --batch 64 --context 2048
     python -m tandem_b200.kernels.microbench prefill-attention --tokens 2048
     python -m tandem_b200.kernels.microbench tokenwise --tokens 2048
+    python -m tandem_b200.kernels.microbench norm-gemm --m 8 --n 6144 --k 4096
 
 Timing follows 12vivi/tandem's kernel benchmarks (benchmarks/bench_gemv.py:3-6,35-56): the calls are
 captured in one CUDA graph so that launch cost does not count, and weights or caches are rotated
@@ -65,6 +66,28 @@ def bench_gemm(args) -> None:
     for name, us in rows:
         print(f"gemm M={M} N={N} K={K}  {name:24s} {us:8.1f} us  {N * K * 2 / us / 1e3:7.0f} GB/s weights  "
               f"{2.0 * M * N * K / us / 1e6:7.1f} TFLOP/s")
+
+
+def bench_norm_gemm(args) -> None:
+    """add_rmsnorm followed by the matrix product that reads its output, as a block runs them
+    (TANDEM_PDL=0 shows what the programmatic dependent launch between the two is worth)."""
+    from tandem_b200.kernels import gemm_bf16, ops
+
+    M, N, K = args.m, args.n, args.k
+    ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies_for(N * K * 2))]
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    res, w = torch.randn(M, K, device="cuda"), torch.ones(K, device="cuda")
+    for impl, gemm in (("tcgen05 skinny kernel", gemm_bf16.skinny), ("library (cuBLAS)", gemm_bf16._library)):
+        if impl.startswith("tcgen05") and not gemm_bf16.skinny_applies(M, N, K):
+            continue
+
+        def step(i):
+            gemm(ops.add_rmsnorm(x, res, w, 1e-6, torch.bfloat16), ws[i % len(ws)], torch.bfloat16)
+
+        alone = time_calls(lambda i: gemm(x, ws[i % len(ws)], torch.bfloat16), args.iters, args.graph)
+        norm = time_calls(lambda i: ops.add_rmsnorm(x, res, w, 1e-6, torch.bfloat16), args.iters, args.graph)
+        both = time_calls(step, args.iters, args.graph)
+        print(f"norm + gemm M={M} N={N} K={K}  {impl:24s} {both:8.1f} us  (alone: gemm {alone:.1f} us, norm {norm:.1f} us)")
 
 
 def _cache(pages: int, nkv: int, ps: int, hd: int):
@@ -147,6 +170,11 @@ def main(argv=None) -> None:
     g.add_argument("--f32-out", action="store_true")
     g.add_argument("--impl", choices=["both", "skinny", "library"], default="both")
     g.set_defaults(fn=bench_gemm)
+    ng = sub.add_parser("norm-gemm", parents=[common])
+    ng.add_argument("--m", type=int, default=8)
+    ng.add_argument("--n", type=int, default=6144)
+    ng.add_argument("--k", type=int, default=4096)
+    ng.set_defaults(fn=bench_norm_gemm)
     shape = argparse.ArgumentParser(add_help=False)
     shape.add_argument("--heads", type=int, default=32)
     shape.add_argument("--kv-heads", type=int, default=8)

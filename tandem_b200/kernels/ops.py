@@ -102,10 +102,31 @@ def take_tokens(ids: torch.Tensor, source: torch.Tensor, tokens: torch.Tensor) -
     _check(lib.tb_take_tokens(_stream(), _ptr(ids), _ptr(source), _ptr(tokens), ids.numel(), tokens.numel()), "take_tokens")
 
 
-def add_rmsnorm(x: Optional[torch.Tensor], residual: torch.Tensor, weight: torch.Tensor, eps: float,
+def _split(x):
+    """(tensor, partial pointer, tiles pointer, padded rows) of a tensor or a split output."""
+    if isinstance(x, torch.Tensor) or x is None:
+        return x, None, None, 0
+    x.check()
+    return x.y, _ptr(x.partial), _ptr(x.tiles), x.mpad
+
+
+def as_tensor(x):
+    """A split output made whole (one small kernel); tensors pass through."""
+    if isinstance(x, torch.Tensor) or x is None:
+        return x
+    x.check()
+    M, N = x.y.shape
+    _check(load_library("gemm_skinny").tb_split_resolve(_stream(), _ptr(x.y), _ptr(x.partial), _ptr(x.tiles), x.mpad, M, N),
+           "split_resolve")
+    return x.y
+
+
+def add_rmsnorm(x, residual: torch.Tensor, weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """residual += x (in place, float32; skipped when x is None); returns RMSNorm(residual) * weight
-    in ``out_dtype``.  With ``rows`` [R] int32 only those rows are updated and returned, in that order."""
+    in ``out_dtype``.  With ``rows`` [R] int32 only those rows are updated and returned, in that order.
+    ``x`` may be a split output of the matrix product."""
+    x, partial, tiles, mpad = _split(x)
     _need(residual, "residual", torch.float32)
     _need(weight, "norm weight", torch.float32)
     T, H = residual.shape
@@ -122,18 +143,21 @@ def add_rmsnorm(x: Optional[torch.Tensor], residual: torch.Tensor, weight: torch
     y = torch.empty((n, H), dtype=out_dtype, device=residual.device)
     lib = load_library("tokenwise")
     _check(lib.tb_add_rmsnorm(_stream(), _ptr(x), _ptr(residual), _ptr(weight), _ptr(y), _ptr(rows), n, H,
-                              ctypes.c_float(eps), _code(out_dtype)), "add_rmsnorm")
+                              ctypes.c_float(eps), _code(out_dtype), partial, tiles, mpad), "add_rmsnorm")
     return y
 
 
-def qk_norm_rope_kv(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor],
+def qk_norm_rope_kv(qkv, positions: torch.Tensor, slots: Optional[torch.Tensor],
                     q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
                     k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], num_heads: int,
                     num_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int, eps: float,
-                    write_kv: bool = True) -> None:
+                    write_kv: bool = True) -> torch.Tensor:
     """In place on qkv [T, (nh + 2 nkv) hd]: per-head RMSNorm (if weights) and rotary encoding of q
     and k; k and v of every token are stored at ``slots[t]`` of the caches
-    [pages, nkv, page_size, hd] (unless ``write_kv`` is false or the slot is negative)."""
+    [pages, nkv, page_size, hd] (unless ``write_kv`` is false or the slot is negative).  ``qkv`` may
+    be a split output of the matrix product: its tensor is whole afterwards where this kernel wrote
+    (the query heads)."""
+    qkv, partial, tiles, mpad = _split(qkv)
     _need(qkv, "qkv")
     T = qkv.shape[0]
     if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
@@ -162,25 +186,30 @@ def qk_norm_rope_kv(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[
     _check(lib.tb_qk_norm_rope_kv(_stream(), _ptr(qkv), _ptr(positions), _ptr(slots), _ptr(q_weight), _ptr(k_weight),
                                   _ptr(cos_sin), _ptr(k_cache), _ptr(v_cache), T, num_heads, num_kv_heads, head_dim,
                                   rotary_dim, page_size, ctypes.c_float(eps), int(bool(write_kv)), max_pos,
-                                  _code(qkv.dtype)), "qk_norm_rope_kv")
+                                  _code(qkv.dtype), partial, tiles, mpad), "qk_norm_rope_kv")
+    return qkv
 
 
-def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
-    """[T, 2I] = [gate | up] -> silu(gate) * up, [T, I]."""
+def silu_mul(gate_up) -> torch.Tensor:
+    """[T, 2I] = [gate | up] -> silu(gate) * up, [T, I].  ``gate_up`` may be a split output."""
+    gate_up, partial, tiles, mpad = _split(gate_up)
     _need(gate_up, "gate_up")
     T, two_i = gate_up.shape
     if two_i % 2:
         raise KernelError("gate_up must have an even number of columns")
     out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     lib = load_library("tokenwise")
-    _check(lib.tb_silu_mul(_stream(), _ptr(gate_up), _ptr(out), T, two_i // 2, _code(gate_up.dtype)), "silu_mul")
+    _check(lib.tb_silu_mul(_stream(), _ptr(gate_up), _ptr(out), T, two_i // 2, _code(gate_up.dtype), partial, tiles, mpad),
+           "silu_mul")
     return out
 
 
 # ----------------------------------------------------------------------------- matrix products
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None, split_ok: bool = False):
     """x [M, K] @ weight [N, K]^T -> [M, N].  float32 operands run the CUDA-core kernel (true
-    32-bit arithmetic); bfloat16 operands run on the tensor cores with float32 accumulation."""
+    32-bit arithmetic); bfloat16 operands run on the tensor cores with float32 accumulation.
+    ``split_ok``: the result goes to a kernel that takes split input (add_rmsnorm, qk_norm_rope_kv,
+    silu_mul) or through ``as_tensor``; a split output may then come back instead of a tensor."""
     _need(x, "x")
     _need(weight, "weight")
     if x.dtype != weight.dtype:
@@ -199,7 +228,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         return out
     from tandem_b200.kernels import gemm_bf16
 
-    return gemm_bf16.linear(x, weight, out_dtype)
+    return gemm_bf16.linear(x, weight, out_dtype, split_ok)
 
 
 # ----------------------------------------------------------------------------- attention

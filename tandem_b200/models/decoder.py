@@ -16,6 +16,7 @@ import torch
 from tandem_b200.config.plan import ModelPlan, ParamSpec, WeightSource
 from tandem_b200.kernels import ops
 from tandem_b200.parts.base import StepContext
+from tandem_b200.parts.block import norm_input
 from tandem_b200.registry import part
 from tandem_b200.weights.loader import TensorSource, load_parameters
 
@@ -93,5 +94,5 @@ class Decoder:
             x = layer.block.forward(layer, x, residual, ctx)
         if logit_rows is not None and logit_rows.numel() == 0:  # the step only filled the cache
             return torch.empty((0, self.plan.head.vocab_size), dtype=torch.float32, device=self.device)
-        h = self.final_norm.forward(x, residual, self.dtype, rows=logit_rows)
+        h = self.final_norm.forward(norm_input(self.final_norm, x), residual, self.dtype, rows=logit_rows)
         return ops.linear(h, self.head, out_dtype=torch.float32)

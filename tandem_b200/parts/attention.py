@@ -76,8 +76,8 @@ class PagedAttention(Mixer):
         s = self.spec
         qkv = ops.linear(x, self.qkv)
         kv = ctx.kv()
-        ops.qk_norm_rope_kv(qkv, ctx.positions, kv.slots, self.q_norm, self.k_norm, self.position.cos_sin,
+        qkv = ops.qk_norm_rope_kv(qkv, ctx.positions, kv.slots, self.q_norm, self.k_norm, self.position.cos_sin,
                             kv.k, kv.v, s.num_heads, s.num_kv_heads, s.head_dim, self.position.rotary_dim,
                             kv.page_size, s.qk_norm_eps, write_kv=kv.writable)
         o = attention_kernels.paged_attention(qkv, kv, ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
-        return ops.linear(o, self.o)
+        return ops.linear(o, self.o, split_ok=True)  # for the block: a norm that takes split input, or ops.as_tensor

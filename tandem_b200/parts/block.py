@@ -11,12 +11,20 @@ from typing import Optional
 
 import torch
 
+from tandem_b200.kernels import ops
 from tandem_b200.parts.base import StepContext
 
 
+def norm_input(norm, x):
+    """What a mixer or a feed-forward returned, as the norm behind it can take it: the matrix
+    products of this package may return a split output, which norms that declare
+    ``takes_split_input`` add up themselves and all others get as a tensor."""
+    return x if getattr(norm, "takes_split_input", False) else ops.as_tensor(x)
+
+
 class PreNormBlock:
-    def forward(self, layer, x: Optional[torch.Tensor], residual: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        h = layer.mixer_norm.forward(x, residual, ctx.dtype)
+    def forward(self, layer, x, residual: torch.Tensor, ctx: StepContext):
+        h = layer.mixer_norm.forward(norm_input(layer.mixer_norm, x), residual, ctx.dtype)
         a = layer.mixer.forward(h, ctx)
-        h = layer.feed_forward_norm.forward(a, residual, ctx.dtype)
+        h = layer.feed_forward_norm.forward(norm_input(layer.feed_forward_norm, a), residual, ctx.dtype)
         return layer.feed_forward.forward(h, ctx)

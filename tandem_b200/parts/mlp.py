@@ -29,4 +29,5 @@ class GatedMLP(FeedForward):
         self.down = weights["down"]
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        return ops.linear(ops.silu_mul(ops.linear(x, self.gate_up)), self.down)
+        # the second product may come back as a split output: the block hands it to a norm that takes one
+        return ops.linear(ops.silu_mul(ops.linear(x, self.gate_up)), self.down, split_ok=True)

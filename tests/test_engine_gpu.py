@@ -255,7 +255,9 @@ def test_each_part_alone(dtype):
     wg, wu, wd = rnd(I, H, s=0.2), rnd(I, H, s=0.2), rnd(H, I, s=0.2)
     mlp = GatedMLP(GatedMLPSpec("gated_mlp", "m", H, I), {"gate_up": torch.cat([wg, wu]).cuda(), "down": wd.cuda()}, dtype, "cuda")
     wdict = {"m.gate_proj.weight": wg.float(), "m.up_proj.weight": wu.float(), "m.down_proj.weight": wd.float()}
-    torch.testing.assert_close(mlp.forward(x.cuda(), None).cpu().float(), plain.swiglu(x.float(), wdict, "m"), **tol)
+    from tandem_b200.kernels import ops  # a part may return the product's split output: as_tensor makes it whole
+
+    torch.testing.assert_close(ops.as_tensor(mlp.forward(x.cuda(), None)).cpu().float(), plain.swiglu(x.float(), wdict, "m"), **tol)
 
     # position table
     table = RotaryTable(PositionSpec("rope", rotary_dim=hd, theta=777.0, max_position=64), "cuda")
@@ -290,7 +292,7 @@ def test_each_part_alone(dtype):
         assert manager.grow("r", start + n)
         ctx, _ = ex.build_context([StepEntry("r", [0] * n, [])])
         ctx.run = 0
-        outs.append(mixer.forward(x[start: start + n].cuda(), ctx))
+        outs.append(ops.as_tensor(mixer.forward(x[start: start + n].cuda(), ctx)))
         manager.commit("r", n)
     d = dict(nh=nh, nkv=nkv, hd=hd, eps=1e-5)
     wdict = {"a.q_proj.weight": wq.float(), "a.k_proj.weight": wk.float(), "a.v_proj.weight": wv.float(),
@@ -498,3 +500,23 @@ def test_overlap_scheduling_changes_no_token(tiny_folder, dtype):
     # 10 pages of 8 tokens: five requests of up to 60 tokens do not fit, some are preempted
     small, eng = run(True, greedy, num_kv_blocks=10, max_num_seqs=5)
     assert small == sync and eng.scheduler.num_preemptions > 0
+
+
+def test_split_outputs_change_no_logit(tiny_folder, monkeypatch):
+    """With the skinny product forced and its split outputs on (the norms add the partial sums of
+    shared tiles on their way in), replay gives bit for bit the logits it gives with them off."""
+    from tandem_b200.engine.core import build_executor, load_model
+    from tandem_b200.engine.executor import StepEntry
+
+    folder = tiny_folder("B", 0.1)
+    tokens = random_tokens(91, 40, 1000)
+    monkeypatch.setenv("TANDEM_GEMM", "skinny")
+    logits = {}
+    for split in ("0", "1"):
+        monkeypatch.setenv("TANDEM_SPLIT_OUTPUT", split)
+        decoder, _ = load_model(folder, "bfloat16", "cuda:0")
+        ex = build_executor(decoder, 8, 16, 1.0, 4)
+        out = [ex.step([StepEntry("a", tokens[:9], [8]), StepEntry("b", tokens[20:22], [1])])]
+        out += [ex.step([StepEntry("a", [tokens[9 + i]], [0]), StepEntry("b", [tokens[22 + i]], [0])]) for i in range(6)]
+        logits[split] = torch.cat(out).cpu()
+    assert torch.equal(logits["0"], logits["1"])
