@@ -52,12 +52,17 @@ __device__ __forceinline__ const int* cache_table(const int* table, int* table_s
 }
 
 // The producer warp: fills stage after stage with keys [s0 + it*64, +64) of the request whose block
-// table is `table`, restricted to [kb, ke).  Lane i owns the i-th piece of a stage (a piece: the
-// rows of one page that fall into the stage): it looks the page up, the warp adds up the bytes,
-// lane 0 tells the barrier, and every lane issues its own copies.  With swizzled tiles and pages of
-// 8 keys or more a piece is copied in whole row groups (rows of a group that lie outside [kb, ke)
-// come along; the consumers mask them and clear their values), else row by row.  Pages that were
-// given back are not copied.
+// table is `table`, restricted to [kb, ke).  A piece is the rows of one page that fall into the
+// stage; with at most 16 pieces per stage (pages of 4 keys or more) lane i brings the keys of
+// piece i and lane 16 + i its values, else every lane brings both of its pieces, 32 pieces a
+// round.  With swizzled tiles and pages of 8 keys or more a piece is copied in whole row groups
+// (rows of a group that lie outside [kb, ke) come along; the consumers mask them and clear their
+// values), else row by row.  Pages that were given back are not copied.
+//
+// One warp's chain of dependent instructions is what bounds a kernel that waits for its stages,
+// so everything that does not need the stage itself (page lookup, addresses, byte counts) is done
+// *before* the wait for the stage to be free, stages that lie wholly inside [kb, ke) skip the
+// byte count's reduction, and all lanes wait on the barrier themselves (no broadcast).
 __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache, const int* table,
                                           int kvh, int nkv, int ps, int kb, int ke, int s0, int num_stages,
                                           int stages, __nv_bfloat16* stage_mem, uint64_t* full, uint64_t* empty,
@@ -65,6 +70,56 @@ __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __
   const int piece = ps % 64 == 0 ? 64 : ps % 32 == 0 ? 32 : ps % 16 == 0 ? 16 : ps;  // divides the page and the stage
   const int pieces = STAGE_KEYS / piece;
   const bool groups = SWZ && ps >= 8;
+  const bool whole_rows = groups || !SWZ;  // rows (or row groups) are contiguous in the page as in the stage
+  const int ps_shift = (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1;
+  const long long tile_elems = (long long)ps * HD, page_elems = tile_elems * nkv, head_off = (long long)kvh * tile_elems;
+  if (pieces <= 16) {
+    const int my_piece = lane & 15;
+    const __nv_bfloat16* cache = lane < 16 ? k_cache : v_cache;
+    const int side = lane < 16 ? 0 : STAGE_KEYS * HD;  // keys, then values
+    for (int it = 0; it < num_stages; ++it) {
+      const int slot = it % stages;
+      const int base = s0 + it * STAGE_KEYS;
+      const int kp = base + my_piece * piece;
+      const bool inside = base >= kb && base + STAGE_KEYS <= ke;  // every row of the stage is wanted
+      const bool mine = my_piece < pieces && kp < ke && kp + piece > kb;
+      int page = -1;
+      if (mine) {
+        page = table[ps_shift >= 0 ? kp >> ps_shift : kp / ps];
+        if (page < 0) atomicExch(status, STATUS_BAD_PAGE);
+      }
+      int lo = 0, hi = 0;
+      if (page >= 0) {
+        lo = max(0, kb - kp);
+        hi = min(piece, ke - kp);
+        if (groups) { lo &= ~7; hi = (hi + 7) & ~7; }
+      }
+      const int n = hi - lo;
+      uint32_t bytes = (uint32_t)STAGE_ELEMS * 2u;
+      if (!inside || __any_sync(0xffffffffu, mine && page < 0)) {
+        bytes = (uint32_t)n * HD * 2u;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, o);
+      }
+      const int r0 = (ps_shift >= 0 ? kp & (ps - 1) : kp % ps) + lo, i0 = kp - base + lo;  // first row in the page, in the stage
+      const long long src = (long long)page * page_elems + head_off;
+      __nv_bfloat16* dst = stage_mem + slot * STAGE_ELEMS + side;
+      if (it >= stages && !mbar_wait(empty + slot, ((it / stages) & 1) ^ 1, abort_flag, status)) break;
+      if (lane == 0) mbar_arrive_expect_tx(full + slot, bytes);
+      __syncwarp();
+      if (n > 0) {
+        if (whole_rows) {
+          bulk_load(dst + i0 * HD, cache + src + (long long)r0 * HD, n * HD * 2, full + slot);
+        } else {  // a page of fewer than 8 rows is one short group: [column block][rows][64]
+#pragma unroll
+          for (int b = 0; b < NB; ++b)
+            bulk_load(dst + (((i0 >> 3) * NB + b) * 8 + (i0 & 7)) * 64, cache + src + ((long long)b * ps + r0) * 64, n * 128, full + slot);
+        }
+      }
+    }
+    return;
+  }
+  // pages of one or two keys: 32 or 64 pieces a stage, every lane brings keys and values of its pieces
   bool alive = true;
   for (int it = 0; it < num_stages && alive; ++it) {
     const int slot = it % stages;
@@ -76,7 +131,7 @@ __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __
     __nv_bfloat16* ks = stage_mem + slot * STAGE_ELEMS;
     __nv_bfloat16* vs = ks + STAGE_KEYS * HD;
     const int base = s0 + it * STAGE_KEYS;
-    for (int p0 = 0; p0 < pieces; p0 += 32) {  // more than 32 pieces only for pages of one key
+    for (int p0 = 0; p0 < pieces; p0 += 32) {
       const int kp = base + (p0 + lane) * piece;
       const bool mine = (p0 + lane) < pieces && kp < ke && kp + piece > kb;
       int page = -1;
@@ -84,12 +139,10 @@ __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __
         page = table[kp / ps];
         if (page < 0) atomicExch(status, STATUS_BAD_PAGE);
       }
-      // rows [lo, hi) of the piece
       int lo = 0, hi = 0;
       if (page >= 0) {
         lo = max(0, kb - kp);
         hi = min(piece, ke - kp);
-        if (groups) { lo &= ~7; hi = (hi + 7) & ~7; }
       }
       const int n = hi - lo;
       uint32_t bytes = 2u * (uint32_t)n * HD * 2u;
@@ -102,12 +155,12 @@ __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __
       }
       __syncwarp();
       if (n > 0) {
-        const int r0 = kp % ps + lo, i0 = kp - base + lo;  // first row in the page and in the stage
+        const int r0 = kp % ps + lo, i0 = kp - base + lo;
         const long long tile = cache_tile(page, kvh, nkv, ps, HD);
-        if (groups || !SWZ) {  // rows (or row groups) are contiguous in the page as in the stage
+        if (!SWZ) {
           bulk_load(ks + i0 * HD, k_cache + tile + (long long)r0 * HD, n * HD * 2, full + slot);
           bulk_load(vs + i0 * HD, v_cache + tile + (long long)r0 * HD, n * HD * 2, full + slot);
-        } else {  // a page of fewer than 8 rows is one short group: [column block][rows][64]
+        } else {
 #pragma unroll
           for (int b = 0; b < NB; ++b) {
             const long long src = tile + ((long long)b * ps + r0) * 64;

@@ -9,9 +9,11 @@
 //            memory (a thread of its own, so that the scores of the next block never queue behind
 //            a wait for this block's probabilities);
 //   warps 0-7  a row of the MMA is a lane of tensor memory, and a warp reaches the 32 lanes of its
-//            number modulo 4: warps w and w + 4 share 32 query rows, each thread taking half of a
-//            row's keys (and half of its output columns); the two exchange their row maxima through
-//            shared memory.  They
+//            number modulo 4: warps 0-3 take the even blocks of keys and warps 4-7 the odd ones,
+//            one query row per thread, so that on every scheduler one warp exponentiates (the
+//            special-function unit is the narrow resource: 64 x 128 exp2 per block) while the
+//            other loads, masks and waits.  The two threads of a row hand the row's reference
+//            maximum to each other through shared memory, block by block.  They
 //            read a row of S with tcgen05.ld, mask it, keep the running maximum and sum in
 //            float32 (exp2), write the probabilities as bfloat16 into the swizzled shared-memory
 //            tile that is the A operand of the second MMA, and rescale O in tensor memory when
@@ -35,9 +37,9 @@ static_assert(HD == 64 || HD == 128, "the tcgen05 prefill kernel takes head size
 constexpr int BM = 128;            // rows of a query tile
 constexpr int BLOCK_KEYS = 64;     // keys per stage
 #ifndef TB_PF_STAGES
-#define TB_PF_STAGES (TB_HD == 128 ? 4 : 3)
+#define TB_PF_STAGES (TB_HD == 128 ? 4 : 6)
 #endif
-constexpr int STAGES = TB_PF_STAGES;  // head size 128: one block per SM; 64: two
+constexpr int STAGES = TB_PF_STAGES;  // one block per SM
 constexpr int SOFTMAX_WARPS = 8, PRODUCER_WARP = 8, SCORE_WARP = 9, OUTPUT_WARP = 10;
 constexpr int THREADS = 352;
 constexpr int TILE_INTS = 4;       // first token row, request, first position, number of tokens
@@ -119,7 +121,7 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------------------- kernel
-__global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_tc_kernel(const PrefillArgs a) {
+__global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const PrefillArgs a) {
   extern __shared__ unsigned char smem_unaligned[];
   pdl_wait();
   unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
@@ -132,12 +134,12 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
   uint64_t* s_empty = s_full + 2;         // [2]
   uint64_t* p_full = s_empty + 2;         // [2]
   uint64_t* pv_done = p_full + 2;         // [2]
-  uint64_t* pair_bar = pv_done + 2;       // [4]: the two warps that share 32 rows
+  uint64_t* pair_bar = pv_done + 2;       // [4]: the two warps that share 32 rows hand the reference maximum over
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* mx_s = reinterpret_cast<float*>(const_cast<int*>(abort_flag) + 1);  // [2 blocks][2 halves][128 rows]
-  float* l_s = mx_s + 4 * BM;                                                // [2 halves][128 rows]
-  int* table_s = reinterpret_cast<int*>(l_s + 2 * BM);
+  float* m_s = reinterpret_cast<float*>(const_cast<int*>(abort_flag) + 1);  // [2 blocks][128 rows] reference maxima
+  float* l_s = m_s + 4 * BM;                                                // [2 groups][128 rows] sums, then [2][128] their references
+  int* table_s = reinterpret_cast<int*>(l_s + 4 * BM);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int* tile = a.tiles + (size_t)blockIdx.x * TILE_INTS;
@@ -150,10 +152,10 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(s_full + b, 1); mbar_init(s_empty + b, SOFTMAX_WARPS);
-      mbar_init(p_full + b, SOFTMAX_WARPS); mbar_init(pv_done + b, 1);
+      mbar_init(s_full + b, 1); mbar_init(s_empty + b, 4);
+      mbar_init(p_full + b, 4); mbar_init(pv_done + b, 1);
     }
-    for (int q = 0; q < 4; ++q) mbar_init(pair_bar + q, 2);
+    for (int q = 0; q < 4; ++q) mbar_init(pair_bar + q, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -230,94 +232,94 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
       }
     }
   } else if (warp < SOFTMAX_WARPS) {
-    // ------------------------------------------------------------------ softmax: half a row per thread
-    const int quarter = warp & 3, half = warp >> 2;
+    // ------------------------------------------------------------------ softmax: one row per thread, every other block
+    const int quarter = warp & 3, group = warp >> 2;
     const int row = quarter * 32 + lane;  // = lane of tensor memory
     const int tl = row / G;
     const bool live = tl < ntok;
     const int qpos = p0 + min(tl, ntok - 1);
     const int lo = W > 0 ? max(0, qpos - W + 1) : 0;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    constexpr int OC = HD / 2;            // output columns of this thread
-    const uint32_t my_o = tmem_o + lane_base + (uint32_t)(half * OC);
-    uint64_t* pair = pair_bar + quarter;
-    float m_ref = -INFINITY, l = 0.f;
+    uint64_t* pair = pair_bar + quarter;  // phase j completes when block j's reference maximum stands in m_s
+    // m_mine: the reference this thread's sum l is kept against (the one of its last block)
+    float m_mine = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < num_blocks && ok; ++j) {
-      const int base = s0 + j * BLOCK_KEYS, cbase = base + half * 32;
+    for (int j = group; j < num_blocks && ok; j += 2) {
+      const int base = s0 + j * BLOCK_KEYS;
       ok = mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_flag, a.status);
       if (!ok) break;
       tc_fence_after();
-      float s[32];
-      tmem_ld32(tmem_base + lane_base + (uint32_t)((j & 1) * BLOCK_KEYS + half * 32), s);
+      float s[64];
+      tmem_ld32_issue(tmem_base + lane_base + (uint32_t)((j & 1) * BLOCK_KEYS), s);
+      tmem_ld32_issue(tmem_base + lane_base + (uint32_t)((j & 1) * BLOCK_KEYS + 32), s + 32);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty + (j & 1));
-      if (cbase + 31 > qpos || cbase < lo) {  // a block at the causal or the window's edge
+      if (base + BLOCK_KEYS - 1 > qpos || base < lo) {  // a block at the causal or the window's edge
 #pragma unroll
-        for (int c = 0; c < 32; ++c)
-          if (cbase + c > qpos || cbase + c < lo) s[c] = -INFINITY;
+        for (int c = 0; c < 64; ++c)
+          if (base + c > qpos || base + c < lo) s[c] = -INFINITY;
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // the row's maximum over both halves
-      mx_s[((j & 1) * 2 + half) * BM + row] = mx;
+      for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;  // the scale is positive
+      // the row's reference after the block before this one, from the thread that had that block
+      float m_prev = -INFINITY;
+      if (j >= 1) {
+        ok = mbar_wait(pair, (j - 1) & 1, abort_flag, a.status);
+        if (!ok) break;
+        m_prev = m_s[((j - 1) & 1) * BM + row];
+      }
+      // move the reference only when it pays (any row of the warp: the tensor-memory instructions
+      // below are executed by whole warps)
+      const bool warp_need = __any_sync(0xffffffffu, mx > m_prev + RESCALE_AT);
+      const float m_new = warp_need ? fmaxf(m_prev, mx) : m_prev;
+      m_s[(j & 1) * BM + row] = m_new;
       __syncwarp();
       if (lane == 0) mbar_arrive(pair);
-      ok = mbar_wait(pair, j & 1, abort_flag, a.status);
-      if (!ok) break;
-      mx = fmaxf(mx, mx_s[((j & 1) * 2 + (half ^ 1)) * BM + row]) * a.scale_log2;  // the scale is positive
-      // move the reference maximum only when it pays (any row of the warp: the tensor-memory
-      // instructions below are executed by whole warps; both warps of a pair decide alike)
-      const bool need = mx > m_ref + RESCALE_AT;
-      const bool warp_need = __any_sync(0xffffffffu, need);
-      float corr = 1.f;
-      if (warp_need) {
-        const float m_new = fmaxf(m_ref, mx);
-        corr = m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_new);
-        m_ref = m_new;
-        l *= corr;
-      }
+      l *= m_mine == -INFINITY ? 0.f : exp2f(m_mine - m_new);  // every move since this thread's last block
+      m_mine = m_new;
       if (j >= 2) {  // this block's buffer of P is free once O += P V of the block before the last has completed
         ok = mbar_wait(pv_done + (j & 1), ((j - 2) >> 1) & 1, abort_flag, a.status);
         if (!ok) break;
       }
-      if (j >= 1 && warp_need) {  // O is touched only between two of the tensor cores' updates
+      if (j >= 1 && warp_need) {  // O is touched only between two of the tensor cores' updates; this move is this thread's
         ok = mbar_wait(pv_done + ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, a.status);
         if (!ok) break;
         tc_fence_after();
+        const float corr = m_prev == -INFINITY ? 0.f : exp2f(m_prev - m_new);
 #pragma unroll
-        for (int c0 = 0; c0 < OC; c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 32) {
           float o[32];
-          tmem_ld32(my_o + c0, o);
+          tmem_ld32(tmem_o + lane_base + c0, o);
 #pragma unroll
           for (int c = 0; c < 32; ++c) o[c] *= corr;
-          tmem_st32(my_o + c0, o);
+          tmem_st32(tmem_o + lane_base + c0, o);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+      const float neg_m = m_new == -INFINITY ? 0.f : -m_new;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c8 = 0; c8 < 4; ++c8) {  // four 16-byte chunks of the row of P
+      for (int c8 = 0; c8 < 8; ++c8) {  // eight 16-byte chunks of the row of P
         float p[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           p[c] = fast_exp2(fmaf(s[c8 * 8 + c], a.scale_log2, neg_m));
           sum4[c & 3] += p[c];
         }
-        *reinterpret_cast<uint4*>(p_s + (j & 1) * P_BYTES + row * 128 + (((half * 4 + c8) ^ (row & 7)) << 4)) =
+        *reinterpret_cast<uint4*>(p_s + (j & 1) * P_BYTES + row * 128 + ((c8 ^ (row & 7)) << 4)) =
             make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       if (base < kb || base + BLOCK_KEYS > ke) {
         // an edge block: value rows of keys outside [kb, ke) get zero weights, but must not hold NaN
-        // patterns (they were not copied, or came along with their row group): this warp clears its eighth of the stage's rows
+        // patterns (they were not copied, or came along with their row group): this warp clears its quarter
         unsigned char* vs = stage_mem + (size_t)(j % STAGES) * STAGE_BYTES + K_BYTES;
-        for (int i = lane; i < 8 * NB * 8; i += 32) {
-          const int r = warp * 8 + i / (NB * 8), bc = i % (NB * 8);
+        for (int i = lane; i < 16 * NB * 8; i += 32) {
+          const int r = quarter * 16 + i / (NB * 8), bc = i % (NB * 8);
           if (base + r < kb || base + r >= ke)
             *reinterpret_cast<uint4*>(vs + ((r >> 3) * NB + (bc >> 3)) * 1024 + (r & 7) * 128 + ((bc & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
@@ -328,22 +330,32 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
       if (lane == 0) mbar_arrive(p_full + (j & 1));
     }
     // ------------------------------------------------------------------ epilogue
-    if (ok) {  // the row's sum over both halves
-      l_s[half * BM + row] = l;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pair);
-      ok = mbar_wait(pair, num_blocks & 1, abort_flag, a.status);
-    }
-    if (ok) ok = mbar_wait(pv_done + ((num_blocks - 1) & 1), ((num_blocks - 1) >> 1) & 1, abort_flag, a.status);
+    // The last block's thread knows the final reference; both sums are brought to it and added.
+    // Each of the two threads of a row then writes half of the row's output columns.
+    constexpr int OC = HD / 2;
+    const int last_group = (num_blocks - 1) & 1;
     if (ok) {
+      l_s[group * BM + row] = l;
+      l_s[(2 + group) * BM + row] = m_mine;
+    }
+    tc_fence_before();
+    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");  // all softmax warps (every path reaches it)
+    if (ok && !*abort_flag) ok = mbar_wait(pv_done + ((num_blocks - 1) & 1), ((num_blocks - 1) >> 1) & 1, abort_flag, a.status);
+    if (ok && !*abort_flag) {
       tc_fence_after();
-      l += l_s[(half ^ 1) * BM + row];
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = a.out + (size_t)(t0 + tl) * a.nh * HD + (size_t)(kvh * G + row % G) * HD + half * OC;
+      const float m_final = l_s[(2 + last_group) * BM + row];
+      float total = 0.f;
+#pragma unroll
+      for (int gg = 0; gg < 2; ++gg) {
+        const float mg = l_s[(2 + gg) * BM + row];
+        total += mg == -INFINITY ? 0.f : l_s[gg * BM + row] * exp2f(mg - m_final);
+      }
+      const float inv = total > 0.f ? 1.f / total : 0.f;
+      __nv_bfloat16* dst = a.out + (size_t)(t0 + tl) * a.nh * HD + (size_t)(kvh * G + row % G) * HD + group * OC;
 #pragma unroll
       for (int c0 = 0; c0 < OC; c0 += 32) {
         float o[32];
-        tmem_ld32(my_o + c0, o);
+        tmem_ld32(tmem_o + lane_base + (uint32_t)(group * OC + c0), o);
         if (live) {
 #pragma unroll
           for (int c = 0; c < 32; c += 8)
@@ -363,7 +375,7 @@ __global__ void __launch_bounds__(THREADS, HD == 128 ? 1 : 2) attention_prefill_
   }
 }
 
-constexpr size_t smem_bytes() { return 1024 + Q_BYTES + 2 * P_BYTES + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 12) * 8 + 16 + 6 * BM * 4 + TABLE_CACHE * 4; }
+constexpr size_t smem_bytes() { return 1024 + Q_BYTES + 2 * P_BYTES + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 12) * 8 + 16 + 8 * BM * 4 + TABLE_CACHE * 4; }
 
 }  // namespace tb
 
