@@ -7,7 +7,11 @@
 //            buffers in tensor memory;
 //   warp 10  issues O += P V (M = 128, N = head size) into the output accumulator, also in tensor
 //            memory (a thread of its own, so that the scores of the next block never queue behind
-//            a wait for this block's probabilities);
+//            a wait for this block's probabilities).
+//            The A operands of both products live in tensor memory too: the query tile (stored
+//            there once, by the threads that own its rows) and the probabilities (two buffers).
+//            Shared memory then carries only what it must, the keys and values: with Q and P in
+//            shared memory its bandwidth (128 bytes a cycle) was what bounded the kernel;
 //   warps 0-7  a row of the MMA is a lane of tensor memory, and a warp reaches the 32 lanes of its
 //            number modulo 4: warps 0-3 take the even blocks of keys and warps 4-7 the odd ones,
 //            one query row per thread, so that on every scheduler one warp exponentiates (the
@@ -15,8 +19,8 @@
 //            other loads, masks and waits.  The two threads of a row hand the row's reference
 //            maximum to each other through shared memory, block by block.  They
 //            read a row of S with tcgen05.ld, mask it, keep the running maximum and sum in
-//            float32 (exp2), write the probabilities as bfloat16 into the swizzled shared-memory
-//            tile that is the A operand of the second MMA, and rescale O in tensor memory when
+//            float32 (exp2), write the probabilities as bfloat16 pairs into tensor memory
+//            (tcgen05.st), the A operand of the second MMA, and rescale O in tensor memory when
 //            the reference maximum has to move (only when a row's maximum grew by more than 2^8
 //            since the reference was set: the sum is kept against the same reference, so the
 //            result is exact);
@@ -37,15 +41,15 @@ static_assert(HD == 64 || HD == 128, "the tcgen05 prefill kernel takes head size
 constexpr int BM = 128;            // rows of a query tile
 constexpr int BLOCK_KEYS = 64;     // keys per stage
 #ifndef TB_PF_STAGES
-#define TB_PF_STAGES (TB_HD == 128 ? 4 : 6)
+#define TB_PF_STAGES (TB_HD == 128 ? 6 : 8)
 #endif
 constexpr int STAGES = TB_PF_STAGES;  // one block per SM
 constexpr int SOFTMAX_WARPS = 8, PRODUCER_WARP = 8, SCORE_WARP = 9, OUTPUT_WARP = 10;
 constexpr int THREADS = 352;
 constexpr int TILE_INTS = 4;       // first token row, request, first position, number of tokens
 constexpr int K_BYTES = BLOCK_KEYS * HD * 2, STAGE_BYTES = 2 * K_BYTES;
-constexpr int Q_BYTES = BM * HD * 2, P_BYTES = BM * BLOCK_KEYS * 2;
-constexpr int TMEM_COLS = 256;     // S0 at 0, S1 at 64, O at 128
+constexpr int TMEM_COLS = 512;     // S0 at 0, S1 at 64, O at 128, P0 at 256, P1 at 288, Q at 320 (bfloat16 pairs per column)
+constexpr int TMEM_O = 128, TMEM_P = 256, TMEM_Q = 320;
 constexpr float RESCALE_AT = 8.f;  // move a row's reference maximum when it has grown by 2^8
 
 struct PrefillArgs {
@@ -79,6 +83,12 @@ __device__ __forceinline__ void umma(uint32_t d, uint64_t a, uint64_t b, uint32_
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {  // A in tensor memory
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -103,6 +113,16 @@ __device__ __forceinline__ float fast_exp2(float x) {  // 2^x, -inf -> 0
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ void tmem_st32_words(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};" ::"r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+      "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+      "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+      "r"(v[30]), "r"(v[31]), "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
@@ -125,9 +145,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
   extern __shared__ unsigned char smem_unaligned[];
   pdl_wait();
   unsigned char* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
-  unsigned char* q_s = smem;                       // [NB][128 rows][128 bytes]
-  unsigned char* p_s = q_s + Q_BYTES;              // [2][128 rows][128 bytes]
-  unsigned char* stage_mem = p_s + 2 * P_BYTES;    // [STAGES][K | V]
+  unsigned char* stage_mem = smem;                 // [STAGES][K | V]
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(stage_mem + STAGES * STAGE_BYTES);
   uint64_t* kv_empty = kv_full + STAGES;
   uint64_t* s_full = kv_empty + STAGES;   // [2]
@@ -135,7 +153,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
   uint64_t* p_full = s_empty + 2;         // [2]
   uint64_t* pv_done = p_full + 2;         // [2]
   uint64_t* pair_bar = pv_done + 2;       // [4]: the two warps that share 32 rows hand the reference maximum over
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 4);
+  uint64_t* q_full = pair_bar + 4;        // the query tile stands in tensor memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* m_s = reinterpret_cast<float*>(const_cast<int*>(abort_flag) + 1);  // [2 blocks][128 rows] reference maxima
   float* l_s = m_s + 4 * BM;                                                // [2 groups][128 rows] sums, then [2][128] their references
@@ -156,6 +175,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
       mbar_init(p_full + b, 4); mbar_init(pv_done + b, 1);
     }
     for (int q = 0; q < 4; ++q) mbar_init(pair_bar + q, 1);
+    mbar_init(q_full, 4);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -164,22 +184,12 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // the query tile, row = token * G + head of the group, in the swizzled K-major layout of an A operand
-  for (int i = tid; i < BM * (HD / 8); i += THREADS) {
-    const int row = i / (HD / 8), c = i % (HD / 8);
-    const int tl = row / G, g = row % G;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (tl < ntok)
-      v = *reinterpret_cast<const uint4*>(a.q + (size_t)(t0 + tl) * a.q_stride + (size_t)(kvh * G + g) * HD + c * 8);
-    *reinterpret_cast<uint4*>(q_s + (c >> 3) * (BM * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = v;
-  }
   {  // the request's page numbers for this tile's keys
     const int* table = a.block_table + (size_t)req * a.table_stride;
     const int first = s0 / ps, count = (ke + ps - 1) / ps - first;
     if (count <= TABLE_CACHE)
       for (int i = tid; i < count; i += THREADS) table_s[i] = table[first + i];
   }
-  fence_proxy_async();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -187,7 +197,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
   // waits for this grid to end, so every block of this grid must have its own columns first.
   pdl_launch_dependents();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 128;
+  const uint32_t tmem_o = tmem_base + TMEM_O;
 
   if (warp == PRODUCER_WARP) {
     const int* table = a.block_table + (size_t)req * a.table_stride;
@@ -198,7 +208,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     // ------------------------------------------------------------------ S_j = Q K_j^T
     if (lane == 0) {
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_KEYS >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      for (int j = 0; j < num_blocks; ++j) {
+      bool ok = mbar_wait(q_full, 0, abort_flag, a.status);
+      for (int j = 0; j < num_blocks && ok; ++j) {
         const int slot = j % STAGES;
         if (!mbar_wait(kv_full + slot, (j / STAGES) & 1, abort_flag, a.status)) break;
         if (j >= 2 && !mbar_wait(s_empty + (j & 1), ((j >> 1) & 1) ^ 1, abort_flag, a.status)) break;
@@ -208,8 +219,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
         for (int b = 0; b < NB; ++b)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma(tmem_base + (uint32_t)((j & 1) * BLOCK_KEYS), desc_k_major(q_s + b * (BM * 128), 1024) + 2 * k,
-                 desc_k_major(ks + b * 1024, NB * 1024) + 2 * k, idesc_s, (b | k) ? 1u : 0u);
+            umma_ts(tmem_base + (uint32_t)((j & 1) * BLOCK_KEYS), tmem_base + (uint32_t)(TMEM_Q + (b * 4 + k) * 8),  // 16 elements: 8 columns
+                    desc_k_major(ks + b * 1024, NB * 1024) + 2 * k, idesc_s, (b | k) ? 1u : 0u);
         umma_commit(s_full + (j & 1));
       }
     }
@@ -224,9 +235,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
         tc_fence_after();
         const unsigned char* vs = stage_mem + (size_t)slot * STAGE_BYTES + K_BYTES;
 #pragma unroll
-        for (int k = 0; k < BLOCK_KEYS / 16; ++k)  // 16 keys: 32 bytes along a row of P, two row groups down V
-          umma(tmem_o, desc_k_major(p_s + (i & 1) * P_BYTES, 1024) + 2 * k, desc_mn_major(vs + k * (2 * NB * 1024), 1024, NB * 1024),
-               idesc_o, (i | k) ? 1u : 0u);
+        for (int k = 0; k < BLOCK_KEYS / 16; ++k)  // 16 keys: 8 columns of P, two row groups down V
+          umma_ts(tmem_o, tmem_base + (uint32_t)(TMEM_P + (i & 1) * 32 + k * 8), desc_mn_major(vs + k * (2 * NB * 1024), 1024, NB * 1024),
+                  idesc_o, (i | k) ? 1u : 0u);
         umma_commit(kv_empty + slot);  // the scores of this stage completed before its probabilities were made
         umma_commit(pv_done + (i & 1));
       }
@@ -241,6 +252,23 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     const int lo = W > 0 ? max(0, qpos - W + 1) : 0;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     uint64_t* pair = pair_bar + quarter;  // phase j completes when block j's reference maximum stands in m_s
+    if (group == 0) {  // this thread's row of the query tile goes to tensor memory: two elements per column
+      const __nv_bfloat16* src = a.q + (size_t)(t0 + tl) * a.q_stride + (size_t)(kvh * G + row % G) * HD;
+#pragma unroll
+      for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+        uint32_t w[32];
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          const uint4 v = live ? *reinterpret_cast<const uint4*>(src + (c0 + c) * 2) : make_uint4(0, 0, 0, 0);
+          w[c] = v.x; w[c + 1] = v.y; w[c + 2] = v.z; w[c + 3] = v.w;
+        }
+        tmem_st32_words(tmem_base + lane_base + (uint32_t)(TMEM_Q + c0), w);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_full);
+    }
     // m_mine: the reference this thread's sum l is kept against (the one of its last block)
     float m_mine = -INFINITY, l = 0.f;
     bool ok = true;
@@ -302,17 +330,15 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
       }
       const float neg_m = m_new == -INFINITY ? 0.f : -m_new;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pw[32];  // the row of P, two probabilities per word
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {  // eight 16-byte chunks of the row of P
-        float p[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          p[c] = fast_exp2(fmaf(s[c8 * 8 + c], a.scale_log2, neg_m));
-          sum4[c & 3] += p[c];
-        }
-        *reinterpret_cast<uint4*>(p_s + (j & 1) * P_BYTES + row * 128 + ((c8 ^ (row & 7)) << 4)) =
-            make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
+      for (int c = 0; c < 64; c += 2) {
+        const float p0 = fast_exp2(fmaf(s[c], a.scale_log2, neg_m)), p1 = fast_exp2(fmaf(s[c + 1], a.scale_log2, neg_m));
+        sum4[c & 3] += p0;
+        sum4[(c + 1) & 3] += p1;
+        pw[c >> 1] = pack_bf16(p0, p1);
       }
+      tmem_st32_words(tmem_base + lane_base + (uint32_t)(TMEM_P + (j & 1) * 32), pw);
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       if (base < kb || base + BLOCK_KEYS > ke) {
         // an edge block: value rows of keys outside [kb, ke) get zero weights, but must not hold NaN
@@ -323,8 +349,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
           if (base + r < kb || base + r >= ke)
             *reinterpret_cast<uint4*>(vs + ((r >> 3) * NB + (bc >> 3)) * 1024 + (r & 7) * 128 + ((bc & 7) << 4)) = make_uint4(0, 0, 0, 0);
         }
+        fence_proxy_async();  // the cleared rows are read by the tensor cores through the async proxy
       }
-      fence_proxy_async();  // P (and the cleared rows) are read by the tensor cores through the async proxy
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + (j & 1));
@@ -375,7 +402,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
   }
 }
 
-constexpr size_t smem_bytes() { return 1024 + Q_BYTES + 2 * P_BYTES + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 12) * 8 + 16 + 8 * BM * 4 + TABLE_CACHE * 4; }
+constexpr size_t smem_bytes() { return 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 13) * 8 + 16 + 8 * BM * 4 + TABLE_CACHE * 4; }
 
 }  // namespace tb
 
