@@ -62,11 +62,12 @@ __device__ __forceinline__ const int* cache_table(const int* table, int* table_s
 // One warp's chain of dependent instructions is what bounds a kernel that waits for its stages,
 // so everything that does not need the stage itself (page lookup, addresses, byte counts) is done
 // *before* the wait for the stage to be free, stages that lie wholly inside [kb, ke) skip the
-// byte count's reduction, and all lanes wait on the barrier themselves (no broadcast).
+// byte count's reduction, and all lanes wait on the barrier themselves (no broadcast).  Two warps
+// may share the work: each takes the stages first, first + step, ...
 __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache, const int* table,
                                           int kvh, int nkv, int ps, int kb, int ke, int s0, int num_stages,
                                           int stages, __nv_bfloat16* stage_mem, uint64_t* full, uint64_t* empty,
-                                          volatile int* abort_flag, int* status, int lane) {
+                                          volatile int* abort_flag, int* status, int lane, int first = 0, int step = 1) {
   const int piece = ps % 64 == 0 ? 64 : ps % 32 == 0 ? 32 : ps % 16 == 0 ? 16 : ps;  // divides the page and the stage
   const int pieces = STAGE_KEYS / piece;
   const bool groups = SWZ && ps >= 8;
@@ -77,7 +78,7 @@ __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __
     const int my_piece = lane & 15;
     const __nv_bfloat16* cache = lane < 16 ? k_cache : v_cache;
     const int side = lane < 16 ? 0 : STAGE_KEYS * HD;  // keys, then values
-    for (int it = 0; it < num_stages; ++it) {
+    for (int it = first; it < num_stages; it += step) {
       const int slot = it % stages;
       const int base = s0 + it * STAGE_KEYS;
       const int kp = base + my_piece * piece;
@@ -121,7 +122,7 @@ __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __
   }
   // pages of one or two keys: 32 or 64 pieces a stage, every lane brings keys and values of its pieces
   bool alive = true;
-  for (int it = 0; it < num_stages && alive; ++it) {
+  for (int it = first; it < num_stages && alive; it += step) {
     const int slot = it % stages;
     if (it >= stages) {
       if (lane == 0) alive = mbar_wait(empty + slot, ((it / stages) & 1) ^ 1, abort_flag, status);

@@ -24,7 +24,9 @@
 //            the reference maximum has to move (only when a row's maximum grew by more than 2^8
 //            since the reference was set: the sum is kept against the same reference, so the
 //            result is exact);
-//   warp 8   is the producer (bulk copies of cache tiles, completing on mbarriers).
+//   warps 8 and 11  are the producers (bulk copies of cache tiles, completing on mbarriers), one
+//            for the even stages and one for the odd ones: a stage costs a warp about a thousand
+//            cycles of dependent instructions, more than the tensor cores need for it.
 //
 // While the softmax warps work on block j, the tensor cores already compute the scores of block
 // j + 1.  The cache's own tile layout (cache_layout.cuh) is the 128-byte-swizzled layout that
@@ -44,8 +46,8 @@ constexpr int BLOCK_KEYS = 64;     // keys per stage
 #define TB_PF_STAGES (TB_HD == 128 ? 6 : 8)
 #endif
 constexpr int STAGES = TB_PF_STAGES;  // one block per SM
-constexpr int SOFTMAX_WARPS = 8, PRODUCER_WARP = 8, SCORE_WARP = 9, OUTPUT_WARP = 10;
-constexpr int THREADS = 352;
+constexpr int SOFTMAX_WARPS = 8, PRODUCER_WARP = 8, SCORE_WARP = 9, OUTPUT_WARP = 10, PRODUCER_WARP_2 = 11;
+constexpr int THREADS = 384;
 constexpr int TILE_INTS = 4;       // first token row, request, first position, number of tokens
 constexpr int K_BYTES = BLOCK_KEYS * HD * 2, STAGE_BYTES = 2 * K_BYTES;
 constexpr int TMEM_COLS = 512;     // S0 at 0, S1 at 64, O at 128, P0 at 256, P1 at 288, Q at 320 (bfloat16 pairs per column)
@@ -87,6 +89,24 @@ __device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b,
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Four MMAs along K (16 elements each) in one straight line: A moves on by 8 columns of tensor
+// memory, B's descriptor by BSTEP (in 16-byte units).  One thread issues all MMAs of the kernel,
+// and what it computes between two of them is what bounds their rate: measured 96 cycles per MMA
+// with the operands worked out in between, 46 (N = 64) and 64 (N = 128, the nominal rate) without.
+template <int BSTEP>
+__device__ __forceinline__ void umma_ts_x4(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred p0, p1;\n\t.reg .b32 a1, a2, a3;\n\t.reg .b64 b1, b2, b3;\n\t"
+      "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+      "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\t"
+      "add.s64 b1, %2, %5;\n\tadd.s64 b2, %2, %6;\n\tadd.s64 b3, %2, %7;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %3, p1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %3, p1;\n\t}" ::"r"(d),
+      "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate_first), "n"(BSTEP), "n"(2 * BSTEP), "n"(3 * BSTEP)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -199,11 +219,12 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + TMEM_O;
 
-  if (warp == PRODUCER_WARP) {
+  if (warp == PRODUCER_WARP || warp == PRODUCER_WARP_2) {
     const int* table = a.block_table + (size_t)req * a.table_stride;
     const int first = s0 / ps, count = (ke + ps - 1) / ps - first;
     stream_kv(a.k_cache, a.v_cache, count <= TABLE_CACHE ? table_s - first : table, kvh, a.nkv, ps, kb, ke, s0, num_blocks,
-              STAGES, reinterpret_cast<__nv_bfloat16*>(stage_mem), kv_full, kv_empty, abort_flag, a.status, lane);
+              STAGES, reinterpret_cast<__nv_bfloat16*>(stage_mem), kv_full, kv_empty, abort_flag, a.status, lane,
+              warp == PRODUCER_WARP ? 0 : 1, 2);
   } else if (warp == SCORE_WARP) {
     // ------------------------------------------------------------------ S_j = Q K_j^T
     if (lane == 0) {
@@ -215,12 +236,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
         if (j >= 2 && !mbar_wait(s_empty + (j & 1), ((j >> 1) & 1) ^ 1, abort_flag, a.status)) break;
         tc_fence_after();
         const unsigned char* ks = stage_mem + (size_t)slot * STAGE_BYTES;
+        const uint64_t kd = desc_k_major(ks, NB * 1024);
 #pragma unroll
-        for (int b = 0; b < NB; ++b)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_ts(tmem_base + (uint32_t)((j & 1) * BLOCK_KEYS), tmem_base + (uint32_t)(TMEM_Q + (b * 4 + k) * 8),  // 16 elements: 8 columns
-                    desc_k_major(ks + b * 1024, NB * 1024) + 2 * k, idesc_s, (b | k) ? 1u : 0u);
+        for (int b = 0; b < NB; ++b)  // 64 elements of the head: 32 columns of Q, the next column block of K (1,024 bytes on)
+          umma_ts_x4<2>(tmem_base + (uint32_t)((j & 1) * BLOCK_KEYS), tmem_base + (uint32_t)(TMEM_Q + b * 32), kd + b * 64, idesc_s, b ? 1u : 0u);
         umma_commit(s_full + (j & 1));
       }
     }
@@ -234,10 +253,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
         if (!mbar_wait(p_full + (i & 1), (i >> 1) & 1, abort_flag, a.status)) break;
         tc_fence_after();
         const unsigned char* vs = stage_mem + (size_t)slot * STAGE_BYTES + K_BYTES;
-#pragma unroll
-        for (int k = 0; k < BLOCK_KEYS / 16; ++k)  // 16 keys: 8 columns of P, two row groups down V
-          umma_ts(tmem_o, tmem_base + (uint32_t)(TMEM_P + (i & 1) * 32 + k * 8), desc_mn_major(vs + k * (2 * NB * 1024), 1024, NB * 1024),
-                  idesc_o, (i | k) ? 1u : 0u);
+        // 16 keys a step: 8 columns of P, two row groups (2 x NB x 1,024 bytes) down V
+        umma_ts_x4<NB * 128>(tmem_o, tmem_base + (uint32_t)(TMEM_P + (i & 1) * 32), desc_mn_major(vs, 1024, NB * 1024), idesc_o, i ? 1u : 0u);
         umma_commit(kv_empty + slot);  // the scores of this stage completed before its probabilities were made
         umma_commit(pv_done + (i & 1));
       }
