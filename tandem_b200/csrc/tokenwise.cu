@@ -70,6 +70,32 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
   float* res = residual + (size_t)src * H;
   const T* xr = x ? x + (size_t)src * H : nullptr;
   float ss = 0.f;
+  if (sizeof(T) == 2 && (H & 7) == 0 && H <= (int)blockDim.x * 8) {  // one turn: the sums stay in registers
+    const int i = threadIdx.x * 8;
+    float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
+    if (i < H) {
+      s0 = *reinterpret_cast<const float4*>(res + i);
+      s1 = *reinterpret_cast<const float4*>(res + i + 4);
+      if (xr) {
+        float v[8];
+        split_load8(reinterpret_cast<const __nv_bfloat16*>(xr), sv, first, src, i, v);
+        s0.x += v[0]; s0.y += v[1]; s0.z += v[2]; s0.w += v[3];
+        s1.x += v[4]; s1.y += v[5]; s1.z += v[6]; s1.w += v[7];
+        *reinterpret_cast<float4*>(res + i) = s0;
+        *reinterpret_cast<float4*>(res + i + 4) = s1;
+      }
+      ss = s0.x * s0.x + s0.y * s0.y + s0.z * s0.z + s0.w * s0.w + s1.x * s1.x + s1.y * s1.y + s1.z * s1.z + s1.w * s1.w;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    if (i < H) {
+      const float4 w0 = *reinterpret_cast<const float4*>(weight + i), w1 = *reinterpret_cast<const float4*>(weight + i + 4);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(y) + (size_t)r * H + i) =
+          make_uint4(pack2(s0.x * inv * w0.x, s0.y * inv * w0.y), pack2(s0.z * inv * w0.z, s0.w * inv * w0.w),
+                     pack2(s1.x * inv * w1.x, s1.y * inv * w1.y), pack2(s1.z * inv * w1.z, s1.w * inv * w1.w));
+    }
+    return;
+  }
   if (sizeof(T) == 2 && (H & 7) == 0) {  // eight elements per thread and turn: 16-byte loads and stores
     for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
       float4 s0 = *reinterpret_cast<const float4*>(res + i), s1 = *reinterpret_cast<const float4*>(res + i + 4);
@@ -228,6 +254,80 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
   }
 }
 
+// The same for bfloat16 when the whole head rotates (rd == hd) and hd is a power of two from 16 to
+// 256: a head takes hd / 8 lanes, each with four neighbouring elements of the lower half and the
+// four they pair with in the upper half (8-byte loads and stores), so a warp does 256 / hd heads at
+// a time; a block of four warps does `heads_per_block` heads of one token, and every lane loads its
+// eight angles once for all of them.
+__global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                                            const int* __restrict__ slots, const float* __restrict__ q_w,
+                                            const float* __restrict__ k_w, const float* __restrict__ cos_sin,
+                                            __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                            int nh, int nkv, int hd, int page_size, float eps, int write_kv, int max_pos,
+                                            int heads_per_block) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int heads = nh + 2 * nkv, half = hd >> 1;
+  const int lanes_per_head = hd >> 3, heads_per_warp = 32 / lanes_per_head;
+  const int sub = lane % lanes_per_head, j = sub * 4;  // elements j..j+3 and half+j..half+j+3
+  // the lanes of this lane's head: they take every branch below together, other heads of the warp may not
+  const unsigned head_lanes = (lanes_per_head == 32 ? 0xffffffffu : ((1u << lanes_per_head) - 1u)) << (lane - sub);
+  const int t = blockIdx.x, h_begin = blockIdx.y * heads_per_block, h_end = min(heads, h_begin + heads_per_block);
+  float wq[8], wk[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {  // norm weights are written by no kernel
+    wq[i] = q_w ? q_w[j + i] : 1.f; wq[4 + i] = q_w ? q_w[half + j + i] : 1.f;
+    wk[i] = k_w ? k_w[j + i] : 1.f; wk[4 + i] = k_w ? k_w[half + j + i] : 1.f;
+  }
+  pdl_wait();
+  int pos = positions[t];
+  pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);  // the host checks positions
+  const float4 c = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + j);
+  const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + j);
+  const int slot = slots ? slots[t] : -1;
+  __nv_bfloat16* row = qkv + (size_t)t * heads * hd;
+  for (int h = h_begin + warp * heads_per_warp + lane / lanes_per_head; h < h_end; h += 4 * heads_per_warp) {
+    const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+    if (!is_q && (slot < 0 || !write_kv)) continue;
+    __nv_bfloat16* x = row + (size_t)h * hd;
+    const uint2 lo_raw = *reinterpret_cast<const uint2*>(x + j), hi_raw = *reinterpret_cast<const uint2*>(x + half + j);
+    __nv_bfloat16* dst = x;
+    int at_lo = j, at_hi = half + j;
+    if (!is_q) {
+      const int kvh = is_k ? h - nh : h - nh - nkv, r = slot % page_size;
+      dst = (is_k ? k_cache : v_cache) + cache_tile(slot / page_size, kvh, nkv, page_size, hd);
+      at_lo = cache_offset<__nv_bfloat16>(r, j, page_size, hd);
+      at_hi = cache_offset<__nv_bfloat16>(r, half + j, page_size, hd);
+    }
+    if (!is_q && !is_k) {  // v: plain copy
+      *reinterpret_cast<uint2*>(dst + at_lo) = lo_raw;
+      *reinterpret_cast<uint2*>(dst + at_hi) = hi_raw;
+      continue;
+    }
+    const float2 l0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo_raw.x)),
+                 l1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo_raw.y)),
+                 h0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi_raw.x)),
+                 h1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi_raw.y));
+    float a[4] = {l0.x, l0.y, l1.x, l1.y}, b[4] = {h0.x, h0.y, h1.x, h1.y};
+    const float* w = is_q ? wq : wk;
+    if (is_q ? q_w != nullptr : k_w != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ss += a[i] * a[i] + b[i] * b[i];
+      for (int o = lanes_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(head_lanes, ss, o);
+      const float inv = rsqrtf(ss / (float)hd + eps);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = a[i] * inv * w[i]; b[i] = b[i] * inv * w[4 + i]; }
+    }
+    const float cc[4] = {c.x, c.y, c.z, c.w}, ssn[4] = {sn.x, sn.y, sn.z, sn.w};
+    float lo_out[4], hi_out[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { lo_out[i] = a[i] * cc[i] - b[i] * ssn[i]; hi_out[i] = b[i] * cc[i] + a[i] * ssn[i]; }
+    *reinterpret_cast<uint2*>(dst + at_lo) = make_uint2(pack2(lo_out[0], lo_out[1]), pack2(lo_out[2], lo_out[3]));
+    *reinterpret_cast<uint2*>(dst + at_hi) = make_uint2(pack2(hi_out[0], hi_out[1]), pack2(hi_out[2], hi_out[3]));
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]
 template <typename T>
@@ -247,7 +347,9 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
       uint32_t* r2 = reinterpret_cast<uint32_t*>(&r);
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        r2[j] = pack2(g[2 * j] / (1.f + expf(-g[2 * j])) * u[2 * j], g[2 * j + 1] / (1.f + expf(-g[2 * j + 1])) * u[2 * j + 1]);
+        // the result is rounded to bfloat16: the fast exponential and division are exact enough by far
+        r2[j] = pack2(__fdividef(g[2 * j], 1.f + __expf(-g[2 * j])) * u[2 * j],
+                      __fdividef(g[2 * j + 1], 1.f + __expf(-g[2 * j + 1])) * u[2 * j + 1]);
       *reinterpret_cast<uint4*>(out + e * 8) = r;
     }
     return;
@@ -296,6 +398,16 @@ int tb_qk_norm_rope_kv(void* stream, void* qkv, const int* positions, const int*
   if (rd < 0 || rd > hd || (rd & 1) || page_size <= 0) return TB_ERR_BAD_SIZE;
   if (partial && (dtype != TB_BF16 || (hd & 7))) return TB_ERR_BAD_SIZE;
   const tb::SplitView sv{partial, tiles, mpad};
+  const bool pow2 = hd >= 16 && hd <= 256 && (hd & (hd - 1)) == 0;
+  if (dtype == TB_BF16 && !partial && rd == hd && pow2 && T_tokens <= 65535 * 32) {
+    const int heads = nh + 2 * nkv, per_warp = 256 / hd;
+    // few tokens: spread a token's heads over several blocks; many: one block keeps its angles for 8 x more heads
+    const int heads_per_block = T_tokens >= 256 ? 8 * 4 * per_warp : 4 * per_warp;
+    dim3 grid(T_tokens, (heads + heads_per_block - 1) / heads_per_block);
+    return tb::launch(tb::qk_norm_rope_kv_bf16_kernel, grid, dim3(128), 0, stream, (__nv_bfloat16*)qkv, positions, slots, q_w, k_w,
+                      cos_sin, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, hd, page_size, eps, write_kv, max_pos,
+                      heads_per_block);
+  }
   const long long warps = (long long)T_tokens * (nh + 2 * nkv);
   const int blocks = (int)((warps + 3) / 4);
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::qk_norm_rope_kv_kernel<T>, dim3(blocks), dim3(128), 0, stream, (T*)qkv, positions, slots,

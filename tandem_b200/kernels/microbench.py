@@ -148,6 +148,15 @@ def bench_tokenwise(args) -> None:
     gu = torch.randn(T, 2 * I, device="cuda", dtype=bf)
     us = time_calls(lambda i: ops.silu_mul(gu), args.iters, args.graph)
     print(f"silu_mul    T={T} I={I}  {us:8.1f} us  {T * I * 6 / us / 1e3:7.0f} GB/s")
+    nh, nkv, hd, ps = 32, 8, 128, 16
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device="cuda", dtype=bf)
+    pages = -(-T // ps)
+    kc, vc = _cache(pages, nkv, ps, hd)
+    cs = torch.randn(max(T, 16), hd, device="cuda")
+    pos = torch.arange(T, dtype=torch.int32, device="cuda")
+    qw = torch.ones(hd, device="cuda")
+    us = time_calls(lambda i: ops.qk_norm_rope_kv(qkv, pos, pos, qw, qw, cs, kc, vc, nh, nkv, hd, hd, ps, 1e-6), args.iters, args.graph)
+    print(f"qk_norm_rope_kv T={T} heads={nh}/{nkv} hd={hd}  {us:8.1f} us  {T * (nh + 2 * nkv) * hd * 2 * 2 / us / 1e3:7.0f} GB/s")
     table = torch.randn(32768, H, device="cuda", dtype=bf)
     ids = torch.randint(0, 32768, (T,), device="cuda", dtype=torch.int32)
     us = time_calls(lambda i: ops.embedding(ids, table), args.iters, args.graph)

@@ -72,13 +72,15 @@ def _rope_reference(x, pos, theta, rd):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,rd,ps,norm", [(4, 2, 16, 16, 4, True), (6, 2, 32, 32, 8, True), (5, 5, 48, 48, 16, True),
-                                                 (8, 2, 128, 128, 16, True), (3, 1, 80, 32, 8, False), (2, 1, 256, 256, 16, True)])
-def test_qk_norm_rope_kv(ops, dtype, nh, nkv, hd, rd, ps, norm):
+                                                 (8, 2, 128, 128, 16, True), (3, 1, 80, 32, 8, False), (2, 1, 256, 256, 16, True),
+                                                 (5, 3, 64, 64, 8, True), (7, 1, 128, 128, 16, False), (9, 3, 32, 32, 4, True)])
+@pytest.mark.parametrize("T", [13, 300])
+def test_qk_norm_rope_kv(ops, dtype, nh, nkv, hd, rd, ps, norm, T):
     from tandem_b200.config.plan import PositionSpec
     from tandem_b200.parts.rope import RotaryTable
 
     g = torch.Generator().manual_seed(2)
-    T, pages, eps, theta = 13, 9, 1e-5, 12345.0
+    pages, eps, theta = -(-(T + 3) // ps) + 4, 1e-5, 12345.0
     qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype)
     pos = torch.randint(0, 300, (T,), generator=g, dtype=torch.int32)
     slots = torch.randperm(pages * ps, generator=g)[:T].to(torch.int32)
