@@ -79,18 +79,6 @@ __device__ __forceinline__ uint64_t desc_mn_major(const void* p, uint32_t block_
   return (uint64_t)((smem_u32(p) & 0x3FFFFu) >> 4) | ((uint64_t)(block_stride_bytes >> 4) << 16) |
          ((uint64_t)(group_stride_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
-__device__ __forceinline__ void umma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {  // A in tensor memory
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // Four MMAs along K (16 elements each) in one straight line: A moves on by 8 columns of tensor
 // memory, B's descriptor by BSTEP (in 16-byte units).  One thread issues all MMAs of the kernel,
 // and what it computes between two of them is what bounds their rate: measured 96 cycles per MMA

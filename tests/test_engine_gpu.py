@@ -520,3 +520,144 @@ def test_split_outputs_change_no_logit(tiny_folder, monkeypatch):
         out += [ex.step([StepEntry("a", [tokens[9 + i]], [0]), StepEntry("b", [tokens[22 + i]], [0])]) for i in range(6)]
         logits[split] = torch.cat(out).cpu()
     assert torch.equal(logits["0"], logits["1"])
+
+
+@dataclass(frozen=True)
+class RoutedSpec:
+    kind: str = "toy_routed"
+    prefix: str = ""
+    hidden_size: int = 0
+    experts: int = 3
+    width: int = 0
+
+
+class RoutedFeedForward:
+    """A toy feed-forward with routing, defined here, not in the package: every token goes to the
+    expert whose router logit (float32) is largest and is scaled by its softmax weight."""
+
+    @staticmethod
+    def params(spec):
+        from tandem_b200.config.plan import ParamSpec, WeightSource
+
+        out = {"router": ParamSpec((spec.experts, spec.hidden_size), (WeightSource(f"{spec.prefix}.router"),))}
+        for e in range(spec.experts):
+            out[f"up{e}"] = ParamSpec((spec.width, spec.hidden_size), (WeightSource(f"{spec.prefix}.e{e}.up"),))
+            out[f"down{e}"] = ParamSpec((spec.hidden_size, spec.width), (WeightSource(f"{spec.prefix}.e{e}.down"),))
+        return out
+
+    def __init__(self, spec, weights, dtype, device):
+        self.spec, self.w = spec, weights
+
+    def forward(self, x, ctx):
+        from tandem_b200.kernels import ops
+
+        logits = x.float() @ self.w["router"].float().T
+        gate, choice = torch.softmax(logits, -1).max(-1)
+        out = torch.zeros_like(x)
+        for e in range(self.spec.experts):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():  # the package's own matrix product on the expert's rows
+                h = torch.relu(ops.as_tensor(ops.linear(x[rows].contiguous(), self.w[f"up{e}"])))
+                out[rows] = (gate[rows, None] * ops.as_tensor(ops.linear(h, self.w[f"down{e}"])).float()).to(x.dtype)
+        return out
+
+
+class HalfRateRotary:
+    """A toy position encoding: the rotary table of the package's layout, with angles that advance
+    half as fast and only over the first half of the pairs (the rest stay unrotated)."""
+
+    def __init__(self, spec, device):
+        self.rotary_dim = spec.rotary_dim
+        half = spec.rotary_dim // 2
+        inv = 1.0 / (spec.theta ** (torch.arange(half, dtype=torch.float32) / half))
+        inv[half // 2:] = 0.0
+        ang = torch.outer(0.5 * torch.arange(spec.max_position, dtype=torch.float32), inv)
+        self.cos_sin = torch.cat([ang.cos(), ang.sin()], -1).contiguous().to(device)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(dtype):
+    """Registered from here, chosen layer by layer in a plan beside the package's own parts, built
+    and stepped without a change to the package; portions and a mixed batch give what whole
+    prompts give, and the whole prompt gives what plain torch gives."""
+    from tandem_b200.config.plan import AttentionSpec, PositionSpec
+    from tandem_b200.engine.core import build_executor
+    from tandem_b200.engine.executor import StepEntry
+    from tandem_b200.models.decoder import Decoder
+    from tandem_b200.registry import register_part
+    from tandem_b200.weights.loader import TensorDict
+
+    register_part("feed_forward", "toy_routed", RoutedFeedForward)
+    register_part("position", "toy_half_rate", HalfRateRotary)
+    H, V, hd, nh, nkv = 64, 90, 32, 4, 2
+    plan = _toy_plan(V, H, [
+        AttentionSpec("attention", prefix=f"l{i}.attn", hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                      scale=hd ** -0.5, qk_norm=False,
+                      position=PositionSpec("toy_half_rate" if i == 0 else "rope", rotary_dim=hd, theta=50.0, max_position=128))
+        for i in range(2)])
+    layers = list(plan.layers)
+    layers[1] = replace(layers[1], feed_forward=RoutedSpec(prefix="l1.moe", hidden_size=H, experts=3, width=48))
+    plan = replace(plan, layers=tuple(layers))
+
+    def extra(g):
+        out = {}
+        for i in range(2):
+            out.update({f"l{i}.attn.q_proj.weight": torch.randn(nh * hd, H, generator=g) * 0.2,
+                        f"l{i}.attn.k_proj.weight": torch.randn(nkv * hd, H, generator=g) * 0.2,
+                        f"l{i}.attn.v_proj.weight": torch.randn(nkv * hd, H, generator=g) * 0.2,
+                        f"l{i}.attn.o_proj.weight": torch.randn(H, nh * hd, generator=g) * 0.2})
+        out["l1.moe.router"] = torch.randn(3, H, generator=g)
+        for e in range(3):
+            out[f"l1.moe.e{e}.up"] = torch.randn(48, H, generator=g) * 0.2
+            out[f"l1.moe.e{e}.down"] = torch.randn(H, 48, generator=g) * 0.2
+        return out
+
+    weights = {k: v for k, v in _toy_weights(plan, extra, seed=3).items() if not k.startswith("l1.mlp.")}
+    decoder = Decoder(plan, TensorDict(dict(weights)), dtype, "cuda")
+    ex = build_executor(decoder, page_size=8, num_pages=24, max_requests=3)
+    a, b = random_tokens(5, 37, V), random_tokens(6, 21, V)
+    whole_a = ex.step([StepEntry("a", a, list(range(37)))], end=["a"])
+    whole_b = ex.step([StepEntry("b", b, list(range(21)))], end=["b"])
+    got_a, got_b, ia, ib = [], [], 0, 0
+    for na, nb in ((9, 2), (2, 7), (25, 1), (1, 11)):
+        out = ex.step([StepEntry("a2", a[ia: ia + na], list(range(na))), StepEntry("b2", b[ib: ib + nb], list(range(nb)))])
+        got_a.append(out[:na]), got_b.append(out[na:])
+        ia, ib = ia + na, ib + nb
+    ex.step([], end=["a2", "b2"])
+    assert ex.manager.all_free()
+    cut = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=0.15, rtol=0.05)
+    torch.testing.assert_close(torch.cat(got_a), whole_a, **cut)
+    torch.testing.assert_close(torch.cat(got_b), whole_b, **cut)
+    if dtype != torch.float32:
+        return  # in bfloat16 a token near a routing tie may take another expert than plain float64 does
+
+    # plain torch, whole prompt, float64
+    w = {k: v.double() for k, v in weights.items()}
+    T = len(a)
+    h = w["emb"][torch.tensor(a)]
+    pos = torch.arange(T, dtype=torch.float64)
+    for i in range(2):
+        x = plain.rms_norm(h, w[f"l{i}.n1"], 1e-5)
+        q = (x @ w[f"l{i}.attn.q_proj.weight"].T).view(T, nh, hd)
+        k = (x @ w[f"l{i}.attn.k_proj.weight"].T).view(T, nkv, hd)
+        v = (x @ w[f"l{i}.attn.v_proj.weight"].T).view(T, nkv, hd)
+        half = hd // 2
+        inv = 1.0 / (50.0 ** (torch.arange(half, dtype=torch.float64) / half))
+        if i == 0:
+            inv[half // 2:] = 0.0
+            ang = torch.outer(0.5 * pos, inv)
+        else:
+            ang = torch.outer(pos, inv)
+        cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+        q, k = plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin)
+        h = h + plain.attention_scores(q, k, v, None).reshape(T, -1) @ w[f"l{i}.attn.o_proj.weight"].T
+        x = plain.rms_norm(h, w[f"l{i}.n2"], 1e-5)
+        if i == 0:
+            h = h + plain.swiglu(x, w, "l0.mlp")
+        else:
+            gate, choice = torch.softmax(x @ w["l1.moe.router"].T, -1).max(-1)
+            y = torch.stack([gate[t] * (torch.relu(x[t] @ w[f"l1.moe.e{int(choice[t])}.up"].T) @ w[f"l1.moe.e{int(choice[t])}.down"].T)
+                             for t in range(T)])
+            h = h + y
+    want = plain.rms_norm(h, w["fn"], 1e-5) @ w["emb"].T
+    torch.testing.assert_close(whole_a.cpu().double(), want, atol=2e-4, rtol=2e-4)
