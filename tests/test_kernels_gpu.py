@@ -581,3 +581,50 @@ def test_a_split_output_cannot_be_read_after_the_next_product(ops):
     gemm_bf16.skinny(x, w, torch.bfloat16)
     with pytest.raises(ops.KernelError, match="reused its scratch"):
         ops.as_tensor(stale)
+
+
+# ----------------------------------------------------------------------------- long contexts
+@pytest.mark.parametrize("hd,ps,window", [(128, 16, None), (128, 16, 3000), (64, 8, None), (48, 16, None)])
+def test_attention_over_more_pages_than_the_kernels_cache(ops, hd, ps, window):
+    """A context of 9,000 keys on pages of 8 or 16 has more pages than a block keeps in shared
+    memory (512): the kernels then read the block table from global memory.  A portion of 150
+    tokens at the end (prefill kernels) and one decoded token (decode kernel, cut into items);
+    with a window, the pages in front of it are given back and hold NaN."""
+    from tandem_b200.kernels import attention as A
+    from tandem_b200.parts.base import KVView
+
+    nh, nkv = 4, 2
+    g = torch.Generator().manual_seed(50 + hd)
+    start, n = 8850, 150
+    seqs = [(start, n)]
+    qkv, kc, vc, table, seq_of, pos, Q, K, V = _paged_case(g, torch.bfloat16, seqs, nh, nkv, hd, ps)
+    assert table.shape[1] > 512
+    scale = hd ** -0.5
+    if window:
+        for j in range((start - window + 1) // ps):  # pages that lie before every query's window are given back
+            kc[table[0, j]] = float("nan")
+            vc[table[0, j]] = float("nan")
+            table[0, j] = -1
+    kv = KVView(phys(kc), phys(vc), dev(table), None, ps, True)
+    tiles = A.plan_prefill([(0, 0, start, n)], nh // nkv)
+    flat = torch.tensor([x for t in tiles for x in t], dtype=torch.int32)
+    want = _attention_reference(Q, K, V, seqs, scale, window)
+    for impl in ("tcgen05", "mma"):
+        if impl == "tcgen05" and not A.tcgen05_prefill_applies(hd, ps):
+            continue
+        import os
+        os.environ["TANDEM_PREFILL"] = impl
+        try:
+            out = A.paged_attention_prefill(dev(qkv), kv, dev(flat), nh, nkv, hd, window, scale)
+        finally:
+            os.environ.pop("TANDEM_PREFILL", None)
+        torch.testing.assert_close(out.cpu().double(), want, atol=2e-2, rtol=2e-2)
+    # the last token alone through the decode kernel, its keys cut into items
+    L = start + n
+    items = A.plan_decode([(0, 0, L - 1)], window, nkv)
+    assert len(items) > 1
+    flat = torch.tensor([x for it in items for x in it], dtype=torch.int32)
+    out = A.paged_attention_decode(dev(qkv[-1:].contiguous()), kv, dev(flat), dev(torch.tensor([len(items)], dtype=torch.int32)),
+                                   nh, nkv, hd, scale)
+    torch.testing.assert_close(out.cpu().double(), want[-1:], atol=2e-2, rtol=2e-2)
+    ops.check_status("cuda")
