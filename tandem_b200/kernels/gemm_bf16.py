@@ -133,6 +133,23 @@ def skinny(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, split:
     return SplitOutput(y, partial, tiles, 16 if M <= 16 else (32 if M <= 32 else 64), _serial[dev])
 
 
+def wide(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, gated: bool = False) -> torch.Tensor:
+    """The tcgen05 kernel for many rows (``csrc/gemm_wide.cu``): 128 x 256 output tiles, one
+    persistent block per SM.  ``gated``: the weight's rows are [gate | up]; returns
+    silu(x gate^T) * (x up^T), [M, rows / 2]."""
+    M, K = x.shape
+    N = weight.shape[0]
+    y = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+    lib = load_library("gemm_wide")
+    ops._check(lib.tb_gemm_wide(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(y), ops._ptr(ops.status_word(x.device)),
+                                M, N, K, int(out_dtype == torch.float32), int(gated), sm_count(x.device)), "gemm_wide")
+    return y
+
+
+def wide_applies(M: int, N: int, K: int) -> bool:
+    return M > 0 and K % 8 == 0 and N % 8 == 0
+
+
 def _measure(fn, x, weight, out_dtype, flush) -> float:
     """Median device time of fn over a few runs, the weights pushed out of L2 before each."""
     times = []
@@ -168,6 +185,45 @@ def skinny_preferred(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dty
             b = _measure(_library, x, weight, out_dtype, _flush[dev])
         _choice[key] = a <= b
     return _choice[key]
+
+
+def _row_bucket(M: int) -> int:
+    """Row counts are measured in classes: up to 128, 256, 512, ... (powers of two)."""
+    b = 128
+    while b < M:
+        b *= 2
+    return b
+
+
+def gated(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """silu(x gate^T) * (x up^T) for a weight whose rows are [gate | up]: [M, rows / 2] bfloat16.
+    Few rows: the product, then the activation kernel (which takes a split output).  Many rows: the
+    wide tcgen05 kernel with the activation in its epilogue, if that was measured to be faster than
+    the library product followed by the activation kernel for this class of shapes
+    (``TANDEM_GEMM=wide`` or ``=library`` forces one)."""
+    M, K = x.shape
+    N = weight.shape[0]
+    if M <= SKINNY_MAX_ROWS or not wide_applies(M, N, K) or N % 16:
+        return ops.silu_mul(linear(x, weight, torch.bfloat16, split_ok=True))
+    forced = os.environ.get("TANDEM_GEMM")
+    if forced in ("wide", "library", "skinny"):
+        use_wide = forced == "wide"
+    else:
+        key = ("gated", _row_bucket(M), N, K)
+        if key not in _choice:
+            if torch.cuda.is_current_stream_capturing():
+                return ops.silu_mul(_library(x, weight, torch.bfloat16))
+            dev = str(x.device)
+            with torch.inference_mode():
+                if dev not in _flush:
+                    _flush[dev] = torch.empty(192 << 20, dtype=torch.uint8, device=x.device)
+                a = _measure(lambda x_, w_, d_: wide(x_, w_, d_, gated=True), x, weight, torch.bfloat16, _flush[dev])
+                b = _measure(lambda x_, w_, d_: ops.silu_mul(_library(x_, w_, d_)), x, weight, torch.bfloat16, _flush[dev])
+            _choice[key] = a <= b
+        use_wide = _choice[key]
+    if use_wide:
+        return wide(x, weight, torch.bfloat16, gated=True)
+    return ops.silu_mul(_library(x, weight, torch.bfloat16))
 
 
 def choices() -> dict:

@@ -61,8 +61,15 @@ def bench_gemm(args) -> None:
     rows = []
     if gemm_bf16.skinny_applies(M, N, K) and args.impl in ("both", "skinny"):
         rows.append(("tcgen05 skinny kernel", time_calls(lambda i: gemm_bf16.skinny(x, ws[i % len(ws)], out), args.iters, args.graph)))
+    if args.impl in ("both", "wide") and M > gemm_bf16.SKINNY_MAX_ROWS and gemm_bf16.wide_applies(M, N, K):
+        rows.append(("tcgen05 wide kernel", time_calls(lambda i: gemm_bf16.wide(x, ws[i % len(ws)], out), args.iters, args.graph)))
     if args.impl in ("both", "library"):
         rows.append(("library (cuBLAS)", time_calls(lambda i: gemm_bf16._library(x, ws[i % len(ws)], out), args.iters, args.graph)))
+    if args.gated and M > gemm_bf16.SKINNY_MAX_ROWS:
+        from tandem_b200.kernels import ops
+
+        rows.append(("wide kernel, silu*up fused", time_calls(lambda i: gemm_bf16.wide(x, ws[i % len(ws)], out, gated=True), args.iters, args.graph)))
+        rows.append(("library + silu_mul kernel", time_calls(lambda i: ops.silu_mul(gemm_bf16._library(x, ws[i % len(ws)], out)), args.iters, args.graph)))
     for name, us in rows:
         print(f"gemm M={M} N={N} K={K}  {name:24s} {us:8.1f} us  {N * K * 2 / us / 1e3:7.0f} GB/s weights  "
               f"{2.0 * M * N * K / us / 1e6:7.1f} TFLOP/s")
@@ -177,7 +184,8 @@ def main(argv=None) -> None:
     g.add_argument("--n", type=int, default=24576)
     g.add_argument("--k", type=int, default=4096)
     g.add_argument("--f32-out", action="store_true")
-    g.add_argument("--impl", choices=["both", "skinny", "library"], default="both")
+    g.add_argument("--gated", action="store_true", help="also time the product with the SiLU * up epilogue (rows of W = [gate | up])")
+    g.add_argument("--impl", choices=["both", "skinny", "wide", "library"], default="both")
     g.set_defaults(fn=bench_gemm)
     ng = sub.add_parser("norm-gemm", parents=[common])
     ng.add_argument("--m", type=int, default=8)

@@ -231,6 +231,20 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     return gemm_bf16.linear(x, weight, out_dtype, split_ok)
 
 
+def gated_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """silu(x gate^T) * (x up^T) for a weight [2I, K] whose rows are [gate | up]: [M, I].  In
+    bfloat16 with many rows the activation may run in the epilogue of the product."""
+    if x.dtype == torch.float32:
+        return silu_mul(linear(x, weight))
+    _need(x, "x")
+    _need(weight, "weight", x.dtype)
+    if x.shape[1] != weight.shape[1] or weight.shape[0] % 2:
+        raise KernelError(f"x {tuple(x.shape)} and the gate/up weight {tuple(weight.shape)} do not fit")
+    from tandem_b200.kernels import gemm_bf16
+
+    return gemm_bf16.gated(x, weight)
+
+
 # ----------------------------------------------------------------------------- attention
 def paged_attention_simt(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                          seq_of_token: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int,

@@ -30,4 +30,4 @@ class GatedMLP(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         # the second product may come back as a split output: the block hands it to a norm that takes one
-        return ops.linear(ops.silu_mul(ops.linear(x, self.gate_up)), self.down, split_ok=True)
+        return ops.linear(ops.gated_linear(x, self.gate_up), self.down, split_ok=True)
