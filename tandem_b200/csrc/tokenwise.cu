@@ -155,6 +155,63 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
   }
 }
 
+// The same for many rows of bfloat16 whose width fits one turn of the block (H <= 8 * threads):
+// a block takes two neighbouring rows and issues the loads of both before it uses any, so twice
+// as many bytes are on their way per thread (the kernel is bound by memory latency: a row is
+// loaded, reduced, stored).
+__global__ void add_rmsnorm_rows2_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ residual,
+                                         const float* __restrict__ weight, __nv_bfloat16* __restrict__ y, int num_rows, int H,
+                                         float eps) {
+  __shared__ float scratch[2][33];
+  pdl_launch_dependents();
+  const int i = threadIdx.x * 8;
+  const bool on = i < H;
+  float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
+  if (on) { w0 = *reinterpret_cast<const float4*>(weight + i); w1 = *reinterpret_cast<const float4*>(weight + i + 4); }  // written by no kernel
+  pdl_wait();
+  const int r0 = blockIdx.x * 2;
+  float4 s[2][2];
+  uint4 xv[2];
+  bool have[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    have[k] = on && r0 + k < num_rows;
+    s[k][0] = s[k][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    xv[k] = make_uint4(0, 0, 0, 0);
+    if (have[k]) {
+      const float* res = residual + (size_t)(r0 + k) * H + i;
+      s[k][0] = *reinterpret_cast<const float4*>(res);
+      s[k][1] = *reinterpret_cast<const float4*>(res + 4);
+      if (x) xv[k] = *reinterpret_cast<const uint4*>(x + (size_t)(r0 + k) * H + i);
+    }
+  }
+  float ss[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    if (x && have[k]) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&xv[k]);
+      const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]), c = __bfloat1622float2(h[2]), d = __bfloat1622float2(h[3]);
+      s[k][0].x += a.x; s[k][0].y += a.y; s[k][0].z += b.x; s[k][0].w += b.y;
+      s[k][1].x += c.x; s[k][1].y += c.y; s[k][1].z += d.x; s[k][1].w += d.y;
+      float* res = residual + (size_t)(r0 + k) * H + i;
+      *reinterpret_cast<float4*>(res) = s[k][0];
+      *reinterpret_cast<float4*>(res + 4) = s[k][1];
+    }
+    ss[k] = s[k][0].x * s[k][0].x + s[k][0].y * s[k][0].y + s[k][0].z * s[k][0].z + s[k][0].w * s[k][0].w +
+            s[k][1].x * s[k][1].x + s[k][1].y * s[k][1].y + s[k][1].z * s[k][1].z + s[k][1].w * s[k][1].w;
+  }
+  ss[0] = block_sum(ss[0], scratch[0]);
+  ss[1] = block_sum(ss[1], scratch[1]);
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    if (!have[k]) continue;
+    const float inv = rsqrtf(ss[k] / (float)H + eps);
+    *reinterpret_cast<uint4*>(y + (size_t)(r0 + k) * H + i) =
+        make_uint4(pack2(s[k][0].x * inv * w0.x, s[k][0].y * inv * w0.y), pack2(s[k][0].z * inv * w0.z, s[k][0].w * inv * w0.w),
+                   pack2(s[k][1].x * inv * w1.x, s[k][1].y * inv * w1.y), pack2(s[k][1].z * inv * w1.z, s[k][1].w * inv * w1.w));
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // One warp per (token, head) of the fused projection qkv [T, (nh + 2 nkv) * hd]:
 //   q heads: optional RMSNorm over hd, rotary, written back in place;
@@ -255,10 +312,10 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
 }
 
 // The same for bfloat16 when the whole head rotates (rd == hd) and hd is a power of two from 16 to
-// 256: a head takes hd / 8 lanes, each with four neighbouring elements of the lower half and the
-// four they pair with in the upper half (8-byte loads and stores), so a warp does 256 / hd heads at
-// a time; a block of four warps does `heads_per_block` heads of one token, and every lane loads its
-// eight angles once for all of them.
+// 256: a head takes hd / 16 lanes, each with eight neighbouring elements of the lower half and the
+// eight they pair with in the upper half (16-byte loads and stores), so a warp does 512 / hd heads
+// at a time; a block of four warps does `heads_per_block` heads of one token, and every lane loads
+// its sixteen angles once for all of them.
 __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
                                             const int* __restrict__ slots, const float* __restrict__ q_w,
                                             const float* __restrict__ k_w, const float* __restrict__ cos_sin,
@@ -268,29 +325,34 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* __restrict__ qkv, con
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int heads = nh + 2 * nkv, half = hd >> 1;
-  const int lanes_per_head = hd >> 3, heads_per_warp = 32 / lanes_per_head;
-  const int sub = lane % lanes_per_head, j = sub * 4;  // elements j..j+3 and half+j..half+j+3
+  const int lanes_per_head = hd >> 4, heads_per_warp = 32 / lanes_per_head;
+  const int sub = lane % lanes_per_head, j = sub * 8;  // elements j..j+7 and half+j..half+j+7
   // the lanes of this lane's head: they take every branch below together, other heads of the warp may not
   const unsigned head_lanes = (lanes_per_head == 32 ? 0xffffffffu : ((1u << lanes_per_head) - 1u)) << (lane - sub);
   const int t = blockIdx.x, h_begin = blockIdx.y * heads_per_block, h_end = min(heads, h_begin + heads_per_block);
-  float wq[8], wk[8];
+  float wq[16], wk[16];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {  // norm weights are written by no kernel
-    wq[i] = q_w ? q_w[j + i] : 1.f; wq[4 + i] = q_w ? q_w[half + j + i] : 1.f;
-    wk[i] = k_w ? k_w[j + i] : 1.f; wk[4 + i] = k_w ? k_w[half + j + i] : 1.f;
+  for (int i = 0; i < 8; ++i) {  // norm weights are written by no kernel
+    wq[i] = q_w ? q_w[j + i] : 1.f; wq[8 + i] = q_w ? q_w[half + j + i] : 1.f;
+    wk[i] = k_w ? k_w[j + i] : 1.f; wk[8 + i] = k_w ? k_w[half + j + i] : 1.f;
   }
   pdl_wait();
   int pos = positions[t];
   pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);  // the host checks positions
-  const float4 c = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + j);
-  const float4 sn = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + j);
+  float cc[8], ssn[8];
+  {
+    const float4 c0 = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + j), c1 = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + j + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + j), s1 = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + j + 4);
+    cc[0] = c0.x; cc[1] = c0.y; cc[2] = c0.z; cc[3] = c0.w; cc[4] = c1.x; cc[5] = c1.y; cc[6] = c1.z; cc[7] = c1.w;
+    ssn[0] = s0.x; ssn[1] = s0.y; ssn[2] = s0.z; ssn[3] = s0.w; ssn[4] = s1.x; ssn[5] = s1.y; ssn[6] = s1.z; ssn[7] = s1.w;
+  }
   const int slot = slots ? slots[t] : -1;
   __nv_bfloat16* row = qkv + (size_t)t * heads * hd;
   for (int h = h_begin + warp * heads_per_warp + lane / lanes_per_head; h < h_end; h += 4 * heads_per_warp) {
     const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
     if (!is_q && (slot < 0 || !write_kv)) continue;
     __nv_bfloat16* x = row + (size_t)h * hd;
-    const uint2 lo_raw = *reinterpret_cast<const uint2*>(x + j), hi_raw = *reinterpret_cast<const uint2*>(x + half + j);
+    const uint4 lo_raw = *reinterpret_cast<const uint4*>(x + j), hi_raw = *reinterpret_cast<const uint4*>(x + half + j);
     __nv_bfloat16* dst = x;
     int at_lo = j, at_hi = half + j;
     if (!is_q) {
@@ -300,31 +362,38 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* __restrict__ qkv, con
       at_hi = cache_offset<__nv_bfloat16>(r, half + j, page_size, hd);
     }
     if (!is_q && !is_k) {  // v: plain copy
-      *reinterpret_cast<uint2*>(dst + at_lo) = lo_raw;
-      *reinterpret_cast<uint2*>(dst + at_hi) = hi_raw;
+      *reinterpret_cast<uint4*>(dst + at_lo) = lo_raw;
+      *reinterpret_cast<uint4*>(dst + at_hi) = hi_raw;
       continue;
     }
-    const float2 l0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo_raw.x)),
-                 l1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo_raw.y)),
-                 h0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi_raw.x)),
-                 h1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi_raw.y));
-    float a[4] = {l0.x, l0.y, l1.x, l1.y}, b[4] = {h0.x, h0.y, h1.x, h1.y};
+    float a[8], b[8];
+    {
+      const __nv_bfloat162* lp = reinterpret_cast<const __nv_bfloat162*>(&lo_raw);
+      const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&hi_raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 l2 = __bfloat1622float2(lp[i]), h2 = __bfloat1622float2(hp[i]);
+        a[2 * i] = l2.x; a[2 * i + 1] = l2.y; b[2 * i] = h2.x; b[2 * i + 1] = h2.y;
+      }
+    }
     const float* w = is_q ? wq : wk;
     if (is_q ? q_w != nullptr : k_w != nullptr) {
       float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) ss += a[i] * a[i] + b[i] * b[i];
+      for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
       for (int o = lanes_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(head_lanes, ss, o);
       const float inv = rsqrtf(ss / (float)hd + eps);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { a[i] = a[i] * inv * w[i]; b[i] = b[i] * inv * w[4 + i]; }
+      for (int i = 0; i < 8; ++i) { a[i] = a[i] * inv * w[i]; b[i] = b[i] * inv * w[8 + i]; }
     }
-    const float cc[4] = {c.x, c.y, c.z, c.w}, ssn[4] = {sn.x, sn.y, sn.z, sn.w};
-    float lo_out[4], hi_out[4];
+    uint32_t lo_out[4], hi_out[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { lo_out[i] = a[i] * cc[i] - b[i] * ssn[i]; hi_out[i] = b[i] * cc[i] + a[i] * ssn[i]; }
-    *reinterpret_cast<uint2*>(dst + at_lo) = make_uint2(pack2(lo_out[0], lo_out[1]), pack2(lo_out[2], lo_out[3]));
-    *reinterpret_cast<uint2*>(dst + at_hi) = make_uint2(pack2(hi_out[0], hi_out[1]), pack2(hi_out[2], hi_out[3]));
+    for (int i = 0; i < 4; ++i) {
+      lo_out[i] = pack2(a[2 * i] * cc[2 * i] - b[2 * i] * ssn[2 * i], a[2 * i + 1] * cc[2 * i + 1] - b[2 * i + 1] * ssn[2 * i + 1]);
+      hi_out[i] = pack2(b[2 * i] * cc[2 * i] + a[2 * i] * ssn[2 * i], b[2 * i + 1] * cc[2 * i + 1] + a[2 * i + 1] * ssn[2 * i + 1]);
+    }
+    *reinterpret_cast<uint4*>(dst + at_lo) = make_uint4(lo_out[0], lo_out[1], lo_out[2], lo_out[3]);
+    *reinterpret_cast<uint4*>(dst + at_hi) = make_uint4(hi_out[0], hi_out[1], hi_out[2], hi_out[3]);
   }
 }
 
@@ -334,7 +403,42 @@ template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I, const SplitView sv) {
   pdl_launch_dependents();
   pdl_wait();
-  if (sizeof(T) == 2 && (I & 7) == 0) {  // eight elements per thread: 16-byte loads and stores
+  if (sizeof(T) == 2 && (I & 7) == 0 && !sv.partial) {  // plain input: two groups of eight per thread and turn, four loads in flight
+    const long long groups = total / 8, stride = (long long)gridDim.x * blockDim.x;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < groups; e += 2 * stride) {
+      uint4 g4[2], u4[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const long long ek = e + k * stride;
+        g4[k] = u4[k] = make_uint4(0, 0, 0, 0);
+        if (ek < groups) {
+          const long long t = (ek * 8) / I;
+          const int i = (int)((ek * 8) % I);
+          const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(gu) + t * 2 * I;
+          g4[k] = *reinterpret_cast<const uint4*>(row + i);
+          u4[k] = *reinterpret_cast<const uint4*>(row + I + i);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const long long ek = e + k * stride;
+        if (ek >= groups) continue;
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4[k]);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4[k]);
+        uint4 r;
+        uint32_t* r2 = reinterpret_cast<uint32_t*>(&r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+          // the result is rounded to bfloat16: the fast exponential and division are exact enough by far
+          r2[j] = pack2(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
+        }
+        *reinterpret_cast<uint4*>(out + ek * 8) = r;
+      }
+    }
+    return;
+  }
+  if (sizeof(T) == 2 && (I & 7) == 0) {  // eight elements per thread: 16-byte loads and stores (split input)
     const long long groups = total / 8;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < groups; e += (long long)gridDim.x * blockDim.x) {
       const long long t = (e * 8) / I;
@@ -385,6 +489,9 @@ int tb_add_rmsnorm(void* stream, const void* x, float* residual, const float* we
   if (num_rows <= 0) return 0;
   if (partial && (dtype != TB_BF16 || (H & 7))) return TB_ERR_BAD_SIZE;
   const int threads = H >= 4096 ? 512 : 256;
+  if (dtype == TB_BF16 && !partial && !rows && num_rows >= 512 && (H & 7) == 0 && H <= threads * 8)
+    return tb::launch(tb::add_rmsnorm_rows2_kernel, dim3((num_rows + 1) / 2), dim3(threads), 0, stream, (const __nv_bfloat16*)x,
+                      residual, weight, (__nv_bfloat16*)y, num_rows, H, eps);
   const tb::SplitView sv{partial, tiles, mpad};
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::add_rmsnorm_kernel<T>, dim3(num_rows), dim3(threads), 0, stream, (const T*)x, residual,
                                       weight, (T*)y, rows, H, eps, sv));
@@ -400,7 +507,7 @@ int tb_qk_norm_rope_kv(void* stream, void* qkv, const int* positions, const int*
   const tb::SplitView sv{partial, tiles, mpad};
   const bool pow2 = hd >= 16 && hd <= 256 && (hd & (hd - 1)) == 0;
   if (dtype == TB_BF16 && !partial && rd == hd && pow2 && T_tokens <= 65535 * 32) {
-    const int heads = nh + 2 * nkv, per_warp = 256 / hd;
+    const int heads = nh + 2 * nkv, per_warp = 512 / hd;
     // few tokens: spread a token's heads over several blocks; many: one block keeps its angles for 8 x more heads
     const int heads_per_block = T_tokens >= 256 ? 8 * 4 * per_warp : 4 * per_warp;
     dim3 grid(T_tokens, (heads + heads_per_block - 1) / heads_per_block);

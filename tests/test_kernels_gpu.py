@@ -38,7 +38,8 @@ def test_embedding(ops, dtype, T, H, V):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,H,eps", [(1, 64, 1e-6), (5, 100, 1e-5), (19, 4096, 1e-6), (3, 5120, 3e-6), (2, 7, 1e-2)])
+@pytest.mark.parametrize("T,H,eps", [(1, 64, 1e-6), (5, 100, 1e-5), (19, 4096, 1e-6), (3, 5120, 3e-6), (2, 7, 1e-2),
+                                     (513, 4096, 1e-6), (600, 1000, 1e-5), (1025, 104, 1e-6)])
 def test_add_rmsnorm(ops, dtype, T, H, eps):
     g = torch.Generator().manual_seed(1)
     x = torch.randn(T, H, generator=g).to(dtype)
