@@ -80,17 +80,26 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
     *abort_flag = 0;
     *last_flag = 0;
     mbar_fence_init();
+    fence_proxy_async();
   }
-  const int* table = cache_table(a.block_table + (size_t)req * a.table_stride, table_s, s0, ke, ps, tid, THREADS);
+  __syncthreads();  // the barriers stand; nothing slow has been waited for yet
+  // The producer needs the page numbers only and starts to stream as soon as it has them; the
+  // consumers load the query tile meanwhile and meet among themselves.
+  const int* table = nullptr;
+  if (warp == WARPS) {
+    table = cache_table(a.block_table + (size_t)req * a.table_stride, table_s, s0, ke, ps, lane, 32);
+    __syncwarp();
+  }
   pdl_wait();
-  for (int i = tid; i < 16 * (HD / 8); i += THREADS) {  // the query tile, 16 bytes at a time
-    const int g = i / (HD / 8), c = i % (HD / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (g < rows) v = *reinterpret_cast<const uint4*>(a.q + (size_t)t * a.q_stride + (size_t)(kvh * G + row0 + g) * HD + c * 8);
-    *reinterpret_cast<uint4*>(q_s + g * QS + c * 8) = v;
+  if (warp < WARPS) {
+    for (int i = tid; i < 16 * (HD / 8); i += WARPS * 32) {  // the query tile, 16 bytes at a time
+      const int g = i / (HD / 8), c = i % (HD / 8);
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (g < rows) v = *reinterpret_cast<const uint4*>(a.q + (size_t)t * a.q_stride + (size_t)(kvh * G + row0 + g) * HD + c * 8);
+      *reinterpret_cast<uint4*>(q_s + g * QS + c * 8) = v;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory");  // the four consumer warps: every path reaches it
   }
-  fence_proxy_async();
-  __syncthreads();
 
   float o[HD / 8][4];
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
