@@ -15,6 +15,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
+import numpy as np
 import torch
 
 from tandem_b200.cache.manager import CacheManager, OutOfPages
@@ -63,10 +64,11 @@ class Executor:
             if e.pending is not None and (self.pending_tokens is None or not 0 <= e.pending < self.pending_tokens.numel()):
                 raise ValueError(f"request {e.request_id!r} takes its token from row {e.pending} of a step in flight "
                                  "that has no such row")
-            for tok in (e.tokens if e.pending is None else e.tokens[:-1]):
-                if not 0 <= int(tok) < self.vocab_size:
-                    raise ValueError(f"token id {tok} of request {e.request_id!r} is outside the vocabulary "
-                                     f"[0, {self.vocab_size})")
+            toks = np.asarray(e.tokens if e.pending is None else e.tokens[:-1], dtype=np.int64)
+            bad = (toks < 0) | (toks >= self.vocab_size)
+            if bad.any():
+                raise ValueError(f"token id {int(toks[bad][0])} of request {e.request_id!r} is outside the vocabulary "
+                                 f"[0, {self.vocab_size})")
             for w in e.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.request_id!r} wants logits at place {w} of {n} tokens")
@@ -78,22 +80,22 @@ class Executor:
         self.validate(entries)
         ids, positions, seq_of_token, cu, starts, lens, slots_host, rows = [], [], [], [0], [], [], [], []
         pending = []  # (token row, row of pending_tokens)
-        for b, e in enumerate(entries):
+        for b, e in enumerate(entries):  # per-token work in numpy: a prompt portion has thousands of tokens
             n = len(e.tokens)
             start = m.num_tokens(e.request_id)
             rows.extend(cu[-1] + w for w in e.want)
-            if e.pending is None:
-                ids.extend(int(t) for t in e.tokens)
-            else:
-                ids.extend(int(t) for t in e.tokens[:-1])
-                ids.append(0)
+            tok = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
+            if e.pending is not None:
+                tok[-1] = 0
                 pending.append((cu[-1] + n - 1, e.pending))
-            positions.extend(range(start, start + n))
-            seq_of_token.extend([b] * n)
+            ids.append(tok)
+            positions.append(np.arange(start, start + n, dtype=np.int32))
+            seq_of_token.append(np.full(n, b, dtype=np.int32))
             cu.append(cu[-1] + n)
             starts.append(start)
             lens.append(n)
             slots_host.append(m.slot(e.request_id))
+        ids, positions, seq_of_token = np.concatenate(ids), np.concatenate(positions), np.concatenate(seq_of_token)
         T, B = len(ids), len(entries)
         max_total = max((s + n for s, n in zip(starts, lens)), default=0)
         width = max(1, -(-max_total // ps))
@@ -118,9 +120,13 @@ class Executor:
                 if len(t) * ps < start + n:
                     raise OutOfPages(f"request {e.request_id!r} holds {len(t)} pages, {start + n} tokens need more")
                 table.extend(t[:width] + [-1] * (width - len(t[:width])))
-                slot_list.extend(m.slot_index(g, e.request_id, p) for p in range(start, start + n))
+                pos = np.arange(start, start + n)
+                pages = np.asarray(t, dtype=np.int64)[pos // ps]
+                if (pages < 0).any():  # the per-token form of CacheManager.slot_index
+                    raise RuntimeError(f"position {int(pos[pages < 0][0])} of {e.request_id!r} lies in a page that was given back")
+                slot_list.append((pages * ps + pos % ps).astype(np.int32))
             arrays[("table", g)] = table
-            arrays[("kvslots", g)] = slot_list
+            arrays[("kvslots", g)] = np.concatenate(slot_list) if slot_list else np.zeros(0, dtype=np.int32)
         extras: dict = {}
         for layer in self.mixers:  # integer arrays that mixers want on the device for this step
             layer.step_arrays(ctx, extras)
@@ -132,7 +138,7 @@ class Executor:
                            pin_memory=self.device.type == "cuda")
         offsets, off = {}, 0
         for k, v in arrays.items():  # every array starts on a 16-byte boundary
-            flat[off: off + sizes[k]] = torch.as_tensor(v, dtype=torch.int32).reshape(-1)
+            flat[off: off + sizes[k]] = torch.from_numpy(v) if isinstance(v, np.ndarray) else torch.as_tensor(v, dtype=torch.int32).reshape(-1)
             offsets[k] = off
             off += -(-sizes[k] // 4) * 4
         dev = flat[:off].to(self.device, non_blocking=True)
