@@ -661,3 +661,38 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(dtype):
             h = h + y
     want = plain.rms_norm(h, w["fn"], 1e-5) @ w["emb"].T
     torch.testing.assert_close(whole_a.cpu().double(), want, atol=2e-4, rtol=2e-4)
+
+
+def test_overlap_scheduling_under_random_workloads(tiny_folder):
+    """Random prompts, lengths, stop tokens, budgets, policies and pool sizes (some so small that
+    requests are preempted): the overlap loop returns what the synchronous loop returns, request
+    by request, and gives every page back."""
+    import random
+
+    from tandem_b200 import EngineConfig, LLMEngine, SamplingParams
+
+    folder = tiny_folder("A", 0.1)
+    rng = random.Random(7)
+    preempted = 0
+    for trial in range(6):
+        n = rng.randint(3, 9)
+        prompts = [random_tokens(1000 * trial + i, rng.randint(1, 45), 512) for i in range(n)]
+        sps = []
+        for i in range(n):
+            greedy = rng.random() < 0.5
+            sps.append(SamplingParams(max_tokens=rng.randint(1, 24), temperature=0.0 if greedy else 0.8,
+                                      top_k=-1 if greedy else 40, seed=trial * 100 + i, ignore_eos=True,
+                                      stop_token_ids=[rng.randrange(512) for _ in range(rng.randint(0, 40))]))
+        options = dict(block_size=rng.choice([4, 8, 16]), max_num_batched_tokens=rng.choice([8, 16, 64]),
+                       schedule_policy=rng.choice(["decode_first", "prefill_first"]), max_num_seqs=rng.choice([2, 4, 8]))
+        options["num_kv_blocks"] = max(-(-70 // options["block_size"]) + 1, rng.choice([6, 12, 40]))
+        results = []
+        for overlap in (False, True):
+            eng = LLMEngine(EngineConfig(model=folder, dtype="float32", overlap_schedule=overlap, **options))
+            outs = eng.generate(prompts, sps)
+            results.append([(o.output_token_ids, o.finish_reason) for o in outs])
+            eng.cache.check()
+            assert eng.cache.all_free() and eng.inflight is None and not eng.requests
+            preempted += eng.scheduler.num_preemptions
+        assert results[0] == results[1], (trial, options)
+    assert preempted > 0
