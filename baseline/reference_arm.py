@@ -1,7 +1,7 @@
 """The reference arm of bench.py: 12vivi/tandem itself, unmodified, from ``baseline/_ref``.
 
-``baseline/_ref`` is where ``pip install --target baseline/_ref /root/reference`` would put the
-reference.  Its build backend (hatchling) is not in the offline wheelhouse, so the install fails
+``baseline/_ref`` is where ``pip install --target baseline/_ref <reference checkout>`` would put
+the reference.  Its build backend (hatchling) is not in the offline wheelhouse, so the install fails
 here and the arm reports itself unavailable."""
 
 from __future__ import annotations

@@ -1,8 +1,8 @@
 """Writes tests/golden/tiny{A,B}.npz: logits of 12vivi/tandem's own model code on tiny random models.
 
-Run once on the CPU, with the reference checkout at $TANDEM_REFERENCE (default /root/reference):
+Run once on the CPU, with $TANDEM_REFERENCE naming a checkout of 12vivi/tandem:
 
-    python tests/golden/make_golden.py
+    TANDEM_REFERENCE=<checkout> python tests/golden/make_golden.py
 
 For each tiny configuration it writes a random-weights folder (seeded, so the test can write
 the same folder again), loads it with the reference's own config parser, model builder and
@@ -21,7 +21,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 sys.path.insert(0, os.path.dirname(HERE))
-sys.path.insert(0, os.path.join(os.environ.get("TANDEM_REFERENCE", "/root/reference"), "python"))
+sys.path.insert(0, os.path.join(os.environ["TANDEM_REFERENCE"], "python"))
 
 from conftest import TINY, random_tokens  # noqa: E402
 from tandem_b200.weights.random_init import write_random_model  # noqa: E402
