@@ -295,12 +295,15 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     return out
 
 
+_sample_scratch: dict = {}
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-           min_p: torch.Tensor, uniform: torch.Tensor, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+           min_p: torch.Tensor, uniform: torch.Tensor, any_top_k: bool = True, any_top_p: bool = True) -> torch.Tensor:
     """One token per row of logits [R, V] float32.  Per-row options as tensors [R]: temperature
     (< 1e-5: argmax), top_k (<= 0: off), top_p (>= 1: off), min_p (<= 0: off) and the uniform
-    number in [0, 1) that decides the draw.  ``scratch`` [R, V] float32 holds the filtered
-    probabilities while the kernel runs."""
+    number in [0, 1) that decides the draw.  ``any_top_k`` / ``any_top_p``: whether any row uses that
+    filter at all (its passes over the logits are skipped otherwise)."""
     _need(logits, "logits", torch.float32)
     R, V = logits.shape
     for t, n, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
@@ -309,13 +312,14 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
         _need(t, n, dt)
         if t.numel() != R:
             raise KernelError(f"{n} has {t.numel()} entries for {R} rows")
-    if scratch is None:
-        scratch = torch.empty((R, V), dtype=torch.float32, device=logits.device)
-    _need(scratch, "scratch", torch.float32)
-    if scratch.numel() < R * V:
-        raise KernelError("scratch is smaller than the logits")
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     lib = load_library("sampling")
+    per_row = lib.tb_sample_scratch_bytes()
+    key = str(logits.device)
+    scratch = _sample_scratch.get(key)
+    if scratch is None or scratch.numel() < R * per_row:  # histograms and partial sums of the rows, kept per device
+        scratch = _sample_scratch[key] = torch.empty(max(R, 64) * per_row, dtype=torch.uint8, device=logits.device)
+    scratch[: R * per_row].zero_()
     _check(lib.tb_sample(_stream(), _ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p),
-                         _ptr(uniform), _ptr(scratch), _ptr(out), R, V), "sample")
+                         _ptr(uniform), _ptr(scratch), _ptr(out), R, V, int(any_top_k), int(any_top_p)), "sample")
     return out

@@ -4,7 +4,7 @@ The rules are 12vivi/tandem's (python/tandem/layers/sampler.py:19-64): a request
 its temperature is below 1e-5; otherwise logits / temperature, keep the top_k largest, softmax,
 keep the smallest head of the sorted distribution whose preceding mass exceeds top_p nowhere,
 drop what is below min_p times the largest probability, renormalise, draw.  All of it runs in
-one CUDA kernel per step (``tandem_b200/csrc/sampling.cu``); the draw is the inverse CDF at a
+a few small CUDA kernels per step, many blocks per row (``tandem_b200/csrc/sampling.cu``); the draw is the inverse CDF at a
 uniform number that depends only on the request's seed and the index of the token, so it does
 not depend on the batch (``tandem_b200.sampling.rng``).
 """
@@ -42,4 +42,5 @@ def sample_on_device(logits: torch.Tensor, params: Sequence[SamplingParams], see
     ks = torch.tensor([p.top_k for p in params], dtype=torch.int32).pin_memory()
     f = host.to(dev, non_blocking=True)
     k = ks.to(dev, non_blocking=True)
-    return ops.sample(logits, f[0], k, f[1], f[2], f[3])
+    return ops.sample(logits, f[0], k, f[1], f[2], f[3], any_top_k=any(p.top_k > 0 for p in params),
+                      any_top_p=any(p.top_p < 1.0 for p in params))
