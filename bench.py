@@ -1,6 +1,7 @@
 """Decode and prefill throughput of the engine on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl reference]
+                    [--shape 8b|14b|32b] [--prompt-len P] [--new-tokens T] [--workload decode|mixed]
 
 The model has the layer sizes of Qwen3-8B with seeded random weights made on the device; prompts
 are seeded random token ids.  A step is one decode step of ``--batch`` requests whose prompts
@@ -10,6 +11,12 @@ same through ``LLMEngine.step()`` with host token ids in and sampled tokens out 
 Every decode step reads all weights (15 GB, far larger than the 126 MB L2), so nothing is served
 from L2 between iterations.  12vivi/tandem measures the same quantities with
 benchmarks/bench_offline.py:54-62 (random ids, greedy, ignore_eos).
+
+``--shape`` takes the layer sizes of Qwen3-14B or Qwen3-32B instead (the default line is the one
+of Qwen3-8B).  ``--workload mixed`` runs requests with prompts of random lengths (128 to 4,096
+tokens) through the scheduler with 128 greedy tokens each, prompt portions of up to 2,048 tokens
+beside decoded tokens, and prints its own line: generated and processed tokens per second of
+wall-clock time (benchmarks/bench_offline.py:64-86 of 12vivi/tandem).
 """
 
 from __future__ import annotations
@@ -30,6 +37,9 @@ sys.path.insert(0, ROOT)
 QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=4096,
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936,
                 rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
+QWEN3_14B = dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
+SHAPES = {"8b": ("Qwen3-8B shape", QWEN3_8B), "14b": ("Qwen3-14B shape", QWEN3_14B), "32b": ("Qwen3-32B shape", QWEN3_32B)}
 PROMPT, NEW_TOKENS, PAGE = 2048, 256, 16
 
 
@@ -83,24 +93,26 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_engine(layers: int, max_seqs: int, tokens_per_seq: int, cuda_graph: bool = True):
+def build_engine(shape: dict, layers: int, max_seqs: int, tokens_per_seq: int, cuda_graph: bool = True,
+                 policy: str = "prefill_first", pages: int = 0):
     from tandem_b200 import EngineConfig, LLMEngine
     from tandem_b200.engine.core import random_model
 
-    decoder, cfg = random_model(QWEN3_8B, seed=0, dtype="bfloat16", num_layers=layers)
-    pages = max_seqs * (-(-tokens_per_seq // PAGE)) + 8
+    max_len = max(4096, -(-tokens_per_seq // PAGE) * PAGE)
+    decoder, cfg = random_model(dict(shape, max_position_embeddings=max_len), seed=0, dtype="bfloat16", num_layers=layers)
+    pages = pages or max_seqs * (-(-tokens_per_seq // PAGE)) + 8
     eng = LLMEngine(EngineConfig(model="", dtype="bfloat16", block_size=PAGE, num_kv_blocks=pages, max_num_seqs=max_seqs,
-                                 max_num_batched_tokens=2048, max_model_len=4096, schedule_policy="prefill_first",
+                                 max_num_batched_tokens=2048, max_model_len=max_len, schedule_policy=policy,
                                  cuda_graph=cuda_graph, cuda_graph_max_bs=max_seqs),
                     decoder=decoder, model_config=cfg, load_tokenizer=False)
     return eng
 
 
-def prompts(batch: int, seed: int = 0) -> list:
+def prompts(batch: int, seed: int = 0, length: int = PROMPT) -> list:
     import torch
 
     g = torch.Generator().manual_seed(seed)
-    return [torch.randint(10, 100000, (PROMPT,), generator=g).tolist() for _ in range(batch)]
+    return [torch.randint(10, 100000, (length,), generator=g).tolist() for _ in range(batch)]
 
 
 def decode_bytes(eng, batch: int, context: int) -> float:
@@ -113,16 +125,16 @@ def decode_bytes(eng, batch: int, context: int) -> float:
     return weights + batch * context * kv_bytes_per_token(d)
 
 
-def measure_decode(eng, batch: int, steps: int, warmup: int) -> dict:
-    """Device time of ``steps`` decode steps of ``batch`` requests at context ~2,048, then the same
-    through LLMEngine.step()."""
+def measure_decode(eng, batch: int, steps: int, warmup: int, prompt_len: int = PROMPT, new_tokens: int = NEW_TOKENS) -> dict:
+    """Device time of ``steps`` decode steps of ``batch`` requests just behind their prompts of
+    ``prompt_len`` tokens, then the same through LLMEngine.step()."""
     import torch
 
     from tandem_b200 import SamplingParams
     from tandem_b200.kernels import ops
 
-    sp = SamplingParams(max_tokens=NEW_TOKENS, temperature=0.0, ignore_eos=True)
-    for p in prompts(batch, seed=batch):
+    sp = SamplingParams(max_tokens=new_tokens + steps + 2 * warmup + 16, temperature=0.0, ignore_eos=True)
+    for p in prompts(batch, seed=batch, length=prompt_len):
         eng.add_request(p, sp)
     while any(not r.is_decoding for r in eng.requests.values()) or eng.scheduler.waiting:
         eng.step()  # prefill, untimed
@@ -188,16 +200,75 @@ def measure_prefill(eng, warmup: int, reps: int = 3) -> dict:
     return dict(ms=ms, tok_s=PROMPT * 1000.0 / ms, flops=linear + attn)
 
 
+def measure_mixed(eng, num_requests: int, new_tokens: int, seed: int = 0) -> dict:
+    """Requests with prompts of random lengths through the scheduler: portions of prompts beside
+    decoded tokens, until every request has its ``new_tokens``.  Wall-clock time."""
+    import torch
+
+    from tandem_b200 import SamplingParams
+    from tandem_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(128, 4097, (num_requests,), generator=g).tolist()
+    sp = SamplingParams(max_tokens=new_tokens, temperature=0.0, ignore_eos=True)
+    result = {}
+    for rep in range(2):  # the first pass builds graphs and measures product dispatch; the second is timed
+        for n in lengths:
+            eng.add_request(torch.randint(10, 100000, (n,), generator=g).tolist(), sp)
+        torch.cuda.synchronize()
+        before, steps, t0 = ops.launches, 0, time.perf_counter()
+        while eng.has_unfinished_requests():
+            eng.step()
+            steps += 1
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        assert eng.cache.all_free()
+        result = dict(seconds=seconds, steps=steps, launches=ops.launches - before, prompt_tokens=sum(lengths),
+                      new_tokens=num_requests * new_tokens, preemptions=eng.scheduler.num_preemptions)
+    return result
+
+
+def main_mixed(args, name: str, shape: dict) -> int:
+    pk = peaks()
+    per_request = 4096 + args.new_tokens
+    eng = build_engine(shape, args.layers, args.batch, per_request, not args.no_cuda_graph, policy=args.policy)
+    sampler = ClockSampler()
+    sampler.start()
+    r = measure_mixed(eng, args.batch, args.new_tokens)
+    clocks = sampler.stop()
+    c = eng.model_config
+    out = {
+        "metric": f"generated tok/s, {args.batch} requests with prompts of 128-4,096 tokens, {name} (one B200)",
+        "value": round(r["new_tokens"] / r["seconds"], 1), "unit": "tok/s", "n_gpus": 1, "steps": r["steps"],
+        "processed_tok_s": round((r["new_tokens"] + r["prompt_tokens"]) / r["seconds"], 1), "seconds": round(r["seconds"], 3),
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02) and random token ids",
+        "config": {"model": name, "layers": c.num_hidden_layers, "layers_full": shape["num_hidden_layers"],
+                   "hidden": c.hidden_size, "q_heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
+                   "head_dim": c.head_dim, "intermediate": c.intermediate_size, "vocab": c.vocab_size,
+                   "requests": args.batch, "prompt_tokens": r["prompt_tokens"], "new_tokens": r["new_tokens"],
+                   "token_budget": 2048, "policy": args.policy, "page_size": PAGE, "preemptions": r["preemptions"],
+                   "peaks": pk["source"]},
+        "gpu_launches": r["launches"], "clocks": clocks,
+    }
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-cuda-graph", action="store_true")
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES))
+    ap.add_argument("--prompt-len", type=int, default=PROMPT, help="prompt length of the decode measurements")
+    ap.add_argument("--new-tokens", type=int, default=None)
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"])
+    ap.add_argument("--policy", default="prefill_first", choices=["prefill_first", "decode_first"])
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured (use --gpus 1)")
@@ -208,32 +279,41 @@ def main() -> int:
         print(json.dumps(run_reference(args)))
         return 0
     args.warmup = max(3, args.warmup)
-
-    import torch
+    name, shape = SHAPES[args.shape]
+    if args.layers is None:
+        args.layers = shape["num_hidden_layers"]
+    if args.workload == "mixed":
+        args.new_tokens = args.new_tokens or 128
+        if args.batch == 8:
+            args.batch = 32
+        return main_mixed(args, name, shape)
+    args.new_tokens = args.new_tokens or NEW_TOKENS
 
     pk = peaks()
     max_batch = max(args.batch, 1 if args.no_points else 64)
-    eng = build_engine(args.layers, max_batch, PROMPT + NEW_TOKENS + args.steps + 2 * args.warmup + 16, not args.no_cuda_graph)
+    eng = build_engine(shape, args.layers, max_batch,
+                       max(args.prompt_len, PROMPT) + args.new_tokens + args.steps + 2 * args.warmup + 32, not args.no_cuda_graph)
     sampler = ClockSampler()
     sampler.start()
-    main_pt = measure_decode(eng, args.batch, args.steps, args.warmup)
+    main_pt = measure_decode(eng, args.batch, args.steps, args.warmup, args.prompt_len, args.new_tokens)
     pre = measure_prefill(eng, args.warmup)
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            points[f"decode_b{b}"] = round(measure_decode(eng, b, args.steps, args.warmup)["tok_s"], 1)
+            points[f"decode_b{b}"] = round(measure_decode(eng, b, args.steps, args.warmup, args.prompt_len,
+                                                          args.new_tokens)["tok_s"], 1)
     clocks = sampler.stop()
     c = eng.model_config
     achieved = main_pt["bytes"] / (main_pt["ms"] * 1e-3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8, Qwen3-8B shape, 2,048-token prompts (one B200)",
+        "metric": f"decode tok/s at batch {args.batch}, {name}, {args.prompt_len:,}-token prompts (one B200)",
         "value": round(main_pt["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main_pt["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02) and random token ids",
-        "config": {"model": "Qwen3-8B shape", "layers": c.num_hidden_layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+        "config": {"model": name, "layers": c.num_hidden_layers, "layers_full": shape["num_hidden_layers"],
                    "hidden": c.hidden_size, "q_heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
                    "head_dim": c.head_dim, "intermediate": c.intermediate_size, "vocab": c.vocab_size,
-                   "global_batch": args.batch, "seq_len": main_pt["context"], "prompt_len": PROMPT, "page_size": PAGE,
+                   "global_batch": args.batch, "seq_len": main_pt["context"], "prompt_len": args.prompt_len, "page_size": PAGE,
                    "parallelism": "single GPU", "cuda_graph": eng.graphs is not None,
                    "l2": "inputs larger than L2: each step streams every weight", "peaks": pk["source"]},
         "e2e": {"value": round(main_pt["e2e_tok_s"], 1), "unit": "tok/s", "ms_per_step": round(main_pt["e2e_ms"], 4),
