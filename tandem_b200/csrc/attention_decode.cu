@@ -86,9 +86,18 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   // The producer needs the page numbers only and starts to stream as soon as it has them; the
   // consumers load the query tile meanwhile and meet among themselves.
   const int* table = nullptr;
+  int streamed = 0;
   if (warp == WARPS) {
     table = cache_table(a.block_table + (size_t)req * a.table_stride, table_s, s0, ke, ps, lane, 32);
     __syncwarp();
+    // Of the cache, only the request's newest row (key ke - 1 of its last item) is written in this
+    // step; every older row was written by steps that ended before this step's description was
+    // copied to the device.  So the first stages are on their way before the kernel in front of
+    // this one has finished, all but the stage that holds the newest row.
+    const bool newest_here = (int)blockIdx.x == first_item + nsplits - 1;
+    streamed = min(STAGES, num_stages - (newest_here ? 1 : 0));
+    stream_kv(a.k_cache, a.v_cache, table, kvh, a.nkv, ps, kb, ke, s0,
+              streamed, STAGES, stage_mem, full, empty, abort_flag, a.status, lane);
   }
   pdl_wait();
   if (warp < WARPS) {
@@ -109,7 +118,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   if (warp == WARPS) {
     // ------------------------------------------------------------------ producer
     stream_kv(a.k_cache, a.v_cache, table, kvh, a.nkv, ps, kb, ke, s0,
-              num_stages, STAGES, stage_mem, full, empty, abort_flag, a.status, lane);
+              num_stages, STAGES, stage_mem, full, empty, abort_flag, a.status, lane, streamed);
   } else {
     // ------------------------------------------------------------------ consumers
     uint32_t qf[HD / 16][4];
