@@ -89,17 +89,21 @@ _workspaces: dict = {}
 
 def _workspace(device, items: int, num_kv_heads: int, groups: int, head_dim: int):
     """Scratch of the decode kernel, kept and grown per device: partial outputs, their (max, sum)
-    and arrival counters (zero between launches)."""
+    and arrival counters (zero between launches).  A scratch that was outgrown is kept, not freed:
+    CUDA graphs captured while it was current still write to it when they are replayed."""
     key = str(device)
     rows = items * num_kv_heads * groups
     ws = _workspaces.get(key)
     if ws is None or ws["rows"] < rows or ws["hd"] < head_dim:
         rows = max(rows, ws["rows"] if ws else 0)
         hd = max(head_dim, ws["hd"] if ws else 0)
-        ws = dict(rows=rows, hd=hd,
+        retired = (ws["retired"] + [ws]) if ws else []
+        ws = dict(rows=rows, hd=hd, retired=retired,
                   part_o=torch.empty(rows * hd, dtype=torch.float32, device=device),
                   part_ml=torch.empty(rows * 2, dtype=torch.float32, device=device),
                   counters=torch.zeros(rows + 64, dtype=torch.int32, device=device))
+        if retired:
+            retired[-1]["retired"] = []
         _workspaces[key] = ws
     return ws
 

@@ -127,6 +127,39 @@ def test_cuda_graph_decode_matches_eager(tiny_folder):
     assert not graphs.takes([StepEntry(live[0], [1, 2], [1])])
 
 
+def test_replayed_graphs_keep_the_scratch_they_were_captured_with(tiny_folder):
+    """The decode kernel's scratch grows with the batch; a graph captured before it grew still
+    writes to the scratch of its day when it is replayed, so that memory must not go to anyone else."""
+    from tandem_b200.engine.core import build_executor, load_model
+    from tandem_b200.engine.cuda_graph import DecodeGraphs
+    from tandem_b200.engine.executor import StepEntry
+    from tandem_b200.kernels import attention as attention_kernels
+
+    decoder, cfg = load_model(tiny_folder("B"), "bfloat16", "cuda:0")
+    ex = build_executor(decoder, page_size=16, num_pages=64, max_requests=8)
+    graphs = DecodeGraphs.maybe(ex, 8, 512)
+    ex.step([StepEntry("a", random_tokens(5, 450, 1000), [])])  # long enough to be cut into two items
+
+    def decode(token):
+        assert ex.manager.grow("a", ex.manager.num_tokens("a") + 1)
+        logits = graphs.run([StepEntry("a", [token], [0])]).clone()
+        ex.manager.commit("a", 1)
+        return logits
+
+    decode(1), decode(2)  # eager and capture, then a replay
+    ws = attention_kernels._workspaces["cuda:0"]
+    sizes = [ws["part_o"].numel(), ws["part_ml"].numel()]
+    heads = cfg.num_attention_heads
+    grown = attention_kernels._workspace(decoder.device, 2 * ws["rows"] // heads + 1, cfg.num_key_value_heads,
+                                         heads // cfg.num_key_value_heads, cfg.head_dim)
+    assert grown is not ws
+    del ws
+    canaries = [torch.zeros(n, dtype=torch.float32, device=decoder.device) for n in sizes for _ in range(4)]
+    decode(3)  # the graph of bucket 1, captured with the scratch that has been outgrown
+    torch.cuda.synchronize()
+    assert all(int(c.count_nonzero()) == 0 for c in canaries)
+
+
 def test_generation_with_cuda_graphs(tiny_folder):
     from tandem_b200 import LLM, SamplingParams
 
