@@ -47,6 +47,7 @@ class Qwen3Config:
     tie_word_embeddings: bool
     sliding_window: Optional[int] = None  # keys each windowed layer sees, None: every layer sees all
     max_window_layers: int = 0  # layers with index >= this are windowed (when sliding_window is set)
+    layer_types: Optional[tuple] = None  # per layer "full_attention" | "sliding_attention"; overrides max_window_layers
     eos_token_ids: tuple = ()
     torch_dtype: Optional[str] = None
     extra: dict = field(default_factory=dict, compare=False)  # unread keys, kept for to_dict()
@@ -61,6 +62,8 @@ class Qwen3Config:
         return self.num_key_value_heads * self.head_dim
 
     def layer_window(self, layer: int) -> Optional[int]:
+        if self.layer_types is not None:
+            return self.sliding_window if self.layer_types[layer] == "sliding_attention" else None
         if self.sliding_window is None or layer < self.max_window_layers:
             return None
         return self.sliding_window
@@ -107,6 +110,19 @@ class Qwen3Config:
         layers = _positive_int(d, "num_hidden_layers", _require(d, "num_hidden_layers"))
         if first_window_layer is None:
             first_window_layer = layers if window is None else 0
+        # newer config.json files name each layer's kind; where they do, that list decides
+        layer_types = d.get("layer_types")
+        if layer_types is not None:
+            layer_types = tuple(layer_types)
+            if len(layer_types) != layers:
+                raise ConfigError(f"layer_types has {len(layer_types)} entries for {layers} layers")
+            for kind in layer_types:
+                if kind not in ("full_attention", "sliding_attention"):
+                    raise ConfigError(f"layer type {kind!r} is not supported (full_attention or sliding_attention)")
+            if "sliding_attention" in layer_types:
+                window = _positive_int(d, "sliding_window", _require(d, "sliding_window"))
+            else:
+                window = None
 
         eos = d.get("eos_token_id")
         eos_ids = () if eos is None else ((eos,) if isinstance(eos, int) else tuple(eos))
@@ -116,7 +132,7 @@ class Qwen3Config:
             "num_key_value_heads", "head_dim", "intermediate_size", "rms_norm_eps", "rope_theta", "rope_scaling",
             "rope_parameters", "max_position_embeddings", "tie_word_embeddings", "attention_bias", "hidden_act",
             "use_sliding_window", "sliding_window", "max_window_layers", "eos_token_id", "torch_dtype", "dtype",
-            "quantization_config",
+            "quantization_config", "layer_types",
         }
         return cls(
             architecture=arch,
@@ -133,6 +149,7 @@ class Qwen3Config:
             tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
             sliding_window=window,
             max_window_layers=int(first_window_layer),
+            layer_types=layer_types,
             eos_token_ids=eos_ids,
             torch_dtype=d.get("torch_dtype") or d.get("dtype"),
             extra={k: v for k, v in d.items() if k not in known},
@@ -161,6 +178,8 @@ class Qwen3Config:
             sliding_window=self.sliding_window,
             max_window_layers=self.max_window_layers,
         )
+        if self.layer_types is not None:
+            d["layer_types"] = list(self.layer_types)
         if self.eos_token_ids:
             d["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) > 1 else self.eos_token_ids[0]
         if self.torch_dtype:

@@ -39,7 +39,11 @@ def derived(cfg: dict) -> dict:
     """Sizes that config.json may leave out (python/tandem/model_config.py:100-101,125,128-132)."""
     nh = cfg["num_attention_heads"]
     rope = cfg.get("rope_parameters") or {}
-    window = cfg.get("sliding_window") if cfg.get("use_sliding_window") else None
+    kinds = cfg.get("layer_types")  # newer files name each layer "full_attention" or "sliding_attention"
+    if kinds is not None:
+        window = cfg.get("sliding_window") if "sliding_attention" in kinds else None
+    else:
+        window = cfg.get("sliding_window") if cfg.get("use_sliding_window") else None
     return dict(
         L=cfg["num_hidden_layers"],
         H=cfg["hidden_size"],
@@ -50,7 +54,8 @@ def derived(cfg: dict) -> dict:
         theta=float(rope.get("rope_theta") or cfg.get("rope_theta") or 10000.0),
         tied=bool(cfg.get("tie_word_embeddings", False)),
         window=window,
-        first_window_layer=cfg.get("max_window_layers", cfg["num_hidden_layers"]) if window else None,
+        first_window_layer=(cfg.get("max_window_layers") or 0) if window else None,
+        windowed=[k == "sliding_attention" for k in kinds] if kinds is not None else None,
     )
 
 
@@ -131,7 +136,10 @@ def swiglu(x: torch.Tensor, w: dict, prefix: str) -> torch.Tensor:
 def decoder_layer(h: torch.Tensor, w: dict, i: int, d: dict, cos, sin) -> torch.Tensor:
     """h <- h + attn(norm(h)); h <- h + mlp(norm(h))  (python/tandem/models/llama_family.py:11-16,59-67)."""
     p = f"model.layers.{i}"
-    window = d["window"] if d["window"] is not None and i >= d["first_window_layer"] else None
+    if d["windowed"] is not None:
+        window = d["window"] if d["windowed"][i] else None
+    else:
+        window = d["window"] if d["window"] is not None and i >= d["first_window_layer"] else None
     h = h + attention_block(rms_norm(h, w[f"{p}.input_layernorm.weight"], d["eps"]), w, f"{p}.self_attn", d, cos, sin, window)
     h = h + swiglu(rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], d["eps"]), w, f"{p}.mlp")
     return h

@@ -49,6 +49,21 @@ def test_rejects_what_it_does_not_implement(patch, word):
         Qwen3Config.from_dict(dict(TINY_A, **patch))
 
 
+def test_layer_types_decide_which_layers_have_a_window():
+    kinds = ["sliding_attention", "full_attention", "sliding_attention", "full_attention"]
+    c = Qwen3Config.from_dict(dict(TINY_C, layer_types=kinds, use_sliding_window=False))
+    assert [c.layer_window(i) for i in range(4)] == [20, None, 20, None]
+    assert Qwen3Config.from_dict(c.to_dict()) == c
+    none = Qwen3Config.from_dict(dict(TINY_C, layer_types=["full_attention"] * 4))
+    assert [none.layer_window(i) for i in range(4)] == [None] * 4
+    with pytest.raises(ConfigError, match="4 layers"):
+        Qwen3Config.from_dict(dict(TINY_C, layer_types=kinds[:3]))
+    with pytest.raises(ConfigError, match="chunked_attention"):
+        Qwen3Config.from_dict(dict(TINY_C, layer_types=["chunked_attention"] * 4))
+    with pytest.raises(ConfigError, match="sliding_window"):
+        Qwen3Config.from_dict(dict(TINY_A, layer_types=["sliding_attention"] * 2))
+
+
 def test_unknown_architecture_lists_supported():
     with pytest.raises(NotImplementedError, match="Qwen3ForCausalLM"):
         resolve_architecture({"architectures": ["GPT2LMHeadModel"]})

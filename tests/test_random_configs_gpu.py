@@ -27,9 +27,13 @@ def random_config(rng: random.Random) -> dict:
                vocab_size=rng.randint(100, 3000), rope_theta=rng.choice([1e4, 5e5, 1e6]),
                rms_norm_eps=rng.choice([1e-6, 1e-5, 3e-6]), tie_word_embeddings=rng.random() < 0.5,
                max_position_embeddings=512)
-    if rng.random() < 0.4:
+    kind = rng.random()
+    if kind < 0.3:
         cfg.update(use_sliding_window=True, sliding_window=rng.randint(4, 70),
                    max_window_layers=rng.randint(0, cfg["num_hidden_layers"]))
+    elif kind < 0.5:  # the newer spelling: a kind per layer
+        cfg.update(sliding_window=rng.randint(4, 70),
+                   layer_types=[rng.choice(["full_attention", "sliding_attention"]) for _ in range(cfg["num_hidden_layers"])])
     return cfg
 
 
