@@ -53,6 +53,11 @@ def cmd_generate(args) -> None:
         prompt = [int(t) for t in args.prompt_ids.replace(",", " ").split()]
     elif args.prompt is not None:
         prompt = args.prompt
+        if args.chat:  # python/tandem/entrypoints/cli.py:113-114 of 12vivi/tandem
+            if engine.tokenizer is None:
+                raise SystemExit("--chat needs a tokenizer with a chat template in the model folder")
+            prompt = engine.tokenizer.apply_chat_template([{"role": "user", "content": prompt}], tokenize=False,
+                                                          add_generation_prompt=True)
     else:
         raise SystemExit("give --prompt (text) or --prompt-ids (token ids)")
     sp = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p,
@@ -93,6 +98,7 @@ def main(argv=None) -> None:
     _engine_args(p)
     p.add_argument("--prompt", default=None, help="text (needs a tokenizer in the model folder)")
     p.add_argument("--prompt-ids", default=None, help="token ids separated by spaces or commas")
+    p.add_argument("--chat", action="store_true", help="wrap the prompt with the tokenizer's chat template")
     p.add_argument("--max-tokens", type=int, default=128)
     p.add_argument("--temperature", type=float, default=0.0)
     p.add_argument("--top-p", type=float, default=1.0)
