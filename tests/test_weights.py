@@ -73,6 +73,21 @@ def test_fused_rows_and_held_dtypes(tmp_path):
     assert full["head"].dtype == torch.float32 and torch.equal(full["head"], raw["lm_head.weight"].float())
 
 
+def test_tensors_spread_over_several_files(tmp_path):
+    """A folder may hold its tensors in several *.safetensors files (python/tandem/models/loader.py:67-78)."""
+    folder = write_random_model(TINY_B, str(tmp_path / "m"), seed=5)
+    path = os.path.join(folder, "model.safetensors")
+    raw = load_file(path)
+    names = sorted(raw)
+    params, plan = _params(TINY_B)
+    whole = load_parameters(params, SafetensorsFolder(folder), torch.bfloat16, "cpu", plan.ignored_weights)
+    os.remove(path)
+    for i in range(3):
+        save_file({n: raw[n] for n in names[i::3]}, os.path.join(folder, f"model-{i + 1:05d}-of-00003.safetensors"))
+    parts = load_parameters(params, SafetensorsFolder(folder), torch.bfloat16, "cpu", plan.ignored_weights)
+    assert parts.keys() == whole.keys() and all(torch.equal(parts[k], whole[k]) for k in whole)
+
+
 def test_a_32_bit_vector_stays_32_bit(tmp_path):
     folder = write_random_model(TINY_A, str(tmp_path / "m"), seed=5)
     path = os.path.join(folder, "model.safetensors")
