@@ -91,13 +91,32 @@ argmax_split_kernel(const float* __restrict__ logits, int* __restrict__ out, uns
   __shared__ unsigned long long warp_best[8];
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.y, len = (V + chunks - 1) / chunks;
-  const int begin = blockIdx.x * len, end = min(V, begin + len);
+  const int r = blockIdx.y, len = ((V + chunks - 1) / chunks + 3) & ~3;  // chunks start on 16-byte boundaries of the row
+  const int begin = min(V, (int)blockIdx.x * len), end = min(V, begin + len);
   const float* x = logits + (size_t)r * V;
   unsigned long long mine = 0ull;
-  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-    const unsigned long long cand = ((unsigned long long)ordered_key(x[i]) << 32) | (0xFFFFFFFFu - (unsigned)i);
+  auto take = [&](float v, int i) {
+    const unsigned long long cand = ((unsigned long long)ordered_key(v) << 32) | (0xFFFFFFFFu - (unsigned)i);
     mine = cand > mine ? cand : mine;
+  };
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {  // four logits a load, two loads in flight
+    const int quads = (end - begin) >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x + begin);
+    int q = threadIdx.x;
+    for (; q + (int)blockDim.x < quads; q += 2 * blockDim.x) {
+      const float4 a = x4[q], b = x4[q + blockDim.x];
+      const int ia = begin + 4 * q, ib = ia + 4 * blockDim.x;
+      take(a.x, ia), take(a.y, ia + 1), take(a.z, ia + 2), take(a.w, ia + 3);
+      take(b.x, ib), take(b.y, ib + 1), take(b.z, ib + 2), take(b.w, ib + 3);
+    }
+    if (q < quads) {
+      const float4 a = x4[q];
+      const int ia = begin + 4 * q;
+      take(a.x, ia), take(a.y, ia + 1), take(a.z, ia + 2), take(a.w, ia + 3);
+    }
+    for (int i = begin + 4 * quads + threadIdx.x; i < end; i += blockDim.x) take(x[i], i);
+  } else {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) take(x[i], i);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

@@ -282,7 +282,7 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     R, V = logits.shape
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     lib = load_library("sampling")
-    chunks = min(64, max(296 // max(1, R), V // 16384), V // 2048)
+    chunks = min(64, max(592 // max(1, R), V // 8192), V // 2048)
     if chunks < 2 or R > _ARGMAX_ROWS:
         _check(lib.tb_argmax(_stream(), _ptr(logits), _ptr(out), R, V), "argmax")
         return out
