@@ -1,0 +1,185 @@
+// y[m, n] = sum_k x[m, k] * w[n, k] for up to eight rows of x (a batch of so many decoding
+// requests): bfloat16 in, float32 sums, bfloat16 or float32 out.
+//
+// With so few rows the product is a stream of weights and nothing else, and what decides its time
+// is how soon the stream starts and how little happens after it ends.  So: no shared-memory ring
+// for the weights, no tensor memory, no split of K between blocks and hence no merge between
+// blocks.  A block of 16 warps takes 16 rows of the weight matrix at a time; its warps share the
+// K range, each streams its slice of the 16 rows straight from global memory into registers
+// (16 bytes a load, eight loads in flight per lane and the next eight issued before the last
+// eight are used) and multiplies with `mma.sync` m16n8k16: the weights are the A operand (16
+// rows), the rows of x the B operand (8 columns; rows that x does not have are zeros).  The
+// registers that a lane loads are not in the order the instruction names, but a sum over k does
+// not care in which order k is walked as long as A and B walk it alike: the lane with thread
+// index t in its group takes, of every 64 k, the eight at 8 t and the eight at 32 + 8 t, for A
+// from global memory and for B from the copy of x in shared memory (where x is too large for a
+// copy that leaves the L1 cache enough room to keep the loads in flight, 164 KB, B comes from
+// global memory too, along with the weights of its round).  The 16 partial tiles of a
+// block are added in warp order by 128 of its threads.  The first loads are on their way before
+// the kernel in front of this one has finished (weights are written by no kernel).  Every sum is
+// taken in one fixed order whatever the grid and however many rows x has.
+// 12vivi/tandem has kernels of this kind for the same case (python/tandem/layers/triton_gemv.py:25-88).
+#include "common.cuh"
+
+namespace tb {
+
+constexpr int GV_WARPS = 16, GV_THREADS = GV_WARPS * 32;
+constexpr int GV_STEPS = 2;  // steps of 64 k per round: 2 rows x 2 pieces x 2 steps = 8 loads of 16 bytes in flight per lane
+
+__device__ __forceinline__ uint4 load_weights(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <bool X_IN_SMEM>
+struct Round {  // what a lane holds of one round: [step][row g | row g + 8][piece t | piece 4 + t]
+  uint4 w[GV_STEPS][2][2];
+  uint4 b[X_IN_SMEM ? 1 : GV_STEPS][2];  // the lane's pieces of row g of x, where x is not in shared memory
+};
+
+template <bool X_IN_SMEM>
+__global__ void __launch_bounds__(GV_THREADS, 1)
+gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __restrict__ y, int M, int N, int pieces,
+            int x_stride, int out_f32) {
+  extern __shared__ uint4 smem[];
+  uint4* xs = smem;                                                    // [M][x_stride] pieces of 8 k
+  float* red = reinterpret_cast<float*>(smem + (X_IN_SMEM ? (size_t)M * x_stride : 0));  // [2][GV_WARPS][16 rows][8 columns]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+  const int steps = (pieces + 7) >> 3;  // steps of 64 k
+  const int s0 = warp * steps / GV_WARPS, s1 = (warp + 1) * steps / GV_WARPS;  // this warp's part of K
+  const int groups = (N + 15) >> 4;
+  const int my_groups = ((int)blockIdx.x < groups) ? (groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+
+  auto load_x = [&](int s, Round<X_IN_SMEM>& r) {
+    if (X_IN_SMEM) return;
+#pragma unroll
+    for (int u = 0; u < GV_STEPS; ++u)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int c = (s + u) * 8 + h * 4 + t;
+        r.b[X_IN_SMEM ? 0 : u][h] = (g < M && s + u < s1 && c < pieces) ? __ldg(x + (size_t)g * pieces + c) : make_uint4(0, 0, 0, 0);
+      }
+  };
+  auto load_round = [&](int j, int s, Round<X_IN_SMEM>& r) {  // group number j of this block, steps s .. s + GV_STEPS - 1
+    const int row_a = ((int)blockIdx.x + j * (int)gridDim.x) * 16 + g, row_b = row_a + 8;
+    const uint4* wa = w + (size_t)row_a * pieces;
+    const uint4* wb = w + (size_t)row_b * pieces;
+#pragma unroll
+    for (int u = 0; u < GV_STEPS; ++u) {
+      const bool live = s + u < s1;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int c = (s + u) * 8 + h * 4 + t;
+        const bool in_k = live && c < pieces;
+        r.w[u][0][h] = (in_k && row_a < N) ? load_weights(wa + c) : make_uint4(0, 0, 0, 0);
+        r.w[u][1][h] = (in_k && row_b < N) ? load_weights(wb + c) : make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+
+  Round<X_IN_SMEM> cur, nxt;
+  const bool streams = s0 < s1 && my_groups > 0;
+  if (streams) load_round(0, s0, cur);
+  pdl_wait();  // x is the output of the kernel in front
+  if (X_IN_SMEM) {
+    for (int i = threadIdx.x; i < M * pieces; i += GV_THREADS) xs[(i / pieces) * x_stride + i % pieces] = x[i];
+    __syncthreads();
+  } else if (streams) {
+    load_x(s0, cur);
+  }
+
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  int j = 0, s = s0;
+  while (j < my_groups) {
+    int nj = j, ns = s + GV_STEPS;
+    if (ns >= s1) { ns = s0; ++nj; }
+    if (streams) {
+      if (nj < my_groups) { load_round(nj, ns, nxt); load_x(ns, nxt); }
+#pragma unroll
+      for (int u = 0; u < GV_STEPS; ++u) {
+        if (s + u < s1) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int c = (s + u) * 8 + h * 4 + t;
+            uint4 b = make_uint4(0, 0, 0, 0);
+            if (X_IN_SMEM) {
+              if (g < M && c < pieces) b = xs[g * x_stride + c];
+            } else {
+              b = cur.b[X_IN_SMEM ? 0 : u][h];
+            }
+            const uint4 &a0 = cur.w[u][0][h], &a1 = cur.w[u][1][h];
+            mma_16816(acc, a0.x, a1.x, a0.y, a1.y, b.x, b.y);
+            mma_16816(acc, a0.z, a1.z, a0.w, a1.w, b.z, b.w);
+          }
+        }
+      }
+    }
+    if (nj != j) {  // the group is complete as far as this warp goes: the block adds its 16 partial tiles up
+      float* mine = red + ((size_t)(j & 1) * GV_WARPS + warp) * 128;
+      *reinterpret_cast<float2*>(mine + g * 8 + 2 * t) = make_float2(acc[0], acc[1]);
+      *reinterpret_cast<float2*>(mine + (g + 8) * 8 + 2 * t) = make_float2(acc[2], acc[3]);
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      __syncthreads();
+      if (threadIdx.x < 128) {
+        const int row = threadIdx.x >> 3, col = threadIdx.x & 7;
+        const float* part = red + (size_t)(j & 1) * GV_WARPS * 128 + threadIdx.x;
+        float sum = 0.f;
+#pragma unroll
+        for (int q = 0; q < GV_WARPS; ++q) sum += part[q * 128];
+        const int n = ((int)blockIdx.x + j * (int)gridDim.x) * 16 + row;
+        if (col < M && n < N) {
+          if (out_f32) reinterpret_cast<float*>(y)[(size_t)col * N + n] = sum;
+          else reinterpret_cast<__nv_bfloat16*>(y)[(size_t)col * N + n] = __float2bfloat16_rn(sum);
+        }
+      }
+    }
+    if (streams) cur = nxt;
+    j = nj;
+    s = ns;
+  }
+  // Only now may the kernel behind this one become resident: measured, blocks of a dependent kernel
+  // that wait on the same SM while this one streams through the L1 cache's load path double its time
+  // (a whole decode step at batch 8: 6.15 ms with the trigger at the top, 3.80 ms with it here).
+  pdl_launch_dependents();
+}
+
+}  // namespace tb
+
+extern "C" {
+
+// Rows of x the kernel takes, and the shared memory up to which x is copied there (the next
+// larger carve-out of the SM's memory leaves the L1 cache 28 KB, and the loads in flight halve).
+int tb_gemv_max_rows() { return 8; }
+int tb_gemv_max_smem_bytes() { return 164 * 1024; }
+
+// Pieces (of 8 k) between two rows of x in shared memory: four more than a multiple of eight, so that
+// the 16-byte reads of a quarter warp (two rows, four pieces each) fall into eight different bank groups.
+static int x_stride_of(int pieces) { return pieces + ((4 - pieces % 8) + 8) % 8; }
+
+static const int kReduceBytes = 2 * tb::GV_WARPS * 128 * 4;
+
+// x [M, K] and w [N, K] bfloat16, both contiguous and 16-byte aligned, K a multiple of 8; y [M, N].
+int tb_gemv(void* stream, const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int blocks) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > tb_gemv_max_rows() || K <= 0 || (K & 7) || blocks <= 0) return TB_ERR_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return TB_ERR_BAD_SIZE;
+  const int stride = x_stride_of(K / 8), with_x = M * stride * 16 + kReduceBytes;
+  const bool in_smem = with_x <= tb_gemv_max_smem_bytes();
+  auto kernel = in_smem ? tb::gemv_kernel<true> : tb::gemv_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tb_gemv_max_smem_bytes());
+  if (e != cudaSuccess) return (int)e;
+  const int groups = (N + 15) / 16;
+  return tb::launch(kernel, dim3(blocks < groups ? blocks : groups), dim3(tb::GV_THREADS),
+                    (size_t)(in_smem ? with_x : kReduceBytes), stream, (const uint4*)x, (const uint4*)w, y, M, N, K / 8, stride,
+                    out_f32);
+}
+
+}  // extern "C"

@@ -6,7 +6,10 @@ kernels take over for the shapes on which they beat cuBLAS, by a table measured 
 (python/tandem/layers/triton_gemv.py:221-297).  The same is done here: up to 64 rows may go to
 this package's tcgen05 weight-streaming kernel (``csrc/gemm_skinny.cu``); which of the two is
 faster for a shape is measured once, the first time the shape is seen outside a stream capture.
-``TANDEM_GEMM=skinny`` or ``=library`` forces one of them.
+Up to eight rows may also go to a kernel that streams the weights through registers into ``mma.sync``
+(``csrc/gemv_bf16.cu``, no shared-memory ring, no tensor memory, no merge between blocks),
+measured against the other two in the same way.  ``TANDEM_GEMM=skinny``, ``=gemv`` or ``=library``
+forces one of them where it applies.
 
 A caller whose output goes to a kernel that takes split input (``ops.add_rmsnorm``,
 ``ops.qk_norm_rope_kv``, ``ops.silu_mul``) may allow a ``SplitOutput``: the skinny kernel then
@@ -29,10 +32,11 @@ from tandem_b200.kernels import ops
 from tandem_b200.kernels.build import load_library
 
 SKINNY_MAX_ROWS = 64
+GEMV_MAX_ROWS = 8  # tb_gemv_max_rows() of csrc/gemv_bf16.cu
 SPLIT_MAX_ROWS = 32  # beyond this the partials are more than a reader should add up
 _mm_out_dtype = True  # torch.mm(..., out_dtype=) is tried once
 _sm_count: dict = {}
-_choice: dict = {}  # (padded rows, N, K, out dtype) -> True: the skinny kernel is the faster one
+_choice: dict = {}  # (class of rows, N, K, out dtype, split) -> "skinny" | "gemv" | "library", the fastest when measured
 _flush: dict = {}
 
 
@@ -165,25 +169,50 @@ def _measure(fn, x, weight, out_dtype, flush) -> float:
     return sorted(times)[len(times) // 2]
 
 
-def skinny_preferred(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, split: bool = False) -> bool:
+def gemv_applies(M: int, N: int, K: int) -> bool:
+    """What the register-streaming kernel takes: up to eight rows."""
+    return 0 < M <= GEMV_MAX_ROWS and K > 0 and K % 8 == 0
+
+
+def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """The weight-streaming kernel for up to eight rows (``csrc/gemv_bf16.cu``): weights from global
+    memory straight into registers, ``mma.sync`` against the rows of x in shared memory."""
     M, K = x.shape
     N = weight.shape[0]
-    if not skinny_applies(M, N, K):
-        return False
+    y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    ops._check(load_library("gemv_bf16").tb_gemv(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(y), M, N, K,
+                                                 int(out_dtype == torch.float32), sm_count(x.device)), "gemv")
+    return y
+
+
+def preferred(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, split: bool = False) -> str:
+    """"skinny", "gemv" or "library": the fastest of those that take the shape, measured once per
+    class of shapes (rows 1 to 8 each, up to 16, 32, 64), the weights pushed out of L2 before each run."""
+    M, K = x.shape
+    N = weight.shape[0]
+    can = [name for name, ok in (("skinny", skinny_applies(M, N, K)),
+                                 ("gemv", gemv_applies(M, N, K) and not split and x.is_contiguous()
+                                  and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)) if ok]
+    if not can:
+        return "library"
     forced = os.environ.get("TANDEM_GEMM")
-    if forced in ("skinny", "library"):
-        return forced == "skinny"
-    key = (16 if M <= 16 else (32 if M <= 32 else 64), N, K, out_dtype, split)
+    if forced in ("skinny", "gemv", "library"):
+        return forced if forced == "library" or forced in can else ("skinny" if "skinny" in can else "library")
+    key = (M if M <= GEMV_MAX_ROWS else (16 if M <= 16 else (32 if M <= 32 else 64)), N, K, out_dtype, split)
     if key not in _choice:
         if torch.cuda.is_current_stream_capturing():
-            return M <= 16  # nothing can be timed while a graph is being captured
+            return "skinny" if M <= 16 and "skinny" in can else "library"  # nothing can be timed while a graph is being captured
         dev = str(x.device)
         with torch.inference_mode():
             if dev not in _flush:
                 _flush[dev] = torch.empty(192 << 20, dtype=torch.uint8, device=x.device)  # larger than L2
-            a = _measure(lambda x_, w_, d_: skinny(x_, w_, d_, split), x, weight, out_dtype, _flush[dev])
-            b = _measure(_library, x, weight, out_dtype, _flush[dev])
-        _choice[key] = a <= b
+            runs = {"library": _library}
+            if "skinny" in can:
+                runs["skinny"] = lambda x_, w_, d_: skinny(x_, w_, d_, split)
+            if "gemv" in can:
+                runs["gemv"] = gemv
+            times = {name: _measure(fn, x, weight, out_dtype, _flush[dev]) for name, fn in runs.items()}
+        _choice[key] = min(times, key=times.get)
     return _choice[key]
 
 
@@ -227,7 +256,7 @@ def gated(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 
 def choices() -> dict:
-    """What has been measured so far: (padded rows, N, K, out dtype) -> the skinny kernel won."""
+    """What has been measured so far: (class of rows, N, K, out dtype, split) -> the kernel that won."""
     return dict(_choice)
 
 
@@ -238,6 +267,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, split_
         raise ops.KernelError(f"the bfloat16 product returns bfloat16 or float32, not {out_dtype}")
     split = (split_ok and out_dtype == torch.bfloat16 and x.shape[0] <= SPLIT_MAX_ROWS and weight.shape[0] % 8 == 0
              and split_enabled())
-    if skinny_preferred(x, weight, out_dtype, split):
+    which = preferred(x, weight, out_dtype, split)
+    if which == "skinny":
         return skinny(x, weight, out_dtype, split)
+    if which == "gemv":
+        return gemv(x, weight, out_dtype)
     return _library(x, weight, out_dtype)

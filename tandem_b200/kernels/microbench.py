@@ -61,6 +61,8 @@ def bench_gemm(args) -> None:
     rows = []
     if gemm_bf16.skinny_applies(M, N, K) and args.impl in ("both", "skinny"):
         rows.append(("tcgen05 skinny kernel", time_calls(lambda i: gemm_bf16.skinny(x, ws[i % len(ws)], out), args.iters, args.graph)))
+    if gemm_bf16.gemv_applies(M, N, K) and args.impl in ("both", "gemv"):
+        rows.append(("mma.sync streaming kernel", time_calls(lambda i: gemm_bf16.gemv(x, ws[i % len(ws)], out), args.iters, args.graph)))
     if args.impl in ("both", "wide") and M > gemm_bf16.SKINNY_MAX_ROWS and gemm_bf16.wide_applies(M, N, K):
         rows.append(("tcgen05 wide kernel", time_calls(lambda i: gemm_bf16.wide(x, ws[i % len(ws)], out), args.iters, args.graph)))
     if args.impl in ("both", "library"):
@@ -185,7 +187,7 @@ def main(argv=None) -> None:
     g.add_argument("--k", type=int, default=4096)
     g.add_argument("--f32-out", action="store_true")
     g.add_argument("--gated", action="store_true", help="also time the product with the SiLU * up epilogue (rows of W = [gate | up])")
-    g.add_argument("--impl", choices=["both", "skinny", "wide", "library"], default="both")
+    g.add_argument("--impl", choices=["both", "skinny", "gemv", "wide", "library"], default="both")
     g.set_defaults(fn=bench_gemm)
     ng = sub.add_parser("norm-gemm", parents=[common])
     ng.add_argument("--m", type=int, default=8)

@@ -174,6 +174,34 @@ def test_gemm_bf16(ops, M, N, K, out_dtype):
     ops.check_status("cuda")
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (2, 1000, 96), (1, 4096, 4096), (2, 6144, 4096), (1, 4096, 12288),
+                                   (2, 24, 8), (1, 151936, 512), (2, 130, 2056), (1, 7, 2048), (1, 3000, 25600),
+                                   (3, 4096, 4096), (4, 1000, 12288), (4, 77, 200), (8, 6144, 4096), (8, 4096, 12288),
+                                   (5, 2500, 1000), (8, 17, 72), (7, 24576, 4096), (6, 33, 8200), (7, 100, 20000),
+                                   (8, 300, 25600)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemv_bf16(ops, M, N, K, out_dtype):
+    """Up to eight rows through the register-streaming kernel: odd N, fewer rows of the weight
+    than a block takes, K that is no multiple of a step or of the warps' shares, and the same bits every time."""
+    from tandem_b200.kernels import gemm_bf16
+
+    g = torch.Generator().manual_seed(6)
+    x, w = torch.randn(M, K, generator=g).bfloat16(), (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16()
+    want = x.double() @ w.double().T
+    xd, wd = dev(x), dev(w)
+    assert gemm_bf16.gemv_applies(M, N, K)
+    first = gemm_bf16.gemv(xd, wd, out_dtype)
+    assert first.dtype == out_dtype and first.shape == (M, N)
+    err = (first.cpu().double() - want).abs().max()
+    assert err < (2e-2 if out_dtype == torch.bfloat16 else 2e-4 * math.sqrt(K) / 8 + 1e-4), err
+    assert torch.equal(first, gemm_bf16.gemv(xd, wd, out_dtype))
+    if M > 1:  # a row alone gives the bits it gives beside others
+        assert torch.equal(gemm_bf16.gemv(xd[M - 1:].contiguous(), wd, out_dtype)[0], first[M - 1])
+    assert not gemm_bf16.gemv_applies(9, N, K) and not gemm_bf16.gemv_applies(1, N, K + 4)
+    with pytest.raises(Exception):
+        gemm_bf16.gemv(dev(torch.zeros(9, K).bfloat16()), wd, out_dtype)
+
+
 # ----------------------------------------------------------------------------- attention
 def _paged_case(g, dtype, seqs, nh, nkv, hd, ps, extra_pages=5):
     """seqs: [(start, n)] -> (qkv rows for the new tokens, caches with shuffled pages holding keys 0..start+n-1, ...)."""
