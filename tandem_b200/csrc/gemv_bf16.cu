@@ -145,9 +145,10 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
     j = nj;
     s = ns;
   }
-  // Only now may the kernel behind this one become resident: measured, blocks of a dependent kernel
-  // that wait on the same SM while this one streams through the L1 cache's load path double its time
-  // (a whole decode step at batch 8: 6.15 ms with the trigger at the top, 3.80 ms with it here).
+  // Only now may the kernel behind this one become resident.  Measured: with the trigger at the top
+  // of the kernel, or where a block issues its last loads, this kernel streams at half its speed
+  // while the blocks of the kernel behind it wait on the same SMs (a whole decode step at batch 8:
+  // 6.15 ms either way, against 3.80 ms with the trigger here); the cause was not found.
   pdl_launch_dependents();
 }
 
