@@ -187,7 +187,7 @@ def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch
 
 def preferred(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, split: bool = False) -> str:
     """"skinny", "gemv" or "library": the fastest of those that take the shape, measured once per
-    class of shapes (rows 1 to 8 each, up to 16, 32, 64), the weights pushed out of L2 before each run."""
+    class of shapes (rows up to 1, 2, 4, 8, 16, 32, 64), the weights pushed out of L2 before each run."""
     M, K = x.shape
     N = weight.shape[0]
     can = [name for name, ok in (("skinny", skinny_applies(M, N, K)),
@@ -198,7 +198,10 @@ def preferred(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, spl
     forced = os.environ.get("TANDEM_GEMM")
     if forced in ("skinny", "gemv", "library"):
         return forced if forced == "library" or forced in can else ("skinny" if "skinny" in can else "library")
-    key = (M if M <= GEMV_MAX_ROWS else (16 if M <= 16 else (32 if M <= 32 else 64)), N, K, out_dtype, split)
+    # classes of rows as the CUDA graphs' buckets are (1, 2, 4, 8, 16, ...): a batch of 5 is measured when it
+    # first runs and decides for the graph of 8 that is captured right after it
+    rows = next(c for c in (1, 2, 4, 8, 16, 32, 64) if M <= c)
+    key = (rows, N, K, out_dtype, split)
     if key not in _choice:
         if torch.cuda.is_current_stream_capturing():
             return "skinny" if M <= 16 and "skinny" in can else "library"  # nothing can be timed while a graph is being captured
@@ -213,7 +216,8 @@ def preferred(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, spl
                 runs["gemv"] = gemv
             times = {name: _measure(fn, x, weight, out_dtype, _flush[dev]) for name, fn in runs.items()}
         _choice[key] = min(times, key=times.get)
-    return _choice[key]
+    best = _choice[key]
+    return best if best == "library" or best in can else ("skinny" if "skinny" in can else "library")
 
 
 def _row_bucket(M: int) -> int:
