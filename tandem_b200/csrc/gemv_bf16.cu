@@ -18,6 +18,10 @@
 // block are added in warp order by 128 of its threads.  The first loads are on their way before
 // the kernel in front of this one has finished (weights are written by no kernel).  Every sum is
 // taken in one fixed order whatever the grid and however many rows x has.
+// With `gated` the rows of w are [gate | up] halves of I rows each and y [M, I] = silu(x gate^T) *
+// (x up^T): the 16 rows a block takes at a time are 8 gate rows (the upper half of the MMA tile)
+// and the 8 up rows that go with them (the lower half), and the thread that adds a place's gate
+// sum up adds its up sum up too (both rounded to bfloat16, as the product alone would store them).
 // 12vivi/tandem has kernels of this kind for the same case (python/tandem/layers/triton_gemv.py:25-88).
 #include "common.cuh"
 
@@ -48,15 +52,18 @@ struct Round {  // what a lane holds of one round: [step][row g | row g + 8][pie
 template <bool X_IN_SMEM>
 __global__ void __launch_bounds__(GV_THREADS, 1)
 gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __restrict__ y, int M, int N, int pieces,
-            int x_stride, int out_f32) {
+            int x_stride, int out_f32, int gated) {
   extern __shared__ uint4 smem[];
   uint4* xs = smem;                                                    // [M][x_stride] pieces of 8 k
   float* red = reinterpret_cast<float*>(smem + (X_IN_SMEM ? (size_t)M * x_stride : 0));  // [2][GV_WARPS][16 rows][8 columns]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int steps = (pieces + 7) >> 3;  // steps of 64 k
   const int s0 = warp * steps / GV_WARPS, s1 = (warp + 1) * steps / GV_WARPS;  // this warp's part of K
-  const int groups = (N + 15) >> 4;
+  // groups of 16 rows; gated: 8 gate rows and their 8 up rows, I = N / 2 a multiple of 8
+  const int half_rows = N >> 1;
+  const int groups = gated ? half_rows >> 3 : (N + 15) >> 4;
   const int my_groups = ((int)blockIdx.x < groups) ? (groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int group_rows = gated ? 8 : 16, second_half = gated ? half_rows : 8;  // rows g and g + 8 of the tile in w
 
   auto load_x = [&](int s, Round<X_IN_SMEM>& r) {
     if (X_IN_SMEM) return;
@@ -69,7 +76,7 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
       }
   };
   auto load_round = [&](int j, int s, Round<X_IN_SMEM>& r) {  // group number j of this block, steps s .. s + GV_STEPS - 1
-    const int row_a = ((int)blockIdx.x + j * (int)gridDim.x) * 16 + g, row_b = row_a + 8;
+    const int row_a = ((int)blockIdx.x + j * (int)gridDim.x) * group_rows + g, row_b = row_a + second_half;
     const uint4* wa = w + (size_t)row_a * pieces;
     const uint4* wb = w + (size_t)row_b * pieces;
 #pragma unroll
@@ -131,13 +138,22 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
       if (threadIdx.x < 128) {
         const int row = threadIdx.x >> 3, col = threadIdx.x & 7;
         const float* part = red + (size_t)(j & 1) * GV_WARPS * 128 + threadIdx.x;
-        float sum = 0.f;
+        float sum = 0.f, second = 0.f;
 #pragma unroll
         for (int q = 0; q < GV_WARPS; ++q) sum += part[q * 128];
-        const int n = ((int)blockIdx.x + j * (int)gridDim.x) * 16 + row;
-        if (col < M && n < N) {
-          if (out_f32) reinterpret_cast<float*>(y)[(size_t)col * N + n] = sum;
-          else reinterpret_cast<__nv_bfloat16*>(y)[(size_t)col * N + n] = __float2bfloat16_rn(sum);
+        const int n = ((int)blockIdx.x + j * (int)gridDim.x) * group_rows + row;
+        if (!gated) {
+          if (col < M && n < N) {
+            if (out_f32) reinterpret_cast<float*>(y)[(size_t)col * N + n] = sum;
+            else reinterpret_cast<__nv_bfloat16*>(y)[(size_t)col * N + n] = __float2bfloat16_rn(sum);
+          }
+        } else if (row < 8) {  // the formula of the activation kernel (tokenwise.cu), on the values it would read
+#pragma unroll
+          for (int q = 0; q < GV_WARPS; ++q) second += part[q * 128 + 64];
+          const float gate = __bfloat162float(__float2bfloat16_rn(sum)), up = __bfloat162float(__float2bfloat16_rn(second));
+          if (col < M)
+            reinterpret_cast<__nv_bfloat16*>(y)[(size_t)col * half_rows + n] =
+                __float2bfloat16_rn(__fdividef(gate, 1.f + __expf(-gate)) * up);
         }
       }
     }
@@ -167,20 +183,30 @@ static int x_stride_of(int pieces) { return pieces + ((4 - pieces % 8) + 8) % 8;
 
 static const int kReduceBytes = 2 * tb::GV_WARPS * 128 * 4;
 
-// x [M, K] and w [N, K] bfloat16, both contiguous and 16-byte aligned, K a multiple of 8; y [M, N].
-int tb_gemv(void* stream, const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int blocks) {
+// x [M, K] and w [N, K] bfloat16, both contiguous and 16-byte aligned, K a multiple of 8; y [M, N], or with
+// gated (bfloat16 out only, N = 2 I with I a multiple of 8) y [M, I] = silu(x w[:I]^T) * (x w[I:]^T).
+int tb_gemv(void* stream, const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int gated, int blocks) {
   if (M <= 0 || N <= 0) return 0;
   if (M > tb_gemv_max_rows() || K <= 0 || (K & 7) || blocks <= 0) return TB_ERR_BAD_SIZE;
+  if (gated && (out_f32 || N % 16 != 0)) return TB_ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return TB_ERR_BAD_SIZE;
   const int stride = x_stride_of(K / 8), with_x = M * stride * 16 + kReduceBytes;
   const bool in_smem = with_x <= tb_gemv_max_smem_bytes();
   auto kernel = in_smem ? tb::gemv_kernel<true> : tb::gemv_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tb_gemv_max_smem_bytes());
+  static bool allowed[64][2] = {};  // the larger shared memory is asked for once per device and kernel
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return (int)e;
-  const int groups = (N + 15) / 16;
+  if (device < 0 || device >= 64) return TB_ERR_BAD_SIZE;
+  if (!allowed[device][in_smem]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tb_gemv_max_smem_bytes());
+    if (e != cudaSuccess) return (int)e;
+    allowed[device][in_smem] = true;
+  }
+  const int groups = gated ? N / 16 : (N + 15) / 16;
   return tb::launch(kernel, dim3(blocks < groups ? blocks : groups), dim3(tb::GV_THREADS),
                     (size_t)(in_smem ? with_x : kReduceBytes), stream, (const uint4*)x, (const uint4*)w, y, M, N, K / 8, stride,
-                    out_f32);
+                    out_f32, gated);
 }
 
 }  // extern "C"

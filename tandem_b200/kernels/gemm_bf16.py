@@ -159,6 +159,7 @@ def _measure(fn, x, weight, out_dtype, flush) -> float:
     times = []
     for i in range(5):
         flush.zero_()
+        flush.zero_()  # twice: the device is still busy when the timed launch has been queued, so host time is not measured
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         fn(x, weight, out_dtype)
@@ -174,14 +175,16 @@ def gemv_applies(M: int, N: int, K: int) -> bool:
     return 0 < M <= GEMV_MAX_ROWS and K > 0 and K % 8 == 0
 
 
-def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, gated: bool = False) -> torch.Tensor:
     """The weight-streaming kernel for up to eight rows (``csrc/gemv_bf16.cu``): weights from global
-    memory straight into registers, ``mma.sync`` against the rows of x in shared memory."""
+    memory straight into registers, ``mma.sync`` against the rows of x in shared memory.  ``gated``:
+    the weight's rows are [gate | up]; returns silu(x gate^T) * (x up^T), [M, rows / 2], the values
+    the product followed by ``ops.silu_mul`` gives."""
     M, K = x.shape
     N = weight.shape[0]
-    y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    y = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
     ops._check(load_library("gemv_bf16").tb_gemv(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(y), M, N, K,
-                                                 int(out_dtype == torch.float32), sm_count(x.device)), "gemv")
+                                                 int(out_dtype == torch.float32), int(gated), sm_count(x.device)), "gemv")
     return y
 
 
@@ -236,6 +239,8 @@ def gated(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     (``TANDEM_GEMM=wide`` or ``=library`` forces one)."""
     M, K = x.shape
     N = weight.shape[0]
+    if M <= GEMV_MAX_ROWS and N % 16 == 0 and preferred(x, weight, torch.bfloat16) == "gemv":
+        return gemv(x, weight, torch.bfloat16, gated=True)  # the streaming kernel won the product alone: the activation rides along
     if M <= SKINNY_MAX_ROWS or not wide_applies(M, N, K) or N % 16:
         return ops.silu_mul(linear(x, weight, torch.bfloat16, split_ok=True))
     forced = os.environ.get("TANDEM_GEMM")

@@ -202,6 +202,25 @@ def test_gemv_bf16(ops, M, N, K, out_dtype):
         gemm_bf16.gemv(dev(torch.zeros(9, K).bfloat16()), wd, out_dtype)
 
 
+@pytest.mark.parametrize("M,I,K", [(1, 16, 64), (8, 12288, 4096), (3, 104, 200), (5, 1000, 1000), (8, 40, 12288), (2, 4096, 520)])
+def test_gemv_gated_gives_the_bits_of_product_then_activation(ops, M, I, K):
+    """silu(x gate^T) * (x up^T) inside the streaming kernel (8 gate rows and their 8 up rows share a
+    tile); bit for bit what the product followed by ops.silu_mul gives."""
+    from tandem_b200.kernels import gemm_bf16
+
+    g = torch.Generator().manual_seed(8)
+    x, w = dev(torch.randn(M, K, generator=g).bfloat16()), dev((torch.randn(2 * I, K, generator=g) / math.sqrt(K) * 3).bfloat16())
+    fused = gemm_bf16.gemv(x, w, torch.bfloat16, gated=True)
+    assert fused.shape == (M, I)
+    plain = ops.silu_mul(gemm_bf16.gemv(x, w, torch.bfloat16))
+    assert torch.equal(fused, plain), ((fused.float() - plain.float()).abs().max(), int((fused != plain).sum()))
+    gu = x.double().cpu() @ w.double().cpu().T
+    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    torch.testing.assert_close(fused.cpu().double(), want, atol=2e-2, rtol=2e-2)  # gate, up and the result are rounded to bfloat16
+    with pytest.raises(Exception):
+        gemm_bf16.gemv(x, w[: 2 * I - 8].contiguous(), torch.bfloat16, gated=True)  # halves that are no multiple of 8 rows
+
+
 # ----------------------------------------------------------------------------- attention
 def _paged_case(g, dtype, seqs, nh, nkv, hd, ps, extra_pages=5):
     """seqs: [(start, n)] -> (qkv rows for the new tokens, caches with shuffled pages holding keys 0..start+n-1, ...)."""
