@@ -72,7 +72,7 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int c = (s + u) * 8 + h * 4 + t;
-        r.b[X_IN_SMEM ? 0 : u][h] = (g < M && s + u < s1 && c < pieces) ? __ldg(x + (size_t)g * pieces + c) : make_uint4(0, 0, 0, 0);
+        r.b[X_IN_SMEM ? 0 : u][h] = (g < M && s + u < s1 && c < pieces) ? __ldcg(x + (size_t)g * pieces + c) : make_uint4(0, 0, 0, 0);
       }
   };
   auto load_round = [&](int j, int s, Round<X_IN_SMEM>& r) {  // group number j of this block, steps s .. s + GV_STEPS - 1
