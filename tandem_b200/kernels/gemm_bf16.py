@@ -207,7 +207,8 @@ def preferred(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, spl
     key = (rows, N, K, out_dtype, split)
     if key not in _choice:
         if torch.cuda.is_current_stream_capturing():
-            return "skinny" if M <= 16 and "skinny" in can else "library"  # nothing can be timed while a graph is being captured
+            # nothing can be timed while a graph is being captured: what usually wins
+            return "gemv" if "gemv" in can else ("skinny" if M <= 16 and "skinny" in can else "library")
         dev = str(x.device)
         with torch.inference_mode():
             if dev not in _flush:
@@ -233,7 +234,8 @@ def _row_bucket(M: int) -> int:
 
 def gated(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """silu(x gate^T) * (x up^T) for a weight whose rows are [gate | up]: [M, rows / 2] bfloat16.
-    Few rows: the product, then the activation kernel (which takes a split output).  Many rows: the
+    Up to eight rows: inside the streaming kernel where that kernel wins the product.  Otherwise few
+    rows: the product, then the activation kernel (which takes a split output).  Many rows: the
     wide tcgen05 kernel with the activation in its epilogue, if that was measured to be faster than
     the library product followed by the activation kernel for this class of shapes
     (``TANDEM_GEMM=wide`` or ``=library`` forces one)."""
