@@ -48,7 +48,9 @@ struct DecodeArgs {
 
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeArgs a) {
   extern __shared__ unsigned char smem_unaligned[];
-  pdl_launch_dependents();
+  // No early griddepcontrol.launch_dependents here: the kernel behind this one (the output projection)
+  // becomes resident as this one's blocks exit.  Measured at Qwen3-8B sizes: with the trigger at the
+  // top a decode step takes 3.75 ms at batch 8 and 3.37 ms at batch 1, without it 3.64 and 3.26 ms.
   // The batch's description (items, their number, block tables) is written by the host before the
   // step's first kernel: it is read, and the barriers are set up, while the kernel in front of
   // this one still runs.  The queries and the newest cache rows are that kernel's output.
