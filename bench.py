@@ -276,7 +276,7 @@ def main() -> int:
     if args.impl == "reference":
         from baseline.reference_arm import run_reference
 
-        print(json.dumps(run_reference(args)))
+        print(json.dumps(run_reference(args, SHAPES, prompts, ClockSampler)))
         return 0
     args.warmup = max(3, args.warmup)
     name, shape = SHAPES[args.shape]

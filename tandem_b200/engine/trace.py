@@ -21,21 +21,32 @@ import sys
 from tandem_b200.cache.manager import cdiv
 
 
+ROUNDING = 64  # --max-tokens counts every live request rounded up to a multiple of this
+
+
+def pool_pages(max_tokens: int, page_size: int) -> int:
+    """Pages per cache group for ``--max-tokens``: the most tokens live requests hold at any time,
+    each request's count rounded up to a multiple of 64, or of the page size where pages are larger.
+    Every unit of 64 tokens may belong to another request, so each unit gets whole pages of its
+    own: 64 / page_size of them where that divides, ceil(64 / page_size) otherwise (pages of 48
+    tokens: two per unit).  With pages of 64 tokens or more a request's count is a multiple of the
+    page size already, and the pool is ``max_tokens / page_size`` pages."""
+    if page_size >= ROUNDING:
+        return max(1, cdiv(max_tokens, page_size))
+    return max(1, cdiv(max_tokens, ROUNDING) * cdiv(ROUNDING, page_size))
+
+
 def replay(model: str, dtype: str, out_dir: str, max_tokens: int, lines, device: str = "cuda:0",
            page_size: int = 16, echo=None) -> int:
-    """Run the steps read from ``lines``.  The cache pool holds ``max_tokens`` tokens (each
-    request's count rounded up to 64, which whole pages of ``page_size`` divide), so pages are
-    used again as requests end.  Returns the number of steps run."""
-    import numpy as np
-
+    """Run the steps read from ``lines``.  The cache pool holds ``max_tokens`` tokens
+    (``pool_pages``), so pages are used again as requests end.  Returns the number of steps run."""
     from tandem_b200.engine.core import build_executor, load_model
     from tandem_b200.engine.executor import StepEntry
+    from tandem_b200.kernels import ops
 
-    if 64 % page_size:
-        raise ValueError("page_size must divide 64")
     os.makedirs(out_dir, exist_ok=True)
     decoder, _ = load_model(model, dtype, device)
-    executor = build_executor(decoder, page_size=page_size, num_pages=max(1, cdiv(max_tokens, page_size)),
+    executor = build_executor(decoder, page_size=page_size, num_pages=pool_pages(max_tokens, page_size),
                               max_requests=64)
     steps = 0
     for line in lines:
@@ -45,6 +56,7 @@ def replay(model: str, dtype: str, out_dir: str, max_tokens: int, lines, device:
         rec = json.loads(line)
         entries = [StepEntry(str(e["id"]), list(e["tokens"]), list(e.get("want", []))) for e in rec.get("entries", [])]
         logits = executor.step(entries, end=[str(r) for r in rec.get("end", [])])
+        ops.check_status(executor.device)  # a kernel that gave up a wait or met a missing page: no logits are written
         if logits.shape[0]:
             arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
             tmp = os.path.join(out_dir, f".{rec['step']}.f32.tmp")
@@ -63,7 +75,7 @@ def main(argv=None) -> int:
     p.add_argument("--out", required=True, help="folder for <step>.f32 files")
     p.add_argument("--max-tokens", type=int, required=True, help="tokens the cache pool holds")
     p.add_argument("--device", default="cuda:0")
-    p.add_argument("--block-size", type=int, default=16, help="tokens per cache page (divides 64)")
+    p.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     args = p.parse_args(argv)
 
     def echo(text: str) -> None:

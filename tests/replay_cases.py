@@ -116,3 +116,28 @@ def tokens_needed(steps: list, round_to: int = 64) -> int:
         for rid in st["end"]:
             held.pop(rid, None)
     return peak
+
+
+def pages_handed_twice(steps: list, page_size: int, num_pages: int) -> tuple:
+    """The trace run through the cache manager's bookkeeping alone (no device): how many pages of
+    a pool of ``num_pages`` go to a second holder, and how many of those while another request is
+    live.  Raises if the pool cannot hold the trace."""
+    from tandem_b200.cache.manager import CacheManager, KVNeed
+
+    m = CacheManager([KVNeed(1, 16, None)], page_size, num_pages, 64)
+    handed, beside_live = {}, 0
+    for st in steps:
+        for e in st["entries"]:
+            rid = e["id"]
+            if not m.has(rid):
+                m.begin(rid)
+            held = len(m.table(0, rid))
+            if not m.grow(rid, m.num_tokens(rid) + len(e["tokens"])):
+                raise RuntimeError(f"step {st['step']}: the pool of {num_pages} pages is too small")
+            for page in m.table(0, rid)[held:]:
+                handed[page] = handed.get(page, 0) + 1
+                beside_live += handed[page] > 1 and len(m.live) > 1
+            m.commit(rid, len(e["tokens"]))
+        for rid in st["end"]:
+            m.end(rid)
+    return sum(1 for n in handed.values() if n > 1), beside_live

@@ -45,12 +45,39 @@ def oracle(tiny_folder):
     return get
 
 
-def run_in_process(folder, dtype, steps, page_size, max_tokens):
+class PageLog:
+    """Every page number the pools hand out, and how often a page went to a new holder while
+    another request was live (its keys lie beside pages that are being read)."""
+
+    def __init__(self, manager) -> None:
+        self.handed: dict = {}
+        self.reused_beside_live = 0
+        for g, group in enumerate(manager.groups):
+            group.pool.allocate = self._wrap(group.pool.allocate, g, manager)
+
+    def _wrap(self, allocate, g, manager):
+        def logged(n):
+            ids = allocate(n)
+            for i in ids:
+                self.handed[(g, i)] = self.handed.get((g, i), 0) + 1
+                if self.handed[(g, i)] > 1 and len(manager.live) > 1:
+                    self.reused_beside_live += 1
+            return ids
+
+        return logged
+
+    @property
+    def pages_reused(self) -> int:
+        return sum(1 for n in self.handed.values() if n > 1)
+
+
+def run_in_process(folder, dtype, steps, page_size, max_tokens, log=None):
     from tandem_b200.engine.core import build_executor, load_model
     from tandem_b200.engine.executor import StepEntry
 
     decoder, _ = load_model(folder, dtype, "cuda:0")
     ex = build_executor(decoder, page_size=page_size, num_pages=-(-max_tokens // page_size), max_requests=8)
+    pages = PageLog(ex.manager)
     out = {}
     for st in steps:
         logits = ex.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in st["entries"]], end=st["end"])
@@ -58,6 +85,8 @@ def run_in_process(folder, dtype, steps, page_size, max_tokens):
             out[st["step"]] = logits.cpu().double().numpy()
         ex.manager.check()
     assert ex.manager.all_free()
+    if log is not None:
+        log.append(pages)
     return out
 
 
@@ -88,8 +117,12 @@ def test_replay_regimes(tiny_folder, oracle, name, dtype, regime):
     if regime == "mixed":
         assert max(len(s["entries"]) for s in steps) == 4
         assert any(len({len(e["tokens"]) == 1 for e in s["entries"]}) == 2 for s in steps)  # portions beside single tokens
-    need = rc.tokens_needed(steps)
-    out = run_in_process(tiny_folder(name), dtype, steps, PAGE[name], need)
+    need = rc.tokens_needed(steps, round_to=PAGE[name])  # whole pages of this pool, nothing to spare
+    log = []
+    out = run_in_process(tiny_folder(name), dtype, steps, PAGE[name], need, log)
+    assert log[0].pages_reused > 0, "no page was handed out twice: the pool is too large for this trace"
+    if regime == "mixed":  # pages that a finished request gave back are written while other requests are read
+        assert log[0].reused_beside_live >= 3, log[0].reused_beside_live
     check(name, dtype, rc.collect(steps, out), oracle)
 
 
@@ -101,7 +134,9 @@ def test_float32_is_bitwise_the_same_however_it_is_cut(tiny_folder, dtype):
     runs = {}
     for regime in ("whole", "portions", "mixed"):
         steps = BUILDERS[regime](reqs)
-        out = run_in_process(tiny_folder("B"), dtype, steps, PAGE["B"], rc.tokens_needed(steps))
+        log = []
+        out = run_in_process(tiny_folder("B"), dtype, steps, PAGE["B"], rc.tokens_needed(steps, round_to=PAGE["B"]), log)
+        assert log[0].pages_reused > 0
         runs[regime] = {rid: np.stack(rows) for rid, rows in rc.collect(steps, out).items()}
     for rid in reqs:
         for regime in ("portions", "mixed"):
@@ -109,16 +144,26 @@ def test_float32_is_bitwise_the_same_however_it_is_cut(tiny_folder, dtype):
             assert diff == 0.0 if dtype == "float32" else diff < 0.05, (rid, regime, diff)
 
 
+MANY = [30, 9, 61, 17, 2, 44, 58, 25, 12, 63, 37, 5, 50, 21]  # 14 requests: four live hold 256 of their 434 tokens at most
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_program(tiny_folder, oracle, tmp_path, dtype):
-    """The program itself, as a user runs it: steps on stdin, ``done <step>`` lines, .f32 files."""
-    name = "B"
-    reqs = requests_of(name)
+@pytest.mark.parametrize("name,block_size", [("B", 8), ("A", 16), ("B", 48)])
+def test_trace_run_program(tiny_folder, tmp_path, name, block_size, dtype):
+    """The program itself, as a user runs it: steps on stdin, ``done <step>`` lines, .f32 files,
+    ``--max-tokens`` as the tool defines it (every live request rounded up to 64 tokens); so many
+    short requests that the pool's pages go round more than once."""
+    from tandem_b200.engine.trace import pool_pages
+
+    vocab = TINY[name]["vocab_size"]
+    reqs = {f"m{i}": random_tokens(977 * ord(name) + i, n, vocab) for i, n in enumerate(MANY)}
     steps = rc.mixed(reqs)
-    need = rc.tokens_needed(steps)
+    need = rc.tokens_needed(steps, round_to=max(64, block_size))
+    twice, beside_live = rc.pages_handed_twice(steps, block_size, pool_pages(need, block_size))
+    assert twice >= 3 and beside_live >= 3, (twice, beside_live)
     out_dir = tmp_path / "out"
     proc = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", tiny_folder(name), "--dtype", dtype,
-                             "--out", str(out_dir), "--max-tokens", str(need)],
+                             "--out", str(out_dir), "--max-tokens", str(need), "--block-size", str(block_size)],
                             stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
     for st in steps:  # the next step goes in only after the last one's "done"
         proc.stdin.write(json.dumps(st) + "\n")
@@ -126,7 +171,6 @@ def test_trace_run_program(tiny_folder, oracle, tmp_path, dtype):
         assert proc.stdout.readline().strip() == f"done {st['step']}"
     proc.stdin.close()
     assert proc.wait(timeout=120) == 0
-    vocab = TINY[name]["vocab_size"]
     outputs = {}
     for st in steps:
         wanted = sum(len(e["want"]) for e in st["entries"])
@@ -135,7 +179,18 @@ def test_trace_run_program(tiny_folder, oracle, tmp_path, dtype):
             outputs[st["step"]] = np.fromfile(path, dtype="<f4").reshape(wanted, vocab).astype(np.float64)
         else:
             assert not path.exists()
-    check(name, dtype, rc.collect(steps, outputs), oracle)
+    folder = tiny_folder(name)
+    cfg, w64 = plain.read_folder(folder, torch.float64)
+    _, w16 = plain.read_folder(folder, torch.bfloat16)
+    got = rc.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        ref = plain.forward(cfg, w64, toks, torch.float64)
+        err = (torch.from_numpy(np.stack(got[rid])) - ref).abs().max().item()
+        if dtype == "float32":
+            assert err < 1e-4, (rid, err)
+        else:
+            base = (plain.forward(cfg, w16, toks, torch.bfloat16).double() - ref).abs().max().item()
+            assert err <= 1.5 * base + 0.02, (rid, err, base)
 
 
 def test_out_of_pages_is_refused_before_anything_runs(tiny_folder):
