@@ -317,7 +317,7 @@ def main() -> int:
                    "parallelism": "single GPU", "cuda_graph": eng.graphs is not None,
                    "l2": "inputs larger than L2: each step streams every weight", "peaks": pk["source"]},
         "e2e": {"value": round(main_pt["e2e_tok_s"], 1), "unit": "tok/s", "ms_per_step": round(main_pt["e2e_ms"], 4),
-                "h2d_bytes_per_step": eng.executor.h2d_bytes_last, "d2h_bytes_per_step": 4 * args.batch},
+                "h2d_bytes_per_step": eng.executor.h2d_bytes_last, "d2h_bytes_per_step": 4 * (args.batch + 1)},
         "gpu_launches": int(main_pt["launches"]) * args.steps,
         "prefill": {"value": round(pre["tok_s"], 1), "tokens": PROMPT, "ms": round(pre["ms"], 3),
                     "frac": round(pre["flops"] / (pre["ms"] * 1e-3) / (pk["tflops"] * 1e12), 4)},

@@ -1,8 +1,8 @@
 """The model plan: what an architecture hands to the generic decoder.
 
-A plan is data.  It lists the layers (each a block arrangement, a norm, a mixer and a
-feed-forward, every one a *spec*: a kind name plus the sizes and constants that part takes),
-and the order in which the layers run.  The order is a list of :class:`RunStep`: it may name a
+A plan is data.  It lists the layers (each a block arrangement and the parts it arranges under
+slot names of its own: norms, mixers, feed-forwards, every one a *spec*, a kind name plus the
+sizes and constants that part takes), and the order in which the layers run.  The order is a list of :class:`RunStep`: it may name a
 layer twice (the second run gets a cache of its own) or let a run read the cache that an
 earlier run wrote (``cache_of``), in which case it writes none.
 
@@ -41,13 +41,16 @@ class ParamSpec:
 
 @dataclass(frozen=True)
 class PartSpec:
-    """Base of every spec: ``kind`` picks the implementation in the registry."""
+    """Base of every spec: ``kind`` picks the implementation in the registry, within the spec's
+    ``family`` ("mixer", "feed_forward", "norm", "position")."""
 
     kind: str
+    family = None  # set by the base class of each family
 
 
 @dataclass(frozen=True)
 class NormSpec(PartSpec):
+    family = "norm"
     size: int = 0
     eps: float = 1e-6
     weight: str = ""  # checkpoint tensor name
@@ -58,6 +61,7 @@ class PositionSpec(PartSpec):
     """kind "rope": rotate_half rotary encoding over the first ``rotary_dim`` dims of a head.
     kind "none": no position encoding."""
 
+    family = "position"
     rotary_dim: int = 0
     theta: float = 10000.0
     max_position: int = 0
@@ -65,6 +69,7 @@ class PositionSpec(PartSpec):
 
 @dataclass(frozen=True)
 class MixerSpec(PartSpec):
+    family = "mixer"
     prefix: str = ""  # checkpoint name prefix, e.g. "model.layers.3.self_attn"
 
 
@@ -83,6 +88,7 @@ class AttentionSpec(MixerSpec):
 
 @dataclass(frozen=True)
 class FeedForwardSpec(PartSpec):
+    family = "feed_forward"
     prefix: str = ""
 
 
@@ -95,11 +101,40 @@ class GatedMLPSpec(FeedForwardSpec):
 
 @dataclass(frozen=True)
 class LayerSpec:
-    block: str  # arrangement kind, e.g. "prenorm"
-    mixer: MixerSpec
-    feed_forward: FeedForwardSpec
-    mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    """One layer: the kind of its block arrangement and the parts that arrangement works with, as
+    (slot name, family, spec).  Which slots there are is the arrangement's business: "prenorm" has
+    ``mixer_norm``, ``mixer``, ``feed_forward_norm`` and ``feed_forward``; another arrangement may
+    have four norms, no feed-forward, or two mixers side by side."""
+
+    block: str
+    parts: tuple
+
+    @classmethod
+    def of(cls, block: str, **slots: PartSpec) -> "LayerSpec":
+        """``LayerSpec.of("prenorm", mixer=..., feed_forward=..., mixer_norm=..., feed_forward_norm=...)``:
+        the family of each part is the one its spec class belongs to."""
+        for name, spec in slots.items():
+            if getattr(spec, "family", None) is None:
+                raise TypeError(f"slot {name!r}: {type(spec).__name__} belongs to no part family "
+                                "(derive it from MixerSpec, FeedForwardSpec, NormSpec or PositionSpec)")
+        return cls(block, tuple((name, spec.family, spec) for name, spec in slots.items()))
+
+    def slot(self, name: str) -> PartSpec:
+        for slot, _, spec in self.parts:
+            if slot == name:
+                return spec
+        raise KeyError(f"the layer has no slot {name!r} (it has {[s for s, _, _ in self.parts]})")
+
+    def with_slot(self, name: str, spec: PartSpec) -> "LayerSpec":
+        """A copy in which the slot holds ``spec`` (put behind the others if the slot is new)."""
+        entry = (name, spec.family, spec)
+        if any(slot == name for slot, _, _ in self.parts):
+            return LayerSpec(self.block, tuple(entry if slot == name else (slot, fam, sp) for slot, fam, sp in self.parts))
+        return LayerSpec(self.block, self.parts + (entry,))
+
+    def of_family(self, family: str) -> list:
+        """(slot name, spec) of the layer's parts of one family, in the order they were given."""
+        return [(slot, spec) for slot, fam, spec in self.parts if fam == family]
 
 
 @dataclass(frozen=True)
@@ -110,16 +145,25 @@ class RunStep:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
+    """Start of the residual stream: ``scale * table[token]``, plus ``positions[position]`` where
+    the model has a learned table of absolute positions (a checkpoint tensor [max_position, hidden])."""
+
     vocab_size: int
     hidden_size: int
     weight: str
+    scale: float = 1.0
+    positions: Optional[str] = None
 
 
 @dataclass(frozen=True)
 class HeadSpec:
+    """Logits = ``scale * (h @ weight^T)``, then ``softcap * tanh(logits / softcap)`` where a cap is given."""
+
     vocab_size: int
     hidden_size: int
     weight: Optional[str]  # None: tied to the embedding table
+    scale: float = 1.0
+    softcap: Optional[float] = None
 
 
 @dataclass(frozen=True)

@@ -13,8 +13,7 @@
 // SM in contiguous, equal ranges, so every SM streams the same number of bytes whatever N and K
 // are.  A tile whose K range is shared by several blocks is summed by the block that arrives last
 // (an atomic counter per tile, reset by that block), from float32 partials in scratch memory, in
-// block order: the result does not depend on timing.  With a *split output* (split_output.cuh)
-// the partials are left for the kernel that reads the output, and nothing is counted or added here.
+// block order: the result does not depend on timing.
 //
 // 12vivi/tandem has Triton weight-streaming kernels for batch <= 8 in this place
 // (python/tandem/layers/triton_gemv.py:26-87,285-297) and cuBLAS beyond.
@@ -22,7 +21,6 @@
 
 #include "common.cuh"
 #include "sm100_primitives.cuh"
-#include "split_output.cuh"
 
 namespace tb {
 
@@ -32,13 +30,22 @@ constexpr int BOXES = 2;   // boxes per stage, next to each other along K (256 c
 constexpr int BK = BOX_K * BOXES;  // K elements per stage
 constexpr int SK_THREADS = 192;
 
+// first chunk of block p when `total` chunks are dealt to `blocks` blocks
+__host__ __device__ __forceinline__ long long range_start(long long p, long long total, long long blocks) { return p * total / blocks; }
+
+__host__ __device__ __forceinline__ int block_of_chunk(long long c, long long total, long long blocks) {
+  long long p = c * blocks / total;
+  while (p + 1 < blocks && range_start(p + 1, total, blocks) <= c) ++p;
+  while (p > 0 && range_start(p, total, blocks) > c) --p;
+  return (int)p;
+}
+
 struct SkinnyArgs {
   void* y;         // [M, N] bf16 or f32
   float* partial;  // [grid][2][Mpad][BN] float32
   int* counters;   // [tiles * 4], zero between launches
   int* status;
   int M, N, K, mpad, out_f32, stages;
-  int split;  // leave the partials of shared tiles to the reader of y
 };
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -234,7 +241,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty + buf);
       ++seg;
-      if (whole || a.split) continue;
+      if (whole) continue;
       // A shared tile: each warp owns 32 of the tile's columns in every block that works on the tile;
       // the warp that arrives last for its quarter adds up that quarter's partials, in block order.
       __syncwarp();
@@ -284,20 +291,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
 }
 
-__global__ void split_resolve_kernel(__nv_bfloat16* __restrict__ y, const SplitView sv, int M, int N) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (g >= (long long)M * (N / 8)) return;
-  const int t = (int)(g / (N / 8)), n0 = (int)(g % (N / 8)) * 8;
-  const int* info = sv.tiles + 3 * (n0 / SPLIT_BN);
-  if (info[0] == info[1]) return;  // final already
-  float v[8];
-  split_load8(y + (size_t)t * N, sv, t, n0, v);
-  *reinterpret_cast<uint4*>(y + (size_t)t * N + n0) =
-      make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-}
-
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -333,12 +326,10 @@ extern "C" {
 
 // Scratch the caller provides: partial >= blocks * 2 * 64 * 128 floats, counters >= 4 * ceil(N / 128)
 // ints that are zero (the kernel leaves them zero).  `blocks`: persistent blocks (one per SM).
-// split != 0 (bfloat16 output only): shared tiles stay in `partial` for the reader of y, as
-// tb_gemm_skinny_tiles describes them.
 int tb_gemm_skinny(void* stream, const void* x, const void* w, void* y, float* partial, int* counters, int* status,
-                   int M, int N, int K, int out_f32, int blocks, int split) {
+                   int M, int N, int K, int out_f32, int blocks) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 64 || K <= 0 || K % 8 != 0 || blocks <= 0 || (split && out_f32)) return TB_ERR_BAD_SIZE;
+  if (M > 64 || K <= 0 || K % 8 != 0 || blocks <= 0) return TB_ERR_BAD_SIZE;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return TB_ERR_BAD_SIZE;
   const int mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   CUtensorMap map_w, map_x;
@@ -358,33 +349,9 @@ int tb_gemm_skinny(void* stream, const void* x, const void* w, void* y, float* p
   const long long total = (long long)((K + tb::BK - 1) / tb::BK) * ((N + tb::BN - 1) / tb::BN);
   tb::SkinnyArgs a;
   a.y = y; a.partial = partial; a.counters = counters; a.status = status;
-  a.M = M; a.N = N; a.K = K; a.mpad = mpad; a.out_f32 = out_f32; a.stages = stages; a.split = split;
+  a.M = M; a.N = N; a.K = K; a.mpad = mpad; a.out_f32 = out_f32; a.stages = stages;
   const int grid = (int)(total < blocks ? total : blocks);
   return tb::launch(tb::gemm_skinny_kernel, dim3(grid), dim3(tb::SK_THREADS), smem, stream, map_w, map_x, a);
-}
-
-// The tiles of a product of these sizes run by `blocks` blocks: out[3 * tile] = first contributing
-// block, [+1] = last, [+2] = slot of the first one's partial (host memory, 3 ints per tile).
-// Returns the number of blocks the launch uses.
-int tb_gemm_skinny_tiles(int N, int K, int blocks, int* out) {
-  const long long KC = (K + tb::BK - 1) / tb::BK, NT = (N + tb::BN - 1) / tb::BN, total = KC * NT;
-  const long long grid = total < blocks ? total : blocks;
-  for (long long tile = 0; tile < NT; ++tile) {
-    const int p_lo = tb::block_of_chunk(tile * KC, total, grid), p_hi = tb::block_of_chunk((tile + 1) * KC - 1, total, grid);
-    out[3 * tile] = p_lo;
-    out[3 * tile + 1] = p_hi;
-    out[3 * tile + 2] = tb::range_start(p_lo, total, grid) >= tile * KC ? 0 : 1;
-  }
-  return (int)grid;
-}
-
-// y[t, n] = the sum of the partials of its tile, for every shared tile: a split output made whole.
-int tb_split_resolve(void* stream, void* y, const float* partial, const int* tiles, int mpad, int M, int N) {
-  if (M <= 0 || N <= 0) return 0;
-  if (N % 8 != 0) return TB_ERR_BAD_SIZE;
-  const long long groups = (long long)M * (N / 8);
-  return tb::launch(tb::split_resolve_kernel, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, stream,
-                    (__nv_bfloat16*)y, tb::SplitView{partial, tiles, mpad}, M, N);
 }
 
 }  // extern "C"

@@ -5,16 +5,17 @@
 // rotate_half), python/tandem/layers/triton_ops.py:21-113 (the fused prologue and the fused
 // add+norm, which add in float32 and round once, as these kernels do).
 #include "cache_layout.cuh"
-#include "split_output.cuh"
 #include "common.cuh"
 
 namespace tb {
 
 // ---------------------------------------------------------------------------------------------
-// Embedding: out[t, :] = float(table[ids[t], :]).  The residual stream is float32 in both modes.
+// Embedding: out[t, :] = scale * float(table[ids[t], :]) (+ float(pos_table[positions[t], :]) where
+// the model has a learned table of absolute positions).  The residual stream is float32 in both modes.
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ out, int H, int V) {
+                                 float* __restrict__ out, int H, int V, float scale, const int* __restrict__ positions,
+                                 const T* __restrict__ pos_table, int max_pos) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -25,6 +26,16 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     return;
   }
   const T* row = table + (size_t)id * H;
+  if (pos_table || scale != 1.f) {
+    const T* prow = nullptr;
+    if (pos_table) {
+      int pos = positions[t];
+      pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);  // the host checks positions
+      prow = pos_table + (size_t)pos * H;
+    }
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = scale * to_float(row[i]) + (prow ? to_float(prow[i]) : 0.f);
+    return;
+  }
   if (sizeof(T) == 2 && (H & 7) == 0) {  // 16 bytes in, two 16-byte stores out
     for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
       const uint4 raw = *reinterpret_cast<const uint4*>(row + i);
@@ -53,17 +64,23 @@ __global__ void take_tokens_kernel(int* __restrict__ ids, const int* __restrict_
   if (s >= 0 && s < num_tokens) ids[i] = tokens[s];
 }
 
+// Eight neighbouring bfloat16 values (16-byte aligned) as floats.
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&out)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); out[2 * j] = f.x; out[2 * j + 1] = f.y; }
+}
+
 // ---------------------------------------------------------------------------------------------
 // residual[src] += x[src] (if x); y[r] = residual[src] * rsqrt(mean(residual[src]^2) + eps) * w
 // with src = rows ? rows[r] : r.  One block per output row.
-// x may be a split output (bfloat16 only): the partials of its shared tiles are added on the way in.
 template <typename T>
 __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ residual,
                                    const float* __restrict__ weight, T* __restrict__ y,
-                                   const int* __restrict__ rows, int H, float eps, const SplitView sv) {
+                                   const int* __restrict__ rows, int H, float eps) {
   __shared__ float scratch[33];
   pdl_launch_dependents();
-  const SplitTile first = split_tile(sv, min((int)threadIdx.x * 8, H - 1));  // this thread's first columns (host-written table)
   pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -78,7 +95,7 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
       s1 = *reinterpret_cast<const float4*>(res + i + 4);
       if (xr) {
         float v[8];
-        split_load8(reinterpret_cast<const __nv_bfloat16*>(xr), sv, first, src, i, v);
+        load8(reinterpret_cast<const __nv_bfloat16*>(xr) + i, v);
         s0.x += v[0]; s0.y += v[1]; s0.z += v[2]; s0.w += v[3];
         s1.x += v[4]; s1.y += v[5]; s1.z += v[6]; s1.w += v[7];
         *reinterpret_cast<float4*>(res + i) = s0;
@@ -101,7 +118,7 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
       float4 s0 = *reinterpret_cast<const float4*>(res + i), s1 = *reinterpret_cast<const float4*>(res + i + 4);
       if (xr) {
         float v[8];
-        split_load8(reinterpret_cast<const __nv_bfloat16*>(xr), sv, i == (int)threadIdx.x * 8 ? first : split_tile(sv, i), src, i, v);
+        load8(reinterpret_cast<const __nv_bfloat16*>(xr) + i, v);
         s0.x += v[0]; s0.y += v[1]; s0.z += v[2]; s0.w += v[3];
         s1.x += v[4]; s1.y += v[5]; s1.z += v[6]; s1.w += v[7];
         *reinterpret_cast<float4*>(res + i) = s0;
@@ -227,7 +244,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
                                        const float* __restrict__ k_w, const float* __restrict__ cos_sin,
                                        T* __restrict__ k_cache, T* __restrict__ v_cache, int T_tokens, int nh,
                                        int nkv, int hd, int rd, int page_size, float eps, int write_kv,
-                                       int max_pos, const SplitView sv) {
+                                       int max_pos) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -239,19 +256,6 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, const int* __restric
   const int slot = slots ? slots[t] : -1;
   const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
   if (!is_q && (slot < 0 || !write_kv)) return;
-  if (sizeof(T) == 2 && sv.partial) {  // a split output (hd is a multiple of 8): this head's columns are made whole first
-    __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(qkv) + (size_t)t * heads * hd;
-    for (int c = lane; c < hd / 8; c += 32) {
-      const int n0 = h * hd + c * 8;
-      const int* info = sv.tiles + 3 * (n0 / SPLIT_BN);
-      if (info[0] == info[1]) continue;
-      float v[8];
-      split_load8(row, sv, t, n0, v);
-      *reinterpret_cast<uint4*>(row + n0) = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
-    }
-    __syncwarp();
-  }
-
   T* dst = x;   // q: in place.  k, v: the tile of (page, kv head); `row` is the token's row in it
   int row = -1;
   if (!is_q) {
@@ -400,10 +404,10 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* __restrict__ qkv, con
 // ---------------------------------------------------------------------------------------------
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I, const SplitView sv) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int I) {
   pdl_launch_dependents();
   pdl_wait();
-  if (sizeof(T) == 2 && (I & 7) == 0 && !sv.partial) {  // plain input: two groups of eight per thread and turn, four loads in flight
+  if (sizeof(T) == 2 && (I & 7) == 0) {  // two groups of eight per thread and turn, four loads in flight
     const long long groups = total / 8, stride = (long long)gridDim.x * blockDim.x;
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < groups; e += 2 * stride) {
       uint4 g4[2], u4[2];
@@ -438,26 +442,6 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
     }
     return;
   }
-  if (sizeof(T) == 2 && (I & 7) == 0) {  // eight elements per thread: 16-byte loads and stores (split input)
-    const long long groups = total / 8;
-    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < groups; e += (long long)gridDim.x * blockDim.x) {
-      const long long t = (e * 8) / I;
-      const int i = (int)((e * 8) % I);
-      const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(gu) + t * 2 * I;
-      float g[8], u[8];
-      split_load8(row, sv, (int)t, i, g);
-      split_load8(row, sv, (int)t, I + i, u);
-      uint4 r;
-      uint32_t* r2 = reinterpret_cast<uint32_t*>(&r);
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        // the result is rounded to bfloat16: the fast exponential and division are exact enough by far
-        r2[j] = pack2(__fdividef(g[2 * j], 1.f + __expf(-g[2 * j])) * u[2 * j],
-                      __fdividef(g[2 * j + 1], 1.f + __expf(-g[2 * j + 1])) * u[2 * j + 1]);
-      *reinterpret_cast<uint4*>(out + e * 8) = r;
-    }
-    return;
-  }
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
        e += (long long)gridDim.x * blockDim.x) {
     const long long t = e / I;
@@ -468,14 +452,38 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Output-head hooks of architectures that scale or cap their logits: x <- scale * x, then
+// x <- cap * tanh(x / cap) where cap > 0.
+__global__ void scale_softcap_kernel(float* __restrict__ x, long long n, float scale, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float v = x[i] * scale;
+    if (cap > 0.f) v = cap * tanhf(v / cap);
+    x[i] = v;
+  }
+}
+
 }  // namespace tb
 
 extern "C" {
 
+// positions / pos_table [max_pos, H] may be null (no learned absolute positions).
 int tb_embedding(void* stream, const int* ids, const void* table, float* out, int T_tokens, int H, int V,
-                 int dtype) {
+                 int dtype, float scale, const int* positions, const void* pos_table, int max_pos) {
   if (T_tokens <= 0) return 0;
-  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::embedding_kernel<T>, dim3(T_tokens), dim3(256), 0, stream, ids, (const T*)table, out, H, V));
+  if (pos_table && (!positions || max_pos <= 0)) return TB_ERR_BAD_SIZE;
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::embedding_kernel<T>, dim3(T_tokens), dim3(256), 0, stream, ids, (const T*)table, out, H, V,
+                                      scale, positions, (const T*)pos_table, max_pos));
+}
+
+// logits = scale * logits, then cap * tanh(logits / cap) where cap > 0 (in place, float32).
+int tb_scale_softcap(void* stream, float* logits, long long n, float scale, float cap) {
+  if (n <= 0) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return tb::launch(tb::scale_softcap_kernel, dim3((int)blocks), dim3(256), 0, stream, logits, n, scale, cap);
 }
 
 int tb_take_tokens(void* stream, int* ids, const int* source, const int* tokens, int n, int num_tokens) {
@@ -483,30 +491,24 @@ int tb_take_tokens(void* stream, int* ids, const int* source, const int* tokens,
   return tb::launch(tb::take_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, source, tokens, n, num_tokens);
 }
 
-// partial, tiles, mpad: x is a split output (split_output.cuh); null partial: a plain tensor.
 int tb_add_rmsnorm(void* stream, const void* x, float* residual, const float* weight, void* y, const int* rows,
-                   int num_rows, int H, float eps, int dtype, const float* partial, const int* tiles, int mpad) {
+                   int num_rows, int H, float eps, int dtype) {
   if (num_rows <= 0) return 0;
-  if (partial && (dtype != TB_BF16 || (H & 7))) return TB_ERR_BAD_SIZE;
   const int threads = H >= 4096 ? 512 : 256;
-  if (dtype == TB_BF16 && !partial && !rows && num_rows >= 512 && (H & 7) == 0 && H <= threads * 8)
+  if (dtype == TB_BF16 && !rows && num_rows >= 512 && (H & 7) == 0 && H <= threads * 8)
     return tb::launch(tb::add_rmsnorm_rows2_kernel, dim3((num_rows + 1) / 2), dim3(threads), 0, stream, (const __nv_bfloat16*)x,
                       residual, weight, (__nv_bfloat16*)y, num_rows, H, eps);
-  const tb::SplitView sv{partial, tiles, mpad};
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::add_rmsnorm_kernel<T>, dim3(num_rows), dim3(threads), 0, stream, (const T*)x, residual,
-                                      weight, (T*)y, rows, H, eps, sv));
+                                      weight, (T*)y, rows, H, eps));
 }
 
 int tb_qk_norm_rope_kv(void* stream, void* qkv, const int* positions, const int* slots, const float* q_w,
                        const float* k_w, const float* cos_sin, void* k_cache, void* v_cache, int T_tokens, int nh,
-                       int nkv, int hd, int rd, int page_size, float eps, int write_kv, int max_pos, int dtype,
-                       const float* partial, const int* tiles, int mpad) {
+                       int nkv, int hd, int rd, int page_size, float eps, int write_kv, int max_pos, int dtype) {
   if (T_tokens <= 0) return 0;
   if (rd < 0 || rd > hd || (rd & 1) || page_size <= 0) return TB_ERR_BAD_SIZE;
-  if (partial && (dtype != TB_BF16 || (hd & 7))) return TB_ERR_BAD_SIZE;
-  const tb::SplitView sv{partial, tiles, mpad};
   const bool pow2 = hd >= 16 && hd <= 256 && (hd & (hd - 1)) == 0;
-  if (dtype == TB_BF16 && !partial && rd == hd && pow2 && T_tokens <= 65535 * 32) {
+  if (dtype == TB_BF16 && rd == hd && pow2 && T_tokens <= 65535 * 32) {
     const int heads = nh + 2 * nkv, per_warp = 512 / hd;
     // few tokens: spread a token's heads over several blocks; many: one block keeps its angles for 8 x more heads
     const int heads_per_block = T_tokens >= 256 ? 8 * 4 * per_warp : 4 * per_warp;
@@ -519,18 +521,15 @@ int tb_qk_norm_rope_kv(void* stream, void* qkv, const int* positions, const int*
   const int blocks = (int)((warps + 3) / 4);
   TB_DISPATCH_DTYPE(dtype, tb::launch(tb::qk_norm_rope_kv_kernel<T>, dim3(blocks), dim3(128), 0, stream, (T*)qkv, positions, slots,
                                       q_w, k_w, cos_sin, (T*)k_cache, (T*)v_cache, T_tokens, nh, nkv, hd, rd, page_size, eps,
-                                      write_kv, max_pos, sv));
+                                      write_kv, max_pos));
 }
 
-int tb_silu_mul(void* stream, const void* gu, void* out, int T_tokens, int I, int dtype, const float* partial,
-                const int* tiles, int mpad) {
+int tb_silu_mul(void* stream, const void* gu, void* out, int T_tokens, int I, int dtype) {
   const long long total = (long long)T_tokens * I;
   if (total <= 0) return 0;
-  if (partial && (dtype != TB_BF16 || (I & 7))) return TB_ERR_BAD_SIZE;
-  const tb::SplitView sv{partial, tiles, mpad};
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::silu_mul_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (const T*)gu, (T*)out, total, I, sv));
+  TB_DISPATCH_DTYPE(dtype, tb::launch(tb::silu_mul_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (const T*)gu, (T*)out, total, I));
 }
 
 }  // extern "C"

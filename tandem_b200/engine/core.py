@@ -89,6 +89,6 @@ def build_executor(decoder: Decoder, page_size: int = 16, num_pages: Optional[in
             raise ValueError(f"kv cache of {cache_gb} GiB holds no page of {per_page} bytes")
     kv_needs = decoder.kv_needs()
     manager = CacheManager(kv_needs, page_size, num_pages, max_requests)
-    storage = CacheStorage(manager, kv_needs, [r.cache_of for r in decoder.plan.order], decoder.state_needs(),
-                           decoder.dtype, decoder.device)
+    storage = CacheStorage(manager, kv_needs, decoder.cache_sources(), decoder.state_needs(), decoder.dtype,
+                           decoder.device, users=decoder.cache_users)
     return Executor(decoder, manager, storage)

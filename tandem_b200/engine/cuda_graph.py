@@ -9,10 +9,14 @@ carry token 0 at position 0 with a negative cache slot (the cache-write kernel s
 attention item; their outputs are never read.  Logits and sampling stay outside the graph
 (cuda_graph.py:10-11 of the reference).
 
-Only models whose mixers all declare ``capturable = True`` (everything they do in ``forward`` is
-kernel launches on the current stream, with no host-side reading of the batch) run under graphs.
-Mixers that asked for per-step arrays (``step_arrays``) say how large they can get for a bucket
-through ``step_array_capacity(bucket, max_model_len, page_size, out)``.
+Only models whose mixers all declare ``capturable = True`` run under graphs: everything such a
+mixer does in ``forward`` is kernel launches on the current stream, and what it knows of the batch
+it reads from the device arrays of the context (``positions``, ``seq_starts``, ``state_slots``,
+its own ``extras``), never from the host-side lists, which a replay does not see.  A mixer with
+per-request state indexes its state tensor by ``ctx.state_slots`` on the device; padding rows
+point at the state tensor's last row, which belongs to no request.  Mixers that asked for per-step
+arrays (``step_arrays``) say how large they can get for a bucket through
+``step_array_capacity(bucket, max_model_len, page_size, out)``.
 """
 
 from __future__ import annotations
@@ -56,8 +60,14 @@ class _Captured:
         for k, n in self.sizes.items():
             self.offsets[k] = off
             off += -(-n // 4) * 4
-        self.host = torch.zeros(off, dtype=torch.int32, pin_memory=True)
-        self.host_np = self.host.numpy()
+        # Two pinned copies of the description, used in turn: with overlap scheduling the host fills
+        # step N+1 while the copy of step N may still be on its way to the device, and a buffer is
+        # written again only after the copy that last read it has landed (its event).
+        self.hosts = [torch.zeros(off, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.copied = [None, None]
+        self.turn = 0
+        self.hosts_np = [h.numpy() for h in self.hosts]
+        self.host, self.host_np = self.hosts[0], self.hosts_np[0]
         self.device = torch.zeros(off, dtype=torch.int32, device=executor.device)
         self.graph = None
         self.logits = None
@@ -73,6 +83,10 @@ class _Captured:
     def fill(self, entries: Sequence[StepEntry]) -> StepContext:
         """Write this step's batch description into the pinned buffer and copy it to the device."""
         ex, m, ps, Bk, B = self.executor, self.executor.manager, self.executor.manager.page_size, self.bucket, len(entries)
+        self.turn = 1 - self.turn
+        self.host, self.host_np = self.hosts[self.turn], self.hosts_np[self.turn]
+        if self.copied[self.turn] is not None:
+            self.copied[self.turn].synchronize()  # almost always long past
         starts = [m.num_tokens(e.request_id) for e in entries]
         pad = Bk - B
         self.put("ids", [int(e.tokens[0]) if e.pending is None else 0 for e in entries] + [0] * pad)
@@ -83,7 +97,7 @@ class _Captured:
         self.put("cu", list(range(Bk + 1)))
         self.put("starts", starts + [0] * pad)
         slots = [m.slot(e.request_id) for e in entries]
-        self.put("slots", slots + [0] * pad)
+        self.put("slots", slots + [ex.storage.scratch_slot] * pad)
         self.put("rows", list(range(Bk)))
         for g in range(len(m.groups)):
             o = self.offsets[("table", g)]
@@ -113,6 +127,9 @@ class _Captured:
         for g in range(len(m.groups)):
             ctx.tables[g] = (self.view(("table", g)).view(Bk, self.width), self.view(("kvslots", g)))
         self.device.copy_(self.host, non_blocking=True)
+        if self.copied[self.turn] is None:
+            self.copied[self.turn] = torch.cuda.Event()
+        self.copied[self.turn].record()
         ex.h2d_bytes_last = self.host.numel() * 4
         if any_pending:  # tokens of the step in flight enter the batch on the device, before the graph reads it
             ops.take_tokens(self.view("ids"), self.view("pending"), ex.pending_tokens)
@@ -137,12 +154,10 @@ class DecodeGraphs:
 
     @classmethod
     def maybe(cls, executor: Executor, max_batch: int, max_model_len: int):
-        """Graphs need every mixer of the model to be capturable: no per-request state tensors
-        touched from the host, and array capacities known for those that plan on the host."""
-        if executor.storage.state:
-            return None
-        for layer in executor.decoder.layers:
-            if not getattr(layer.mixer, "capturable", False):
+        """Graphs need every mixer of the model to be capturable, and array capacities known for
+        those that plan on the host."""
+        for mixer in executor.decoder.mixers():
+            if not getattr(mixer, "capturable", False):
                 return None
         for mixer in executor.mixers:
             if not hasattr(mixer, "step_array_capacity"):

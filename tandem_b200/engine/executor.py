@@ -40,7 +40,7 @@ class Executor:
         self.device = decoder.device
         self.vocab_size = decoder.plan.embedding.vocab_size
         self.max_position = decoder.plan.max_position
-        self.mixers = [layer.mixer for layer in getattr(decoder, "layers", []) if hasattr(layer.mixer, "step_arrays")]
+        self.mixers = [m for m in (decoder.mixers() if hasattr(decoder, "mixers") else []) if hasattr(m, "step_arrays")]
         self.num_steps = 0
         self.h2d_bytes_last = 0  # bytes of the last step's batch description copied to the device
         self.pending_tokens: Optional[torch.Tensor] = None  # int32 on the device: tokens of the step in flight

@@ -21,6 +21,8 @@ from tandem_b200.engine.core import build_executor, load_model
 from tandem_b200.engine.executor import StepEntry
 from tandem_b200.engine.request import PLACEHOLDER, Request, RequestOutput, RequestStatus
 from tandem_b200.engine.scheduler import Scheduler, StepPlan
+from tandem_b200.engine.text import OutputText
+from tandem_b200.kernels import ops
 from tandem_b200.sampling.params import SamplingParams
 from tandem_b200.sampling.sampler import sample_on_device
 
@@ -37,15 +39,23 @@ class _InFlight:
         self.host = None
         self.event = None
         if tokens.is_cuda:
-            self.host = torch.empty(tokens.shape, dtype=tokens.dtype, pin_memory=True)
-            self.host.copy_(tokens, non_blocking=True)
+            # the tokens and, behind them, the word in which kernels record a fault they survived
+            n = tokens.numel()
+            self.host = torch.empty(n + 1, dtype=torch.int32, pin_memory=True)
+            self.host[:n].copy_(tokens, non_blocking=True)
+            self.host[n:].copy_(ops.status_word(tokens.device), non_blocking=True)
             self.event = torch.cuda.Event()
             self.event.record()
 
     def resolve(self) -> dict:
+        """Request id -> token.  Raises ``KernelError`` if a kernel of the step recorded a fault (a
+        bounded wait that gave up, a missing page): its tokens were sampled from invalid logits."""
         if self.event is not None:
             self.event.synchronize()
             values = self.host.tolist()
+            status = values.pop()
+            if status:
+                ops.raise_status(self.tokens.device, status)
         else:
             values = self.tokens.tolist()
         return {r.request_id: t for r, t in zip(self.requests, values)}
@@ -83,8 +93,9 @@ class LLMEngine:
         self.requests: dict = {}
         self._ids = itertools.count()
         self.num_steps = 0
+        self.trace = None  # engine.trace.TraceWriter: every launched step, in the replay tool's format
         self.graphs = None
-        if config.cuda_graph and decoder.dtype == torch.bfloat16:
+        if config.cuda_graph:
             from tandem_b200.engine.cuda_graph import DecodeGraphs
 
             self.graphs = DecodeGraphs.maybe(self.executor, config.cuda_graph_max_bs, self.max_model_len)
@@ -110,6 +121,9 @@ class LLMEngine:
                 raise ValueError(f"token id {t} is outside the vocabulary [0, {vocab})")
         if len(prompt_token_ids) >= self.max_model_len:
             raise ValueError(f"prompt has {len(prompt_token_ids)} tokens; max_model_len is {self.max_model_len}")
+        if sp.stop and self.tokenizer is None:
+            raise ValueError("stop strings are matched against decoded text and need a tokenizer; this engine has none "
+                             "(use stop_token_ids, or give the engine a tokenizer)")
         index = next(self._ids)
         rid = request_id or f"req-{index}"
         if rid in self.requests:
@@ -117,6 +131,8 @@ class LLMEngine:
         # a request without a seed draws from the engine's seed and its own arrival number
         seed = sp.seed if sp.seed is not None else (self.config.seed * 1_000_003 + index + 1)
         req = Request(rid, list(prompt_token_ids), sp, self.eos_token_ids, sample_seed=seed)
+        if self.tokenizer is not None:
+            req.text = OutputText(self.tokenizer, sp.skip_special_tokens, sp.stop)
         self.scheduler.add_request(req)
         self.requests[rid] = req
         return rid
@@ -154,7 +170,7 @@ class LLMEngine:
         launched = None
         if not plan.is_empty:
             launched = self._launch(plan)
-            self.scheduler.on_launch(plan)
+            self.scheduler.book_launch(plan)
             for row, req in enumerate(launched.requests):
                 req.inflight_row = row
             self.num_steps += 1
@@ -163,7 +179,7 @@ class LLMEngine:
         previous, self.inflight = self.inflight, launched
         self.executor.pending_tokens = launched.tokens if launched is not None else None
         if previous is not None:
-            outputs += self._emit(self.scheduler.update_resolved(previous.plan, previous.resolve()))
+            outputs += self._emit(self.scheduler.deliver_tokens(previous.plan, previous.resolve()))
         return outputs
 
     def drain(self) -> list:
@@ -172,12 +188,17 @@ class LLMEngine:
         self.executor.pending_tokens = None
         if previous is None:
             return []
-        return self._emit(self.scheduler.update_resolved(previous.plan, previous.resolve()))
+        return self._emit(self.scheduler.deliver_tokens(previous.plan, previous.resolve()))
 
     def _emit(self, updated: list) -> list:
         outputs = []
         for req in updated:
-            outputs.append(self._make_output(req))
+            delta = ""
+            if req.text is not None:
+                delta = req.text.feed(req.output_token_ids, req.finished)
+                if req.text.stopped and not req.finished:  # llm_engine.py:382-383 of the reference
+                    self.scheduler.finish_request(req, RequestStatus.FINISHED_STOPPED)
+            outputs.append(self._make_output(req, delta))
             if req.finished:
                 self.requests.pop(req.request_id, None)
         return outputs
@@ -188,16 +209,28 @@ class LLMEngine:
         entries = []
         for s in plan.scheduled:
             req, n = s.request, s.num_tokens
-            start = req.num_computed_tokens
-            tokens = req.token_ids_in_range(start, start + n)
+            tokens = req.next_tokens(n)
             # only the newest token can still be on its way (model_runner.py:95-99 of the reference)
             pending = req.inflight_row if tokens[-1] == PLACEHOLDER else None
-            entries.append(StepEntry(req.request_id, tokens, [n - 1] if start + n >= req.num_tokens else [], pending))
+            reaches_newest = req.num_computed_tokens + n >= req.num_tokens
+            entries.append(StepEntry(req.request_id, tokens, [n - 1] if reaches_newest else [], pending))
         return entries
+
+    def record_steps(self, path: str) -> None:
+        """Write every step from now on to ``path`` as the replay tool reads it (one JSON object a
+        line), so that this run's logits can be reproduced and dumped by ``trace_run``.  What
+        12vivi/tandem's TANDEM_TRACE records of a step (python/tandem/executor/step_timer.py:57-68),
+        with the tokens themselves added."""
+        from tandem_b200.engine.trace import TraceWriter
+
+        self.drain()
+        self.trace = TraceWriter(path)
 
     def _launch(self, plan: StepPlan) -> _InFlight:
         """Run the plan's step and its sampling on the device; nothing is read back here."""
         entries = self.entries_of(plan)
+        if self.trace is not None:
+            self.trace.step(plan, entries)
         sampling = [s.request for s, e in zip(plan.scheduled, entries) if e.want]
         if self.graphs is not None and self.graphs.takes(entries):
             logits = self.graphs.run(entries)
@@ -210,19 +243,17 @@ class LLMEngine:
             tokens = torch.empty(0, dtype=torch.int32, device=logits.device)
         return _InFlight(plan, sampling, tokens)
 
-    def _make_output(self, req: Request) -> RequestOutput:
+    def _make_output(self, req: Request, delta_text: str = "") -> RequestOutput:
         metrics = {}
         if req.first_token_time is not None:
             metrics["ttft"] = req.first_token_time - req.arrival_time
         if req.finished and req.finish_time is not None:
             metrics["latency"] = req.finish_time - req.arrival_time
             metrics["preemptions"] = req.num_preemptions
-        text = ""
-        if self.tokenizer is not None and req.finished:
-            text = self.tokenizer.decode(req.output_token_ids, skip_special_tokens=req.sampling_params.skip_special_tokens)
-        return RequestOutput(req.request_id, req.prompt_token_ids,
-                             list(req.output_token_ids) if req.finished else [], text, list(req.new_token_ids),
-                             req.finished, req.finish_reason, metrics, req.num_output_tokens)
+        text = req.text.text if req.text is not None else ""
+        return RequestOutput(req.request_id, req.prompt_token_ids, req.output_token_ids if req.finished else [], text,
+                             list(req.new_token_ids), req.finished, req.finish_reason, metrics, req.num_known_outputs,
+                             delta_text)
 
     # ------------------------------------------------------------------ offline API
     def generate(self, prompts: Sequence[PromptType],

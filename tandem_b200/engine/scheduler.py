@@ -1,34 +1,33 @@
 """Continuous batching with chunked prefill under a token budget.
 
-The state machine of python/tandem/scheduler/scheduler.py:216-288,364-407 without its prefix
-cache, host tier and short-prefill lane:
+What a step is made of (the rules of 12vivi/tandem's scheduler, python/tandem/scheduler/scheduler.py:216-288,
+without its prefix cache, host tier and short-prefill lane):
 
-* two queues, ``waiting`` (first in, first out) and ``running``;
-* each step has ``max_num_batched_tokens`` tokens to give; a request takes
-  ``min(tokens it still lacks, budget left)``, so a prompt is cut into portions wherever the
-  budget ends;
-* ``prefill_first``: while anything waits or is still reading its prompt, a step carries no
-  decoding request (falling back to a decode step if nothing could be prefilled);
-  ``decode_first``: every decoding request first, one token each, then prompt portions, then
-  admissions, all in one mixed step;
-* admission in arrival order while the budget, ``max_num_seqs`` and the pages allow; a request
-  that does not fit stays at the head of the queue and nothing behind it overtakes it.
+* requests wait in arrival order and run until they end; a step has ``max_num_batched_tokens``
+  tokens to give, and every request it serves takes ``min(tokens it lacks, tokens left)``: a
+  prompt is cut wherever the budget ends, and a decoding request lacks exactly one token;
+* ``decode_first`` serves the decoding requests, then the requests still reading their prompts,
+  then admits from the queue, all in one step; ``prefill_first`` leaves the decoding requests out
+  of a step while any prompt work is there, unless that step would come out empty;
+* admission stops at the first request that does not fit (budget, ``max_num_seqs``, pages):
+  nothing overtakes the head of the queue.
 
-When pages run out for a running request, the request that is last in this step's order (the
-youngest, not yet scheduled) is preempted: everything it holds is given back, its computed-token
-count returns to zero, and it goes to the *front* of the waiting queue to be recomputed later,
-its generated tokens included.  A step that preempted admits nobody.  Because no request may be
-longer than one group's whole pool (``token_capacity``), the oldest request can always finish,
-so the queue always drains.
+When the pool cannot give a served request its pages, requests are taken from the *end* of the
+step's service order (the youngest, not yet served), one at a time, until the pages are there:
+each gives back all it holds, forgets how far it had been computed, and moves to the *front* of
+the queue, to be read again later with the tokens it has generated.  The request in need may turn
+out to be the last one itself.  A step that took pages away admits nobody.  No request may grow
+beyond one group's whole pool (``token_capacity``), so the oldest request can always finish and
+the queue always drains.
 
-Overlap scheduling (scheduler.py:409-469 of the reference): the engine may launch step N before
-the tokens of step N-1 have reached the host.  ``on_launch`` books a launched step at once, with a
-placeholder for every token it will produce; ``update_resolved`` fills the placeholders in one
-step later.  A request that turns out to have ended (its token was an end token, or it was
-aborted) may already sit in the next launched step: that step's token for it is dropped.  A
-request whose token in flight is the last it may produce is not scheduled again.  The engine
-resolves the step in flight *before* it schedules whenever pages are so short that a preemption
-is possible (``may_preempt``), so a preempted request never carries a placeholder.
+A step's outcome is applied in two halves, because the engine may launch step N before the host
+has seen the tokens of step N-1 (overlap scheduling; scheduler.py:409-469 of the reference):
+``book_launch`` counts the step's tokens as computed and puts a placeholder where each new token
+will go; ``deliver_tokens`` puts the values in, one step later, and ends what has to end.  A
+request that ended meanwhile (its token was an end token, or it was aborted) may sit in the step
+launched after: that step's token for it is dropped.  A request whose token in flight is the last
+it may produce is not served again.  ``update_from_output`` is both halves at once, for a loop
+that reads every step's tokens before it plans the next.
 """
 
 from __future__ import annotations
@@ -36,9 +35,12 @@ from __future__ import annotations
 import time
 from collections import deque
 from dataclasses import dataclass, field
+from typing import Optional
 
 from tandem_b200.cache.manager import CacheManager
-from tandem_b200.engine.request import PLACEHOLDER, Request, RequestStatus
+from tandem_b200.engine.request import Request, RequestStatus
+
+POLICIES = ("prefill_first", "decode_first")
 
 
 @dataclass
@@ -64,196 +66,169 @@ class StepPlan:
 class Scheduler:
     def __init__(self, cache: CacheManager, max_num_seqs: int, max_num_batched_tokens: int, max_model_len: int,
                  policy: str = "prefill_first") -> None:
-        if policy not in ("decode_first", "prefill_first"):
-            raise ValueError(f"unknown scheduling policy {policy!r}")
-        self.policy = policy
-        self.cache = cache
-        self.max_num_seqs = max_num_seqs
-        self.max_num_batched_tokens = max_num_batched_tokens
-        # a request alone must fit into the pool, or preemption could never help it
-        self.token_capacity = cache.num_pages * cache.page_size
+        if policy not in POLICIES:
+            raise ValueError(f"unknown scheduling policy {policy!r} (known: {', '.join(POLICIES)})")
+        self.policy, self.cache = policy, cache
+        self.max_num_seqs, self.max_num_batched_tokens = max_num_seqs, max_num_batched_tokens
+        self.token_capacity = cache.num_pages * cache.page_size  # what one request can hold when it has the pool to itself
         self.max_model_len = min(max_model_len, self.token_capacity)
         self.waiting: deque = deque()
         self.running: list = []
         self.num_preemptions = 0
 
-    # ------------------------------------------------------------------ queue
+    # ------------------------------------------------------------------ requests come and go
     def add_request(self, req: Request) -> None:
         if req.num_prompt_tokens >= self.max_model_len:
-            raise ValueError(f"prompt has {req.num_prompt_tokens} tokens; at most {self.max_model_len - 1} fit "
-                             f"(max_model_len and the cache pool of {self.token_capacity} tokens)")
+            raise ValueError(f"a prompt of {req.num_prompt_tokens} tokens leaves no room for a new token: requests hold at "
+                             f"most {self.max_model_len} tokens (max_model_len, and the cache pool of {self.token_capacity})")
         req.status = RequestStatus.WAITING
         self.waiting.append(req)
 
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting) or bool(self.running)
 
     def finish_request(self, req: Request, status: RequestStatus) -> None:
-        """Finish a request from outside the step loop (abort)."""
-        if req.finished:
-            return
-        if req in self.running:
-            self.running.remove(req)
-        elif req in self.waiting:
-            self.waiting.remove(req)
-        self._release(req)
-        req.status = status
-        req.finish_time = time.monotonic()
+        """End a request from outside the step loop (an abort, a stop string)."""
+        if not req.finished:
+            self._retire(req, status, time.monotonic())
 
-    # ------------------------------------------------------------------ pages
-    def _release(self, req: Request) -> None:
+    def _retire(self, req: Request, status: RequestStatus, now: float) -> None:
+        for line in (self.running, self.waiting):
+            if req in line:
+                line.remove(req)
+        self._give_back(req)
+        req.drop_unknown()
+        req.status, req.finish_time = status, now
+
+    def _give_back(self, req: Request) -> None:
         if self.cache.has(req.request_id):
             self.cache.end(req.request_id)
 
+    # ------------------------------------------------------------------ planning a step
+    def schedule(self) -> StepPlan:
+        plan = StepPlan()
+        prompt_work = bool(self.waiting) or any(not r.is_decoding for r in self.running)
+        if self.policy == "prefill_first" and prompt_work:
+            self._fill(plan, with_decoding=False)
+            if plan.scheduled:
+                return plan
+        # the same plan goes on: what a first attempt took away stays recorded, and keeps the queue closed
+        self._fill(plan, with_decoding=True)
+        return plan
+
+    def _service_order(self, with_decoding: bool) -> list:
+        reading = [r for r in self.running if not r.is_decoding]
+        if not with_decoding:
+            return reading
+        return [r for r in self.running if r.is_decoding and not self._last_token_in_flight(r)] + reading
+
+    def _fill(self, plan: StepPlan, with_decoding: bool) -> None:
+        left = self.max_num_batched_tokens
+        line = self._service_order(with_decoding)
+        served = 0
+        while served < len(line) and left > 0:
+            req = line[served]
+            share = min(req.tokens_lacking, left)
+            if share > 0:
+                if not self._make_room(req, share, line, plan):
+                    break  # the request itself had to go: nobody is left behind it
+                plan.scheduled.append(ScheduledRequest(req, share))
+                left -= share
+            served += 1
+        if not plan.preempted:
+            self._admit(plan, left)
+
+    def _make_room(self, req: Request, share: int, line: list, plan: StepPlan) -> bool:
+        """Pages for ``share`` more tokens of ``req``, taken from the end of the line if need be.
+        False: ``req`` was the end of the line and has been preempted itself."""
+        while not self.cache.grow(req.request_id, req.num_computed_tokens + share):
+            youngest = line.pop()
+            self._preempt(youngest)
+            plan.preempted.append(youngest)
+            if youngest is req:
+                return False
+        return True
+
     def _preempt(self, req: Request) -> None:
-        self._release(req)
+        self.running.remove(req)
+        self._give_back(req)
         req.num_computed_tokens = 0
         req.status = RequestStatus.WAITING
         req.num_preemptions += 1
         self.num_preemptions += 1
         self.waiting.appendleft(req)
 
-    # ------------------------------------------------------------------ schedule
-    def schedule(self) -> StepPlan:
-        if self.policy == "prefill_first" and (self.waiting or any(not r.is_decoding for r in self.running)):
-            plan = self._schedule(decodes=False)
-            if not plan.is_empty:
-                return plan
-        return self._schedule(decodes=True)
-
-    def _schedule(self, decodes: bool) -> StepPlan:
-        plan = StepPlan()
-        budget = self.max_num_batched_tokens
-        order = ([r for r in self.running if r.is_decoding and not self._awaiting_last_token(r)] if decodes else []) + \
-                [r for r in self.running if not r.is_decoding]
-
-        # 1) running requests: decoding ones first, then prompt portions
-        i = 0
-        while i < len(order) and budget > 0:
-            req = order[i]
-            n = min(req.num_tokens - req.num_computed_tokens, budget)
-            if n <= 0:
-                i += 1
-                continue
-            preempted_self = False
-            while not self.cache.grow(req.request_id, req.num_computed_tokens + n):
-                victim = order.pop()
-                self.running.remove(victim)
-                self._preempt(victim)
-                plan.preempted.append(victim)
-                if victim is req:
-                    preempted_self = True
-                    break
-            if preempted_self:
-                break
-            plan.scheduled.append(ScheduledRequest(req, n))
-            budget -= n
-            i += 1
-
-        # 2) admissions, unless this step had to preempt
-        while not plan.preempted and self.waiting and budget > 0 and len(self.running) < self.max_num_seqs:
+    def _admit(self, plan: StepPlan, left: int) -> None:
+        while self.waiting and left > 0 and len(self.running) < self.max_num_seqs:
             req = self.waiting[0]
-            n = min(req.num_tokens - req.num_computed_tokens, budget)
+            share = min(req.tokens_lacking, left)
             self.cache.begin(req.request_id)
-            if not self.cache.grow(req.request_id, n):
+            if not self.cache.grow(req.request_id, share):
                 self.cache.end(req.request_id)
-                break
+                return  # the head of the queue waits, and so does everyone behind it
             self.waiting.popleft()
             req.status = RequestStatus.RUNNING
             self.running.append(req)
-            plan.scheduled.append(ScheduledRequest(req, n))
-            budget -= n
-        return plan
+            plan.scheduled.append(ScheduledRequest(req, share))
+            left -= share
 
-    # ------------------------------------------------------------------ update
-    def update_from_output(self, plan: StepPlan, sampled: dict) -> list:
-        """Apply one step's results: ``sampled`` maps request id -> new token for the requests
-        whose portion reached their newest token.  Returns those requests."""
-        now = time.monotonic()
-        updated = []
-        for s in plan.scheduled:
-            req = s.request
-            req.new_token_ids = []
-            req.num_computed_tokens += s.num_tokens
-            self.cache.commit(req.request_id, s.num_tokens)
-            token = sampled.get(req.request_id)
-            if token is None:  # a portion in the middle of the prompt: no logits this step
-                continue
-            if req.first_token_time is None:
-                req.first_token_time = now
-            self._append_token(req, int(token))
-            updated.append(req)
-            if req.finished:
-                self.running.remove(req)
-                self._release(req)
-                req.finish_time = now
-        return updated
-
-    # ------------------------------------------------------------------ overlap scheduling
-    def _awaiting_last_token(self, req: Request) -> bool:
-        """The token it has in flight is the last one it may produce (scheduler.py:417-421)."""
-        return req.has_pending_token and (req.num_output_tokens >= req.sampling_params.max_tokens
-                                          or req.num_tokens >= self.max_model_len)
+    def _last_token_in_flight(self, req: Request) -> bool:
+        """The token on its way is the last this request may produce."""
+        return req.has_pending_token and self._length_reached(req, req.num_output_tokens, req.num_tokens)
 
     def may_preempt(self) -> bool:
-        """Could the next ``schedule`` run out of pages for a running request?  Every running
-        request may need one more page, and prompt portions at most a budget's worth."""
-        ps = self.cache.page_size
-        need = len(self.running) + -(-self.max_num_batched_tokens // ps) + 1
+        """Could the next ``schedule`` run short of pages for a running request?  Each may need one
+        more page, and prompt portions at most a budget's worth.  The engine then reads the step in
+        flight first, so that no request with a placeholder is ever preempted."""
+        need = len(self.running) + -(-self.max_num_batched_tokens // self.cache.page_size) + 1
         return any(self.cache.free_pages(g) < need for g in range(len(self.cache.groups)))
 
-    def on_launch(self, plan: StepPlan) -> None:
-        """Book a step that has been launched: its tokens count as computed, and every request
-        that reaches its newest token gets a placeholder for the token on its way."""
+    # ------------------------------------------------------------------ a step's outcome
+    def book_launch(self, plan: StepPlan) -> None:
+        """The plan's step has been launched: its tokens count as computed, and a request whose
+        portion reaches its newest token expects one more."""
         for s in plan.scheduled:
             req = s.request
-            produces = req.num_computed_tokens + s.num_tokens >= req.num_tokens
             req.num_computed_tokens += s.num_tokens
             self.cache.commit(req.request_id, s.num_tokens)
-            if produces:
-                req.output_token_ids.append(PLACEHOLDER)
+            if req.num_computed_tokens >= req.num_tokens:
+                req.expect_token()
 
-    def update_resolved(self, plan: StepPlan, sampled: dict) -> list:
-        """The tokens of a launched step have arrived: fill the placeholders in, finish what ends."""
+    def deliver_tokens(self, plan: StepPlan, sampled: dict) -> list:
+        """The tokens of a launched step have arrived (request id -> token, for the requests that
+        were promised one).  Returns the requests that got a token, ended ones included."""
         now = time.monotonic()
-        updated = []
+        got = []
         for s in plan.scheduled:
             req = s.request
-            token = sampled.get(req.request_id)
-            if token is None:
-                continue
+            if req.request_id not in sampled:
+                continue  # a portion inside the prompt
             req.new_token_ids = []
-            if req.finished:  # ended (or was aborted) while this step was in flight: its token is dropped
-                del req.output_token_ids[req.num_resolved_outputs:]
-                continue
-            token = int(token)
-            req.output_token_ids[req.num_resolved_outputs] = token
-            req.num_resolved_outputs += 1
-            req.new_token_ids.append(token)
+            if req.finished:
+                continue  # ended while this step was in flight: its token is of no use
+            token = int(sampled[req.request_id])
+            req.receive_token(token)
             if req.first_token_time is None:
                 req.first_token_time = now
-            updated.append(req)
-            if token in req.eos_token_ids or token in req.stop_token_ids:
-                status = RequestStatus.FINISHED_STOPPED
-            elif (req.num_resolved_outputs >= req.sampling_params.max_tokens
-                  or req.num_prompt_tokens + req.num_resolved_outputs >= self.max_model_len):
-                status = RequestStatus.FINISHED_LENGTH
-            else:
-                continue
-            del req.output_token_ids[req.num_resolved_outputs:]  # the next step's token, if launched, is dropped
-            req.num_computed_tokens = min(req.num_computed_tokens, req.num_tokens)
-            if req in self.running:
-                self.running.remove(req)
-            self._release(req)
-            req.status = status
-            req.finish_time = now
-        return updated
+            got.append(req)
+            ended = self._ending(req, token)
+            if ended is not None:
+                self._retire(req, ended, now)
+        return got
 
-    def _append_token(self, req: Request, token: int) -> None:
-        req.output_token_ids.append(token)
-        req.num_resolved_outputs = len(req.output_token_ids)
-        req.new_token_ids.append(token)
-        if token in req.eos_token_ids or token in req.stop_token_ids:
-            req.status = RequestStatus.FINISHED_STOPPED
-        elif req.num_output_tokens >= req.sampling_params.max_tokens or req.num_tokens >= self.max_model_len:
-            req.status = RequestStatus.FINISHED_LENGTH
+    def update_from_output(self, plan: StepPlan, sampled: dict) -> list:
+        """Both halves at once: for a loop that reads each step's tokens before planning the next."""
+        for s in plan.scheduled:
+            s.request.new_token_ids = []
+        self.book_launch(plan)
+        return self.deliver_tokens(plan, sampled)
+
+    def _length_reached(self, req: Request, outputs: int, tokens: int) -> bool:
+        return outputs >= req.sampling_params.max_tokens or tokens >= self.max_model_len
+
+    def _ending(self, req: Request, token: int) -> Optional[RequestStatus]:
+        if token in req.end_tokens:
+            return RequestStatus.FINISHED_STOPPED
+        if self._length_reached(req, req.num_known_outputs, req.num_known):
+            return RequestStatus.FINISHED_LENGTH
+        return None

@@ -68,6 +68,75 @@ def replay(model: str, dtype: str, out_dir: str, max_tokens: int, lines, device:
     return steps
 
 
+class TraceWriter:
+    """Records the steps an engine launches, as lines this tool replays.
+
+    A step's tokens are noted when the step is launched.  With overlap scheduling the newest
+    token of a decoding request is then still on the device; the step is completed once the value
+    has arrived (by the next launch, or at ``close``).  A request that lost its pages and is read
+    from its start again appears under a new id (``<id>~<n>``); every id ends in the last step
+    that carries it.  ``close`` writes the file and returns the ``--max-tokens`` a replay needs."""
+
+    def __init__(self, path: str) -> None:
+        self.path = path
+        self.records: list = []
+        self.open_record = None  # (record, [(entry index, request, position of its last token)]) not complete yet
+        self.alias: dict = {}  # request id -> its id in the trace
+        self.carried: set = set()  # trace ids that a step has carried
+        self.num_steps = 0
+
+    def step(self, plan, entries) -> None:
+        self._complete()
+        record = {"step": self.num_steps, "entries": [], "end": []}
+        unknown = []
+        for i, (s, e) in enumerate(zip(plan.scheduled, entries)):
+            rid = self.alias.setdefault(e.request_id, e.request_id)
+            if s.request.num_computed_tokens == 0 and rid in self.carried:  # read from its start again
+                rid = self.alias[e.request_id] = f"{e.request_id}~{s.request.num_preemptions}"
+            self.carried.add(rid)
+            record["entries"].append({"id": rid, "tokens": list(e.tokens), "want": list(e.want)})
+            if e.pending is not None:
+                unknown.append((i, s.request, s.request.num_computed_tokens + s.num_tokens - 1))
+        self.num_steps += 1
+        self.open_record = (record, unknown)
+        self._complete()
+
+    def _complete(self, final: bool = False) -> None:
+        if self.open_record is None:
+            return
+        record, unknown = self.open_record
+        if not final and any(position >= req.num_known for _, req, position in unknown):
+            return  # a value is still on its way
+        dropped = set()
+        for i, req, position in unknown:
+            if position < req.num_known:
+                record["entries"][i]["tokens"][-1] = req.token_ids[position]
+            else:
+                dropped.add(i)  # the request ended with this step in flight: the token never reached the host
+        record["entries"] = [e for i, e in enumerate(record["entries"]) if i not in dropped]
+        self.records.append(record)
+        self.open_record = None
+
+    def close(self) -> int:
+        self._complete(final=True)
+        last = {}
+        for index, record in enumerate(self.records):
+            for e in record["entries"]:
+                last[e["id"]] = index
+        for rid, index in last.items():
+            self.records[index]["end"].append(rid)
+        held, peak = {}, 0
+        with open(self.path, "w", encoding="utf-8") as f:
+            for record in self.records:
+                for e in record["entries"]:
+                    held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+                peak = max(peak, sum(cdiv(n, ROUNDING) * ROUNDING for n in held.values()))
+                for rid in record["end"]:
+                    held.pop(rid, None)
+                f.write(json.dumps(record) + "\n")
+        return peak
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="trace_run", description="replay a trace of steps and write logits")
     p.add_argument("--model", required=True, help="folder with config.json and model.safetensors")

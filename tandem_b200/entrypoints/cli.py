@@ -62,9 +62,16 @@ def cmd_generate(args) -> None:
         raise SystemExit("give --prompt (text) or --prompt-ids (token ids)")
     sp = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p,
                         top_k=args.top_k, min_p=args.min_p, seed=args.seed, ignore_eos=args.ignore_eos)
+    if args.trace_out:
+        engine.record_steps(args.trace_out)
     t0 = time.perf_counter()
     out = engine.generate([prompt], sp)[0]
     dt = time.perf_counter() - t0
+    if args.trace_out:
+        need = engine.trace.close()
+        print(f"[{engine.trace.num_steps} steps written to {args.trace_out}; replay them with "
+              f"`tandem replay --model {args.model} --max-tokens {need} --block-size {args.block_size} --out DIR < {args.trace_out}`]",
+              file=sys.stderr)
     print(out.text if engine.tokenizer is not None else " ".join(str(t) for t in out.output_token_ids))
     n = len(out.output_token_ids)
     print(f"\n[{n} tokens in {dt:.2f}s, {n / dt:.2f} tok/s, ttft {out.metrics.get('ttft', 0):.3f}s, "
@@ -106,6 +113,7 @@ def main(argv=None) -> None:
     p.add_argument("--min-p", type=float, default=0.0)
     p.add_argument("--seed", type=int, default=None)
     p.add_argument("--ignore-eos", action="store_true")
+    p.add_argument("--trace-out", default=None, help="write the steps this run takes as a trace that `replay` reads")
     p.set_defaults(fn=cmd_generate)
 
     p = sub.add_parser("replay", help="replay a trace of steps from stdin and write logits")

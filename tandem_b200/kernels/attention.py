@@ -146,14 +146,16 @@ def paged_attention_prefill(qkv: torch.Tensor, kv, tiles: torch.Tensor, num_head
     return out
 
 
-def plan_key(window: Optional[int], num_heads: int, num_kv_heads: int) -> tuple:
-    return ("attention", window, num_heads, num_kv_heads)
+def plan_key(window: Optional[int], num_heads: int, num_kv_heads: int, head_dim: int, dtype: torch.dtype) -> tuple:
+    """What a step's attention plan depends on, and with it which kernel runs: layers that agree in
+    all of this share one plan; two layers with equal head counts and different head sizes do not."""
+    return ("attention", window, num_heads, num_kv_heads, head_dim, str(dtype))
 
 
 def plan_step(ctx, window: Optional[int], num_heads: int, num_kv_heads: int, head_dim: int, out: dict) -> None:
     """Cut this step's attention work for the tensor-core kernels (if they apply) and put the
     arrays into ``out``; what was planned is remembered in ``ctx.scratch`` for ``paged_attention``."""
-    key = plan_key(window, num_heads, num_kv_heads)
+    key = plan_key(window, num_heads, num_kv_heads, head_dim, ctx.dtype)
     groups = num_heads // num_kv_heads
     if key in ctx.scratch or not tensor_core_path_applies(ctx.dtype, head_dim, ctx.page_size, groups):
         return
@@ -172,7 +174,7 @@ def plan_step(ctx, window: Optional[int], num_heads: int, num_kv_heads: int, hea
 def paged_attention(qkv: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int, head_dim: int,
                     window: Optional[int], scale: float) -> torch.Tensor:
     """Attention output [T, nh * hd] for the query heads in the first nh*hd columns of qkv."""
-    key = plan_key(window, num_heads, num_kv_heads)
+    key = plan_key(window, num_heads, num_kv_heads, head_dim, qkv.dtype)
     planned = ctx.scratch.get(key)
     if planned is None:
         return ops.paged_attention_simt(qkv, kv.k, kv.v, kv.block_table, ctx.seq_of_token, ctx.positions, num_heads,

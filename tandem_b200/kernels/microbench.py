@@ -5,6 +5,7 @@
     python -m tandem_b200.kernels.microbench prefill-attention --tokens 2048
     python -m tandem_b200.kernels.microbench tokenwise --tokens 2048
     python -m tandem_b200.kernels.microbench norm-gemm --m 8 --n 6144 --k 4096
+    python -m tandem_b200.kernels.microbench dispatch [--shapes 8b|32b]
 
 Timing follows 12vivi/tandem's kernel benchmarks (benchmarks/bench_gemv.py:3-6,35-56): the calls are
 captured in one CUDA graph so that launch cost does not count, and weights or caches are rotated
@@ -97,6 +98,41 @@ def bench_norm_gemm(args) -> None:
         norm = time_calls(lambda i: ops.add_rmsnorm(x, res, w, 1e-6, torch.bfloat16), args.iters, args.graph)
         both = time_calls(step, args.iters, args.graph)
         print(f"norm + gemm M={M} N={N} K={K}  {impl:24s} {both:8.1f} us  (alone: gemm {alone:.1f} us, norm {norm:.1f} us)")
+
+
+LAYER_SHAPES = {  # (name, N, K) of the products of a layer and the output head
+    "8b": [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096), ("down", 4096, 12288), ("head", 151936, 4096)],
+    "32b": [("qkv", 10240, 5120), ("o", 5120, 8192), ("gate_up", 51200, 5120), ("down", 5120, 25600), ("head", 151936, 5120)],
+}
+
+
+def bench_dispatch(args) -> None:
+    """Every kernel that takes a shape, timed on the products of a layer at each class of rows, next
+    to what the fixed rule of ``gemm_bf16.choose`` picks: the table its thresholds are read off."""
+    from tandem_b200.kernels import gemm_bf16, ops
+
+    bf = torch.bfloat16
+    for name, N, K in LAYER_SHAPES[args.shapes]:
+        ws = [torch.randn(N, K, device="cuda", dtype=bf) * 0.02 for _ in range(copies_for(N * K * 2))]
+        out = torch.float32 if name == "head" else bf
+        for M in (1, 4, 8, 16, 32, 64):
+            x = torch.randn(M, K, device="cuda", dtype=bf)
+            times = {"library": time_calls(lambda i: gemm_bf16._library(x, ws[i % len(ws)], out), args.iters, args.graph)}
+            if gemm_bf16.skinny_applies(M, N, K):
+                times["skinny"] = time_calls(lambda i: gemm_bf16.skinny(x, ws[i % len(ws)], out), args.iters, args.graph)
+            if gemm_bf16.gemv_applies(M, N, K):
+                times["gemv"] = time_calls(lambda i: gemm_bf16.gemv(x, ws[i % len(ws)], out), args.iters, args.graph)
+            rule, best = gemm_bf16.choose(M, N, K), min(times, key=times.get)
+            cells = "  ".join(f"{k} {v:7.1f} us" for k, v in times.items())
+            print(f"{name:8s} M={M:3d} N={N:6d} K={K:5d} ({N * K * 2 >> 20:4d} MiB)  {cells}  rule: {rule}"
+                  + ("" if rule == best else f"  (fastest: {best}, {times[rule] / times[best]:.2f}x)"))
+        if name == "gate_up":
+            for M in (128, 256, 512, 1024, 2048, 4096):
+                x = torch.randn(M, K, device="cuda", dtype=bf)
+                a = time_calls(lambda i: gemm_bf16.wide(x, ws[i % len(ws)], bf, gated=True), args.iters, args.graph)
+                b = time_calls(lambda i: ops.silu_mul(gemm_bf16._library(x, ws[i % len(ws)], bf)), args.iters, args.graph)
+                print(f"gate_up  M={M:4d} gated: wide {a:8.1f} us  library + silu_mul {b:8.1f} us  rule: {gemm_bf16.choose_gated(M, N, K)}")
+        del ws
 
 
 def _cache(pages: int, nkv: int, ps: int, hd: int):
@@ -212,6 +248,9 @@ def main(argv=None) -> None:
     t.add_argument("--hidden", type=int, default=4096)
     t.add_argument("--intermediate", type=int, default=12288)
     t.set_defaults(fn=bench_tokenwise)
+    dp = sub.add_parser("dispatch", parents=[common])
+    dp.add_argument("--shapes", choices=sorted(LAYER_SHAPES), default="8b")
+    dp.set_defaults(fn=bench_dispatch)
     args = p.parse_args(argv)
     with torch.inference_mode():
         args.fn(args)

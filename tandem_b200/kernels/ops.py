@@ -69,25 +69,53 @@ def status_word(device) -> torch.Tensor:
     return _status[key]
 
 
+def raise_status(device, code: int) -> None:
+    """Clear the status word and raise for the fault ``code`` that was read from it."""
+    status_word(device).zero_()
+    what = {1: "a bounded wait inside a kernel gave up", 2: "a kernel met a missing page in a block table"}
+    raise KernelError(f"kernel status {code}: {what.get(code, 'unknown fault')}; results of this step are invalid")
+
+
 def check_status(device) -> None:
     """Read the status word (this waits for the device) and raise if a kernel recorded a fault."""
     code = int(status_word(device).item())
     if code:
-        status_word(device).zero_()
-        what = {1: "a bounded wait inside a kernel gave up", 2: "a kernel met a missing page in a block table"}
-        raise KernelError(f"kernel status {code}: {what.get(code, 'unknown fault')}; results of this step are invalid")
+        raise_status(device, code)
 
 
 # ----------------------------------------------------------------------------- token-wise
-def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
-    """ids [T] int32, table [V, H] -> float32 [T, H] (the start of the residual stream)."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0, positions: Optional[torch.Tensor] = None,
+              position_table: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """ids [T] int32, table [V, H] -> float32 [T, H] (the start of the residual stream):
+    ``scale * table[ids]``, plus ``position_table[positions]`` where a learned table [P, H] of
+    absolute positions is given."""
     _need(ids, "ids", torch.int32)
     _need(table, "embedding table")
     T, (V, H) = ids.numel(), table.shape
+    max_pos = 0
+    if position_table is not None:
+        _need(position_table, "position table", table.dtype)
+        _need(positions, "positions", torch.int32)
+        if position_table.shape[1] != H or positions.numel() != T:
+            raise KernelError(f"position table {tuple(position_table.shape)} / {positions.numel()} positions do not fit "
+                              f"{T} tokens of width {H}")
+        max_pos = position_table.shape[0]
     out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     lib = load_library("tokenwise")
-    _check(lib.tb_embedding(_stream(), _ptr(ids), _ptr(table), _ptr(out), T, H, V, _code(table.dtype)), "embedding")
+    _check(lib.tb_embedding(_stream(), _ptr(ids), _ptr(table), _ptr(out), T, H, V, _code(table.dtype), ctypes.c_float(scale),
+                            _ptr(positions if position_table is not None else None), _ptr(position_table), max_pos), "embedding")
     return out
+
+
+def scale_softcap(logits: torch.Tensor, scale: float = 1.0, softcap: Optional[float] = None) -> torch.Tensor:
+    """In place on float32 logits: ``scale * x``, then ``softcap * tanh(x / softcap)`` where a cap is given."""
+    _need(logits, "logits", torch.float32)
+    if softcap is not None and softcap <= 0:
+        raise KernelError(f"a logit cap must be positive, got {softcap}")
+    lib = load_library("tokenwise")
+    _check(lib.tb_scale_softcap(_stream(), _ptr(logits), ctypes.c_longlong(logits.numel()), ctypes.c_float(scale),
+                                ctypes.c_float(softcap or 0.0)), "scale_softcap")
+    return logits
 
 
 def take_tokens(ids: torch.Tensor, source: torch.Tensor, tokens: torch.Tensor) -> None:
@@ -102,31 +130,10 @@ def take_tokens(ids: torch.Tensor, source: torch.Tensor, tokens: torch.Tensor) -
     _check(lib.tb_take_tokens(_stream(), _ptr(ids), _ptr(source), _ptr(tokens), ids.numel(), tokens.numel()), "take_tokens")
 
 
-def _split(x):
-    """(tensor, partial pointer, tiles pointer, padded rows) of a tensor or a split output."""
-    if isinstance(x, torch.Tensor) or x is None:
-        return x, None, None, 0
-    x.check()
-    return x.y, _ptr(x.partial), _ptr(x.tiles), x.mpad
-
-
-def as_tensor(x):
-    """A split output made whole (one small kernel); tensors pass through."""
-    if isinstance(x, torch.Tensor) or x is None:
-        return x
-    x.check()
-    M, N = x.y.shape
-    _check(load_library("gemm_skinny").tb_split_resolve(_stream(), _ptr(x.y), _ptr(x.partial), _ptr(x.tiles), x.mpad, M, N),
-           "split_resolve")
-    return x.y
-
-
 def add_rmsnorm(x, residual: torch.Tensor, weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """residual += x (in place, float32; skipped when x is None); returns RMSNorm(residual) * weight
-    in ``out_dtype``.  With ``rows`` [R] int32 only those rows are updated and returned, in that order.
-    ``x`` may be a split output of the matrix product."""
-    x, partial, tiles, mpad = _split(x)
+    in ``out_dtype``.  With ``rows`` [R] int32 only those rows are updated and returned, in that order."""
     _need(residual, "residual", torch.float32)
     _need(weight, "norm weight", torch.float32)
     T, H = residual.shape
@@ -143,21 +150,18 @@ def add_rmsnorm(x, residual: torch.Tensor, weight: torch.Tensor, eps: float,
     y = torch.empty((n, H), dtype=out_dtype, device=residual.device)
     lib = load_library("tokenwise")
     _check(lib.tb_add_rmsnorm(_stream(), _ptr(x), _ptr(residual), _ptr(weight), _ptr(y), _ptr(rows), n, H,
-                              ctypes.c_float(eps), _code(out_dtype), partial, tiles, mpad), "add_rmsnorm")
+                              ctypes.c_float(eps), _code(out_dtype)), "add_rmsnorm")
     return y
 
 
-def qk_norm_rope_kv(qkv, positions: torch.Tensor, slots: Optional[torch.Tensor],
+def qk_norm_rope_kv(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor],
                     q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
                     k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], num_heads: int,
                     num_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int, eps: float,
                     write_kv: bool = True) -> torch.Tensor:
     """In place on qkv [T, (nh + 2 nkv) hd]: per-head RMSNorm (if weights) and rotary encoding of q
     and k; k and v of every token are stored at ``slots[t]`` of the caches
-    [pages, nkv, page_size, hd] (unless ``write_kv`` is false or the slot is negative).  ``qkv`` may
-    be a split output of the matrix product: its tensor is whole afterwards where this kernel wrote
-    (the query heads)."""
-    qkv, partial, tiles, mpad = _split(qkv)
+    [pages, nkv, page_size, hd] (unless ``write_kv`` is false or the slot is negative)."""
     _need(qkv, "qkv")
     T = qkv.shape[0]
     if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
@@ -186,30 +190,26 @@ def qk_norm_rope_kv(qkv, positions: torch.Tensor, slots: Optional[torch.Tensor],
     _check(lib.tb_qk_norm_rope_kv(_stream(), _ptr(qkv), _ptr(positions), _ptr(slots), _ptr(q_weight), _ptr(k_weight),
                                   _ptr(cos_sin), _ptr(k_cache), _ptr(v_cache), T, num_heads, num_kv_heads, head_dim,
                                   rotary_dim, page_size, ctypes.c_float(eps), int(bool(write_kv)), max_pos,
-                                  _code(qkv.dtype), partial, tiles, mpad), "qk_norm_rope_kv")
+                                  _code(qkv.dtype)), "qk_norm_rope_kv")
     return qkv
 
 
-def silu_mul(gate_up) -> torch.Tensor:
-    """[T, 2I] = [gate | up] -> silu(gate) * up, [T, I].  ``gate_up`` may be a split output."""
-    gate_up, partial, tiles, mpad = _split(gate_up)
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """[T, 2I] = [gate | up] -> silu(gate) * up, [T, I]."""
     _need(gate_up, "gate_up")
     T, two_i = gate_up.shape
     if two_i % 2:
         raise KernelError("gate_up must have an even number of columns")
     out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     lib = load_library("tokenwise")
-    _check(lib.tb_silu_mul(_stream(), _ptr(gate_up), _ptr(out), T, two_i // 2, _code(gate_up.dtype), partial, tiles, mpad),
-           "silu_mul")
+    _check(lib.tb_silu_mul(_stream(), _ptr(gate_up), _ptr(out), T, two_i // 2, _code(gate_up.dtype)), "silu_mul")
     return out
 
 
 # ----------------------------------------------------------------------------- matrix products
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None, split_ok: bool = False):
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """x [M, K] @ weight [N, K]^T -> [M, N].  float32 operands run the CUDA-core kernel (true
-    32-bit arithmetic); bfloat16 operands run on the tensor cores with float32 accumulation.
-    ``split_ok``: the result goes to a kernel that takes split input (add_rmsnorm, qk_norm_rope_kv,
-    silu_mul) or through ``as_tensor``; a split output may then come back instead of a tensor."""
+    32-bit arithmetic); bfloat16 operands run on the tensor cores with float32 accumulation."""
     _need(x, "x")
     _need(weight, "weight")
     if x.dtype != weight.dtype:
@@ -228,7 +228,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         return out
     from tandem_b200.kernels import gemm_bf16
 
-    return gemm_bf16.linear(x, weight, out_dtype, split_ok)
+    return gemm_bf16.linear(x, weight, out_dtype)
 
 
 def gated_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -35,8 +35,8 @@ def build_plan(cfg: Qwen3Config) -> ModelPlan:
     layers = []
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}"
-        layers.append(LayerSpec(
-            block="prenorm",
+        layers.append(LayerSpec.of(
+            "prenorm",
             mixer=AttentionSpec(
                 "attention", prefix=f"{p}.self_attn", hidden_size=cfg.hidden_size,
                 num_heads=cfg.num_attention_heads, num_kv_heads=cfg.num_key_value_heads,

@@ -61,7 +61,7 @@ class PagedAttention(Mixer):
         """The most entries ``step_arrays`` can produce for a step of up to ``bucket`` single tokens
         (CUDA graphs keep the arrays in static memory); also sizes the decode kernel's scratch."""
         s = self.spec
-        key = attention_kernels.plan_key(s.window, s.num_heads, s.num_kv_heads)
+        key = attention_kernels.plan_key(s.window, s.num_heads, s.num_kv_heads, s.head_dim, self.qkv.dtype)
         groups = s.num_heads // s.num_kv_heads
         if key + ("items",) in out or \
                 not attention_kernels.tensor_core_path_applies(self.qkv.dtype, s.head_dim, page_size, groups):
@@ -75,9 +75,9 @@ class PagedAttention(Mixer):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         s = self.spec
         qkv = ops.linear(x, self.qkv)
-        kv = ctx.kv()
+        kv = ctx.kv(self)
         qkv = ops.qk_norm_rope_kv(qkv, ctx.positions, kv.slots, self.q_norm, self.k_norm, self.position.cos_sin,
                             kv.k, kv.v, s.num_heads, s.num_kv_heads, s.head_dim, self.position.rotary_dim,
                             kv.page_size, s.qk_norm_eps, write_kv=kv.writable)
         o = attention_kernels.paged_attention(qkv, kv, ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
-        return ops.linear(o, self.o, split_ok=True)  # for the block: a norm that takes split input, or ops.as_tensor
+        return ops.linear(o, self.o)

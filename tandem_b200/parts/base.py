@@ -74,12 +74,15 @@ class StepContext:
     run: int = 0  # position in ModelPlan.order of the run in flight
     scratch: dict = field(default_factory=dict)  # per-step values parts may share (keyed by them)
 
-    def kv(self) -> KVView:
-        return self.storage.view(self.run, self)
+    def kv(self, mixer: Any = None) -> KVView:
+        """The paged cache of the mixer that asks (``ctx.kv(self)``), in the run in flight.  A layer
+        with a single mixer may leave the argument out."""
+        return self.storage.view(self.storage.user(self.run, mixer), self)
 
-    def state(self) -> torch.Tensor:
-        """[max requests, *shape] tensor of the run's per-request state."""
-        return self.storage.state[self.run]
+    def state(self, mixer: Any = None) -> torch.Tensor:
+        """[max requests + 1, *shape] tensor of the asking mixer's per-request state in the run in
+        flight; the last row belongs to no request (rows that pad a captured batch point there)."""
+        return self.storage.state[self.storage.user(self.run, mixer)]
 
 
 class Mixer:

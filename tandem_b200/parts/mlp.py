@@ -29,5 +29,4 @@ class GatedMLP(FeedForward):
         self.down = weights["down"]
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        # the second product may come back as a split output: the block hands it to a norm that takes one
-        return ops.linear(ops.gated_linear(x, self.gate_up), self.down, split_ok=True)
+        return ops.linear(ops.gated_linear(x, self.gate_up), self.down)

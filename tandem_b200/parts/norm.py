@@ -17,8 +17,6 @@ from tandem_b200.parts.base import Norm
 
 
 class RMSNorm(Norm):
-    takes_split_input = True  # x may be a split output of the matrix product (kernels/gemm_bf16.py)
-
     @staticmethod
     def params(spec: NormSpec) -> dict:
         return {"weight": ParamSpec((spec.size,), (WeightSource(spec.weight),), role="vector")}

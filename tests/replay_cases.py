@@ -118,6 +118,32 @@ def tokens_needed(steps: list, round_to: int = 64) -> int:
     return peak
 
 
+class PageLog:
+    """Every page number the pools hand out, and how often a page went to a new holder while
+    another request was live (its keys lie beside pages that are being read)."""
+
+    def __init__(self, manager) -> None:
+        self.handed: dict = {}
+        self.reused_beside_live = 0
+        for g, group in enumerate(manager.groups):
+            group.pool.allocate = self._wrap(group.pool.allocate, g, manager)
+
+    def _wrap(self, allocate, g, manager):
+        def logged(n):
+            ids = allocate(n)
+            for i in ids:
+                self.handed[(g, i)] = self.handed.get((g, i), 0) + 1
+                if self.handed[(g, i)] > 1 and len(manager.live) > 1:
+                    self.reused_beside_live += 1
+            return ids
+
+        return logged
+
+    @property
+    def pages_reused(self) -> int:
+        return sum(1 for n in self.handed.values() if n > 1)
+
+
 def pages_handed_twice(steps: list, page_size: int, num_pages: int) -> tuple:
     """The trace run through the cache manager's bookkeeping alone (no device): how many pages of
     a pool of ``num_pages`` go to a second holder, and how many of those while another request is

@@ -81,9 +81,9 @@ def test_round_trip_and_eos(tmp_path):
 
 def test_plan_is_chosen_layer_by_layer():
     plan = build_plan(Qwen3Config.from_dict(TINY_C))
-    assert [l.mixer.window for l in plan.layers] == [None, None, 20, 20]
+    assert [l.slot("mixer").window for l in plan.layers] == [None, None, 20, 20]
     assert [r.layer for r in plan.order] == [0, 1, 2, 3] and all(r.cache_of is None for r in plan.order)
-    m = plan.layers[0].mixer
+    m = plan.layers[0].slot("mixer")
     assert (m.num_heads, m.num_kv_heads, m.head_dim, m.qk_norm, m.qk_norm_eps) == (6, 3, 48, True, 3e-6)
     assert m.scale == 48 ** -0.5 and m.position.theta == 500000.0 and m.position.rotary_dim == 48
     assert plan.head.weight == "lm_head.weight" and build_plan(Qwen3Config.from_dict(TINY_A)).head.weight is None

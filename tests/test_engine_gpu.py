@@ -127,6 +127,92 @@ def test_cuda_graph_decode_matches_eager(tiny_folder):
     assert not graphs.takes([StepEntry(live[0], [1, 2], [1])])
 
 
+@pytest.mark.parametrize("name,page", [("B", 16), ("A", 16), ("C", 16)])
+def test_cuda_graph_decode_follows_the_plain_implementation(tiny_folder, name, page):
+    """Decode steps replayed from CUDA graphs against the plain logits: three live requests (the
+    bucket of 4, one padding row), then five (the bucket of 8, three padding rows), then three
+    others (the bucket of 4 again, replayed with other requests on pages that finished requests
+    gave back), then two.  Every request is fed its own given tokens, so each row of logits has a
+    place in the plain implementation's whole-sequence output."""
+    import replay_cases as rc
+    from tandem_b200.engine.core import build_executor, load_model
+    from tandem_b200.engine.cuda_graph import DecodeGraphs
+    from tandem_b200.engine.executor import StepEntry
+
+    folder = tiny_folder(name)
+    vocab = TINY[name]["vocab_size"]
+    cfg, w64 = plain.read_folder(folder, torch.float64)
+    _, w16 = plain.read_folder(folder, torch.bfloat16)
+    lengths = {"r0": 70, "r1": 45, "r2": 100, "r3": 33, "r4": 120, "r5": 90}
+    head = {"r0": 50, "r1": 30, "r2": 81, "r3": 2, "r4": 97, "r5": 64}  # tokens read as one portion; the rest one by one
+    toks = {rid: random_tokens(500 + i, n, vocab) for i, (rid, n) in enumerate(lengths.items())}
+    decoder, _ = load_model(folder, "bfloat16", "cuda:0")
+    ex = build_executor(decoder, page_size=page, num_pages=23, max_requests=8)
+    log = rc.PageLog(ex.manager)
+    graphs = DecodeGraphs.maybe(ex, 8, 256)
+    assert graphs is not None
+    at, got = {}, {rid: {} for rid in toks}
+
+    def admit(*rids):
+        ex.step([StepEntry(rid, toks[rid][: head[rid]], []) for rid in rids])
+        for rid in rids:
+            at[rid] = head[rid]
+
+    def decode(live, steps):
+        for _ in range(steps):
+            entries = [StepEntry(rid, [toks[rid][at[rid]]], [0]) for rid in live if at[rid] < lengths[rid]]
+            assert graphs.takes(entries)
+            for e in entries:
+                assert ex.manager.grow(e.request_id, at[e.request_id] + 1)
+            logits = graphs.run(entries).double().cpu()
+            for row, e in zip(logits, entries):
+                ex.manager.commit(e.request_id, 1)
+                got[e.request_id][at[e.request_id]] = row
+                at[e.request_id] += 1
+            ex.manager.check()
+
+    admit("r0", "r1", "r2")
+    decode(["r0", "r1", "r2"], 9)  # eager + capture of bucket 4, then replays
+    admit("r3", "r4")
+    decode(["r0", "r1", "r2", "r3", "r4"], 6)  # bucket 8
+    for rid in ("r0", "r1", "r2"):
+        ex.manager.end(rid)
+    admit("r5")  # onto pages that r0..r2 held
+    decode(["r3", "r4", "r5"], 12)  # bucket 4 replayed with other requests and other pages
+    ex.manager.end("r3")
+    decode(["r4", "r5"], 11)  # bucket 2
+    ex.manager.end("r4"), ex.manager.end("r5")
+    assert ex.manager.all_free()
+    assert set(graphs.captured) >= {2, 4, 8} and log.reused_beside_live >= 3
+    for rid, rows in got.items():
+        assert rows, rid
+        ref = plain.forward(cfg, w64, toks[rid], torch.float64)
+        low = plain.forward(cfg, w16, toks[rid], torch.bfloat16).double()
+        base = (low - ref).abs().max().item()
+        for pos, row in rows.items():
+            err = (row - ref[pos]).abs().max().item()
+            assert err <= 1.5 * base + 0.02, (rid, pos, err, base)
+
+
+def test_a_fault_recorded_by_a_kernel_stops_the_engine(tiny_folder):
+    """Kernels that survive a fault (a bounded wait that gave up, a missing page) record it in a
+    status word; the engine reads the word with the step's tokens and raises instead of handing
+    out tokens sampled from invalid logits.  The word is set by hand here."""
+    from tandem_b200 import EngineConfig, LLMEngine, SamplingParams
+    from tandem_b200.kernels import ops
+
+    for overlap in (False, True):
+        eng = LLMEngine(EngineConfig(model=tiny_folder("A"), dtype="bfloat16", block_size=16, num_kv_blocks=16,
+                                     overlap_schedule=overlap))
+        eng.add_request([5, 6, 7], SamplingParams(max_tokens=8, **GREEDY))
+        eng.step()
+        ops.status_word(eng.decoder.device).fill_(2)
+        with pytest.raises(ops.KernelError, match="missing page"):
+            for _ in range(3):
+                eng.step()
+        assert int(ops.status_word(eng.decoder.device).item()) == 0  # cleared: the next engine starts clean
+
+
 def test_replayed_graphs_keep_the_scratch_they_were_captured_with(tiny_folder):
     """The decode kernel's scratch grows with the batch; a graph captured before it grew still
     writes to the scratch of its day when it is replayed, so that memory must not go to anyone else."""
@@ -175,16 +261,18 @@ def test_generation_with_cuda_graphs(tiny_folder):
     assert llm.engine.cache.all_free()
 
 
-def test_qwen3_8b_widths_bfloat16_follows_float32_however_it_is_cut():
+def test_qwen3_8b_widths_follow_the_plain_implementation_however_they_are_cut():
     """The real layer sizes (hidden 4096, 32 query and 8 kv heads of 128, intermediate 12288,
     vocabulary 151936, pages of 16), three layers of them with random weights made on the device:
     a 330-token request whole, in portions with its last 30 tokens one by one, and beside another
-    request whose pages it later reuses.  The float32 path gives the same bits however it is cut;
-    bfloat16 stays within what its 8-bit mantissa allows (about 1 % of the logits' spread on
-    average; the bounds below leave a factor of two)."""
+    request whose pages it later reuses.  The float32 path gives the same bits however it is cut,
+    and those bits are the plain implementation's float64 logits to float32 rounding; bfloat16
+    stays within what its 8-bit mantissa allows (about 1 % of the logits' spread on average; the
+    bounds below leave a factor of two)."""
     from bench import QWEN3_8B
     from tandem_b200.engine.core import build_executor, random_model
     from tandem_b200.engine.executor import StepEntry
+    from tandem_b200.registry import resolve_architecture
 
     tokens, other = random_tokens(1, 330, 151936), random_tokens(2, 200, 151936)
     results = {}
@@ -212,6 +300,14 @@ def test_qwen3_8b_widths_bfloat16_follows_float32_however_it_is_cut():
     assert torch.equal(f32[0], f32[1]) and torch.equal(f32[0], f32[2])
     spread = f32[0].std().item()
     assert spread > 0.5  # the logits are not degenerate
+    # the same tensors (same seeds, drawn on the same device) through the plain implementation in float64
+    arch = resolve_architecture(QWEN3_8B)
+    cfg3 = dict(QWEN3_8B, num_hidden_layers=3)
+    weights = {n: t.cpu().double() for n, t in arch.random_weights(arch.config_class.from_dict(cfg3), 3, "cuda:0", torch.bfloat16)}
+    ref = plain.forward(cfg3, weights, tokens, torch.float64)[300:]
+    del weights
+    err = (f32[0] - ref).abs().max().item()
+    assert err < 1e-4 * max(1.0, ref.abs().max().item()), (err, ref.abs().max().item(), spread)
     for got in b16:
         err = (got - f32[0]).abs()
         assert err.mean().item() < 0.025 * spread and err.max().item() < 0.15 * spread, (err.mean().item(), err.max().item(), spread)
@@ -244,6 +340,39 @@ def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tiny_folder
         want = plain.inverse_cdf_draw(p, uniform(43, k))
         assert tok == want
         ids.append(tok)
+
+
+class LetterTokenizer:
+    """One letter per token id."""
+
+    def encode(self, text):
+        return [ord(c) - 97 for c in text]
+
+    def decode(self, ids, skip_special_tokens=True):
+        return "".join(chr(97 + i % 26) for i in ids)
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_stop_strings_end_a_request_and_need_a_tokenizer(tiny_folder, overlap):
+    from tandem_b200 import EngineConfig, LLMEngine, SamplingParams
+
+    folder = tiny_folder("A", 0.1)
+    cfg, w = plain.read_folder(folder)
+    tok = LetterTokenizer()
+    prompts = [random_tokens(70 + i, n, 512) for i, n in enumerate([6, 19])]
+    want = [plain.greedy(cfg, w, p, 16) for p in prompts]
+    texts = [tok.decode(t) for t in want]
+    stop = texts[0][7:10]  # the first request stops where these three letters first appear; the second runs on
+    ends = [t.find(stop) for t in texts]
+    config = EngineConfig(model=folder, dtype="float32", block_size=8, num_kv_blocks=32, overlap_schedule=overlap)
+    eng = LLMEngine(config, tokenizer=tok)
+    outs = eng.generate(prompts, [SamplingParams(max_tokens=16, stop=[stop], **GREEDY), SamplingParams(max_tokens=16, **GREEDY)])
+    assert outs[0].finish_reason == "stop" and outs[0].text == texts[0][: ends[0]]
+    assert outs[0].output_token_ids == want[0][: ends[0] + 3]  # tokens up to the one that completed the stop string
+    assert outs[1].finish_reason == "length" and outs[1].text == texts[1] and outs[1].output_token_ids == want[1]
+    assert eng.cache.all_free()
+    with pytest.raises(ValueError, match="tokenizer"):
+        LLMEngine(config, load_tokenizer=False).add_request(prompts[0], SamplingParams(stop=["x"]))
 
 
 def test_command_line(tiny_folder):
@@ -288,9 +417,7 @@ def test_each_part_alone(dtype):
     wg, wu, wd = rnd(I, H, s=0.2), rnd(I, H, s=0.2), rnd(H, I, s=0.2)
     mlp = GatedMLP(GatedMLPSpec("gated_mlp", "m", H, I), {"gate_up": torch.cat([wg, wu]).cuda(), "down": wd.cuda()}, dtype, "cuda")
     wdict = {"m.gate_proj.weight": wg.float(), "m.up_proj.weight": wu.float(), "m.down_proj.weight": wd.float()}
-    from tandem_b200.kernels import ops  # a part may return the product's split output: as_tensor makes it whole
-
-    torch.testing.assert_close(ops.as_tensor(mlp.forward(x.cuda(), None)).cpu().float(), plain.swiglu(x.float(), wdict, "m"), **tol)
+    torch.testing.assert_close(mlp.forward(x.cuda(), None).cpu().float(), plain.swiglu(x.float(), wdict, "m"), **tol)
 
     # position table
     table = RotaryTable(PositionSpec("rope", rotary_dim=hd, theta=777.0, max_position=64), "cuda")
@@ -325,7 +452,7 @@ def test_each_part_alone(dtype):
         assert manager.grow("r", start + n)
         ctx, _ = ex.build_context([StepEntry("r", [0] * n, [])])
         ctx.run = 0
-        outs.append(ops.as_tensor(mixer.forward(x[start: start + n].cuda(), ctx)))
+        outs.append(mixer.forward(x[start: start + n].cuda(), ctx))
         manager.commit("r", n)
     d = dict(nh=nh, nkv=nkv, hd=hd, eps=1e-5)
     wdict = {"a.q_proj.weight": wq.float(), "a.k_proj.weight": wk.float(), "a.v_proj.weight": wv.float(),
@@ -341,6 +468,7 @@ class DecaySpec:
     """A toy mixer with state of its own: y_t = x_t + s_t, s_t = decay * s_{t-1} + x_t @ W,
     s kept per request in a state slot of fixed size (hidden floats)."""
 
+    family = "mixer"  # which kind of part this is a spec of (the package's own specs inherit it from MixerSpec)
     kind: str = "toy_decay"
     prefix: str = ""
     hidden_size: int = 0
@@ -387,7 +515,7 @@ def _toy_plan(vocab, H, layers):
 
     return ModelPlan(
         embedding=EmbeddingSpec(vocab, H, "emb"),
-        layers=tuple(LayerSpec("prenorm", mixer=m, feed_forward=GatedMLPSpec("gated_mlp", f"l{i}.mlp", H, 2 * H),
+        layers=tuple(LayerSpec.of("prenorm", mixer=m, feed_forward=GatedMLPSpec("gated_mlp", f"l{i}.mlp", H, 2 * H),
                                mixer_norm=NormSpec("rmsnorm", H, 1e-5, f"l{i}.n1"),
                                feed_forward_norm=NormSpec("rmsnorm", H, 1e-5, f"l{i}.n2")) for i, m in enumerate(layers)),
         order=tuple(RunStep(i) for i in range(len(layers))),
@@ -535,28 +663,9 @@ def test_overlap_scheduling_changes_no_token(tiny_folder, dtype):
     assert small == sync and eng.scheduler.num_preemptions > 0
 
 
-def test_split_outputs_change_no_logit(tiny_folder, monkeypatch):
-    """With the skinny product forced and its split outputs on (the norms add the partial sums of
-    shared tiles on their way in), replay gives bit for bit the logits it gives with them off."""
-    from tandem_b200.engine.core import build_executor, load_model
-    from tandem_b200.engine.executor import StepEntry
-
-    folder = tiny_folder("B", 0.1)
-    tokens = random_tokens(91, 40, 1000)
-    monkeypatch.setenv("TANDEM_GEMM", "skinny")
-    logits = {}
-    for split in ("0", "1"):
-        monkeypatch.setenv("TANDEM_SPLIT_OUTPUT", split)
-        decoder, _ = load_model(folder, "bfloat16", "cuda:0")
-        ex = build_executor(decoder, 8, 16, 1.0, 4)
-        out = [ex.step([StepEntry("a", tokens[:9], [8]), StepEntry("b", tokens[20:22], [1])])]
-        out += [ex.step([StepEntry("a", [tokens[9 + i]], [0]), StepEntry("b", [tokens[22 + i]], [0])]) for i in range(6)]
-        logits[split] = torch.cat(out).cpu()
-    assert torch.equal(logits["0"], logits["1"])
-
-
 @dataclass(frozen=True)
 class RoutedSpec:
+    family = "feed_forward"
     kind: str = "toy_routed"
     prefix: str = ""
     hidden_size: int = 0
@@ -590,8 +699,8 @@ class RoutedFeedForward:
         for e in range(self.spec.experts):
             rows = (choice == e).nonzero().flatten()
             if rows.numel():  # the package's own matrix product on the expert's rows
-                h = torch.relu(ops.as_tensor(ops.linear(x[rows].contiguous(), self.w[f"up{e}"])))
-                out[rows] = (gate[rows, None] * ops.as_tensor(ops.linear(h, self.w[f"down{e}"])).float()).to(x.dtype)
+                h = torch.relu(ops.linear(x[rows].contiguous(), self.w[f"up{e}"]))
+                out[rows] = (gate[rows, None] * ops.linear(h, self.w[f"down{e}"]).float()).to(x.dtype)
         return out
 
 
@@ -629,7 +738,7 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(dtype):
                       position=PositionSpec("toy_half_rate" if i == 0 else "rope", rotary_dim=hd, theta=50.0, max_position=128))
         for i in range(2)])
     layers = list(plan.layers)
-    layers[1] = replace(layers[1], feed_forward=RoutedSpec(prefix="l1.moe", hidden_size=H, experts=3, width=48))
+    layers[1] = layers[1].with_slot("feed_forward", RoutedSpec(prefix="l1.moe", hidden_size=H, experts=3, width=48))
     plan = replace(plan, layers=tuple(layers))
 
     def extra(g):
@@ -729,3 +838,46 @@ def test_overlap_scheduling_under_random_workloads(tiny_folder):
             preempted += eng.scheduler.num_preemptions
         assert results[0] == results[1], (trial, options)
     assert preempted > 0
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_a_generation_run_is_recorded_as_a_trace_that_replays(tiny_folder, tmp_path, overlap):
+    """``record_steps`` writes what the scheduler really did (portions, mixed steps, a request that
+    is preempted and read again) in the replay tool's format; replaying the file gives, at every
+    place where a token was sampled, logits whose argmax is that token."""
+    import json
+
+    import numpy as np
+
+    from tandem_b200 import EngineConfig, LLMEngine, SamplingParams
+    from tandem_b200.engine.trace import replay
+
+    folder = tiny_folder("A", 0.1)
+    eng = LLMEngine(EngineConfig(model=folder, dtype="float32", block_size=4, num_kv_blocks=12, max_num_batched_tokens=16,
+                                 schedule_policy="decode_first", overlap_schedule=overlap))
+    path = str(tmp_path / "run.jsonl")
+    eng.record_steps(path)
+    prompts = [random_tokens(40 + i, 10, 512) for i in range(4)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=14, **GREEDY))
+    need = eng.trace.close()
+    assert eng.scheduler.num_preemptions > 0
+    steps = [json.loads(line) for line in open(path)]
+    assert any("~" in e["id"] for s in steps for e in s["entries"])  # a recomputed request under its new id
+    assert all(t >= 0 for s in steps for e in s["entries"] for t in e["tokens"])  # no placeholder left
+    out_dir = str(tmp_path / "logits")
+    assert replay(folder, "float32", out_dir, need, open(path), page_size=4) == len(steps)
+    sampled = {o.request_id: list(o.output_token_ids) for o in outs}
+    position = {}  # trace id -> tokens fed so far
+    checked = 0
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        rows = np.fromfile(f"{out_dir}/{s['step']}.f32", dtype="<f4").reshape(wanted, 512) if wanted else []
+        r = 0
+        for e in s["entries"]:
+            position[e["id"]] = position.get(e["id"], 0) + len(e["tokens"])
+            for _ in e["want"]:
+                k = position[e["id"]] - 10  # index of the generated token this row decides
+                assert int(rows[r].argmax()) == sampled[e["id"].split("~")[0]][k]
+                r += 1
+                checked += 1
+    assert checked >= 4 * 14

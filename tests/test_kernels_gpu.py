@@ -562,75 +562,6 @@ def test_refusals(ops):
                                  dev(torch.zeros(1, dtype=torch.int32)), 3, 2, 16, 4, None, 1.0)
 
 
-# ----------------------------------------------------------------------------- split outputs
-@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (8, 6144, 4096), (5, 1024, 12288), (16, 24576, 4096), (20, 4096, 2048),
-                                   (3, 136, 64), (32, 768, 4096)])
-def test_split_output_is_bitwise_the_reduced_output(ops, M, N, K):
-    """The skinny product that leaves its shared tiles in pieces, read through each kernel that
-    takes split input, gives bit for bit what the product that adds them up itself gives."""
-    from tandem_b200.kernels import gemm_bf16
-
-    g = torch.Generator().manual_seed(40 + M)
-    x = dev((torch.randn(M, K, generator=g)).bfloat16())
-    w = dev((torch.randn(N, K, generator=g) * 0.05).bfloat16())
-    whole = gemm_bf16.skinny(x, w, torch.bfloat16)
-    split = gemm_bf16.skinny(x, w, torch.bfloat16, split=True)
-    assert isinstance(split, gemm_bf16.SplitOutput)
-    if N * K >= 1 << 20:
-        t = split.tiles.view(-1, 3).cpu()
-        assert (t[:, 0] != t[:, 1]).any()  # some tiles are shared between blocks
-    # residual add + RMSNorm
-    res, wn = dev(torch.randn(M, N, generator=g)), dev(1 + 0.1 * torch.randn(N, generator=g))
-    r1, r2 = res.clone(), res.clone()
-    y1 = ops.add_rmsnorm(whole, r1, wn, 1e-6, torch.bfloat16)
-    y2 = ops.add_rmsnorm(split, r2, wn, 1e-6, torch.bfloat16)
-    assert torch.equal(y1, y2) and torch.equal(r1, r2)
-    rows = dev(torch.tensor([M - 1, 0], dtype=torch.int32))
-    assert torch.equal(ops.add_rmsnorm(whole, res.clone(), wn, 1e-6, torch.bfloat16, rows),
-                       ops.add_rmsnorm(split, res.clone(), wn, 1e-6, torch.bfloat16, rows))
-    # SiLU(gate) * up
-    if N % 16 == 0:
-        assert torch.equal(ops.silu_mul(whole), ops.silu_mul(split))
-    # made whole
-    split = gemm_bf16.skinny(x, w, torch.bfloat16, split=True)
-    assert torch.equal(ops.as_tensor(split), whole)
-    ops.check_status("cuda")
-
-
-def test_split_output_through_q_k_norm_and_rotary(ops):
-    from tandem_b200.cache.layout import to_logical
-    from tandem_b200.kernels import gemm_bf16
-
-    g = torch.Generator().manual_seed(41)
-    nh, nkv, hd, ps, T, K = 6, 2, 128, 16, 7, 2048
-    x = dev(torch.randn(T, K, generator=g).bfloat16())
-    w = dev((torch.randn((nh + 2 * nkv) * hd, K, generator=g) * 0.05).bfloat16())
-    qw, kw = dev(1 + 0.1 * torch.randn(hd, generator=g)), dev(1 + 0.1 * torch.randn(hd, generator=g))
-    cs = dev(torch.randn(64, hd, generator=g))
-    pos = dev(torch.arange(T, dtype=torch.int32) + 3)
-    slots = dev(torch.arange(T, dtype=torch.int32) + 5)
-    outs = []
-    for split in (False, True):
-        kc = dev(torch.zeros(4, nkv, ps, hd, dtype=torch.bfloat16))
-        vc = dev(torch.zeros(4, nkv, ps, hd, dtype=torch.bfloat16))
-        qkv = gemm_bf16.skinny(x, w, torch.bfloat16, split=split)
-        q = ops.qk_norm_rope_kv(qkv, pos, slots, qw, kw, cs, kc, vc, nh, nkv, hd, hd, ps, 1e-6)
-        outs.append((q[:, : nh * hd].clone(), to_logical(kc), to_logical(vc)))
-    for a, b in zip(*outs):
-        assert torch.equal(a, b)
-    ops.check_status("cuda")
-
-
-def test_a_split_output_cannot_be_read_after_the_next_product(ops):
-    from tandem_b200.kernels import gemm_bf16
-
-    x, w = dev(torch.randn(4, 256).bfloat16()), dev(torch.randn(512, 256).bfloat16())
-    stale = gemm_bf16.skinny(x, w, torch.bfloat16, split=True)
-    gemm_bf16.skinny(x, w, torch.bfloat16)
-    with pytest.raises(ops.KernelError, match="reused its scratch"):
-        ops.as_tensor(stale)
-
-
 # ----------------------------------------------------------------------------- long contexts
 @pytest.mark.parametrize("hd,ps,window", [(128, 16, None), (128, 16, 3000), (64, 8, None), (48, 16, None)])
 def test_attention_over_more_pages_than_the_kernels_cache(ops, hd, ps, window):

@@ -45,39 +45,13 @@ def oracle(tiny_folder):
     return get
 
 
-class PageLog:
-    """Every page number the pools hand out, and how often a page went to a new holder while
-    another request was live (its keys lie beside pages that are being read)."""
-
-    def __init__(self, manager) -> None:
-        self.handed: dict = {}
-        self.reused_beside_live = 0
-        for g, group in enumerate(manager.groups):
-            group.pool.allocate = self._wrap(group.pool.allocate, g, manager)
-
-    def _wrap(self, allocate, g, manager):
-        def logged(n):
-            ids = allocate(n)
-            for i in ids:
-                self.handed[(g, i)] = self.handed.get((g, i), 0) + 1
-                if self.handed[(g, i)] > 1 and len(manager.live) > 1:
-                    self.reused_beside_live += 1
-            return ids
-
-        return logged
-
-    @property
-    def pages_reused(self) -> int:
-        return sum(1 for n in self.handed.values() if n > 1)
-
-
 def run_in_process(folder, dtype, steps, page_size, max_tokens, log=None):
     from tandem_b200.engine.core import build_executor, load_model
     from tandem_b200.engine.executor import StepEntry
 
     decoder, _ = load_model(folder, dtype, "cuda:0")
     ex = build_executor(decoder, page_size=page_size, num_pages=-(-max_tokens // page_size), max_requests=8)
-    pages = PageLog(ex.manager)
+    pages = rc.PageLog(ex.manager)
     out = {}
     for st in steps:
         logits = ex.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in st["entries"]], end=st["end"])

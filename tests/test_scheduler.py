@@ -163,11 +163,12 @@ def overlap_step(s, inflight, tokens):
     """One call of the engine's overlap loop with fake tokens: schedule and book step N, then
     resolve step N-1 (``tokens``: request id -> token for the step being resolved)."""
     plan = s.schedule()
+    plan.promised = [x.request.request_id for x in plan.scheduled
+                     if x.request.num_computed_tokens + x.num_tokens >= x.request.num_tokens]
     if not plan.is_empty:
-        s.on_launch(plan)
+        s.book_launch(plan)
     if inflight is not None:
-        s.update_resolved(inflight, {x.request.request_id: tokens.get(x.request.request_id, 7) for x in inflight.scheduled
-                                     if x.request.output_token_ids or x.request.finished})
+        s.deliver_tokens(inflight, {rid: tokens.get(rid, 7) for rid in inflight.promised})
     return plan
 
 
@@ -178,13 +179,14 @@ def test_overlap_books_a_placeholder_and_fills_it_one_step_later():
     a = req("a", 5, max_tokens=3)
     s.add_request(a)
     p0 = overlap_step(s, None, {})
-    assert sizes(p0) == [("a", 5)] and a.output_token_ids == [PLACEHOLDER] and a.num_resolved_outputs == 0
+    assert sizes(p0) == [("a", 5)] and a.token_ids[5:] == [PLACEHOLDER] and a.output_token_ids == [] and a.num_known_outputs == 0
     p1 = overlap_step(s, p0, {"a": 11})  # decodes with its token still on the way, then learns it
-    assert sizes(p1) == [("a", 1)] and a.output_token_ids == [11, PLACEHOLDER] and a.num_resolved_outputs == 1
+    assert sizes(p1) == [("a", 1)] and a.token_ids[5:] == [11, PLACEHOLDER] and a.output_token_ids == [11]
     p2 = overlap_step(s, p1, {"a": 12})
-    assert sizes(p2) == [("a", 1)] and a.output_token_ids == [11, 12, PLACEHOLDER]
+    assert sizes(p2) == [("a", 1)] and a.token_ids[5:] == [11, 12, PLACEHOLDER] and a.num_output_tokens == 3
     p3 = overlap_step(s, p2, {"a": 13})  # the third token is the last it may produce: not scheduled again
     assert p3.is_empty and a.finished and a.finish_reason == "length" and a.output_token_ids == [11, 12, 13]
+    assert a.token_ids == [1, 2, 3, 4, 5, 11, 12, 13]
     assert not s.has_unfinished() and cache.all_free()
 
 
@@ -206,3 +208,66 @@ def test_overlap_resolves_first_when_pages_are_short():
     assert s.may_preempt()  # fewer free pages than a budget's worth: the engine reads the step in flight before it schedules
     s2, _ = make(pages=64, page_size=4, budget=8)
     assert not s2.may_preempt()
+
+
+def test_a_prompt_that_preempts_itself_is_reported_and_not_admitted_again_in_that_step():
+    """prefill_first: the prompt pass comes out empty because the only request reading its prompt
+    had to give way itself (a decoding request holds the rest of the pool and is not in that
+    pass's line).  The step falls back to decoding; it still reports the preemption and admits
+    nobody, so the request is not read from the start again within the same call."""
+    s, cache = make(policy="prefill_first", pages=6, page_size=4, budget=8, max_len=24)
+    d = req("d", 10, max_tokens=12)
+    s.add_request(d)
+    run_step(s), run_step(s), run_step(s)  # d: 8 + 2 prompt tokens, then decoding; it holds 3 pages
+    assert d.is_decoding
+    p = req("p", 14, max_tokens=2)
+    s.add_request(p)
+    assert sizes(run_step(s)) == [("p", 8)]  # 2 more pages; one page is left
+    plan = run_step(s)  # p needs 2 more pages for its last 6 tokens: it is the whole line of the prompt pass
+    assert [r.request_id for r in plan.preempted] == ["p"] and sizes(plan) == [("d", 1)]
+    assert [r.request_id for r in s.waiting] == ["p"] and not cache.has("p") and p.num_computed_tokens == 0
+    cache.check()
+    steps = 0
+    while s.has_unfinished():
+        run_step(s)
+        cache.check()
+        steps += 1
+        assert steps < 100
+    assert d.num_output_tokens == 12 and p.num_output_tokens == 2 and cache.all_free()
+
+
+def test_sampling_params_are_checked_in_words():
+    for bad in (dict(max_tokens=0), dict(temperature=-0.1), dict(top_p=0.0), dict(top_p=1.5), dict(min_p=2.0), dict(stop=[""])):
+        with pytest.raises(ValueError, match="SamplingParams"):
+            SamplingParams(**bad)
+    sp = SamplingParams(stop="END", stop_token_ids=(3, 4))
+    assert sp.stop == ["END"] and sp.stop_token_ids == [3, 4] and not sp.greedy
+    assert SamplingParams(temperature=0.0).greedy and SamplingParams(stop=None).stop == []
+
+
+class ByteTokenizer:
+    """Token = one byte of UTF-8; ids 256 and up are special tokens."""
+
+    def decode(self, ids, skip_special_tokens=True):
+        data = bytes(i for i in ids if i < 256)
+        extra = "" if skip_special_tokens else "".join(f"<{i}>" for i in ids if i >= 256)
+        return data.decode("utf-8", errors="replace") + extra
+
+
+def test_text_grows_token_by_token_and_stops_at_a_stop_string():
+    from tandem_b200.engine.text import OutputText
+
+    text = "héllo wörld — END of it"
+    ids = list(text.encode("utf-8"))
+    t = OutputText(ByteTokenizer(), stop=["END", "zzz"])
+    grown = ""
+    for n in range(1, len(ids) + 1):
+        delta = t.feed(ids[:n], final=False)
+        assert "\ufffd" not in delta  # a character cut in two is held back until it is whole
+        grown += delta
+        if t.stopped:
+            break
+    assert t.stopped and grown == t.text == "héllo wörld — " and n == len("héllo wörld — END".encode("utf-8"))
+    assert t.feed(ids, final=True) == ""  # nothing more after the stop
+    whole = OutputText(ByteTokenizer())
+    assert "".join(whole.feed(ids[:n], final=n == len(ids)) for n in range(1, len(ids) + 1)) == text

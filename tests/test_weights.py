@@ -22,9 +22,7 @@ def _params(cfg_dict):
     params = {"embedding": ParamSpec((plan.embedding.vocab_size, plan.embedding.hidden_size),
                                      (WeightSource(plan.embedding.weight),))}
     for i, layer in enumerate(plan.layers):
-        for slot, family in (("mixer_norm", "norm"), ("mixer", "mixer"), ("feed_forward_norm", "norm"),
-                             ("feed_forward", "feed_forward")):
-            spec = getattr(layer, slot)
+        for slot, family, spec in layer.parts:
             for local, ps in part(family, spec.kind).params(spec).items():
                 params[f"layers.{i}.{slot}.{local}"] = ps
     params["final_norm.weight"] = ParamSpec((plan.final_norm.size,), (WeightSource(plan.final_norm.weight),), "vector")
