@@ -62,7 +62,7 @@ __device__ __forceinline__ const int* cache_table(const int* table, int* table_s
 // One warp's chain of dependent instructions is what bounds a kernel that waits for its stages,
 // so everything that does not need the stage itself (page lookup, addresses, byte counts) is done
 // *before* the wait for the stage to be free, stages that lie wholly inside [kb, ke) skip the
-// byte count's reduction, and all lanes wait on the barrier themselves (no broadcast).  Two warps
+// byte count's reduction, and all lanes wait on the barrier themselves (one vote, no broadcast).  Two warps
 // may share the work: each takes the stages first, first + step, ...
 __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache, const int* table,
                                           int kvh, int nkv, int ps, int kb, int ke, int s0, int num_stages,
@@ -105,7 +105,8 @@ __device__ __forceinline__ void stream_kv(const __nv_bfloat16* k_cache, const __
       const int r0 = (ps_shift >= 0 ? kp & (ps - 1) : kp % ps) + lo, i0 = kp - base + lo;  // first row in the page, in the stage
       const long long src = (long long)page * page_elems + head_off;
       __nv_bfloat16* dst = stage_mem + slot * STAGE_ELEMS + side;
-      if (it >= stages && !mbar_wait(empty + slot, ((it / stages) & 1) ^ 1, abort_flag, status)) break;
+      // all lanes leave together or not at all: a lane that gave up alone would leave the others at the __syncwarp below
+      if (it >= stages && !__all_sync(0xffffffffu, mbar_wait(empty + slot, ((it / stages) & 1) ^ 1, abort_flag, status))) break;
       if (lane == 0) mbar_arrive_expect_tx(full + slot, bytes);
       __syncwarp();
       if (n > 0) {

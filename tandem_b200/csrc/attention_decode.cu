@@ -50,7 +50,9 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   extern __shared__ unsigned char smem_unaligned[];
   // No early griddepcontrol.launch_dependents here: the kernel behind this one (the output projection)
   // becomes resident as this one's blocks exit.  Measured at Qwen3-8B sizes: with the trigger at the
-  // top a decode step takes 3.75 ms at batch 8 and 3.37 ms at batch 1, without it 3.64 and 3.26 ms.
+  // top a decode step takes 3.75 ms at batch 8 and 3.37 ms at batch 1, without it 3.64 and 3.26 ms; with
+  // the trigger behind the last key, in front of the merge, 3.75 ms as well (this kernel has more blocks
+  // than fit at once: a dependent that moves in early takes the room of blocks that have not started).
   // The batch's description (items, their number, block tables) is written by the host before the
   // step's first kernel: it is read, and the barriers are set up, while the kernel in front of
   // this one still runs.  The queries and the newest cache rows are that kernel's output.
@@ -129,7 +131,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
       ldmatrix_x4(qf[ks], smem_u32(q_s + ((lane & 7) + ((lane >> 3) & 1) * 8) * QS + ks * 16 + (lane >> 4) * 8));
     for (int it = 0; it < num_stages; ++it) {
       const int slot = it % STAGES;
-      if (!mbar_wait(full + slot, (it / STAGES) & 1, abort_flag, a.status)) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(full + slot, (it / STAGES) & 1, abort_flag, a.status))) break;  // the whole warp or nobody
       const int k0 = s0 + it * STAGE_KEYS + warp * TILE;
       if (k0 < ke && k0 + TILE > kb) {
         const __nv_bfloat16* kt = stage_mem + slot * STAGE_ELEMS + warp * TILE * HD;

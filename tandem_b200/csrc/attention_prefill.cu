@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(const Prefil
 
   for (int it = 0; it < num_stages; ++it) {
     const int slot = it % STAGES;
-    if (!mbar_wait(full + slot, (it / STAGES) & 1, abort_flag, a.status)) break;
+    if (!__all_sync(0xffffffffu, mbar_wait(full + slot, (it / STAGES) & 1, abort_flag, a.status))) break;  // the whole warp or nobody
     const int base = s0 + it * STAGE_KEYS;
     __nv_bfloat16* kt = stage_mem + slot * STAGE_ELEMS;
     __nv_bfloat16* vt = kt + STAGE_KEYS * HD;

@@ -279,7 +279,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     bool ok = true;
     for (int j = group; j < num_blocks && ok; j += 2) {
       const int base = s0 + j * BLOCK_KEYS;
-      ok = mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_flag, a.status);
+      // every give-up below is taken by the whole warp or by none of it: the tensor-memory
+      // instructions and __syncwarp that follow a wait want all 32 lanes
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_flag, a.status));
       if (!ok) break;
       tc_fence_after();
       float s[64];
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
       // the row's reference after the block before this one, from the thread that had that block
       float m_prev = -INFINITY;
       if (j >= 1) {
-        ok = mbar_wait(pair, (j - 1) & 1, abort_flag, a.status);
+        ok = __all_sync(0xffffffffu, mbar_wait(pair, (j - 1) & 1, abort_flag, a.status));
         if (!ok) break;
         m_prev = m_s[((j - 1) & 1) * BM + row];
       }
@@ -315,11 +317,11 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
       l *= m_mine == -INFINITY ? 0.f : exp2f(m_mine - m_new);  // every move since this thread's last block
       m_mine = m_new;
       if (j >= 2) {  // this block's buffer of P is free once O += P V of the block before the last has completed
-        ok = mbar_wait(pv_done + (j & 1), ((j - 2) >> 1) & 1, abort_flag, a.status);
+        ok = __all_sync(0xffffffffu, mbar_wait(pv_done + (j & 1), ((j - 2) >> 1) & 1, abort_flag, a.status));
         if (!ok) break;
       }
       if (j >= 1 && warp_need) {  // O is touched only between two of the tensor cores' updates; this move is this thread's
-        ok = mbar_wait(pv_done + ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, a.status);
+        ok = __all_sync(0xffffffffu, mbar_wait(pv_done + ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, a.status));
         if (!ok) break;
         tc_fence_after();
         const float corr = m_prev == -INFINITY ? 0.f : exp2f(m_prev - m_new);
@@ -373,7 +375,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     tc_fence_before();
     asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");  // all softmax warps (every path reaches it)
     if (ok && !*abort_flag) ok = mbar_wait(pv_done + ((num_blocks - 1) & 1), ((num_blocks - 1) >> 1) & 1, abort_flag, a.status);
-    if (ok && !*abort_flag) {
+    ok = __all_sync(0xffffffffu, ok && !*abort_flag);  // the loads from tensor memory below are the whole warp's or nobody's
+    if (ok) {
       tc_fence_after();
       const float m_final = l_s[(2 + last_group) * BM + row];
       float total = 0.f;

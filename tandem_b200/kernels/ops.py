@@ -65,7 +65,8 @@ def status_word(device) -> torch.Tensor:
     wait that gave up (1), a block table entry that should have held a page (2)."""
     key = str(device)
     if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):  # an ordinary tensor: it is written in and outside inference mode
+            _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _status[key]
 
 

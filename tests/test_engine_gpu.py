@@ -206,7 +206,8 @@ def test_a_fault_recorded_by_a_kernel_stops_the_engine(tiny_folder):
                                      overlap_schedule=overlap))
         eng.add_request([5, 6, 7], SamplingParams(max_tokens=8, **GREEDY))
         eng.step()
-        ops.status_word(eng.decoder.device).fill_(2)
+        with torch.inference_mode():
+            ops.status_word(eng.decoder.device).fill_(2)
         with pytest.raises(ops.KernelError, match="missing page"):
             for _ in range(3):
                 eng.step()
