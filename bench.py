@@ -148,6 +148,7 @@ def measure_decode(eng, batch: int, steps: int, warmup: int, prompt_len: int = P
         eng.step()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    h2d = eng.executor.h2d_bytes_last  # what one of these steps copied to the device: its batch description
     eng.drain()  # the step in flight (overlap scheduling)
 
     # device-timed: the step function and the sampling kernel back to back, no host read in between
@@ -173,7 +174,7 @@ def measure_decode(eng, batch: int, steps: int, warmup: int, prompt_len: int = P
         eng.abort_request(rid)
     assert eng.cache.all_free()
     return dict(ms=ms, tok_s=batch * 1000.0 / ms, e2e_tok_s=batch * steps / e2e_s, e2e_ms=e2e_s * 1000 / steps,
-                context=context, launches=launches, bytes=decode_bytes(eng, batch, context))
+                context=context, launches=launches, bytes=decode_bytes(eng, batch, context), h2d=h2d)
 
 
 def measure_prefill(eng, warmup: int, reps: int = 3) -> dict:
@@ -228,6 +229,49 @@ def measure_mixed(eng, num_requests: int, new_tokens: int, seed: int = 0) -> dic
     return result
 
 
+def measure_extras(steps: int, warmup: int) -> dict:
+    """The two other workloads the benchmark is quoted on, each with a model of its own, as flat
+    keys beside the headline: decode at batch 8 at Qwen3-32B sizes (1,024-token prompts), and 32
+    requests with prompts of 128 to 4,096 tokens and 128 new tokens each at Qwen3-14B sizes."""
+    import gc
+
+    import torch
+
+    out: dict = {}
+    pk = peaks()
+
+    def release():
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    try:
+        t0 = time.perf_counter()
+        eng = build_engine(QWEN3_32B, QWEN3_32B["num_hidden_layers"], 8, 1024 + 128 + steps + 2 * warmup + 32)
+        r = measure_decode(eng, 8, steps, warmup, 1024, 128)
+        out.update({"qwen3_32b_layers": eng.model_config.num_hidden_layers, "qwen3_32b_decode_b8_tok_s": round(r["tok_s"], 1),
+                    "qwen3_32b_decode_b8_ms": round(r["ms"], 4), "qwen3_32b_decode_b8_e2e_tok_s": round(r["e2e_tok_s"], 1),
+                    "qwen3_32b_decode_b8_hbm_frac": round(r["bytes"] / (r["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+                    "qwen3_32b_seconds": round(time.perf_counter() - t0, 1)})
+        del eng
+    except Exception as exc:  # the headline stands without it
+        out["qwen3_32b_error"] = f"{type(exc).__name__}: {exc}"[:200]
+    release()
+    try:
+        t0 = time.perf_counter()
+        eng = build_engine(QWEN3_14B, QWEN3_14B["num_hidden_layers"], 32, 4096 + 128)
+        r = measure_mixed(eng, 32, 128)
+        out.update({"qwen3_14b_layers": eng.model_config.num_hidden_layers,
+                    "qwen3_14b_mixed_generated_tok_s": round(r["new_tokens"] / r["seconds"], 1),
+                    "qwen3_14b_mixed_processed_tok_s": round((r["new_tokens"] + r["prompt_tokens"]) / r["seconds"], 1),
+                    "qwen3_14b_mixed_seconds": round(r["seconds"], 3), "qwen3_14b_mixed_steps": r["steps"],
+                    "qwen3_14b_mixed_preemptions": r["preemptions"], "qwen3_14b_seconds": round(time.perf_counter() - t0, 1)})
+        del eng
+    except Exception as exc:
+        out["qwen3_14b_error"] = f"{type(exc).__name__}: {exc}"[:200]
+    release()
+    return out
+
+
 def main_mixed(args, name: str, shape: dict) -> int:
     pk = peaks()
     per_request = 4096 + args.new_tokens
@@ -263,6 +307,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--no-extra", action="store_true", help="skip the Qwen3-32B decode and Qwen3-14B mixed-workload figures")
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES))
     ap.add_argument("--prompt-len", type=int, default=PROMPT, help="prompt length of the decode measurements")
@@ -304,6 +349,14 @@ def main() -> int:
                                                           args.new_tokens)["tok_s"], 1)
     clocks = sampler.stop()
     c = eng.model_config
+    h2d_bytes = main_pt["h2d"]
+    extra = {}
+    if not args.no_extra and not args.no_points and args.shape == "8b" and args.layers == shape["num_hidden_layers"]:
+        del eng  # the other models get the memory
+        extra = measure_extras(min(args.steps, 32), args.warmup)
+        graphs_on = not args.no_cuda_graph
+    else:
+        graphs_on = eng.graphs is not None
     achieved = main_pt["bytes"] / (main_pt["ms"] * 1e-3) / 1e9
     out = {
         "metric": f"decode tok/s at batch {args.batch}, {name}, {args.prompt_len:,}-token prompts (one B200)",
@@ -314,10 +367,10 @@ def main() -> int:
                    "hidden": c.hidden_size, "q_heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
                    "head_dim": c.head_dim, "intermediate": c.intermediate_size, "vocab": c.vocab_size,
                    "global_batch": args.batch, "seq_len": main_pt["context"], "prompt_len": args.prompt_len, "page_size": PAGE,
-                   "parallelism": "single GPU", "cuda_graph": eng.graphs is not None,
+                   "parallelism": "single GPU", "cuda_graph": graphs_on,
                    "l2": "inputs larger than L2: each step streams every weight", "peaks": pk["source"]},
         "e2e": {"value": round(main_pt["e2e_tok_s"], 1), "unit": "tok/s", "ms_per_step": round(main_pt["e2e_ms"], 4),
-                "h2d_bytes_per_step": eng.executor.h2d_bytes_last, "d2h_bytes_per_step": 4 * (args.batch + 1)},
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4 * (args.batch + 1)},
         "gpu_launches": int(main_pt["launches"]) * args.steps,
         "prefill": {"value": round(pre["tok_s"], 1), "tokens": PROMPT, "ms": round(pre["ms"], 3),
                     "frac": round(pre["flops"] / (pre["ms"] * 1e-3) / (pk["tflops"] * 1e12), 4)},
@@ -326,6 +379,8 @@ def main() -> int:
         "points": points,
         "clocks": clocks,
     }
+    if extra:
+        out["extra"] = extra
     print(json.dumps(out))
     return 0
 

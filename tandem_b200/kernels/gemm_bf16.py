@@ -13,10 +13,11 @@ this package beside the library:
 * more rows: the library, except for the gate/up projection, whose activation runs in the
   epilogue of ``csrc/gemm_wide.cu``.
 
-Which kernel computes a shape is a fixed rule (``choose``, ``choose_gated``): the same shape always
-runs the same kernel, so bfloat16 results are reproducible from run to run and a CUDA graph
-captures what an eager step runs.  The thresholds of the rule were read off timings on a B200
-(``python -m tandem_b200.kernels.microbench dispatch`` prints them next to what the rule picks).
+Which kernel computes a shape is fixed (``choose``, ``choose_gated``): a table of shapes that were
+measured on a B200 (``MEASURED``), and a rule for all others.  The same shape always runs the same
+kernel, so bfloat16 results are reproducible from run to run and a CUDA graph captures what an
+eager step runs.  ``python -m tandem_b200.kernels.microbench dispatch`` times every candidate and
+prints the table's lines and what the rule would have picked.
 ``TANDEM_GEMM=skinny``, ``=gemv``, ``=wide`` or ``=library`` forces one kernel where it applies.
 """
 
@@ -35,7 +36,7 @@ GEMV_MAX_K = 16384  # beyond this the streaming kernel's rows of x outgrow share
 # The skinny kernel costs about 9 us whatever the shape; the library's small-batch kernels cost less
 # to start and stream a little more slowly.  The skinny kernel wins from this many weight bytes on
 # (per class of rows; measured: it takes the output head at every class, gate_up of Qwen3-32B up to 16 rows).
-SKINNY_MIN_WEIGHT_BYTES = {8: 200 << 20, 16: 400 << 20, 32: 1 << 30, 64: 1 << 30}
+SKINNY_MIN_WEIGHT_BYTES = {1: 200 << 20, 2: 200 << 20, 4: 400 << 20, 8: 400 << 20, 16: 400 << 20, 32: 1 << 30, 64: 1 << 30}
 # gate/up with the activation in the epilogue of the wide kernel: where one wave of its 128-row
 # tiles is full (up to 128 rows) or the waves are many (from 1536 rows); in between the library's
 # tilings followed by the activation kernel are 5 to 10 % faster.
@@ -130,9 +131,35 @@ def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, gated: b
     return y
 
 
+ROW_CLASSES = (1, 2, 4, 8, 16, 32, 64)
+
+# Measured on a B200: (rows of W, K) -> class of rows -> the fastest kernel (this package's kept where
+# within 2 % of it), for the projections of Qwen3-8B, -14B and -32B and the output head; what
+# ``python -m tandem_b200.kernels.microbench dispatch --shapes 8b|14b|32b`` prints.  Shapes that are
+# not listed follow the rule in ``choose``.  12vivi/tandem keeps such a table per GPU
+# (python/tandem/layers/triton_gemv.py:221-267).
+_G, _S, _L = "gemv", "skinny", "library"
+MEASURED = {
+    (6144, 4096): {1: _G, 2: _G, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
+    (4096, 4096): {1: _G, 2: _G, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
+    (24576, 4096): {1: _G, 2: _G, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
+    (4096, 12288): {1: _G, 2: _G, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
+    (151936, 4096): {1: _G, 2: _G, 4: _G, 8: _G, 16: _S, 32: _S, 64: _S},
+    (7168, 5120): {1: _L, 2: _L, 4: _L, 8: _L, 16: _L, 32: _L, 64: _L},
+    (5120, 5120): {1: _L, 2: _L, 4: _L, 8: _L, 16: _L, 32: _L, 64: _L},
+    (34816, 5120): {1: _G, 2: _G, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
+    (5120, 17408): {1: _L, 2: _L, 4: _L, 8: _L, 16: _L, 32: _L, 64: _L},
+    (151936, 5120): {1: _S, 2: _S, 4: _S, 8: _G, 16: _S, 32: _S, 64: _S},
+    (10240, 5120): {1: _G, 2: _L, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
+    (5120, 8192): {1: _G, 2: _L, 4: _L, 8: _L, 16: _L, 32: _L, 64: _L},
+    (51200, 5120): {1: _G, 2: _G, 4: _G, 8: _G, 16: _S, 32: _S, 64: _L},
+    (5120, 25600): {1: _S, 2: _S, 4: _S, 8: _S, 16: _S, 32: _L, 64: _L},
+}
+
+
 def row_class(M: int) -> int:
-    """Row counts fall into classes as the CUDA graphs' buckets do: up to 8, 16, 32, 64."""
-    return next(c for c in (8, 16, 32, 64) if M <= c) if M <= SKINNY_MAX_ROWS else 0
+    """Row counts fall into classes: up to 1, 2, 4, 8, 16, 32, 64 rows."""
+    return next(c for c in ROW_CLASSES if M <= c) if M <= SKINNY_MAX_ROWS else 0
 
 
 def choose(M: int, N: int, K: int, aligned: bool = True) -> str:
@@ -143,6 +170,9 @@ def choose(M: int, N: int, K: int, aligned: bool = True) -> str:
     forced = os.environ.get("TANDEM_GEMM")
     if forced == "library" or (forced == "gemv" and can_gemv) or (forced == "skinny" and can_skinny):
         return forced
+    measured = MEASURED.get((N, K), {}).get(row_class(M))
+    if measured == "library" or (measured == "gemv" and can_gemv) or (measured == "skinny" and can_skinny):
+        return measured
     if can_gemv and gemv_preferred(M, N, K):
         return "gemv"
     if can_skinny and N * K * 2 >= SKINNY_MIN_WEIGHT_BYTES[row_class(M)]:

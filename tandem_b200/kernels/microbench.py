@@ -5,7 +5,8 @@
     python -m tandem_b200.kernels.microbench prefill-attention --tokens 2048
     python -m tandem_b200.kernels.microbench tokenwise --tokens 2048
     python -m tandem_b200.kernels.microbench norm-gemm --m 8 --n 6144 --k 4096
-    python -m tandem_b200.kernels.microbench dispatch [--shapes 8b|32b]
+    python -m tandem_b200.kernels.microbench dispatch [--shapes 8b|14b|32b]
+    python -m tandem_b200.kernels.microbench step-timeline --batch 8 --layers 4
 
 Timing follows 12vivi/tandem's kernel benchmarks (benchmarks/bench_gemv.py:3-6,35-56): the calls are
 captured in one CUDA graph so that launch cost does not count, and weights or caches are rotated
@@ -102,6 +103,7 @@ def bench_norm_gemm(args) -> None:
 
 LAYER_SHAPES = {  # (name, N, K) of the products of a layer and the output head
     "8b": [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096), ("down", 4096, 12288), ("head", 151936, 4096)],
+    "14b": [("qkv", 7168, 5120), ("o", 5120, 5120), ("gate_up", 34816, 5120), ("down", 5120, 17408), ("head", 151936, 5120)],
     "32b": [("qkv", 10240, 5120), ("o", 5120, 8192), ("gate_up", 51200, 5120), ("down", 5120, 25600), ("head", 151936, 5120)],
 }
 
@@ -115,7 +117,8 @@ def bench_dispatch(args) -> None:
     for name, N, K in LAYER_SHAPES[args.shapes]:
         ws = [torch.randn(N, K, device="cuda", dtype=bf) * 0.02 for _ in range(copies_for(N * K * 2))]
         out = torch.float32 if name == "head" else bf
-        for M in (1, 4, 8, 16, 32, 64):
+        winners = {}
+        for M in gemm_bf16.ROW_CLASSES:
             x = torch.randn(M, K, device="cuda", dtype=bf)
             times = {"library": time_calls(lambda i: gemm_bf16._library(x, ws[i % len(ws)], out), args.iters, args.graph)}
             if gemm_bf16.skinny_applies(M, N, K):
@@ -123,9 +126,12 @@ def bench_dispatch(args) -> None:
             if gemm_bf16.gemv_applies(M, N, K):
                 times["gemv"] = time_calls(lambda i: gemm_bf16.gemv(x, ws[i % len(ws)], out), args.iters, args.graph)
             rule, best = gemm_bf16.choose(M, N, K), min(times, key=times.get)
+            # this package's kernels are kept where they are within 2 % of the fastest (gemv before skinny)
+            winners[M] = next((k for k in ("gemv", "skinny") if k in times and times[k] <= 1.02 * times[best]), best)
             cells = "  ".join(f"{k} {v:7.1f} us" for k, v in times.items())
             print(f"{name:8s} M={M:3d} N={N:6d} K={K:5d} ({N * K * 2 >> 20:4d} MiB)  {cells}  rule: {rule}"
                   + ("" if rule == best else f"  (fastest: {best}, {times[rule] / times[best]:.2f}x)"))
+        print(f"    ({N}, {K}): {winners},")
         if name == "gate_up":
             for M in (128, 256, 512, 1024, 2048, 4096):
                 x = torch.randn(M, K, device="cuda", dtype=bf)
@@ -133,6 +139,55 @@ def bench_dispatch(args) -> None:
                 b = time_calls(lambda i: ops.silu_mul(gemm_bf16._library(x, ws[i % len(ws)], bf)), args.iters, args.graph)
                 print(f"gate_up  M={M:4d} gated: wide {a:8.1f} us  library + silu_mul {b:8.1f} us  rule: {gemm_bf16.choose_gated(M, N, K)}")
         del ws
+
+
+def bench_step_timeline(args) -> None:
+    """When every kernel of one decode step (a CUDA graph replay) starts and ends on the device, from
+    the profiler's activity records: what lies on the critical path and what hides behind a neighbour."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from tandem_b200.config.engine_config import EngineConfig
+    from tandem_b200.engine.core import random_model
+    from tandem_b200.engine.llm_engine import LLMEngine
+    from tandem_b200.kernels import ops
+    from tandem_b200.sampling.params import SamplingParams
+
+    H = {"8b": 4096, "14b": 5120, "32b": 5120}[args.shapes]
+    heads = {"8b": 32, "14b": 40, "32b": 64}[args.shapes]
+    inter = {"8b": 12288, "14b": 17408, "32b": 25600}[args.shapes]
+    config = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=args.layers, hidden_size=H,
+                  num_attention_heads=heads, num_key_value_heads=8, head_dim=128, intermediate_size=inter, vocab_size=151936,
+                  rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=args.context + 256)
+    with torch.inference_mode(False):
+        decoder, cfg = random_model(config, seed=0, dtype="bfloat16")
+        pages = args.batch * (-(-(args.context + 64) // 16)) + 8
+        eng = LLMEngine(EngineConfig(model="", dtype="bfloat16", block_size=16, num_kv_blocks=pages, max_num_seqs=args.batch,
+                                     max_model_len=args.context + 256, cuda_graph_max_bs=args.batch),
+                        decoder=decoder, model_config=cfg, load_tokenizer=False)
+        g = torch.Generator().manual_seed(args.batch)
+        sp = SamplingParams(max_tokens=64, temperature=0.0, ignore_eos=True)
+        for _ in range(args.batch):
+            eng.add_request(torch.randint(10, 100000, (args.context,), generator=g).tolist(), sp)
+        while eng.scheduler.waiting or any(not r.is_decoding for r in eng.requests.values()):
+            eng.step()
+        for _ in range(8):
+            eng.step()
+        eng.drain()
+        entries = eng.entries_of(eng.scheduler.schedule())
+        for e in entries:
+            e.want = [0]
+        for _ in range(5):
+            ops.argmax(eng.graphs.run(entries))
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            ops.argmax(eng.graphs.run(entries))
+            torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if e.device_time_total > 0 and "Memcpy" not in e.name), key=lambda e: e.time_range.start)
+    t0 = events[0].time_range.start
+    print(f"decode step, batch {args.batch}, context {args.context}, {args.layers} layers of Qwen3-{args.shapes} sizes: start, duration, end (us)")
+    for e in events:
+        start = e.time_range.start - t0
+        print(f"{start:9.1f} +{e.device_time_total:7.1f} = {start + e.device_time_total:9.1f}  {e.name[:70]}")
 
 
 def _cache(pages: int, nkv: int, ps: int, hd: int):
@@ -251,6 +306,12 @@ def main(argv=None) -> None:
     dp = sub.add_parser("dispatch", parents=[common])
     dp.add_argument("--shapes", choices=sorted(LAYER_SHAPES), default="8b")
     dp.set_defaults(fn=bench_dispatch)
+    tl = sub.add_parser("step-timeline", parents=[common])
+    tl.add_argument("--batch", type=int, default=8)
+    tl.add_argument("--context", type=int, default=2048)
+    tl.add_argument("--layers", type=int, default=4)
+    tl.add_argument("--shapes", choices=sorted(LAYER_SHAPES), default="8b")
+    tl.set_defaults(fn=bench_step_timeline)
     args = p.parse_args(argv)
     with torch.inference_mode():
         args.fn(args)
