@@ -343,6 +343,27 @@ def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tiny_folder
         ids.append(tok)
 
 
+def test_temperature_sampling_in_bfloat16_is_reproducible(tiny_folder):
+    """Which kernel computes a product is fixed, so a bfloat16 run gives the same logits, and with
+    seeded draws the same tokens, every time; with other seeds it gives other tokens."""
+    from tandem_b200 import EngineConfig, LLMEngine, SamplingParams
+
+    folder = tiny_folder("B", 0.1)
+    prompts = [random_tokens(160 + i, n, 1000) for i, n in enumerate([3, 20, 45])]
+
+    def run(seed):
+        sp = [SamplingParams(max_tokens=16, temperature=0.9, top_k=40, top_p=0.95, min_p=0.01, seed=seed + i, ignore_eos=True)
+              for i in range(3)]
+        eng = LLMEngine(EngineConfig(model=folder, dtype="bfloat16", block_size=16, num_kv_blocks=32, max_num_batched_tokens=32))
+        outs = eng.generate(prompts, sp)
+        assert eng.cache.all_free() and all(0 <= t < 1000 for o in outs for t in o.output_token_ids)
+        return [o.output_token_ids for o in outs]
+
+    first = run(7)
+    assert first == run(7)
+    assert first != run(8)
+
+
 class LetterTokenizer:
     """One letter per token id."""
 
