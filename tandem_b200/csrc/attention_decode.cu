@@ -12,10 +12,18 @@
 // into several items leaves its partials in scratch memory; the block that arrives last (an
 // atomic counter per request and kv head, reset by that block) merges them: nothing waits.
 //
+// In a step of decoded tokens only, the kernel in front of this one (per-head norm, rotary encoding
+// and the cache write of the new token) can be folded in (`DecodeArgs::fresh`): the consumer warps
+// normalise and rotate their query rows as they load them, and in the block that holds a request's
+// newest key the warp whose 16 keys include it makes that key (and copies its value) itself, into
+// its stage of shared memory over the stale row that the bulk copy brought, and into the cache for the
+// steps to come.  The arithmetic is the stand-alone kernel's (rope_core.cuh), bit for bit.
+//
 // It does what 12vivi/tandem's Triton split-KV kernel does
 // (python/tandem/layers/triton_decode_attn.py:28-129), and stands where it otherwise calls
 // FlashInfer's decode wrapper (python/tandem/layers/flashinfer_attention.py:138-157).
 #include "attention_common.cuh"
+#include "rope_core.cuh"
 
 namespace tb {
 
@@ -44,7 +52,34 @@ struct DecodeArgs {
   int* status;
   int nh, nkv, page_size;
   float scale_log2;
+  // fresh != 0: q is the raw projection [T, (nh + 2 nkv) * HD] (q_stride = that width) and the cache has not got the
+  // newest row yet; HD is a power of two and the whole head rotates
+  int fresh;
+  const float* q_norm_w;  // [HD] or null
+  const float* k_norm_w;
+  const float* cos_sin;   // [max_pos, HD]: cos of the HD / 2 angles, then their sin
+  const int* positions;   // [T]
+  const int* slots;       // [T] page * page_size + offset of the new row
+  __nv_bfloat16* k_cache_w;
+  __nv_bfloat16* v_cache_w;
+  float eps;
+  int max_pos;
 };
+
+// The lanes of a head (HD / 16 of them) load, normalise and rotate one row x[0 .. HD) of the raw projection;
+// lane `sub` gets elements [8 sub, 8 sub + 8) in lo and [HD/2 + 8 sub, ...) in hi.  w: norm weight [HD] or null.
+__device__ __forceinline__ void fresh_row(const __nv_bfloat16* x, const float* w, const float* angles, int sub, unsigned head_lanes,
+                                          float eps, uint4& lo, uint4& hi) {
+  constexpr int half = HD / 2, lanes_per_head = HD / 16;
+  const int j = sub * 8;
+  float a[8], b[8], wv[16], cc[8], ssn[8];
+  unpack8(*reinterpret_cast<const uint4*>(x + j), a);
+  unpack8(*reinterpret_cast<const uint4*>(x + half + j), b);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { wv[i] = w ? w[j + i] : 1.f; wv[8 + i] = w ? w[half + j + i] : 1.f; }
+  load_angles(angles, half, j, cc, ssn);
+  norm_rope_pairs(a, b, wv, w != nullptr, cc, ssn, HD, eps, head_lanes, lanes_per_head, lo, hi);
+}
 
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeArgs a) {
   extern __shared__ unsigned char smem_unaligned[];
@@ -89,6 +124,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   __syncthreads();  // the barriers stand; nothing slow has been waited for yet
   // The producer needs the page numbers only and starts to stream as soon as it has them; the
   // consumers load the query tile meanwhile and meet among themselves.
+  const bool newest_block = (int)blockIdx.x == first_item + nsplits - 1;  // this block's keys end with the request's newest
   const int* table = nullptr;
   int streamed = 0;
   if (warp == WARPS) {
@@ -98,18 +134,37 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
     // step; every older row was written by steps that ended before this step's description was
     // copied to the device.  So the first stages are on their way before the kernel in front of
     // this one has finished, all but the stage that holds the newest row.
-    const bool newest_here = (int)blockIdx.x == first_item + nsplits - 1;
-    streamed = min(STAGES, num_stages - (newest_here ? 1 : 0));
+    const bool newest_here = newest_block;
+    streamed = min(STAGES, num_stages - ((newest_here && !a.fresh) ? 1 : 0));  // folded in: the stale row is overwritten in shared memory
     stream_kv(a.k_cache, a.v_cache, table, kvh, a.nkv, ps, kb, ke, s0,
               streamed, STAGES, stage_mem, full, empty, abort_flag, a.status, lane);
   }
   pdl_wait();
   if (warp < WARPS) {
-    for (int i = tid; i < 16 * (HD / 8); i += WARPS * 32) {  // the query tile, 16 bytes at a time
-      const int g = i / (HD / 8), c = i % (HD / 8);
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (g < rows) v = *reinterpret_cast<const uint4*>(a.q + (size_t)t * a.q_stride + (size_t)(kvh * G + row0 + g) * HD + c * 8);
-      *reinterpret_cast<uint4*>(q_s + g * QS + c * 8) = v;
+    if (!a.fresh) {
+      for (int i = tid; i < 16 * (HD / 8); i += WARPS * 32) {  // the query tile, 16 bytes at a time
+        const int g = i / (HD / 8), c = i % (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (g < rows) v = *reinterpret_cast<const uint4*>(a.q + (size_t)t * a.q_stride + (size_t)(kvh * G + row0 + g) * HD + c * 8);
+        *reinterpret_cast<uint4*>(q_s + g * QS + c * 8) = v;
+      }
+    } else if constexpr ((HD & (HD - 1)) == 0) {
+      // the raw query rows, normalised and rotated on their way in: HD / 16 lanes per head
+      constexpr int LPH = HD / 16;
+      int pos = a.positions[t];
+      pos = pos < 0 ? 0 : (pos >= a.max_pos ? a.max_pos - 1 : pos);
+      const float* angles = a.cos_sin + (size_t)pos * HD;
+      const int sub = lane % LPH;
+      const unsigned head_lanes = (LPH == 32 ? 0xffffffffu : ((1u << LPH) - 1u)) << (lane - sub);
+      for (int g0 = 0; g0 < 16; g0 += WARPS * 32 / LPH) {  // whole warps walk the rows together: the shuffles want every lane of a head
+        const int g = g0 + tid / LPH;
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+        if (g < rows) fresh_row(a.q + (size_t)t * a.q_stride + (size_t)(kvh * G + row0 + g) * HD, a.q_norm_w, angles, sub, head_lanes, a.eps, lo, hi);
+        if (g < 16) {
+          *reinterpret_cast<uint4*>(q_s + g * QS + sub * 8) = lo;
+          *reinterpret_cast<uint4*>(q_s + g * QS + HD / 2 + sub * 8) = hi;
+        }
+      }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory");  // the four consumer warps: every path reaches it
   }
@@ -137,6 +192,39 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
         const __nv_bfloat16* kt = stage_mem + slot * STAGE_ELEMS + warp * TILE * HD;
         __nv_bfloat16* vt = stage_mem + slot * STAGE_ELEMS + STAGE_KEYS * HD + warp * TILE * HD;
         if (k0 < kb || k0 + TILE > ke) zero_value_rows(vt, k0, kb, ke, lane);
+        if constexpr ((HD & (HD - 1)) == 0) {
+          if (a.fresh && newest_block && ke - 1 >= k0 && ke - 1 < k0 + TILE) {
+            // this warp's 16 keys include the request's newest one, which no kernel has made yet: the first
+            // HD / 16 lanes make it from the raw projection, for this stage and for the cache
+            constexpr int LPH = HD / 16;
+            if (lane < LPH) {
+              const int i = ke - 1 - k0;  // row in the sub-tile
+              int pos = a.positions[t];
+              pos = pos < 0 ? 0 : (pos >= a.max_pos ? a.max_pos - 1 : pos);
+              const unsigned head_lanes = LPH == 32 ? 0xffffffffu : ((1u << LPH) - 1u);
+              const __nv_bfloat16* raw = a.q + (size_t)t * a.q_stride;
+              uint4 lo, hi;
+              fresh_row(raw + (size_t)(a.nh + kvh) * HD, a.k_norm_w, a.cos_sin + (size_t)pos * HD, lane, head_lanes, a.eps, lo, hi);
+              const __nv_bfloat16* vraw = raw + (size_t)(a.nh + a.nkv + kvh) * HD;
+              const uint4 vlo = *reinterpret_cast<const uint4*>(vraw + lane * 8), vhi = *reinterpret_cast<const uint4*>(vraw + HD / 2 + lane * 8);
+              __nv_bfloat16* ktw = const_cast<__nv_bfloat16*>(kt);
+              *reinterpret_cast<uint4*>(ktw + tile_elem(i, lane * 8, xmask)) = lo;
+              *reinterpret_cast<uint4*>(ktw + tile_elem(i, HD / 2 + lane * 8, xmask)) = hi;
+              *reinterpret_cast<uint4*>(vt + tile_elem(i, lane * 8, xmask)) = vlo;
+              *reinterpret_cast<uint4*>(vt + tile_elem(i, HD / 2 + lane * 8, xmask)) = vhi;
+              const int slot = a.slots[t];
+              if (blockIdx.z == 0 && slot >= 0) {  // one block per (request, kv head) writes the cache
+                const long long tile = cache_tile(slot / ps, kvh, a.nkv, ps, HD);
+                const int r = slot % ps;
+                *reinterpret_cast<uint4*>(a.k_cache_w + tile + cache_offset<__nv_bfloat16>(r, lane * 8, ps, HD)) = lo;
+                *reinterpret_cast<uint4*>(a.k_cache_w + tile + cache_offset<__nv_bfloat16>(r, HD / 2 + lane * 8, ps, HD)) = hi;
+                *reinterpret_cast<uint4*>(a.v_cache_w + tile + cache_offset<__nv_bfloat16>(r, lane * 8, ps, HD)) = vlo;
+                *reinterpret_cast<uint4*>(a.v_cache_w + tile + cache_offset<__nv_bfloat16>(r, HD / 2 + lane * 8, ps, HD)) = vhi;
+              }
+            }
+            __syncwarp();
+          }
+        }
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
@@ -327,8 +415,10 @@ int tb_attention_decode_head_dim() { return tb::HD; }
 int tb_attention_decode(void* stream, const void* q, int q_stride, const void* k_cache, const void* v_cache,
                         const int* block_table, int table_stride, const int* items, const int* num_items,
                         int max_items, void* out, float* part_o, float* part_ml, int* counters, int* status, int nh,
-                        int nkv, int page_size, float scale) {
+                        int nkv, int page_size, float scale, int fresh, const float* q_norm_w, const float* k_norm_w,
+                        const float* cos_sin, const int* positions, const int* slots, float eps, int max_pos) {
   if (max_items <= 0) return 0;
+  if (fresh && ((tb::HD & (tb::HD - 1)) != 0 || !cos_sin || !positions || !slots || max_pos <= 0)) return TB_ERR_BAD_SIZE;
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0) return TB_ERR_BAD_SIZE;
   if (!(page_size == 1 || page_size == 2 || page_size == 4 || page_size == 8 || page_size % 16 == 0))
     return TB_ERR_BAD_SIZE;
@@ -340,6 +430,8 @@ int tb_attention_decode(void* stream, const void* q, int q_stride, const void* k
   a.out = (__nv_bfloat16*)out; a.part_o = part_o; a.part_ml = part_ml; a.counters = counters; a.status = status;
   a.nh = nh; a.nkv = nkv; a.page_size = page_size;
   a.scale_log2 = scale * 1.4426950408889634f;
+  a.fresh = fresh; a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w; a.cos_sin = cos_sin; a.positions = positions; a.slots = slots;
+  a.k_cache_w = (__nv_bfloat16*)k_cache; a.v_cache_w = (__nv_bfloat16*)v_cache; a.eps = eps; a.max_pos = max_pos;
   static bool configured = false;
   const size_t smem = tb::decode_smem_bytes();
   if (!configured) {

@@ -6,6 +6,7 @@
 // add+norm, which add in float32 and round once, as these kernels do).
 #include "cache_layout.cuh"
 #include "common.cuh"
+#include "rope_core.cuh"
 
 namespace tb {
 
@@ -344,12 +345,7 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* __restrict__ qkv, con
   int pos = positions[t];
   pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);  // the host checks positions
   float cc[8], ssn[8];
-  {
-    const float4 c0 = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + j), c1 = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + j + 4);
-    const float4 s0 = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + j), s1 = *reinterpret_cast<const float4*>(cos_sin + (size_t)pos * hd + half + j + 4);
-    cc[0] = c0.x; cc[1] = c0.y; cc[2] = c0.z; cc[3] = c0.w; cc[4] = c1.x; cc[5] = c1.y; cc[6] = c1.z; cc[7] = c1.w;
-    ssn[0] = s0.x; ssn[1] = s0.y; ssn[2] = s0.z; ssn[3] = s0.w; ssn[4] = s1.x; ssn[5] = s1.y; ssn[6] = s1.z; ssn[7] = s1.w;
-  }
+  load_angles(cos_sin + (size_t)pos * hd, half, j, cc, ssn);
   const int slot = slots ? slots[t] : -1;
   __nv_bfloat16* row = qkv + (size_t)t * heads * hd;
   for (int h = h_begin + warp * heads_per_warp + lane / lanes_per_head; h < h_end; h += 4 * heads_per_warp) {
@@ -371,33 +367,12 @@ __global__ void qk_norm_rope_kv_bf16_kernel(__nv_bfloat16* __restrict__ qkv, con
       continue;
     }
     float a[8], b[8];
-    {
-      const __nv_bfloat162* lp = reinterpret_cast<const __nv_bfloat162*>(&lo_raw);
-      const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&hi_raw);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 l2 = __bfloat1622float2(lp[i]), h2 = __bfloat1622float2(hp[i]);
-        a[2 * i] = l2.x; a[2 * i + 1] = l2.y; b[2 * i] = h2.x; b[2 * i + 1] = h2.y;
-      }
-    }
-    const float* w = is_q ? wq : wk;
-    if (is_q ? q_w != nullptr : k_w != nullptr) {
-      float ss = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
-      for (int o = lanes_per_head >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(head_lanes, ss, o);
-      const float inv = rsqrtf(ss / (float)hd + eps);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { a[i] = a[i] * inv * w[i]; b[i] = b[i] * inv * w[8 + i]; }
-    }
-    uint32_t lo_out[4], hi_out[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      lo_out[i] = pack2(a[2 * i] * cc[2 * i] - b[2 * i] * ssn[2 * i], a[2 * i + 1] * cc[2 * i + 1] - b[2 * i + 1] * ssn[2 * i + 1]);
-      hi_out[i] = pack2(b[2 * i] * cc[2 * i] + a[2 * i] * ssn[2 * i], b[2 * i + 1] * cc[2 * i + 1] + a[2 * i + 1] * ssn[2 * i + 1]);
-    }
-    *reinterpret_cast<uint4*>(dst + at_lo) = make_uint4(lo_out[0], lo_out[1], lo_out[2], lo_out[3]);
-    *reinterpret_cast<uint4*>(dst + at_hi) = make_uint4(hi_out[0], hi_out[1], hi_out[2], hi_out[3]);
+    unpack8(lo_raw, a);
+    unpack8(hi_raw, b);
+    uint4 lo_out, hi_out;
+    norm_rope_pairs(a, b, is_q ? wq : wk, is_q ? q_w != nullptr : k_w != nullptr, cc, ssn, hd, eps, head_lanes, lanes_per_head, lo_out, hi_out);
+    *reinterpret_cast<uint4*>(dst + at_lo) = lo_out;
+    *reinterpret_cast<uint4*>(dst + at_hi) = hi_out;
   }
 }
 

@@ -108,11 +108,30 @@ def _workspace(device, items: int, num_kv_heads: int, groups: int, head_dim: int
     return ws
 
 
+FRESH_MAX_TOKENS = 8  # rows up to which the projection in front is this package's streaming kernel
+
+
+def fresh_applies(head_dim: int, rotary_dim: int, writable: bool, num_tokens: int = 1) -> bool:
+    """Whether decode attention should make its query rows and the newest key itself from the raw
+    projection (per-head norm, rotary encoding, cache write folded in): the whole head rotates and
+    the head size is a power of two, as the stand-alone kernel's fast path wants it too, and the
+    step has at most eight tokens.  Measured on a decode step at Qwen3-8B sizes: 3.54 against 3.61 ms
+    at batch 8, 313.5 against 311 tok/s at batch 1; nothing to speak of at 16, 48 and 64 tokens, and
+    5.99 against 5.06 ms at 32, where the kernel in front is then a library product whose blocks do
+    not all fit at once and the attention blocks that move in early take their room."""
+    return (writable and rotary_dim == head_dim and head_dim & (head_dim - 1) == 0 and 16 <= head_dim <= 256
+            and num_tokens <= FRESH_MAX_TOKENS and os.environ.get("TANDEM_FRESH_ATTENTION", "1") != "0")
+
+
 def paged_attention_decode(qkv: torch.Tensor, kv, items: torch.Tensor, count: torch.Tensor, num_heads: int,
                            num_kv_heads: int, head_dim: int, scale: float,
-                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           out: Optional[torch.Tensor] = None, fresh: Optional[dict] = None) -> torch.Tensor:
     """One token per request: ``items`` int32 [capacity * 6] and ``count`` int32 [1] (how many of
-    them are real) as ``plan_decode`` cut them.  Writes the rows of ``out`` that the items name."""
+    them are real) as ``plan_decode`` cut them.  Writes the rows of ``out`` that the items name.
+
+    ``fresh`` (positions, slots, q_norm, k_norm, cos_sin, eps): ``qkv`` is the raw projection; the
+    kernel normalises and rotates its query rows and each request's new key itself and writes
+    the new key and value to the cache (what ``ops.qk_norm_rope_kv`` would have done in front of it)."""
     T = qkv.shape[0]
     capacity = items.numel() // ITEM_INTS
     groups = num_heads // num_kv_heads
@@ -124,8 +143,29 @@ def paged_attention_decode(qkv: torch.Tensor, kv, items: torch.Tensor, count: to
         ops._stream(), ops._ptr(qkv), qkv.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
         kv.block_table.stride(0), ops._ptr(items), ops._ptr(count), capacity, ops._ptr(out), ops._ptr(ws["part_o"]),
         ops._ptr(ws["part_ml"]), ops._ptr(ws["counters"]), ops._ptr(ops.status_word(qkv.device)), num_heads,
-        num_kv_heads, kv.page_size, ctypes.c_float(scale)), "attention_decode")
+        num_kv_heads, kv.page_size, ctypes.c_float(scale), *_fresh_args(fresh, qkv, num_heads, num_kv_heads, head_dim)),
+        "attention_decode")
     return out
+
+
+def _fresh_args(fresh: Optional[dict], qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int) -> tuple:
+    if fresh is None:
+        return (0, None, None, None, None, None, ctypes.c_float(0.0), 0)
+    cos_sin, positions, slots = fresh["cos_sin"], fresh["positions"], fresh["slots"]
+    ops._need(cos_sin, "cos_sin", torch.float32)
+    ops._need(positions, "positions", torch.int32)
+    ops._need(slots, "slots", torch.int32)
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or not qkv.is_contiguous():
+        raise ops.KernelError("decode attention from the raw projection wants qkv [T, (nh + 2 nkv) * hd], contiguous")
+    if cos_sin.shape[1] != head_dim or positions.numel() != qkv.shape[0] or slots.numel() != qkv.shape[0]:
+        raise ops.KernelError("cos_sin, positions or slots do not fit the rows of qkv")
+    for w in (fresh.get("q_norm"), fresh.get("k_norm")):
+        if w is not None:
+            ops._need(w, "norm weight", torch.float32)
+            if w.numel() != head_dim:
+                raise ops.KernelError(f"a head norm weight has {w.numel()} elements, head_dim is {head_dim}")
+    return (1, ops._ptr(fresh.get("q_norm")), ops._ptr(fresh.get("k_norm")), ops._ptr(cos_sin), ops._ptr(positions), ops._ptr(slots),
+            ctypes.c_float(fresh["eps"]), cos_sin.shape[0])
 
 
 def paged_attention_prefill(qkv: torch.Tensor, kv, tiles: torch.Tensor, num_heads: int, num_kv_heads: int,
@@ -171,9 +211,17 @@ def plan_step(ctx, window: Optional[int], num_heads: int, num_kv_heads: int, hea
     ctx.scratch[key] = (len(items), len(tiles))
 
 
+def decodes_only(ctx, num_heads: int, num_kv_heads: int, head_dim: int, window: Optional[int], dtype: torch.dtype) -> bool:
+    """The step was planned for the tensor-core kernels and brings single tokens only: all of its
+    attention is the decode kernel's."""
+    planned = ctx.scratch.get(plan_key(window, num_heads, num_kv_heads, head_dim, dtype))
+    return planned is not None and planned[1] == 0 and planned[0] > 0
+
+
 def paged_attention(qkv: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: int, head_dim: int,
-                    window: Optional[int], scale: float) -> torch.Tensor:
-    """Attention output [T, nh * hd] for the query heads in the first nh*hd columns of qkv."""
+                    window: Optional[int], scale: float, fresh: Optional[dict] = None) -> torch.Tensor:
+    """Attention output [T, nh * hd] for the query heads in the first nh*hd columns of qkv.
+    ``fresh``: see ``paged_attention_decode`` (only for steps for which ``decodes_only`` holds)."""
     key = plan_key(window, num_heads, num_kv_heads, head_dim, qkv.dtype)
     planned = ctx.scratch.get(key)
     if planned is None:
@@ -185,5 +233,5 @@ def paged_attention(qkv: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: in
         paged_attention_prefill(qkv, kv, ctx.extras[key + ("tiles",)], num_heads, num_kv_heads, head_dim, window, scale, out)
     if num_items:
         paged_attention_decode(qkv, kv, ctx.extras[key + ("items",)], ctx.extras[key + ("count",)], num_heads,
-                               num_kv_heads, head_dim, scale, out)
+                               num_kv_heads, head_dim, scale, out, fresh)
     return out

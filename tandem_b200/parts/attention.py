@@ -76,8 +76,15 @@ class PagedAttention(Mixer):
         s = self.spec
         qkv = ops.linear(x, self.qkv)
         kv = ctx.kv(self)
-        qkv = ops.qk_norm_rope_kv(qkv, ctx.positions, kv.slots, self.q_norm, self.k_norm, self.position.cos_sin,
-                            kv.k, kv.v, s.num_heads, s.num_kv_heads, s.head_dim, self.position.rotary_dim,
-                            kv.page_size, s.qk_norm_eps, write_kv=kv.writable)
-        o = attention_kernels.paged_attention(qkv, kv, ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
+        fresh = None
+        if attention_kernels.decodes_only(ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.window, qkv.dtype) and \
+                attention_kernels.fresh_applies(s.head_dim, self.position.rotary_dim, kv.writable, qkv.shape[0]):
+            # single tokens only: decode attention normalises, rotates and stores what it needs itself
+            fresh = dict(positions=ctx.positions, slots=kv.slots, q_norm=self.q_norm, k_norm=self.k_norm,
+                         cos_sin=self.position.cos_sin, eps=s.qk_norm_eps)
+        else:
+            qkv = ops.qk_norm_rope_kv(qkv, ctx.positions, kv.slots, self.q_norm, self.k_norm, self.position.cos_sin,
+                                      kv.k, kv.v, s.num_heads, s.num_kv_heads, s.head_dim, self.position.rotary_dim,
+                                      kv.page_size, s.qk_norm_eps, write_kv=kv.writable)
+        o = attention_kernels.paged_attention(qkv, kv, ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale, fresh)
         return ops.linear(o, self.o)

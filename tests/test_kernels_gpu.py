@@ -376,6 +376,68 @@ def test_paged_attention_decode(ops, nh, nkv, hd, ps, batch, window, target):
         assert max(it[5] for it in items) > 1  # the long request was really split
 
 
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(32, 8, 128, 16), (8, 2, 64, 16), (4, 2, 16, 4), (6, 2, 32, 8), (40, 2, 128, 32), (4, 1, 256, 16),
+                                          (8, 4, 64, 2)])
+@pytest.mark.parametrize("window,target,norm", [(None, 592, True), (None, 4000, False), (70, 8, True)])
+def test_decode_attention_from_the_raw_projection(ops, nh, nkv, hd, ps, window, target, norm):
+    """Decode attention that normalises and rotates its query rows and makes each request's newest key
+    itself, against the stand-alone kernel followed by decode attention: the same output, the same
+    cache, bit for bit.  The stale row it overwrites holds NaN, as does every unwritten slot."""
+    from tandem_b200.cache.layout import to_logical
+    from tandem_b200.kernels import attention as A
+    from tandem_b200.parts.base import KVView
+
+    g = torch.Generator().manual_seed(31 + hd)
+    starts = [0, 15, 16, 63, 64, 200, 641, 1500][: 5 if hd == 256 else 8]
+    seqs = [(s, 1) for s in starts]
+    _, kc, vc, table, seq_of, pos, Q, K, V = _paged_case(g, torch.bfloat16, seqs, nh, nkv, hd, ps)
+    T = len(starts)
+    raw = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).bfloat16()
+    slots = torch.tensor([int(table[b, s // ps]) * ps + s % ps for b, s in enumerate(starts)], dtype=torch.int32)
+    for b, s in enumerate(starts):  # the new token's row has not been written yet
+        kc[table[b, s // ps], :, s % ps] = float("nan")
+        vc[table[b, s // ps], :, s % ps] = float("nan")
+    if window:
+        for b, s in enumerate(starts):
+            for j in range(max(0, s - window + 1) // ps):
+                kc[table[b, j]] = float("nan")
+                vc[table[b, j]] = float("nan")
+                table[b, j] = -1
+    qw = dev(1 + 0.1 * torch.randn(hd, generator=g)) if norm else None
+    kw = dev(1 + 0.1 * torch.randn(hd, generator=g)) if norm else None
+    cos_sin = dev(torch.randn(2000, hd, generator=g))
+    items = A.plan_decode([(b, b, p) for b, p in enumerate(starts)], window, nkv, target)
+    flat = dev(torch.tensor([x for it in items for x in it], dtype=torch.int32))
+    count = dev(torch.tensor([len(items)], dtype=torch.int32))
+    scale = hd ** -0.5
+    assert A.fresh_applies(hd, hd, True)
+
+    def run(fresh):
+        kv = KVView(phys(kc), phys(vc), dev(table), dev(slots), ps, True)
+        qkv = dev(raw.clone())
+        if fresh:
+            out = A.paged_attention_decode(qkv, kv, flat, count, nh, nkv, hd, scale,
+                                           fresh=dict(positions=dev(pos), slots=kv.slots, q_norm=qw, k_norm=kw, cos_sin=cos_sin, eps=1e-5))
+        else:
+            ops.qk_norm_rope_kv(qkv, dev(pos), kv.slots, qw, kw, cos_sin, kv.k, kv.v, nh, nkv, hd, hd, ps, 1e-5)
+            out = A.paged_attention_decode(qkv, kv, flat, count, nh, nkv, hd, scale)
+        return out, to_logical(kv.k), to_logical(kv.v)
+
+    o1, k1, v1 = run(False)
+    o2, k2, v2 = run(True)
+    assert not torch.isnan(o1).any()
+    assert torch.equal(o1, o2), (o1.float() - o2.float()).abs().max()
+    written = torch.zeros(k1.shape[0], ps, dtype=torch.bool)
+    for b, s in enumerate(starts):
+        written[table[b, s // ps], s % ps] = True
+    assert torch.equal(k1.cpu()[written.nonzero(as_tuple=True)[0], :, written.nonzero(as_tuple=True)[1]],
+                       k2.cpu()[written.nonzero(as_tuple=True)[0], :, written.nonzero(as_tuple=True)[1]])
+    assert torch.equal(v1.cpu()[written.nonzero(as_tuple=True)[0], :, written.nonzero(as_tuple=True)[1]],
+                       v2.cpu()[written.nonzero(as_tuple=True)[0], :, written.nonzero(as_tuple=True)[1]])
+    assert not torch.isnan(k2.cpu()[written.nonzero(as_tuple=True)[0], :, written.nonzero(as_tuple=True)[1]].float()).any()
+    ops.check_status("cuda")
+
+
 def test_decode_finds_one_far_key(ops):
     nh, nkv, hd, ps = 8, 2, 128, 16
     g = torch.Generator().manual_seed(21)
