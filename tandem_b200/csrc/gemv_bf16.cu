@@ -16,7 +16,7 @@
 // copy that leaves the L1 cache enough room to keep the loads in flight, 164 KB, B comes from
 // global memory too, along with the weights of its round).  The 16 partial tiles of a
 // block are added in warp order by 128 of its threads.  The first loads are on their way before
-// the kernel in front of this one has finished (weights are written by no kernel).  Every sum is
+// the kernel in front of this one has finished, two rounds of them (weights are written by no kernel).  Every sum is
 // taken in one fixed order whatever the grid and however many rows x has.
 // With `gated` the rows of w are [gate | up] halves of I rows each and y [M, I] = silu(x gate^T) *
 // (x up^T): the 16 rows a block takes at a time are 8 gate rows (the upper half of the MMA tile)
@@ -94,7 +94,15 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
 
   Round<X_IN_SMEM> cur, nxt;
   const bool streams = s0 < s1 && my_groups > 0;
-  if (streams) load_round(0, s0, cur);
+  // Two rounds of weights are on their way before this kernel waits for the one in front (weights are
+  // written by no kernel): what the registers hold anyway, a round in use and the next one.
+  bool second_ahead = false;
+  if (streams) {
+    load_round(0, s0, cur);
+    int nj = 0, ns = s0 + GV_STEPS;
+    if (ns >= s1) { ns = s0; ++nj; }
+    if (nj < my_groups) { load_round(nj, ns, nxt); second_ahead = true; }
+  }
   pdl_wait();  // x is the output of the kernel in front
   if (X_IN_SMEM) {
     for (int i = threadIdx.x; i < M * pieces; i += GV_THREADS) xs[(i / pieces) * x_stride + i % pieces] = x[i];
@@ -117,7 +125,11 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
     // hold the room that blocks not yet started need, and the step takes 5.48 ms.
     if (nj >= my_groups) pdl_launch_dependents();
     if (streams) {
-      if (nj < my_groups) { load_round(nj, ns, nxt); load_x(ns, nxt); }
+      if (nj < my_groups) {
+        if (!second_ahead) load_round(nj, ns, nxt);
+        load_x(ns, nxt);
+      }
+      second_ahead = false;
 #pragma unroll
       for (int u = 0; u < GV_STEPS; ++u) {
         if (s + u < s1) {
