@@ -22,7 +22,18 @@
 // (x up^T): the 16 rows a block takes at a time are 8 gate rows (the upper half of the MMA tile)
 // and the 8 up rows that go with them (the lower half), and the thread that adds a place's gate
 // sum up adds its up sum up too (both rounded to bfloat16, as the product alone would store them).
-// 12vivi/tandem has kernels of this kind for the same case (python/tandem/layers/triton_gemv.py:25-88).
+//
+// The residual add and the RMSNorm that stand between two products of a decoder layer can ride along,
+// so that they need no launch of their own.  RMSNorm scales row m by one number,
+// s[m] = rsqrt(mean(r[m]^2) + eps), and a product is linear in its rows:
+//     (s[m] r[m, :] * g) W^T  =  s[m] ((r[m, :] * g) W^T)        (g: the norm's weight)
+// so the product in front (mode ADD) adds its result into the float32 residual r instead of storing
+// it, writes r * g rounded to bfloat16 beside it, and leaves, per block, the sums of squares of the
+// entries it wrote; the product behind (mode SCALE) reads those rows as its x, adds the partial
+// sums up in block order while its weights stream, and multiplies row m of its result by s[m] in
+// float32 before anything else is done to it.  No block reads a row twice and no block waits.
+// 12vivi/tandem has kernels of this kind for the same case (python/tandem/layers/triton_gemv.py:25-88),
+// with the norm in the product's prologue (triton_gemv.py:92-145).
 #include "common.cuh"
 
 namespace tb {
@@ -43,17 +54,33 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+constexpr int MODE_PLAIN = 0, MODE_ADD = 1, MODE_SCALE = 2;
+
+struct GemvFuse {
+  // MODE_ADD (not gated): the product is not stored but added
+  float* residual;         // [M, N] float32: residual += bfloat16(product)
+  const float* norm_w;     // [N]: the weight of the norm behind the add
+  __nv_bfloat16* scaled;   // [M, N] out: bfloat16(residual * norm_w)
+  float* partials_out;     // [gridDim.x, 8] out: this block's sums of squares of the residual entries it wrote
+  // MODE_SCALE: row m of the product is multiplied by rsqrt(sum_p partials[p][m] / K + eps)
+  const float* partials;   // [parts, 8]
+  int parts;
+  float eps;
+};
+
 template <bool X_IN_SMEM>
 struct Round {  // what a lane holds of one round: [step][row g | row g + 8][piece t | piece 4 + t]
   uint4 w[GV_STEPS][2][2];
   uint4 b[X_IN_SMEM ? 1 : GV_STEPS][2];  // the lane's pieces of row g of x, where x is not in shared memory
 };
 
-template <bool X_IN_SMEM>
+template <bool X_IN_SMEM, int MODE>
 __global__ void __launch_bounds__(GV_THREADS, 1)
 gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __restrict__ y, int M, int N, int pieces,
-            int x_stride, int out_f32, int gated) {
+            int x_stride, int out_f32, int gated, const GemvFuse f) {
   extern __shared__ uint4 smem[];
+  __shared__ float row_scale[8];  // MODE_SCALE: the rows' rsqrt(mean square + eps)
+  __shared__ float ssq_s[4][8];   // MODE_ADD: sums of squares of what this block wrote, per warp and row
   uint4* xs = smem;                                                    // [M][x_stride] pieces of 8 k
   float* red = reinterpret_cast<float*>(smem + (X_IN_SMEM ? (size_t)M * x_stride : 0));  // [2][GV_WARPS][16 rows][8 columns]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -111,6 +138,28 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
     load_x(s0, cur);
   }
 
+  if (MODE == MODE_SCALE && warp < M) {
+    // one warp per row: the partial sums in block order, lane by lane, then the lanes in a fixed tree; the result is
+    // first read in an epilogue, behind the block-wide barrier in front of it
+    float ss = 0.f;
+    for (int p = lane; p < f.parts; p += 32) ss += __ldcg(f.partials + p * 8 + warp);
+    ss = warp_sum(ss);
+    if (lane == 0) row_scale[warp] = rsqrtf(ss / (float)(pieces * 8) + f.eps);
+  }
+  float wrote_sq = 0.f;  // MODE_ADD: squares of the residual entries this thread wrote
+  // MODE_ADD: the residual entry and the norm weight of the place this thread finishes in a group are fetched when
+  // the group begins, not when its sums are ready: a round trip to the L2 less at the end of every group
+  float res_old = 0.f, gain = 0.f;
+  auto fetch_place = [&](int jj) {
+    if (MODE == MODE_ADD && threadIdx.x < 128 && jj < my_groups) {
+      const int n = ((int)blockIdx.x + jj * (int)gridDim.x) * group_rows + (threadIdx.x >> 3), col = threadIdx.x & 7;
+      if (col < M && n < N) {
+        res_old = __ldcg(f.residual + (size_t)col * N + n);
+        gain = f.norm_w[n];
+      }
+    }
+  };
+  fetch_place(0);
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   int j = 0, s = s0;
   while (j < my_groups) {
@@ -162,14 +211,25 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
 #pragma unroll
         for (int q = 0; q < GV_WARPS; ++q) sum += part[q * 128];
         const int n = ((int)blockIdx.x + j * (int)gridDim.x) * group_rows + row;
+        const float scale = (MODE == MODE_SCALE && col < M) ? row_scale[col] : 1.f;
+        if (MODE == MODE_SCALE) sum *= scale;
         if (!gated) {
-          if (col < M && n < N) {
+          if (MODE == MODE_ADD) {
+            if (col < M && n < N) {  // residual += the product as bfloat16 would have stored it
+              const float v = res_old + __bfloat162float(__float2bfloat16_rn(sum));
+              f.residual[(size_t)col * N + n] = v;
+              f.scaled[(size_t)col * N + n] = __float2bfloat16_rn(v * gain);
+              wrote_sq += v * v;
+            }
+            fetch_place(nj);
+          } else if (col < M && n < N) {
             if (out_f32) reinterpret_cast<float*>(y)[(size_t)col * N + n] = sum;
             else reinterpret_cast<__nv_bfloat16*>(y)[(size_t)col * N + n] = __float2bfloat16_rn(sum);
           }
         } else if (row < 8) {  // the formula of the activation kernel (tokenwise.cu), on the values it would read
 #pragma unroll
           for (int q = 0; q < GV_WARPS; ++q) second += part[q * 128 + 64];
+          if (MODE == MODE_SCALE) second *= scale;
           const float gate = __bfloat162float(__float2bfloat16_rn(sum)), up = __bfloat162float(__float2bfloat16_rn(second));
           if (col < M)
             reinterpret_cast<__nv_bfloat16*>(y)[(size_t)col * half_rows + n] =
@@ -180,6 +240,16 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
     if (streams) cur = nxt;
     j = nj;
     s = ns;
+  }
+  if (MODE == MODE_ADD) {  // threads 0..127 hold (row of w = tid / 8, row of x = tid % 8): rows of w summed in a fixed order
+    if (threadIdx.x < 128) {
+      wrote_sq += __shfl_xor_sync(0xffffffffu, wrote_sq, 8);
+      wrote_sq += __shfl_xor_sync(0xffffffffu, wrote_sq, 16);
+      if (lane < 8) ssq_s[warp][lane] = wrote_sq;
+    }
+    __syncthreads();
+    if (threadIdx.x < 8)
+      f.partials_out[(size_t)blockIdx.x * 8 + threadIdx.x] = ssq_s[0][threadIdx.x] + ssq_s[1][threadIdx.x] + ssq_s[2][threadIdx.x] + ssq_s[3][threadIdx.x];
   }
   pdl_launch_dependents();  // (blocks without work)
 }
@@ -199,30 +269,64 @@ static int x_stride_of(int pieces) { return pieces + ((4 - pieces % 8) + 8) % 8;
 
 static const int kReduceBytes = 2 * tb::GV_WARPS * 128 * 4;
 
-// x [M, K] and w [N, K] bfloat16, both contiguous and 16-byte aligned, K a multiple of 8; y [M, N], or with
-// gated (bfloat16 out only, N = 2 I with I a multiple of 8) y [M, I] = silu(x w[:I]^T) * (x w[I:]^T).
-int tb_gemv(void* stream, const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int gated, int blocks) {
+// The number of blocks a launch with these sizes uses: the rows of `partials_out` that MODE_ADD writes.
+int tb_gemv_grid(int N, int gated, int blocks) {
+  const int groups = gated ? N / 16 : (N + 15) / 16;
+  return blocks < groups ? blocks : groups;
+}
+
+static int launch_gemv(void* stream, const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int gated, int blocks,
+                       int mode, const tb::GemvFuse& f) {
   if (M <= 0 || N <= 0) return 0;
   if (M > tb_gemv_max_rows() || K <= 0 || (K & 7) || blocks <= 0) return TB_ERR_BAD_SIZE;
   if (gated && (out_f32 || N % 16 != 0)) return TB_ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return TB_ERR_BAD_SIZE;
   const int stride = x_stride_of(K / 8), with_x = M * stride * 16 + kReduceBytes;
   const bool in_smem = with_x <= tb_gemv_max_smem_bytes();
-  auto kernel = in_smem ? tb::gemv_kernel<true> : tb::gemv_kernel<false>;
-  static bool allowed[64][2] = {};  // the larger shared memory is asked for once per device and kernel
+  void (*kernel)(const uint4*, const uint4*, void*, int, int, int, int, int, int, const tb::GemvFuse) =
+      mode == tb::MODE_ADD     ? (in_smem ? tb::gemv_kernel<true, tb::MODE_ADD> : tb::gemv_kernel<false, tb::MODE_ADD>)
+      : mode == tb::MODE_SCALE ? (in_smem ? tb::gemv_kernel<true, tb::MODE_SCALE> : tb::gemv_kernel<false, tb::MODE_SCALE>)
+                               : (in_smem ? tb::gemv_kernel<true, tb::MODE_PLAIN> : tb::gemv_kernel<false, tb::MODE_PLAIN>);
+  static bool allowed[64][6] = {};  // the larger shared memory is asked for once per device and kernel
   int device = 0;
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return (int)e;
   if (device < 0 || device >= 64) return TB_ERR_BAD_SIZE;
-  if (!allowed[device][in_smem]) {
+  if (!allowed[device][mode * 2 + in_smem]) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tb_gemv_max_smem_bytes());
     if (e != cudaSuccess) return (int)e;
-    allowed[device][in_smem] = true;
+    allowed[device][mode * 2 + in_smem] = true;
   }
   const int groups = gated ? N / 16 : (N + 15) / 16;
   return tb::launch(kernel, dim3(blocks < groups ? blocks : groups), dim3(tb::GV_THREADS),
                     (size_t)(in_smem ? with_x : kReduceBytes), stream, (const uint4*)x, (const uint4*)w, y, M, N, K / 8, stride,
-                    out_f32, gated);
+                    out_f32, gated, f);
+}
+
+// x [M, K] and w [N, K] bfloat16, both contiguous and 16-byte aligned, K a multiple of 8; y [M, N], or with
+// gated (bfloat16 out only, N = 2 I with I a multiple of 8) y [M, I] = silu(x w[:I]^T) * (x w[I:]^T).
+int tb_gemv(void* stream, const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int gated, int blocks) {
+  return launch_gemv(stream, x, w, y, M, N, K, out_f32, gated, blocks, tb::MODE_PLAIN, tb::GemvFuse{});
+}
+
+// residual [M, N] float32 += bfloat16(x w^T); scaled [M, N] = bfloat16(residual * norm_w); partials_out
+// [tb_gemv_grid(N, 0, blocks), 8] = every block's sums of squares of the residual entries it wrote (rows beyond M: zero).
+int tb_gemv_add(void* stream, const void* x, const void* w, float* residual, const float* norm_w, void* scaled, float* partials_out,
+                int M, int N, int K, int blocks) {
+  if (!residual || !norm_w || !scaled || !partials_out) return TB_ERR_BAD_SIZE;
+  tb::GemvFuse f{};
+  f.residual = residual; f.norm_w = norm_w; f.scaled = (__nv_bfloat16*)scaled; f.partials_out = partials_out;
+  return launch_gemv(stream, x, w, nullptr, M, N, K, 0, 0, blocks, tb::MODE_ADD, f);
+}
+
+// As tb_gemv, with row m of the product multiplied by rsqrt(sum_p partials[p][m] / K + eps) before it is rounded (or,
+// with gated, before the activation): x holds rows r * g of which the norm's scale has been left out.
+int tb_gemv_scaled(void* stream, const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int gated, int blocks,
+                   const float* partials, int parts, float eps) {
+  if (!partials || parts <= 0) return TB_ERR_BAD_SIZE;
+  tb::GemvFuse f{};
+  f.partials = partials; f.parts = parts; f.eps = eps;
+  return launch_gemv(stream, x, w, y, M, N, K, out_f32, gated, blocks, tb::MODE_SCALE, f);
 }
 
 }  // extern "C"

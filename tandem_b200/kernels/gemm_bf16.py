@@ -23,6 +23,7 @@ prints the table's lines and what the rule would have picked.
 
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
@@ -118,17 +119,53 @@ def gemv_preferred(M: int, N: int, K: int) -> bool:
     return gemv_applies(M, N, K) and K <= GEMV_MAX_K
 
 
-def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, gated: bool = False) -> torch.Tensor:
+def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, gated: bool = False, scale=None) -> torch.Tensor:
     """The weight-streaming kernel for up to eight rows (``csrc/gemv_bf16.cu``): weights from global
     memory straight into registers, ``mma.sync`` against the rows of x in shared memory.  ``gated``:
     the weight's rows are [gate | up]; returns silu(x gate^T) * (x up^T), [M, rows / 2], the values
-    the product followed by ``ops.silu_mul`` gives."""
+    the product followed by ``ops.silu_mul`` gives.  ``scale`` (a ``deferred.PendingNorm`` whose
+    ``scaled`` rows are x): row m of the product is multiplied by the norm's scale of that row first."""
     M, K = x.shape
     N = weight.shape[0]
     y = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
-    ops._check(load_library("gemv_bf16").tb_gemv(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(y), M, N, K,
-                                                 int(out_dtype == torch.float32), int(gated), sm_count(x.device)), "gemv")
+    lib = load_library("gemv_bf16")
+    if scale is None:
+        ops._check(lib.tb_gemv(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(y), M, N, K,
+                               int(out_dtype == torch.float32), int(gated), sm_count(x.device)), "gemv")
+    else:
+        ops._check(lib.tb_gemv_scaled(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(y), M, N, K, int(out_dtype == torch.float32),
+                                      int(gated), sm_count(x.device), ops._ptr(scale.partials), scale.parts, ctypes.c_float(scale.eps)),
+                   "gemv (rows scaled)")
     return y
+
+
+def gemv_add(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor) -> tuple:
+    """residual [M, N] (float32) += bfloat16(x @ weight^T), by the streaming kernel itself.  Returns
+    (bfloat16(residual * norm_weight) [M, N], the blocks' partial sums of squares of the new rows [parts, 8], parts)."""
+    lib = load_library("gemv_bf16")
+    M, K = x.shape
+    N = weight.shape[0]
+    parts = lib.tb_gemv_grid(N, 0, sm_count(x.device))
+    partials = torch.empty((parts, 8), dtype=torch.float32, device=x.device)
+    scaled = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    ops._check(lib.tb_gemv_add(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(residual), ops._ptr(norm_weight), ops._ptr(scaled),
+                               ops._ptr(partials), M, N, K, sm_count(x.device)), "gemv (added into the residual)")
+    return scaled, partials, parts
+
+
+def add_fusable(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """A product that the streaming kernel runs, and so may add into the residual itself."""
+    if os.environ.get("TANDEM_FUSE_NORM", "1") == "0":
+        return False
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and choose(x.shape[0], weight.shape[0], x.shape[1], _aligned(x, weight)) == "gemv")
+
+
+def scale_fusable(norm, weight: torch.Tensor) -> bool:
+    """A norm with its rows' scale pending whose reader is a product that the streaming kernel runs."""
+    M, K = norm.scaled.shape
+    return (weight.dtype == torch.bfloat16 and weight.shape[1] == K
+            and choose(M, weight.shape[0], K, _aligned(norm.scaled, weight)) == "gemv")
 
 
 ROW_CLASSES = (1, 2, 4, 8, 16, 32, 64)

@@ -132,9 +132,23 @@ def take_tokens(ids: torch.Tensor, source: torch.Tensor, tokens: torch.Tensor) -
 
 
 def add_rmsnorm(x, residual: torch.Tensor, weight: torch.Tensor, eps: float,
-                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, defer: bool = False):
     """residual += x (in place, float32; skipped when x is None); returns RMSNorm(residual) * weight
-    in ``out_dtype``.  With ``rows`` [R] int32 only those rows are updated and returned, in that order."""
+    in ``out_dtype``.  With ``rows`` [R] int32 only those rows are updated and returned, in that order.
+
+    ``x`` may be a product that has not been launched (``deferred.PendingLinear``).  With ``defer``
+    (the reader takes a ``deferred.PendingNorm``) such a product is then added into the residual by
+    its own kernel and the norm comes back with its rows' scale left to the product behind it."""
+    from tandem_b200.kernels import deferred, gemm_bf16
+
+    if isinstance(x, deferred.PendingLinear):
+        if defer and rows is None and out_dtype == torch.bfloat16 and x.shape == tuple(residual.shape) \
+                and gemm_bf16.add_fusable(x.x, x.weight):
+            _need(residual, "residual", torch.float32)
+            _need(weight, "norm weight", torch.float32)
+            scaled, partials, parts = gemm_bf16.gemv_add(x.x, x.weight, residual, weight)
+            return deferred.PendingNorm(residual, weight, eps, out_dtype, scaled, partials, parts)
+        x = deferred.tensor(x)
     _need(residual, "residual", torch.float32)
     _need(weight, "norm weight", torch.float32)
     T, H = residual.shape
@@ -208,9 +222,21 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- matrix products
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+def linear(x, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None, defer: bool = False):
     """x [M, K] @ weight [N, K]^T -> [M, N].  float32 operands run the CUDA-core kernel (true
-    32-bit arithmetic); bfloat16 operands run on the tensor cores with float32 accumulation."""
+    32-bit arithmetic); bfloat16 operands run on the tensor cores with float32 accumulation.
+
+    ``x`` may be a norm whose rows' scale is still pending (``deferred.PendingNorm``).  With
+    ``defer`` the product itself may stay pending (``deferred.PendingLinear``) for a norm that has it
+    added into the residual by its own kernel; that happens only where the streaming kernel runs it."""
+    from tandem_b200.kernels import deferred, gemm_bf16
+
+    if isinstance(x, deferred.PendingNorm):
+        if gemm_bf16.scale_fusable(x, weight):
+            return gemm_bf16.gemv(x.scaled, weight, out_dtype or x.out_dtype, scale=x)
+        x = deferred.tensor(x)
+    if defer and x.dtype == torch.bfloat16 and out_dtype in (None, torch.bfloat16) and gemm_bf16.add_fusable(x, weight):
+        return deferred.PendingLinear(x, weight)
     _need(x, "x")
     _need(weight, "weight")
     if x.dtype != weight.dtype:
@@ -227,22 +253,25 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         lib = load_library("gemm_f32")
         _check(lib.tb_gemm_f32(_stream(), _ptr(x), _ptr(weight), _ptr(out), M, N, K, K, N), "gemm_f32")
         return out
-    from tandem_b200.kernels import gemm_bf16
-
     return gemm_bf16.linear(x, weight, out_dtype)
 
 
-def gated_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+def gated_linear(x, weight: torch.Tensor) -> torch.Tensor:
     """silu(x gate^T) * (x up^T) for a weight [2I, K] whose rows are [gate | up]: [M, I].  In
-    bfloat16 with many rows the activation may run in the epilogue of the product."""
+    bfloat16 with many rows the activation may run in the epilogue of the product.  ``x`` may be a
+    norm whose rows' scale is still pending (``deferred.PendingNorm``)."""
+    from tandem_b200.kernels import deferred, gemm_bf16
+
+    if isinstance(x, deferred.PendingNorm):
+        if weight.shape[0] % 16 == 0 and gemm_bf16.scale_fusable(x, weight):
+            return gemm_bf16.gemv(x.scaled, weight, torch.bfloat16, gated=True, scale=x)
+        x = deferred.tensor(x)
     if x.dtype == torch.float32:
         return silu_mul(linear(x, weight))
     _need(x, "x")
     _need(weight, "weight", x.dtype)
     if x.shape[1] != weight.shape[1] or weight.shape[0] % 2:
         raise KernelError(f"x {tuple(x.shape)} and the gate/up weight {tuple(weight.shape)} do not fit")
-    from tandem_b200.kernels import gemm_bf16
-
     return gemm_bf16.gated(x, weight)
 
 

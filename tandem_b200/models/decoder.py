@@ -15,7 +15,7 @@ import torch
 
 from tandem_b200.config.model_config import ConfigError
 from tandem_b200.config.plan import ModelPlan, ParamSpec, WeightSource
-from tandem_b200.kernels import ops
+from tandem_b200.kernels import deferred, ops
 from tandem_b200.parts.base import StepContext
 from tandem_b200.registry import part
 from tandem_b200.weights.loader import TensorSource, load_parameters
@@ -124,9 +124,13 @@ class Decoder:
         for r, run in enumerate(self.plan.order):
             ctx.run = r
             layer = self.layers[run.layer]
+            if not getattr(layer.block, "takes_deferred", False):
+                x = deferred.tensor(x)  # the arrangement before may have left its last product pending
             x = layer.block.forward(layer, x, residual, ctx)
         if logit_rows is not None and logit_rows.numel() == 0:  # the step only filled the cache
             return torch.empty((0, h.vocab_size), dtype=torch.float32, device=self.device)
+        if not getattr(self.final_norm, "takes_deferred", False):
+            x = deferred.tensor(x)
         hidden = self.final_norm.forward(x, residual, self.dtype, rows=logit_rows)
         logits = ops.linear(hidden, self.head, out_dtype=torch.float32)
         if h.scale != 1.0 or h.softcap is not None:

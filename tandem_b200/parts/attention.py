@@ -22,6 +22,7 @@ from tandem_b200.parts.shared import position_encoding
 
 class PagedAttention(Mixer):
     capturable = True  # forward only launches kernels: decode steps may be captured in CUDA graphs
+    takes_deferred = True  # x may be a norm whose scale is pending; with ``defer`` the output projection may stay pending
 
     @staticmethod
     def params(spec: AttentionSpec) -> dict:
@@ -72,7 +73,7 @@ class PagedAttention(Mixer):
         out[key + ("tiles",)] = 0
         attention_kernels._workspace(self.qkv.device, items, s.num_kv_heads, groups, s.head_dim)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def forward(self, x, ctx: StepContext, defer: bool = False):
         s = self.spec
         qkv = ops.linear(x, self.qkv)
         kv = ctx.kv(self)
@@ -87,4 +88,4 @@ class PagedAttention(Mixer):
                                       kv.k, kv.v, s.num_heads, s.num_kv_heads, s.head_dim, self.position.rotary_dim,
                                       kv.page_size, s.qk_norm_eps, write_kv=kv.writable)
         o = attention_kernels.paged_attention(qkv, kv, ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale, fresh)
-        return ops.linear(o, self.o)
+        return ops.linear(o, self.o, defer=defer)

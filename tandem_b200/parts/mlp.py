@@ -13,6 +13,8 @@ from tandem_b200.parts.base import FeedForward, StepContext
 
 
 class GatedMLP(FeedForward):
+    takes_deferred = True  # x may be a norm whose scale is pending; with ``defer`` the last product may stay pending
+
     @staticmethod
     def params(spec: GatedMLPSpec) -> dict:
         H, I, p = spec.hidden_size, spec.intermediate_size, spec.prefix
@@ -28,5 +30,5 @@ class GatedMLP(FeedForward):
         self.gate_up = weights["gate_up"]
         self.down = weights["down"]
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        return ops.linear(ops.gated_linear(x, self.gate_up), self.down)
+    def forward(self, x, ctx: StepContext, defer: bool = False):
+        return ops.linear(ops.gated_linear(x, self.gate_up), self.down, defer=defer)

@@ -17,6 +17,8 @@ from tandem_b200.parts.base import Norm
 
 
 class RMSNorm(Norm):
+    takes_deferred = True  # x may be a product that is still pending; the result may stay pending (kernels/deferred.py)
+
     @staticmethod
     def params(spec: NormSpec) -> dict:
         return {"weight": ParamSpec((spec.size,), (WeightSource(spec.weight),), role="vector")}
@@ -25,6 +27,6 @@ class RMSNorm(Norm):
         self.eps = spec.eps
         self.weight = weights["weight"]
 
-    def forward(self, x: Optional[torch.Tensor], residual: torch.Tensor, out_dtype: torch.dtype,
-                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return ops.add_rmsnorm(x, residual, self.weight, self.eps, out_dtype, rows)
+    def forward(self, x, residual: torch.Tensor, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+                defer: bool = False):
+        return ops.add_rmsnorm(x, residual, self.weight, self.eps, out_dtype, rows, defer=defer)

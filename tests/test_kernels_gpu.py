@@ -221,6 +221,57 @@ def test_gemv_gated_gives_the_bits_of_product_then_activation(ops, M, I, K):
         gemm_bf16.gemv(x, w[: 2 * I - 8].contiguous(), torch.bfloat16, gated=True)  # halves that are no multiple of 8 rows
 
 
+@pytest.mark.parametrize("M,H,N2,K0", [(1, 4096, 6144, 4096), (8, 4096, 24576, 12288), (5, 1000, 136, 200), (3, 64, 64, 64),
+                                        (8, 96, 512, 256), (7, 4096, 4096, 12288)])
+def test_gemv_takes_the_residual_add_and_the_norm_along(ops, M, H, N2, K0):
+    """A product added into the residual by its own kernel (which also writes residual * norm weight
+    and partial sums of squares), and the product behind it scaling its rows by the norm's
+    rsqrt(mean square + eps), against the three kernels one after the other: the residual bit for
+    bit; the normalised rows (seen through an identity matrix as the second product, float32 out)
+    to within the one bfloat16 rounding that has moved; real products within the usual bounds."""
+    from tandem_b200.kernels import deferred, gemm_bf16
+
+    g = torch.Generator().manual_seed(17 + M)
+    x = dev(torch.randn(M, K0, generator=g).bfloat16())
+    w1 = dev((torch.randn(H, K0, generator=g) / math.sqrt(K0)).bfloat16())
+    res = dev(torch.randn(M, H, generator=g) * 3)
+    wn = dev(1 + 0.1 * torch.randn(H, generator=g))
+    # one after the other
+    res_a = res.clone()
+    h_a = ops.add_rmsnorm(gemm_bf16.gemv(x, w1, torch.bfloat16), res_a, wn, 1e-5, torch.bfloat16)
+    # the add in the first product's epilogue
+    res_b = res.clone()
+    pending = ops.add_rmsnorm(deferred.PendingLinear(x, w1), res_b, wn, 1e-5, torch.bfloat16, defer=True)
+    assert isinstance(pending, deferred.PendingNorm) and pending.residual is res_b
+    assert torch.equal(res_a, res_b)
+    assert pending.partials.shape == (pending.parts, 8) and (pending.partials[:, M:] == 0).all()
+    torch.testing.assert_close(pending.partials.sum(0)[:M].double().cpu(), res_b.double().pow(2).sum(1).cpu(), rtol=1e-5, atol=0)
+    assert torch.equal(pending.scaled, (res_b * wn).bfloat16())
+    # the scale in the second product's epilogue
+    eye = dev(torch.eye(H).bfloat16())
+    assert gemm_bf16.scale_fusable(pending, eye)
+    h_b = ops.linear(pending, eye, torch.float32)
+    assert torch.equal(h_b, ops.linear(pending, eye, torch.float32))  # the same bits every time
+    torch.testing.assert_close(h_b, h_a.float(), rtol=2.0 ** -7, atol=1e-30)
+    exact = (res_b.double() * torch.rsqrt(res_b.double().pow(2).mean(1, keepdim=True) + 1e-5) * wn.double())
+    torch.testing.assert_close(h_b.double(), exact, rtol=2.0 ** -7, atol=1e-30)  # and as close to the true value as the rounded one
+    torch.testing.assert_close(deferred.tensor(pending).float(), h_a.float(), rtol=0, atol=0)  # made whole by the norm kernel: its bits
+    # a real second product, plain and gated
+    w2 = dev((torch.randn(N2, H, generator=g) / math.sqrt(H)).bfloat16())
+    want = exact @ w2.double().T
+    for out_dtype in (torch.bfloat16, torch.float32):
+        torch.testing.assert_close(ops.linear(pending, w2, out_dtype).double(), want, atol=3e-2, rtol=3e-2)
+    if N2 % 16 == 0:
+        I = N2 // 2
+        torch.testing.assert_close(ops.gated_linear(pending, w2).double(), torch.nn.functional.silu(want[:, :I]) * want[:, I:], atol=3e-2, rtol=3e-2)
+    # a reader that the streaming kernel does not run gets the rows from the stand-alone norm kernel
+    wide_x = deferred.PendingNorm(res_b.repeat(9, 1)[:9].contiguous(), wn, 1e-5, torch.bfloat16, pending.scaled.repeat(9, 1)[:9].contiguous(),
+                                  pending.partials, pending.parts)
+    w3 = dev((torch.randn(24, H, generator=g) / math.sqrt(H)).bfloat16())
+    assert not gemm_bf16.scale_fusable(wide_x, w3) and ops.linear(wide_x, w3).shape == (9, 24)
+    ops.check_status("cuda")
+
+
 # ----------------------------------------------------------------------------- attention
 def _paged_case(g, dtype, seqs, nh, nkv, hd, ps, extra_pages=5):
     """seqs: [(start, n)] -> (qkv rows for the new tokens, caches with shuffled pages holding keys 0..start+n-1, ...)."""
