@@ -85,9 +85,16 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   extern __shared__ unsigned char smem_unaligned[];
   // No early griddepcontrol.launch_dependents here: the kernel behind this one (the output projection)
   // becomes resident as this one's blocks exit.  Measured at Qwen3-8B sizes: with the trigger at the
-  // top a decode step takes 3.75 ms at batch 8 and 3.37 ms at batch 1, without it 3.64 and 3.26 ms; with
-  // the trigger behind the last key, in front of the merge, 3.75 ms as well (this kernel has more blocks
-  // than fit at once: a dependent that moves in early takes the room of blocks that have not started).
+  // top a decode step takes 3.75 ms at batch 8 and 3.37 ms at batch 1, without it 3.64 and 3.26 ms.  With
+  // the trigger behind the last key, in front of the merge, and the streaming products behind letting
+  // their own dependents in early (gemv_bf16.cu), *every* streaming product of the rest of the step
+  // runs at half its speed, down to the output head (408 against 180 us; 5.5 against 3.45 ms a step,
+  // at batch 1 as well, where most SMs hold no block of this kernel): an SM keeps the split between
+  // shared memory and L1 that its resident blocks need, this kernel needs nearly all of it as shared
+  // memory, and once a block of the streaming product has moved in beside or right behind one of
+  // these, the SM is never idle again between two kernels of the chain, so the product's loads in
+  // flight stay bounded by a small L1 (the same factor as asking for the largest carve-out for every
+  // kernel).  Kernels with different needs of shared memory must not overlap on an SM.
   // The batch's description (items, their number, block tables) is written by the host before the
   // step's first kernel: it is read, and the barriers are set up, while the kernel in front of
   // this one still runs.  The queries and the newest cache rows are that kernel's output.

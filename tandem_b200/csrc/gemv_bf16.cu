@@ -169,9 +169,9 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
     // blocks find room only as these exit, but the launch itself is out of the way by then.  All blocks
     // of this kernel are resident from the start (one per SM), so none of them can be kept out by a
     // dependent that has moved in early.  Measured on a decode step at batch 8, Qwen3-8B sizes: 3.57 ms
-    // against 3.63 ms with the trigger at the very end.  The same in a kernel with more blocks than
-    // fit at once is harmful: with decode attention triggering before its merge as well, dependents
-    // hold the room that blocks not yet started need, and the step takes 5.48 ms.
+    // against 3.63 ms with the trigger at the very end.  The kernel behind must want the same split of
+    // the SM's memory into shared memory and L1 as this one (another streaming product does): see the
+    // note in attention_decode.cu on what happens otherwise.
     if (nj >= my_groups) pdl_launch_dependents();
     if (streams) {
       if (nj < my_groups) {
