@@ -26,6 +26,9 @@ ITEM_INTS = 6  # token row, request, key begin, key end, first item of the reque
 TILE_INTS = 4  # first token row, request, first position, number of tokens
 STAGE_KEYS = 64  # keys per shared-memory stage: items are cut at multiples of it
 TILE_ROWS = 128  # rows (token x query head of the group) of a prefill tile
+WORK_INTS = 5  # the tcgen05 prefill kernel's item: first token row, request, first position, number of tokens, kv head
+STEP_KEYS = 128  # keys per step of the tcgen05 prefill kernel
+ITEM_FIXED_STEPS = 1.5  # what an item costs beside its steps (query tiles in, output rows out), in steps
 TARGET_BLOCKS = 148 * 2  # one wave at two blocks per SM
 MAX_SPLITS = 64  # items per request the kernel's fast merge takes
 MIN_ITEM_KEYS = 320  # a request is not cut into items shorter than this (measured: decode attention, batch 1 to 16)
@@ -77,11 +80,69 @@ def tcgen05_prefill_applies(head_dim: int, page_size: int) -> bool:
 
 def plan_prefill(seqs, groups: int, tile_rows: int = TILE_ROWS) -> list:
     """``seqs``: (first token row, request, first position, number of tokens) of every request that
-    brings several tokens.  Returns tiles of at most tile_rows // groups tokens, those with the most keys first."""
+    brings several tokens.  Returns tiles of at most tile_rows // groups tokens, those with the most keys first
+    (the mma.sync kernel's plan: one block per tile and kv head)."""
     per_tile = tile_rows // groups
     tiles = [[t0 + off, b, p0 + off, min(per_tile, n - off)] for t0, b, p0, n in seqs for off in range(0, n, per_tile)]
     tiles.sort(key=lambda x: -(x[2] + x[3]))
     return tiles
+
+
+def _item_steps(p0: int, ntok: int, per_tile: int, window: Optional[int]) -> int:
+    """Steps of 128 keys that the two query tiles of an item take together (as the kernel counts them)."""
+    kb = max(0, p0 - window + 1) if window else 0
+    s0 = kb // STEP_KEYS * STEP_KEYS
+    steps = 0
+    for first in (0, per_tile):
+        last = min(ntok, first + per_tile)
+        if last > first:
+            kb_t = max(0, p0 + first - window + 1) if window else 0
+            steps += -(-(p0 + last - s0) // STEP_KEYS) - (kb_t - s0) // STEP_KEYS
+    return steps
+
+
+def plan_prefill_queues(seqs, groups: int, num_kv_heads: int, window: Optional[int], blocks: int,
+                        tile_rows: int = TILE_ROWS) -> list:
+    """The tcgen05 kernel's plan.  ``seqs`` as for ``plan_prefill``; an item is up to two tiles' worth
+    of consecutive tokens of a request for one kv head, [first token row, request, first position,
+    number of tokens, kv head].  One persistent block per SM walks a queue of items; the queues are
+    balanced here (heaviest item first, each to the block with the least work so far), so that the
+    kernel neither counts nor fetches anything at run time.  Returns [queue position][block][5];
+    an item without tokens ends a block's queue."""
+    import heapq
+
+    per_tile = tile_rows // groups
+    items = []
+    for t0, b, p0, n in seqs:
+        for off in range(0, n, 2 * per_tile):
+            ntok = min(2 * per_tile, n - off)
+            cost = _item_steps(p0 + off, ntok, per_tile, window) + ITEM_FIXED_STEPS
+            items.extend((cost, [t0 + off, b, p0 + off, ntok, h]) for h in range(num_kv_heads))
+    if not items:
+        return []
+    items.sort(key=lambda x: -x[0])
+    blocks = max(1, min(blocks, len(items)))
+    queues = [[] for _ in range(blocks)]
+    heap = [(0.0, c) for c in range(blocks)]
+    for cost, item in items:
+        load, c = heapq.heappop(heap)
+        queues[c].append(item)
+        heapq.heappush(heap, (load + cost, c))
+    longest = max(len(q) for q in queues)
+    return [[q[k] if k < len(q) else [0] * WORK_INTS for q in queues] for k in range(longest)]
+
+
+def prefill_plan(seqs, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
+                 device) -> torch.Tensor:
+    """The plan for whichever prefill kernel takes this shape, on the device: [queue position, block, 5]
+    for the tcgen05 kernel, [tiles * 4] for the mma.sync kernel."""
+    groups = num_heads // num_kv_heads
+    if tcgen05_prefill_applies(head_dim, page_size):
+        from tandem_b200.kernels.gemm_bf16 import sm_count
+
+        queues = plan_prefill_queues(seqs, groups, num_kv_heads, window, sm_count(device))
+        return torch.tensor(queues, dtype=torch.int32).view(len(queues), -1, WORK_INTS).to(device)
+    return torch.tensor([x for t in plan_prefill(seqs, groups) for x in t], dtype=torch.int32).to(device)
 
 
 _workspaces: dict = {}
@@ -171,18 +232,27 @@ def _fresh_args(fresh: Optional[dict], qkv: torch.Tensor, num_heads: int, num_kv
 def paged_attention_prefill(qkv: torch.Tensor, kv, tiles: torch.Tensor, num_heads: int, num_kv_heads: int,
                             head_dim: int, window: Optional[int], scale: float,
                             out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Several tokens per request: ``tiles`` int32 [n * 4] as ``plan_prefill`` cut them."""
+    """Several tokens per request: ``tiles`` is the plan that ``prefill_plan`` makes for the kernel
+    that takes this shape (int32 [queue positions, blocks, 5] as ``plan_prefill_queues`` balanced them
+    for the tcgen05 kernel, [n * 4] as ``plan_prefill`` cut them for the mma.sync kernel)."""
     T = qkv.shape[0]
     if out is None:
         out = torch.empty((T, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     if tcgen05_prefill_applies(head_dim, kv.page_size):
-        fn, what = load_library("attention_prefill_tc", (f"TB_HD={head_dim}",)).tb_attention_prefill_tc, "attention_prefill_tc"
-    else:
-        fn, what = prefill_library(head_dim).tb_attention_prefill, "attention_prefill"
-    ops._check(fn(ops._stream(), ops._ptr(qkv), qkv.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
-                  kv.block_table.stride(0), ops._ptr(tiles), tiles.numel() // TILE_INTS, ops._ptr(out),
-                  ops._ptr(ops.status_word(qkv.device)), num_heads, num_kv_heads, kv.page_size, int(window or 0),
-                  ctypes.c_float(scale)), what)
+        if tiles.dim() != 3 or tiles.shape[2] != WORK_INTS:
+            raise ops.KernelError("the tcgen05 prefill kernel wants its plan as [queue positions, blocks, 5]")
+        lib = load_library("attention_prefill_tc", (f"TB_HD={head_dim}",))
+        ops._check(lib.tb_attention_prefill_tc(
+            ops._stream(), ops._ptr(qkv), T, qkv.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
+            kv.block_table.stride(0), ops._ptr(tiles), tiles.shape[0], tiles.shape[1], ops._ptr(out),
+            ops._ptr(ops.status_word(qkv.device)), num_heads, num_kv_heads, kv.page_size, int(window or 0),
+            ctypes.c_float(scale)), "attention_prefill_tc")
+        return out
+    ops._check(prefill_library(head_dim).tb_attention_prefill(
+        ops._stream(), ops._ptr(qkv), qkv.stride(0), ops._ptr(kv.k), ops._ptr(kv.v), ops._ptr(kv.block_table),
+        kv.block_table.stride(0), ops._ptr(tiles), tiles.numel() // TILE_INTS, ops._ptr(out),
+        ops._ptr(ops.status_word(qkv.device)), num_heads, num_kv_heads, kv.page_size, int(window or 0),
+        ctypes.c_float(scale)), "attention_prefill")
     return out
 
 
@@ -204,11 +274,18 @@ def plan_step(ctx, window: Optional[int], num_heads: int, num_kv_heads: int, hea
         (single if n == 1 else several).append((row, b, start) if n == 1 else (row, b, start, n))
         row += n
     items = plan_decode(single, window, num_kv_heads)
-    tiles = plan_prefill(several, groups)
     out[key + ("items",)] = [x for it in items for x in it]
     out[key + ("count",)] = [len(items)]
-    out[key + ("tiles",)] = [x for t in tiles for x in t]
-    ctx.scratch[key] = (len(items), len(tiles))
+    if tcgen05_prefill_applies(head_dim, ctx.page_size):
+        from tandem_b200.kernels.gemm_bf16 import sm_count
+
+        queues = plan_prefill_queues(several, groups, num_kv_heads, window, sm_count(ctx.device))
+        out[key + ("tiles",)] = [x for row in queues for item in row for x in item]
+        ctx.scratch[key] = (len(items), len(queues))
+    else:
+        tiles = plan_prefill(several, groups)
+        out[key + ("tiles",)] = [x for t in tiles for x in t]
+        ctx.scratch[key] = (len(items), len(tiles))
 
 
 def decodes_only(ctx, num_heads: int, num_kv_heads: int, head_dim: int, window: Optional[int], dtype: torch.dtype) -> bool:
@@ -230,7 +307,10 @@ def paged_attention(qkv: torch.Tensor, kv, ctx, num_heads: int, num_kv_heads: in
     num_items, num_tiles = planned
     out = torch.empty((qkv.shape[0], num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     if num_tiles:
-        paged_attention_prefill(qkv, kv, ctx.extras[key + ("tiles",)], num_heads, num_kv_heads, head_dim, window, scale, out)
+        tiles = ctx.extras[key + ("tiles",)]
+        if tcgen05_prefill_applies(head_dim, kv.page_size):
+            tiles = tiles.view(num_tiles, -1, WORK_INTS)  # num_tiles: queue positions
+        paged_attention_prefill(qkv, kv, tiles, num_heads, num_kv_heads, head_dim, window, scale, out)
     if num_items:
         paged_attention_decode(qkv, kv, ctx.extras[key + ("items",)], ctx.extras[key + ("count",)], num_heads,
                                num_kv_heads, head_dim, scale, out, fresh)

@@ -227,13 +227,12 @@ def bench_prefill_attention(args) -> None:
     k, v = _cache(pages, nkv, ps, hd)
     table = torch.randperm(pages, device="cuda").to(torch.int32).view(1, pages)
     kv = KVView(k, v, table, None, ps, True)
-    tiles = A.plan_prefill([(0, 0, start, T)], nh // nkv)
-    flat = torch.tensor([x for t in tiles for x in t], dtype=torch.int32, device="cuda")
+    flat = A.prefill_plan([(0, 0, start, T)], nh, nkv, hd, ps, None, "cuda")
     qkv = torch.randn(T, (nh + 2 * nkv) * hd, device="cuda", dtype=torch.bfloat16)
     us = time_calls(lambda i: A.paged_attention_prefill(qkv, kv, flat, nh, nkv, hd, None, hd ** -0.5), args.iters, args.graph)
     flops = 4.0 * nh * hd * (T * start + T * (T + 1) / 2)
     which = "tcgen05" if A.tcgen05_prefill_applies(hd, ps) else "mma.sync"
-    print(f"prefill attention ({which}) tokens={T} start={start} heads={nh}/{nkv} hd={hd} page={ps} tiles={len(tiles)}  {us:8.1f} us  "
+    print(f"prefill attention ({which}) tokens={T} start={start} heads={nh}/{nkv} hd={hd} page={ps} plan={tuple(flat.shape)}  {us:8.1f} us  "
           f"{flops / us / 1e6:7.1f} TFLOP/s")
 
 

@@ -547,11 +547,11 @@ def test_paged_attention_prefill(ops, monkeypatch, nh, nkv, hd, ps, batch, windo
     for b, (start, n) in enumerate(seqs):
         rows.append((at, b, start, n))
         at += n
-    tiles = A.plan_prefill(rows, nh // nkv)
-    assert sum(t[3] for t in tiles) == at
-    flat = torch.tensor([x for t in tiles for x in t], dtype=torch.int32)
+    plan = A.prefill_plan(rows, nh, nkv, hd, ps, window, "cuda")
+    tokens_planned = plan[..., 3].sum().item() // nkv if plan.dim() == 3 else plan.view(-1, 4)[:, 3].sum().item()
+    assert tokens_planned == at
     kv = KVView(phys(kc), phys(vc), dev(table), None, ps, True)
-    out = A.paged_attention_prefill(dev(qkv), kv, dev(flat), nh, nkv, hd, window, scale)
+    out = A.paged_attention_prefill(dev(qkv), kv, plan, nh, nkv, hd, window, scale)
     want = _attention_reference(Q, K, V, seqs, scale, window)
     torch.testing.assert_close(out.cpu().double(), want, atol=2e-2, rtol=2e-2)
     ops.check_status("cuda")
@@ -590,9 +590,8 @@ def test_prefill_finds_one_far_key_per_row(ops, monkeypatch, impl):
             rows = slice(p * ps, min(L, (p + 1) * ps))
             kc[table[0, p], :, : rows.stop - rows.start] = K[0][rows].transpose(0, 1)
         qkv[:, : nh * hd] = Q[0].reshape(n, -1)
-        tiles = A.plan_prefill([(0, 0, start, n)], nh // nkv)
         kv = KVView(phys(kc), phys(vc), dev(table), None, ps, True)
-        out = A.paged_attention_prefill(dev(qkv), kv, dev(torch.tensor([x for t in tiles for x in t], dtype=torch.int32)),
+        out = A.paged_attention_prefill(dev(qkv), kv, A.prefill_plan([(0, 0, start, n)], nh, nkv, hd, ps, window, "cuda"),
                                         nh, nkv, hd, window, 1.0).cpu().float().view(n, nh, hd)
         ok = 0
         for i, j in enumerate(target):
@@ -698,8 +697,6 @@ def test_attention_over_more_pages_than_the_kernels_cache(ops, hd, ps, window):
             vc[table[0, j]] = float("nan")
             table[0, j] = -1
     kv = KVView(phys(kc), phys(vc), dev(table), None, ps, True)
-    tiles = A.plan_prefill([(0, 0, start, n)], nh // nkv)
-    flat = torch.tensor([x for t in tiles for x in t], dtype=torch.int32)
     want = _attention_reference(Q, K, V, seqs, scale, window)
     for impl in ("tcgen05", "mma"):
         if impl == "tcgen05" and not A.tcgen05_prefill_applies(hd, ps):
@@ -707,7 +704,8 @@ def test_attention_over_more_pages_than_the_kernels_cache(ops, hd, ps, window):
         import os
         os.environ["TANDEM_PREFILL"] = impl
         try:
-            out = A.paged_attention_prefill(dev(qkv), kv, dev(flat), nh, nkv, hd, window, scale)
+            out = A.paged_attention_prefill(dev(qkv), kv, A.prefill_plan([(0, 0, start, n)], nh, nkv, hd, ps, window, "cuda"),
+                                            nh, nkv, hd, window, scale)
         finally:
             os.environ.pop("TANDEM_PREFILL", None)
         torch.testing.assert_close(out.cpu().double(), want, atol=2e-2, rtol=2e-2)
