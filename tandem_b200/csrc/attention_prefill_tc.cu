@@ -72,6 +72,8 @@ struct PrefillArgs {
   float scale_log2;
 };
 
+// With -DTB_PF_TRACE the first block records when its warps pass the stations of their first 64 steps
+// (clock64; tb_attention_prefill_tc_trace reads the record): the timeline the design was read off.
 #ifdef TB_PF_TRACE
 __device__ long long tb_trace[6 * 64 * 8];
 #define TRACE(role, n, ev) do { if (blockIdx.x == 0 && (n) < 64) tb_trace[((role) * 64 + (n)) * 8 + (ev)] = clock64(); } while (0)

@@ -10,7 +10,7 @@ LIBRARIES = [
     ("gemm_f32", ()),
     ("attention_simt", ()),
     ("sampling", ()),
-    ("gemm_skinny", ()), ("gemm_wide", ()), ("gemv_bf16", ()),
+    ("gemm_skinny", ()), ("gemm_wide", ()), ("gemm_wide_pair", ()), ("gemv_bf16", ()),
 ] + [(stem, (f"TB_HD={hd}",)) for hd in (16, 32, 48, 64, 128) for stem in ("attention_decode", "attention_prefill")] \
     + [("attention_prefill_tc", (f"TB_HD={hd}",)) for hd in (64, 128)]
 

@@ -18,7 +18,7 @@ measured on a B200 (``MEASURED``), and a rule for all others.  The same shape al
 kernel, so bfloat16 results are reproducible from run to run and a CUDA graph captures what an
 eager step runs.  ``python -m tandem_b200.kernels.microbench dispatch`` times every candidate and
 prints the table's lines and what the rule would have picked.
-``TANDEM_GEMM=skinny``, ``=gemv``, ``=wide`` or ``=library`` forces one kernel where it applies.
+``TANDEM_GEMM=skinny``, ``=gemv``, ``=wide``, ``=pair`` or ``=library`` forces one kernel where it applies.
 """
 
 from __future__ import annotations
@@ -38,10 +38,15 @@ GEMV_MAX_K = 16384  # beyond this the streaming kernel's rows of x outgrow share
 # to start and stream a little more slowly.  The skinny kernel wins from this many weight bytes on
 # (per class of rows; measured: it takes the output head at every class, gate_up of Qwen3-32B up to 16 rows).
 SKINNY_MIN_WEIGHT_BYTES = {1: 200 << 20, 2: 200 << 20, 4: 400 << 20, 8: 400 << 20, 16: 400 << 20, 32: 1 << 30, 64: 1 << 30}
-# gate/up with the activation in the epilogue of the wide kernel: where one wave of its 128-row
-# tiles is full (up to 128 rows) or the waves are many (from 1536 rows); in between the library's
-# tilings followed by the activation kernel are 5 to 10 % faster.
+# gate/up with the activation in the epilogue of a tcgen05 kernel.  From 192 rows on the kernel of
+# block pairs (256-row tiles) is the fastest by 2 to 10 % (measured at the gate_up sizes of
+# Qwen3-8B, -14B and -32B, 192 to 8,192 rows) unless its last tile of 256 rows is less than half
+# full and the rows are few (384 rows: 75 against 67 us).  Else the single-block kernel where one
+# wave of its 128-row tiles is full (up to 128 rows) or the waves are many (from 1536 rows); in
+# between the library's tilings followed by the activation kernel are 5 to 10 % faster.
 WIDE_GATED_ROWS = ((65, 128), (1536, None))
+PAIR_GATED_MIN_ROWS = 192
+PAIR_MAX_PADDING = 1.08  # rows the pair kernel computes (whole tiles of 256) over those the single-block kernel does (of 128)
 _mm_out_dtype = True  # torch.mm(..., out_dtype=) is tried once
 _sm_count: dict = {}
 
@@ -102,6 +107,19 @@ def wide(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, gated: b
     lib = load_library("gemm_wide")
     ops._check(lib.tb_gemm_wide(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(y), ops._ptr(ops.status_word(x.device)),
                                 M, N, K, int(out_dtype == torch.float32), int(gated), sm_count(x.device)), "gemm_wide")
+    return y
+
+
+def wide_pair(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, gated: bool = False) -> torch.Tensor:
+    """The tcgen05 kernel for many rows by pairs of blocks (``csrc/gemm_wide_pair.cu``, cta_group::2):
+    256 x 256 output tiles per pair, each block bringing its 128 rows of x and its half of the
+    tile's weight rows.  ``gated`` as for ``wide``."""
+    M, K = x.shape
+    N = weight.shape[0]
+    y = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+    lib = load_library("gemm_wide_pair")
+    ops._check(lib.tb_gemm_wide_pair(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(y), ops._ptr(ops.status_word(x.device)),
+                                     M, N, K, int(out_dtype == torch.float32), int(gated), sm_count(x.device)), "gemm_wide_pair")
     return y
 
 
@@ -219,19 +237,23 @@ def choose(M: int, N: int, K: int, aligned: bool = True) -> str:
 
 def choose_gated(M: int, N: int, K: int, aligned: bool = True) -> str:
     """Who computes silu(x gate^T) * (x up^T): "gemv" (activation inside the streaming kernel),
-    "wide" (activation in the epilogue of the tcgen05 kernel for many rows), or "product" (the
-    product as ``choose`` says, then the activation kernel)."""
+    "pair" or "wide" (activation in the epilogue of a tcgen05 kernel for many rows: pairs of blocks,
+    or single blocks), or "product" (the product as ``choose`` says, then the activation kernel)."""
     if N % 16:
         return "product"
     forced = os.environ.get("TANDEM_GEMM")
     if M <= GEMV_MAX_ROWS:
         return "gemv" if choose(M, N, K, aligned) == "gemv" else "product"
-    if forced == "wide":
-        return "wide" if wide_applies(M, N, K) and aligned else "product"
+    if forced in ("wide", "pair"):
+        return forced if wide_applies(M, N, K) and aligned else "product"
     if forced in ("library", "skinny", "gemv"):
         return "product"
+    if not (wide_applies(M, N, K) and aligned):
+        return "product"
+    if M >= PAIR_GATED_MIN_ROWS and -(-M // 256) * 256 <= PAIR_MAX_PADDING * (-(-M // 128) * 128):
+        return "pair"
     in_range = any(lo <= M and (hi is None or M <= hi) for lo, hi in WIDE_GATED_ROWS)
-    return "wide" if in_range and wide_applies(M, N, K) and aligned else "product"
+    return "wide" if in_range else "product"
 
 
 def _aligned(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -247,6 +269,8 @@ def gated(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         return gemv(x, weight, torch.bfloat16, gated=True)
     if which == "wide":
         return wide(x, weight, torch.bfloat16, gated=True)
+    if which == "pair":
+        return wide_pair(x, weight, torch.bfloat16, gated=True)
     return ops.silu_mul(linear(x, weight, torch.bfloat16))
 
 

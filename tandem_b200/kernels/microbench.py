@@ -67,12 +67,15 @@ def bench_gemm(args) -> None:
         rows.append(("mma.sync streaming kernel", time_calls(lambda i: gemm_bf16.gemv(x, ws[i % len(ws)], out), args.iters, args.graph)))
     if args.impl in ("both", "wide") and M > gemm_bf16.SKINNY_MAX_ROWS and gemm_bf16.wide_applies(M, N, K):
         rows.append(("tcgen05 wide kernel", time_calls(lambda i: gemm_bf16.wide(x, ws[i % len(ws)], out), args.iters, args.graph)))
+    if args.impl in ("both", "pair") and M > gemm_bf16.SKINNY_MAX_ROWS and gemm_bf16.wide_applies(M, N, K):
+        rows.append(("tcgen05 pair kernel", time_calls(lambda i: gemm_bf16.wide_pair(x, ws[i % len(ws)], out), args.iters, args.graph)))
     if args.impl in ("both", "library"):
         rows.append(("library (cuBLAS)", time_calls(lambda i: gemm_bf16._library(x, ws[i % len(ws)], out), args.iters, args.graph)))
     if args.gated and M > gemm_bf16.SKINNY_MAX_ROWS:
         from tandem_b200.kernels import ops
 
         rows.append(("wide kernel, silu*up fused", time_calls(lambda i: gemm_bf16.wide(x, ws[i % len(ws)], out, gated=True), args.iters, args.graph)))
+        rows.append(("pair kernel, silu*up fused", time_calls(lambda i: gemm_bf16.wide_pair(x, ws[i % len(ws)], out, gated=True), args.iters, args.graph)))
         rows.append(("library + silu_mul kernel", time_calls(lambda i: ops.silu_mul(gemm_bf16._library(x, ws[i % len(ws)], out)), args.iters, args.graph)))
     for name, us in rows:
         print(f"gemm M={M} N={N} K={K}  {name:24s} {us:8.1f} us  {N * K * 2 / us / 1e3:7.0f} GB/s weights  "
@@ -132,12 +135,23 @@ def bench_dispatch(args) -> None:
             print(f"{name:8s} M={M:3d} N={N:6d} K={K:5d} ({N * K * 2 >> 20:4d} MiB)  {cells}  rule: {rule}"
                   + ("" if rule == best else f"  (fastest: {best}, {times[rule] / times[best]:.2f}x)"))
         print(f"    ({N}, {K}): {winners},")
-        if name == "gate_up":
-            for M in (128, 256, 512, 1024, 2048, 4096):
+        if name == "gate_up" or args.many_rows:
+            gated = name == "gate_up"
+            for M in (96, 128, 192, 256, 384, 512, 768, 1024, 1536, 2048, 3072, 4096, 8192):
                 x = torch.randn(M, K, device="cuda", dtype=bf)
-                a = time_calls(lambda i: gemm_bf16.wide(x, ws[i % len(ws)], bf, gated=True), args.iters, args.graph)
-                b = time_calls(lambda i: ops.silu_mul(gemm_bf16._library(x, ws[i % len(ws)], bf)), args.iters, args.graph)
-                print(f"gate_up  M={M:4d} gated: wide {a:8.1f} us  library + silu_mul {b:8.1f} us  rule: {gemm_bf16.choose_gated(M, N, K)}")
+                if gated:
+                    times = {"wide": time_calls(lambda i: gemm_bf16.wide(x, ws[i % len(ws)], bf, gated=True), args.iters, args.graph),
+                             "pair": time_calls(lambda i: gemm_bf16.wide_pair(x, ws[i % len(ws)], bf, gated=True), args.iters, args.graph),
+                             "product": time_calls(lambda i: ops.silu_mul(gemm_bf16._library(x, ws[i % len(ws)], bf)), args.iters, args.graph)}
+                    rule = gemm_bf16.choose_gated(M, N, K)
+                else:
+                    times = {"pair": time_calls(lambda i: gemm_bf16.wide_pair(x, ws[i % len(ws)], out), args.iters, args.graph),
+                             "library": time_calls(lambda i: gemm_bf16._library(x, ws[i % len(ws)], out), args.iters, args.graph)}
+                    rule = gemm_bf16.choose(M, N, K)
+                best = min(times, key=times.get)
+                cells = "  ".join(f"{k} {v:8.1f} us" for k, v in times.items())
+                print(f"{name:8s} M={M:4d}{' gated' if gated else ''}: {cells}  rule: {rule}"
+                      + ("" if rule == best else f"  (fastest: {best}, {times[rule] / times[best]:.2f}x)"))
         del ws
 
 
@@ -277,7 +291,7 @@ def main(argv=None) -> None:
     g.add_argument("--k", type=int, default=4096)
     g.add_argument("--f32-out", action="store_true")
     g.add_argument("--gated", action="store_true", help="also time the product with the SiLU * up epilogue (rows of W = [gate | up])")
-    g.add_argument("--impl", choices=["both", "skinny", "gemv", "wide", "library"], default="both")
+    g.add_argument("--impl", choices=["both", "skinny", "gemv", "wide", "pair", "library"], default="both")
     g.set_defaults(fn=bench_gemm)
     ng = sub.add_parser("norm-gemm", parents=[common])
     ng.add_argument("--m", type=int, default=8)
@@ -304,6 +318,7 @@ def main(argv=None) -> None:
     t.set_defaults(fn=bench_tokenwise)
     dp = sub.add_parser("dispatch", parents=[common])
     dp.add_argument("--shapes", choices=sorted(LAYER_SHAPES), default="8b")
+    dp.add_argument("--many-rows", action="store_true", help="also the pair kernel against the library at 96 to 8,192 rows, every product")
     dp.set_defaults(fn=bench_dispatch)
     tl = sub.add_parser("step-timeline", parents=[common])
     tl.add_argument("--batch", type=int, default=8)

@@ -723,20 +723,22 @@ def test_attention_over_more_pages_than_the_kernels_cache(ops, hd, ps, window):
 # ----------------------------------------------------------------------------- the many-row tcgen05 product
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 520, 200), (2048, 4096, 4096), (1, 8, 8), (129, 6144, 1024), (1000, 1000, 72)])
 @pytest.mark.parametrize("out", [torch.bfloat16, torch.float32])
-def test_gemm_wide(ops, M, N, K, out):
+@pytest.mark.parametrize("impl", ["wide", "wide_pair"])
+def test_gemm_wide(ops, M, N, K, out, impl):
     from tandem_b200.kernels import gemm_bf16
 
     g = torch.Generator().manual_seed(60 + M)
     x = (torch.randn(M, K, generator=g)).bfloat16()
     w = (torch.randn(N, K, generator=g) * K ** -0.5).bfloat16()
-    y = gemm_bf16.wide(dev(x), dev(w), out)
+    y = getattr(gemm_bf16, impl)(dev(x), dev(w), out)
     want = dev(x).float() @ dev(w).float().T  # float32 products of bfloat16 operands, float32 sums
     torch.testing.assert_close(y.float(), want, **(dict(atol=2e-2, rtol=2e-2) if out == torch.bfloat16 else dict(atol=2e-3, rtol=2e-3)))
     ops.check_status("cuda")
 
 
 @pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 264, 200), (2048, 1536, 4096), (3, 8, 16)])
-def test_gemm_wide_gated(ops, M, I, K):
+@pytest.mark.parametrize("impl", ["wide", "wide_pair"])
+def test_gemm_wide_gated(ops, M, I, K, impl):
     """Rows [gate | up] of the weight in one launch: silu(x gate^T) * (x up^T), both products rounded
     to bfloat16 first, as the separate kernels round them."""
     from tandem_b200.kernels import gemm_bf16
@@ -744,7 +746,7 @@ def test_gemm_wide_gated(ops, M, I, K):
     g = torch.Generator().manual_seed(70 + M)
     x = dev((torch.randn(M, K, generator=g)).bfloat16())
     w = dev((torch.randn(2 * I, K, generator=g) * K ** -0.5).bfloat16())
-    y = gemm_bf16.wide(x, w, torch.bfloat16, gated=True)
+    y = getattr(gemm_bf16, impl)(x, w, torch.bfloat16, gated=True)
     gu = (x.float() @ w.float().T).bfloat16().float()
     want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
     torch.testing.assert_close(y.float(), want, atol=2e-2, rtol=2e-2)
