@@ -99,9 +99,12 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   // step's first kernel: it is read, and the barriers are set up, while the kernel in front of
   // this one still runs.  The queries and the newest cache rows are that kernel's output.
   const int num_items = *a.num_items;
-  const int* item = a.items + (size_t)blockIdx.x * ITEM_INTS;
+  // grid = (kv heads, item slots, groups of 16 query heads): the kv heads run fastest, so that the blocks of
+  // the plan's items are handed out first and those of the empty slots behind them last
+  const int item_index = blockIdx.y;
+  const int* item = a.items + (size_t)item_index * ITEM_INTS;
   const int t = item[0], req = item[1], kb = item[2], ke = item[3], first_item = item[4], nsplits = item[5];
-  if ((int)blockIdx.x >= num_items) return;
+  if (item_index >= num_items) return;
   // 128-byte rows of the swizzled tiles must start on 128-byte boundaries
   unsigned char* smem_raw = smem_unaligned + ((128u - (smem_u32(smem_unaligned) & 127u)) & 127u);
   __nv_bfloat16* stage_mem = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [STAGES][K | V][STAGE_KEYS * HD]
@@ -115,7 +118,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   int* table_s = last_flag + 1;  // [TABLE_CACHE] the request's page numbers for this block's keys
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kvh = blockIdx.y, G = a.nh / a.nkv, ps = a.page_size;
+  const int kvh = blockIdx.x, G = a.nh / a.nkv, ps = a.page_size;
   const int row0 = blockIdx.z * 16, rows = min(16, G - row0);  // query heads of this block: kvh*G + row0 + g
   const int xmask = min(7, ps - 1);
   const int s0 = (kb / STAGE_KEYS) * STAGE_KEYS;
@@ -131,7 +134,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
   __syncthreads();  // the barriers stand; nothing slow has been waited for yet
   // The producer needs the page numbers only and starts to stream as soon as it has them; the
   // consumers load the query tile meanwhile and meet among themselves.
-  const bool newest_block = (int)blockIdx.x == first_item + nsplits - 1;  // this block's keys end with the request's newest
+  const bool newest_block = item_index == first_item + nsplits - 1;  // this block's keys end with the request's newest
   const int* table = nullptr;
   int streamed = 0;
   if (warp == WARPS) {
@@ -308,7 +311,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(const DecodeA
     }
   }
   __syncthreads();
-  const size_t part_row = ((size_t)blockIdx.x * a.nkv + kvh) * G + row0;  // + g
+  const size_t part_row = ((size_t)item_index * a.nkv + kvh) * G + row0;  // + g
   for (int idx = tid; idx < rows * HD; idx += THREADS) {
     const int g = idx / HD, d = idx % HD;
     float mx = -INFINITY;
@@ -418,13 +421,14 @@ extern "C" {
 
 int tb_attention_decode_head_dim() { return tb::HD; }
 
-// items: [max_items, 6] int32 on the device; grid = (max_items, nkv, ceil(G / 16)).
+// items: [max_items, 6] int32 on the device (max_items <= 65535); grid = (nkv, max_items, ceil(G / 16)).
 int tb_attention_decode(void* stream, const void* q, int q_stride, const void* k_cache, const void* v_cache,
                         const int* block_table, int table_stride, const int* items, const int* num_items,
                         int max_items, void* out, float* part_o, float* part_ml, int* counters, int* status, int nh,
                         int nkv, int page_size, float scale, int fresh, const float* q_norm_w, const float* k_norm_w,
                         const float* cos_sin, const int* positions, const int* slots, float eps, int max_pos) {
   if (max_items <= 0) return 0;
+  if (max_items > 65535) return TB_ERR_BAD_SIZE;
   if (fresh && ((tb::HD & (tb::HD - 1)) != 0 || !cos_sin || !positions || !slots || max_pos <= 0)) return TB_ERR_BAD_SIZE;
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0) return TB_ERR_BAD_SIZE;
   if (!(page_size == 1 || page_size == 2 || page_size == 4 || page_size == 8 || page_size % 16 == 0))
@@ -444,10 +448,16 @@ int tb_attention_decode(void* stream, const void* q, int q_stride, const void* k
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(tb::attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+    // All of an SM's memory as shared memory: two blocks are to fit on an SM whatever split the kernel in front
+    // left there (with the default, an SM that still had the split of a kernel with little shared memory took
+    // one block, and a step's attention at 16 or 32 requests ran in two rounds, 73 us instead of 47); the
+    // keys and values come by bulk copies, which do not pass through the L1.
+    e = cudaFuncSetAttribute(tb::attention_decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int G = nh / nkv;
-  dim3 grid(max_items, nkv, (G + 15) / 16);
+  dim3 grid(nkv, max_items, (G + 15) / 16);
   return tb::launch(tb::attention_decode_kernel, grid, dim3(tb::THREADS), smem, stream, a);
 }
 
