@@ -222,7 +222,7 @@ def bench_decode_attention(args) -> None:
         k, v = _cache(B * pages_per_seq, nkv, ps, hd)
         table = torch.randperm(B * pages_per_seq, device="cuda").to(torch.int32).view(B, pages_per_seq)
         views.append(KVView(k, v, table, None, ps, True))
-    items = A.plan_decode([(b, b, L - 1) for b in range(B)], None, nkv)
+    items = A.plan_decode([(b, b, L - 1) for b in range(B)], None, nkv, *([args.pieces * B * nkv] if args.pieces else []))
     spare = args.spare_items  # a CUDA graph's item array has room for the largest plan of its bucket: blocks without an item
     flat = torch.tensor([x for it in items for x in it] + [0] * (A.ITEM_INTS * spare), dtype=torch.int32, device="cuda")
     count = torch.tensor([len(items)], dtype=torch.int32, device="cuda")
@@ -307,6 +307,7 @@ def main(argv=None) -> None:
     d = sub.add_parser("decode-attention", parents=[common, shape])
     d.add_argument("--batch", type=int, default=64)
     d.add_argument("--context", type=int, default=2048)
+    d.add_argument("--pieces", type=int, default=0, help="cut every request's keys into this many items instead of what the rule picks")
     d.add_argument("--spare-items", type=int, default=0, help="room in the item array beyond the plan, as in a CUDA graph's bucket")
     d.set_defaults(fn=bench_decode_attention)
     f = sub.add_parser("prefill-attention", parents=[common, shape])

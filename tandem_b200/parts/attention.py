@@ -67,7 +67,7 @@ class PagedAttention(Mixer):
         if key + ("items",) in out or \
                 not attention_kernels.tensor_core_path_applies(self.qkv.dtype, s.head_dim, page_size, groups):
             return
-        items = attention_kernels.TARGET_BLOCKS // s.num_kv_heads + 2 * bucket + 8
+        items = attention_kernels.decode_items_capacity(bucket, s.num_kv_heads, max_model_len)
         out[key + ("items",)] = items * attention_kernels.ITEM_INTS
         out[key + ("count",)] = 1
         out[key + ("tiles",)] = 0

@@ -73,3 +73,20 @@ def test_decode_items_cover_the_visible_keys():
             assert mine[0][2] == lo and mine[-1][3] == p + 1
             assert all(x[3] == y[2] for x, y in zip(mine, mine[1:]))
             assert all(it[5] == len(mine) and it[4] == items.index(mine[0]) for it in mine)
+
+
+def test_decode_pieces_fill_the_rounds():
+    # few requests: as many items as fill the GPU once, none shorter than 320 keys
+    assert A.decode_pieces(1, 8, 2048) == 7 and A.decode_pieces(8, 8, 2048) == 4 and A.decode_pieces(8, 8, 300) == 1
+    # whole requests that fit at once stay whole
+    assert A.decode_pieces(32, 8, 8192) == 1 and A.decode_pieces(36, 8, 8192) == 1
+    # a round and a bit: shorter items fill the last round
+    assert A.decode_pieces(40, 8, 8192) == 3 and A.decode_pieces(48, 8, 8192) == 3 and A.decode_pieces(40, 8, 600) == 2
+    # nearly two full rounds: nothing to gain
+    assert A.decode_pieces(64, 8, 8192) == 1
+    # the capacity a CUDA graph reserves covers every plan of its bucket
+    for bucket in (1, 8, 64):
+        cap = A.decode_items_capacity(bucket, 8, 4096)
+        for n in range(1, bucket + 1):
+            for length in (1, 319, 4096):
+                assert len(A.plan_decode([(i, i, length - 1) for i in range(n)], None, 8)) <= cap
