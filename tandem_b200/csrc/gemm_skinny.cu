@@ -218,7 +218,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const long long seg_begin = c, seg_end = min(c_end, (tile + 1) * KC);
       c = seg_end;
       const int buf = seg & 1;
-      if (!mbar_wait(acc_full + buf, (seg >> 1) & 1, abort_flag, a.status)) break;
+      // the whole warp gives up or none of it: the loads from tensor memory below want all 32 lanes
+      if (!__all_sync(0xffffffffu, mbar_wait(acc_full + buf, (seg >> 1) & 1, abort_flag, a.status))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const bool whole = seg_begin == tile * KC && seg_end == (tile + 1) * KC;
       const long long n = tile * BN + col;

@@ -184,7 +184,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
       const int mt = tile % a.m_tiles, nt = tile / a.m_tiles;
       const int buf = local & 1;
-      if (!mbar_wait(acc_full + buf, (local >> 1) & 1, abort_flag, a.status)) break;
+      // the whole warp gives up or none of it: the loads from tensor memory below want all 32 lanes
+      if (!__all_sync(0xffffffffu, mbar_wait(acc_full + buf, (local >> 1) & 1, abort_flag, a.status))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = mt * WM + warp * 32 + lane;
       const uint32_t acc = tmem_base + lane_base + (uint32_t)(buf * WN);
