@@ -1,5 +1,6 @@
 // y[m, n] = sum_k x[m, k] * w[n, k] for up to eight rows of x (a batch of so many decoding
-// requests): bfloat16 in, float32 sums, bfloat16 or float32 out.
+// requests), or up to sixteen where they fit into shared memory beside the L1: bfloat16 in,
+// float32 sums, bfloat16 or float32 out.
 //
 // With so few rows the product is a stream of weights and nothing else, and what decides its time
 // is how soon the stream starts and how little happens after it ends.  So: no shared-memory ring
@@ -8,7 +9,8 @@
 // K range, each streams its slice of the 16 rows straight from global memory into registers
 // (16 bytes a load, eight loads in flight per lane and the next eight issued before the last
 // eight are used) and multiplies with `mma.sync` m16n8k16: the weights are the A operand (16
-// rows), the rows of x the B operand (8 columns; rows that x does not have are zeros).  The
+// rows), the rows of x the B operand (8 columns; rows that x does not have are zeros; with nine to
+// sixteen rows of x every weight fragment goes into two MMAs, one per eight rows).  The
 // registers that a lane loads are not in the order the instruction names, but a sum over k does
 // not care in which order k is walked as long as A and B walk it alike: the lane with thread
 // index t in its group takes, of every 64 k, the eight at 8 t and the eight at 32 + 8 t, for A
@@ -61,12 +63,13 @@ struct GemvFuse {
   float* residual;         // [M, N] float32: residual += bfloat16(product)
   const float* norm_w;     // [N]: the weight of the norm behind the add
   __nv_bfloat16* scaled;   // [M, N] out: bfloat16(residual * norm_w)
-  float* partials_out;     // [gridDim.x, 8] out: this block's sums of squares of the residual entries it wrote
+  float* partials_out;     // [gridDim.x, 8 NT] out: this block's sums of squares of the residual entries it wrote
   // MODE_SCALE: row m of the product is multiplied by rsqrt(sum_p partials[p][m] / K + eps)
-  const float* partials;   // [parts, 8]
+  const float* partials;   // [parts, 8 NT]
   int parts;
   float eps;
 };
+// (NT: tiles of eight rows of x, 1 or 2; the rows of `partials` and `partials_out` have 8 NT entries)
 
 template <bool X_IN_SMEM>
 struct Round {  // what a lane holds of one round: [step][row g | row g + 8][piece t | piece 4 + t]
@@ -74,15 +77,23 @@ struct Round {  // what a lane holds of one round: [step][row g | row g + 8][pie
   uint4 b[X_IN_SMEM ? 1 : GV_STEPS][2];  // the lane's pieces of row g of x, where x is not in shared memory
 };
 
-template <bool X_IN_SMEM, int MODE>
+template <bool X_IN_SMEM, int MODE, int NT>
 __global__ void __launch_bounds__(GV_THREADS, 1)
 gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __restrict__ y, int M, int N, int pieces,
-            int x_stride, int out_f32, int gated, const GemvFuse f) {
+            int x_stride, int out_f32, int gated, int sets, const GemvFuse f) {
+  static_assert(NT == 1 || X_IN_SMEM, "more than eight rows of x are taken from shared memory only");
+  constexpr int TILE = 128 * NT;  // floats of a warp's partial tile: 16 rows of w by 8 NT rows of x, [NT][16][8]
+  // Two sets of partial tiles, used in turn, so that a group needs one meeting of the block.  With sixteen rows of x
+  // the second set is given up where it would push the block into the next carve-out of shared memory (`sets` = 1:
+  // a second meeting per group instead): what the copy of x leaves of the SM's memory is the L1, which bounds the
+  // loads in flight.  Measured at K = 4096: 9 to 14 rows (132 KB) stream within 2 to 7 % of 8 rows' time (100 KB),
+  // 15 and 16 rows (164 KB) 15 % behind it; the second meeting costs 1 % of a decode step.
+  const int SETS = NT == 1 ? 2 : sets;
   extern __shared__ uint4 smem[];
-  __shared__ float row_scale[8];  // MODE_SCALE: the rows' rsqrt(mean square + eps)
-  __shared__ float ssq_s[4][8];   // MODE_ADD: sums of squares of what this block wrote, per warp and row
+  __shared__ float row_scale[8 * NT];  // MODE_SCALE: the rows' rsqrt(mean square + eps)
+  __shared__ float ssq_s[4 * NT][8];   // MODE_ADD: sums of squares of what this block wrote, per warp and row
   uint4* xs = smem;                                                    // [M][x_stride] pieces of 8 k
-  float* red = reinterpret_cast<float*>(smem + (X_IN_SMEM ? (size_t)M * x_stride : 0));  // [2][GV_WARPS][16 rows][8 columns]
+  float* red = reinterpret_cast<float*>(smem + (X_IN_SMEM ? (size_t)M * x_stride : 0));  // [SETS][GV_WARPS][NT][16 rows][8 columns]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
   const int steps = (pieces + 7) >> 3;  // steps of 64 k
   const int s0 = warp * steps / GV_WARPS, s1 = (warp + 1) * steps / GV_WARPS;  // this warp's part of K
@@ -142,7 +153,7 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
     // one warp per row: the partial sums in block order, lane by lane, then the lanes in a fixed tree; the result is
     // first read in an epilogue, behind the block-wide barrier in front of it
     float ss = 0.f;
-    for (int p = lane; p < f.parts; p += 32) ss += __ldcg(f.partials + p * 8 + warp);
+    for (int p = lane; p < f.parts; p += 32) ss += __ldcg(f.partials + p * (8 * NT) + warp);
     ss = warp_sum(ss);
     if (lane == 0) row_scale[warp] = rsqrtf(ss / (float)(pieces * 8) + f.eps);
   }
@@ -151,8 +162,9 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
   // the group begins, not when its sums are ready: a round trip to the L2 less at the end of every group
   float res_old = 0.f, gain = 0.f;
   auto fetch_place = [&](int jj) {
-    if (MODE == MODE_ADD && threadIdx.x < 128 && jj < my_groups) {
-      const int n = ((int)blockIdx.x + jj * (int)gridDim.x) * group_rows + (threadIdx.x >> 3), col = threadIdx.x & 7;
+    if (MODE == MODE_ADD && threadIdx.x < TILE && jj < my_groups) {
+      const int n = ((int)blockIdx.x + jj * (int)gridDim.x) * group_rows + ((threadIdx.x & 127) >> 3);
+      const int col = (threadIdx.x & 7) + 8 * (threadIdx.x >> 7);
       if (col < M && n < N) {
         res_old = __ldcg(f.residual + (size_t)col * N + n);
         gain = f.norm_w[n];
@@ -160,7 +172,9 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
     }
   };
   fetch_place(0);
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
   int j = 0, s = s0;
   while (j < my_groups) {
     int nj = j, ns = s + GV_STEPS;
@@ -185,31 +199,38 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int c = (s + u) * 8 + h * 4 + t;
-            uint4 b = make_uint4(0, 0, 0, 0);
-            if (X_IN_SMEM) {
-              if (g < M && c < pieces) b = xs[g * x_stride + c];
-            } else {
-              b = cur.b[X_IN_SMEM ? 0 : u][h];
-            }
             const uint4 &a0 = cur.w[u][0][h], &a1 = cur.w[u][1][h];
-            mma_16816(acc, a0.x, a1.x, a0.y, a1.y, b.x, b.y);
-            mma_16816(acc, a0.z, a1.z, a0.w, a1.w, b.z, b.w);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              uint4 b = make_uint4(0, 0, 0, 0);
+              if (X_IN_SMEM) {
+                if (g + 8 * nt < M && c < pieces) b = xs[(g + 8 * nt) * x_stride + c];
+              } else {
+                b = cur.b[X_IN_SMEM ? 0 : u][h];
+              }
+              mma_16816(acc[nt], a0.x, a1.x, a0.y, a1.y, b.x, b.y);
+              mma_16816(acc[nt], a0.z, a1.z, a0.w, a1.w, b.z, b.w);
+            }
           }
         }
       }
     }
     if (nj != j) {  // the group is complete as far as this warp goes: the block adds its 16 partial tiles up
-      float* mine = red + ((size_t)(j & 1) * GV_WARPS + warp) * 128;
-      *reinterpret_cast<float2*>(mine + g * 8 + 2 * t) = make_float2(acc[0], acc[1]);
-      *reinterpret_cast<float2*>(mine + (g + 8) * 8 + 2 * t) = make_float2(acc[2], acc[3]);
-      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      float* mine = red + ((size_t)(j & (SETS - 1)) * GV_WARPS + warp) * TILE;
+      if (SETS == 1) __syncthreads();  // the sums of the group before have been taken (a group of streaming ago)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        *reinterpret_cast<float2*>(mine + nt * 128 + g * 8 + 2 * t) = make_float2(acc[nt][0], acc[nt][1]);
+        *reinterpret_cast<float2*>(mine + nt * 128 + (g + 8) * 8 + 2 * t) = make_float2(acc[nt][2], acc[nt][3]);
+        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+      }
       __syncthreads();
-      if (threadIdx.x < 128) {
-        const int row = threadIdx.x >> 3, col = threadIdx.x & 7;
-        const float* part = red + (size_t)(j & 1) * GV_WARPS * 128 + threadIdx.x;
+      if (threadIdx.x < TILE) {  // a thread per place of the tile: (row of w, row of x)
+        const int row = (threadIdx.x & 127) >> 3, col = (threadIdx.x & 7) + 8 * (threadIdx.x >> 7);
+        const float* part = red + (size_t)(j & (SETS - 1)) * GV_WARPS * TILE + threadIdx.x;
         float sum = 0.f, second = 0.f;
 #pragma unroll
-        for (int q = 0; q < GV_WARPS; ++q) sum += part[q * 128];
+        for (int q = 0; q < GV_WARPS; ++q) sum += part[q * TILE];
         const int n = ((int)blockIdx.x + j * (int)gridDim.x) * group_rows + row;
         const float scale = (MODE == MODE_SCALE && col < M) ? row_scale[col] : 1.f;
         if (MODE == MODE_SCALE) sum *= scale;
@@ -228,7 +249,7 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
           }
         } else if (row < 8) {  // the formula of the activation kernel (tokenwise.cu), on the values it would read
 #pragma unroll
-          for (int q = 0; q < GV_WARPS; ++q) second += part[q * 128 + 64];
+          for (int q = 0; q < GV_WARPS; ++q) second += part[q * TILE + 64];
           if (MODE == MODE_SCALE) second *= scale;
           const float gate = __bfloat162float(__float2bfloat16_rn(sum)), up = __bfloat162float(__float2bfloat16_rn(second));
           if (col < M)
@@ -241,15 +262,17 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
     j = nj;
     s = ns;
   }
-  if (MODE == MODE_ADD) {  // threads 0..127 hold (row of w = tid / 8, row of x = tid % 8): rows of w summed in a fixed order
-    if (threadIdx.x < 128) {
+  if (MODE == MODE_ADD) {  // threads 0 .. 128 NT - 1 hold (row of w = (tid % 128) / 8, row of x = tid % 8 + 8 (tid / 128)): rows of w summed in a fixed order
+    if (threadIdx.x < TILE) {
       wrote_sq += __shfl_xor_sync(0xffffffffu, wrote_sq, 8);
       wrote_sq += __shfl_xor_sync(0xffffffffu, wrote_sq, 16);
       if (lane < 8) ssq_s[warp][lane] = wrote_sq;
     }
     __syncthreads();
-    if (threadIdx.x < 8)
-      f.partials_out[(size_t)blockIdx.x * 8 + threadIdx.x] = ssq_s[0][threadIdx.x] + ssq_s[1][threadIdx.x] + ssq_s[2][threadIdx.x] + ssq_s[3][threadIdx.x];
+    if (threadIdx.x < 8 * NT) {
+      const int w0 = 4 * (threadIdx.x >> 3), c = threadIdx.x & 7;  // the four warps that hold this row of x
+      f.partials_out[(size_t)blockIdx.x * (8 * NT) + threadIdx.x] = ssq_s[w0][c] + ssq_s[w0 + 1][c] + ssq_s[w0 + 2][c] + ssq_s[w0 + 3][c];
+    }
   }
   pdl_launch_dependents();  // (blocks without work)
 }
@@ -260,14 +283,28 @@ extern "C" {
 
 // Rows of x the kernel takes, and the shared memory up to which x is copied there (the next
 // larger carve-out of the SM's memory leaves the L1 cache 28 KB, and the loads in flight halve).
-int tb_gemv_max_rows() { return 8; }
+// More than 8 rows are taken only from shared memory, and only up to the carve-out below that one:
+// measured at K = 4096, 9 to 14 rows stream within 2 to 7 % of 8 rows' time, 15 and 16 (164 KB) 15 % behind it.
+int tb_gemv_max_rows() { return 16; }
 int tb_gemv_max_smem_bytes() { return 164 * 1024; }
+int tb_gemv_max_smem_bytes_two_tiles() { return 130 * 1024; }
 
 // Pieces (of 8 k) between two rows of x in shared memory: four more than a multiple of eight, so that
 // the 16-byte reads of a quarter warp (two rows, four pieces each) fall into eight different bank groups.
 static int x_stride_of(int pieces) { return pieces + ((4 - pieces % 8) + 8) % 8; }
 
-static const int kReduceBytes = 2 * tb::GV_WARPS * 128 * 4;
+// The sets of partial tiles: two, or with more than 8 rows one where two do not fit beside x.
+static int x_bytes(int M, int K) { return M * x_stride_of(K / 8) * 16; }
+static int sets_of(int M, int K) {
+  return (M <= 8 || x_bytes(M, K) + 2 * tb::GV_WARPS * 256 * 4 <= tb_gemv_max_smem_bytes_two_tiles()) ? 2 : 1;
+}
+static int reduce_bytes(int M, int K) { return sets_of(M, K) * tb::GV_WARPS * (M > 8 ? 256 : 128) * 4; }
+
+// Whether the kernel takes M rows of K: up to 8 always, up to 16 if x fits into shared memory.
+int tb_gemv_takes(int M, int K) {
+  if (M <= 0 || M > tb_gemv_max_rows() || K <= 0 || (K & 7)) return 0;
+  return M <= 8 || x_bytes(M, K) + reduce_bytes(M, K) <= tb_gemv_max_smem_bytes_two_tiles();
+}
 
 // The number of blocks a launch with these sizes uses: the rows of `partials_out` that MODE_ADD writes.
 int tb_gemv_grid(int N, int gated, int blocks) {
@@ -278,29 +315,34 @@ int tb_gemv_grid(int N, int gated, int blocks) {
 static int launch_gemv(void* stream, const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int gated, int blocks,
                        int mode, const tb::GemvFuse& f) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > tb_gemv_max_rows() || K <= 0 || (K & 7) || blocks <= 0) return TB_ERR_BAD_SIZE;
+  if (!tb_gemv_takes(M, K) || blocks <= 0) return TB_ERR_BAD_SIZE;
   if (gated && (out_f32 || N % 16 != 0)) return TB_ERR_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return TB_ERR_BAD_SIZE;
-  const int stride = x_stride_of(K / 8), with_x = M * stride * 16 + kReduceBytes;
+  const int stride = x_stride_of(K / 8), with_x = x_bytes(M, K) + reduce_bytes(M, K);
   const bool in_smem = with_x <= tb_gemv_max_smem_bytes();
-  void (*kernel)(const uint4*, const uint4*, void*, int, int, int, int, int, int, const tb::GemvFuse) =
-      mode == tb::MODE_ADD     ? (in_smem ? tb::gemv_kernel<true, tb::MODE_ADD> : tb::gemv_kernel<false, tb::MODE_ADD>)
-      : mode == tb::MODE_SCALE ? (in_smem ? tb::gemv_kernel<true, tb::MODE_SCALE> : tb::gemv_kernel<false, tb::MODE_SCALE>)
-                               : (in_smem ? tb::gemv_kernel<true, tb::MODE_PLAIN> : tb::gemv_kernel<false, tb::MODE_PLAIN>);
-  static bool allowed[64][6] = {};  // the larger shared memory is asked for once per device and kernel
+  const bool two = M > 8;  // two tiles of eight rows of x (in shared memory then, tb_gemv_takes)
+  typedef void (*Kernel)(const uint4*, const uint4*, void*, int, int, int, int, int, int, int, const tb::GemvFuse);
+  Kernel kernel =
+      two ? (mode == tb::MODE_ADD ? (Kernel)tb::gemv_kernel<true, tb::MODE_ADD, 2>
+             : mode == tb::MODE_SCALE ? (Kernel)tb::gemv_kernel<true, tb::MODE_SCALE, 2> : (Kernel)tb::gemv_kernel<true, tb::MODE_PLAIN, 2>)
+      : mode == tb::MODE_ADD   ? (in_smem ? (Kernel)tb::gemv_kernel<true, tb::MODE_ADD, 1> : (Kernel)tb::gemv_kernel<false, tb::MODE_ADD, 1>)
+      : mode == tb::MODE_SCALE ? (in_smem ? (Kernel)tb::gemv_kernel<true, tb::MODE_SCALE, 1> : (Kernel)tb::gemv_kernel<false, tb::MODE_SCALE, 1>)
+                               : (in_smem ? (Kernel)tb::gemv_kernel<true, tb::MODE_PLAIN, 1> : (Kernel)tb::gemv_kernel<false, tb::MODE_PLAIN, 1>);
+  static bool allowed[64][12] = {};  // the larger shared memory is asked for once per device and kernel
   int device = 0;
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return (int)e;
   if (device < 0 || device >= 64) return TB_ERR_BAD_SIZE;
-  if (!allowed[device][mode * 2 + in_smem]) {
+  const int which = (two ? 6 : 0) + mode * 2 + in_smem;
+  if (!allowed[device][which]) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tb_gemv_max_smem_bytes());
     if (e != cudaSuccess) return (int)e;
-    allowed[device][mode * 2 + in_smem] = true;
+    allowed[device][which] = true;
   }
   const int groups = gated ? N / 16 : (N + 15) / 16;
   return tb::launch(kernel, dim3(blocks < groups ? blocks : groups), dim3(tb::GV_THREADS),
-                    (size_t)(in_smem ? with_x : kReduceBytes), stream, (const uint4*)x, (const uint4*)w, y, M, N, K / 8, stride,
-                    out_f32, gated, f);
+                    (size_t)(in_smem ? with_x : reduce_bytes(M, K)), stream, (const uint4*)x, (const uint4*)w, y, M, N, K / 8, stride,
+                    out_f32, gated, sets_of(M, K), f);
 }
 
 // x [M, K] and w [N, K] bfloat16, both contiguous and 16-byte aligned, K a multiple of 8; y [M, N], or with
@@ -310,7 +352,7 @@ int tb_gemv(void* stream, const void* x, const void* w, void* y, int M, int N, i
 }
 
 // residual [M, N] float32 += bfloat16(x w^T); scaled [M, N] = bfloat16(residual * norm_w); partials_out
-// [tb_gemv_grid(N, 0, blocks), 8] = every block's sums of squares of the residual entries it wrote (rows beyond M: zero).
+// [tb_gemv_grid(N, 0, blocks), 8 or, with more than 8 rows, 16] = every block's sums of squares of the residual entries it wrote (rows beyond M: zero).
 int tb_gemv_add(void* stream, const void* x, const void* w, float* residual, const float* norm_w, void* scaled, float* partials_out,
                 int M, int N, int K, int blocks) {
   if (!residual || !norm_w || !scaled || !partials_out) return TB_ERR_BAD_SIZE;

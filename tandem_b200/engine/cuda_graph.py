@@ -3,7 +3,8 @@
 A step in which every request brings exactly one token launches a few hundred small kernels; at
 small batches their launch cost exceeds their run time.  Such steps are captured once per batch
 *bucket* (1, 2, 4, 8, 16, 24, 32, ... as python/tandem/executor/cuda_graph.py:34-38 of
-12vivi/tandem) and replayed: the batch description lives in one static int32 buffer on the
+12vivi/tandem, and 12 beside them: up to 14 rows the products of a layer are this package's
+streaming kernel, which 16 rows are not) and replayed: the batch description lives in one static int32 buffer on the
 device, refilled by a single copy before each replay.  Rows that pad a batch up to its bucket
 carry token 0 at position 0 with a negative cache slot (the cache-write kernel skips them) and no
 attention item; their outputs are never read.  Logits and sampling stay outside the graph
@@ -31,7 +32,7 @@ from tandem_b200.parts.base import StepContext
 
 
 def bucket_sizes(max_batch: int) -> list:
-    sizes = [b for b in (1, 2, 4, 8, 16) if b <= max_batch] + list(range(24, max_batch + 1, 8))
+    sizes = [b for b in (1, 2, 4, 8, 12, 16) if b <= max_batch] + list(range(24, max_batch + 1, 8))
     if max_batch not in sizes:
         sizes.append(max_batch)
     return sorted(set(sizes))

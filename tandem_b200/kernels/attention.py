@@ -195,19 +195,20 @@ def _workspace(device, items: int, num_kv_heads: int, groups: int, head_dim: int
     return ws
 
 
-FRESH_MAX_TOKENS = 8  # rows up to which the projection in front is this package's streaming kernel
+FRESH_MAX_TOKENS = 8  # rows up to which the projection in front is always taken to be this package's streaming kernel
 
 
-def fresh_applies(head_dim: int, rotary_dim: int, writable: bool, num_tokens: int = 1) -> bool:
+def fresh_applies(head_dim: int, rotary_dim: int, writable: bool, num_tokens: int = 1, streamed: bool = False) -> bool:
     """Whether decode attention should make its query rows and the newest key itself from the raw
     projection (per-head norm, rotary encoding, cache write folded in): the whole head rotates and
     the head size is a power of two, as the stand-alone kernel's fast path wants it too, and the
-    step has at most eight tokens.  Measured on a decode step at Qwen3-8B sizes: 3.54 against 3.61 ms
-    at batch 8, 313.5 against 311 tok/s at batch 1; nothing to speak of at 16, 48 and 64 tokens, and
-    5.99 against 5.06 ms at 32, where the kernel in front is then a library product whose blocks do
-    not all fit at once and the attention blocks that move in early take their room."""
+    step has at most eight tokens, or the projection in front is the streaming kernel (``streamed``).
+    Measured on a decode step at Qwen3-8B sizes: 3.54 against 3.61 ms at batch 8, 313.5 against 311 tok/s
+    at batch 1, 3.95 against 3.99 ms at batch 12 behind the streaming kernel; nothing to speak of at 16,
+    48 and 64 tokens, and 5.99 against 5.06 ms at 32, where the kernel in front is then a library
+    product whose blocks do not all fit at once and the attention blocks that move in early take their room."""
     return (writable and rotary_dim == head_dim and head_dim & (head_dim - 1) == 0 and 16 <= head_dim <= 256
-            and num_tokens <= FRESH_MAX_TOKENS and os.environ.get("TANDEM_FRESH_ATTENTION", "1") != "0")
+            and (num_tokens <= FRESH_MAX_TOKENS or streamed) and os.environ.get("TANDEM_FRESH_ATTENTION", "1") != "0")
 
 
 def paged_attention_decode(qkv: torch.Tensor, kv, items: torch.Tensor, count: torch.Tensor, num_heads: int,

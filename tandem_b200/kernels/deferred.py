@@ -45,7 +45,7 @@ class PendingNorm:
     eps: float
     out_dtype: torch.dtype
     scaled: torch.Tensor  # [M, H] bfloat16(residual * weight): the normalised rows but for their scale
-    partials: torch.Tensor  # [parts, 8] float32: sums of squares of the rows, per block of the kernel that wrote them
+    partials: torch.Tensor  # [parts, 8 or 16] float32 (gemm_bf16.gemv_partial_rows of M): sums of squares of the rows, per block of the kernel that wrote them
     parts: int
 
     @property

@@ -6,9 +6,10 @@ kernels take over for the shapes on which they beat cuBLAS, by a table kept per 
 (python/tandem/layers/triton_gemv.py:221-297).  The same is done here, with three kernels of
 this package beside the library:
 
-* up to 8 rows: ``csrc/gemv_bf16.cu`` streams the weights through registers into ``mma.sync``
-  (no shared-memory ring, no tensor memory, no merge between blocks);
-* 9 to 64 rows: ``csrc/gemm_skinny.cu``, the tcgen05 weight-streaming kernel, where the weight
+* up to 8 rows, and up to 16 where the rows of x fit into shared memory: ``csrc/gemv_bf16.cu``
+  streams the weights through registers into ``mma.sync`` (no shared-memory ring, no tensor
+  memory, no merge between blocks);
+* up to 64 rows: ``csrc/gemm_skinny.cu``, the tcgen05 weight-streaming kernel, where the weight
   matrix is large enough to pay for its fixed cost; the library otherwise;
 * more rows: the library, except for the gate/up projection, whose activation runs in the
   epilogue of ``csrc/gemm_wide.cu``.
@@ -32,7 +33,9 @@ from tandem_b200.kernels import ops
 from tandem_b200.kernels.build import load_library
 
 SKINNY_MAX_ROWS = 64
-GEMV_MAX_ROWS = 8  # tb_gemv_max_rows() of csrc/gemv_bf16.cu
+GEMV_MAX_ROWS = 16  # tb_gemv_max_rows() of csrc/gemv_bf16.cu
+GEMV_ROWS_ANY_K = 8  # up to so many rows x may stay in global memory; more must fit into shared memory
+GEMV_SMEM_BYTES_TWO_TILES = 130 * 1024  # tb_gemv_max_smem_bytes_two_tiles()
 GEMV_MAX_K = 16384  # beyond this the streaming kernel's rows of x outgrow shared memory and it falls behind (measured at K = 25600)
 # The skinny kernel costs about 9 us whatever the shape; the library's small-batch kernels cost less
 # to start and stream a little more slowly.  The skinny kernel wins from this many weight bytes on
@@ -128,17 +131,30 @@ def wide_applies(M: int, N: int, K: int) -> bool:
 
 
 def gemv_applies(M: int, N: int, K: int) -> bool:
-    """What the register-streaming kernel takes: up to eight rows."""
-    return 0 < M <= GEMV_MAX_ROWS and K > 0 and K % 8 == 0
+    """What the register-streaming kernel takes (tb_gemv_takes of csrc/gemv_bf16.cu): up to eight
+    rows, or up to sixteen whose padded copy fits into 130 KB of shared memory beside the block's
+    partial tiles (14 rows of 4,096, 11 of 5,120)."""
+    if not (0 < M <= GEMV_MAX_ROWS and K > 0 and K % 8 == 0):
+        return False
+    if M <= GEMV_ROWS_ANY_K:
+        return True
+    pieces = K // 8
+    stride = pieces + (4 - pieces % 8 + 8) % 8
+    return M * stride * 16 + 16 * 256 * 4 <= GEMV_SMEM_BYTES_TWO_TILES
+
+
+def gemv_partial_rows(M: int) -> int:
+    """Entries in a row of the partial sums of squares that the kernel leaves or reads at M rows."""
+    return 8 if M <= GEMV_ROWS_ANY_K else 16
 
 
 def gemv_preferred(M: int, N: int, K: int) -> bool:
     """Where the streaming kernel is the rule's choice among what takes the shape."""
-    return gemv_applies(M, N, K) and K <= GEMV_MAX_K
+    return gemv_applies(M, N, K) and K <= GEMV_MAX_K and M <= GEMV_ROWS_ANY_K
 
 
 def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, gated: bool = False, scale=None) -> torch.Tensor:
-    """The weight-streaming kernel for up to eight rows (``csrc/gemv_bf16.cu``): weights from global
+    """The weight-streaming kernel for up to sixteen rows (``csrc/gemv_bf16.cu``): weights from global
     memory straight into registers, ``mma.sync`` against the rows of x in shared memory.  ``gated``:
     the weight's rows are [gate | up]; returns silu(x gate^T) * (x up^T), [M, rows / 2], the values
     the product followed by ``ops.silu_mul`` gives.  ``scale`` (a ``deferred.PendingNorm`` whose
@@ -159,12 +175,13 @@ def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, gated: b
 
 def gemv_add(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor) -> tuple:
     """residual [M, N] (float32) += bfloat16(x @ weight^T), by the streaming kernel itself.  Returns
-    (bfloat16(residual * norm_weight) [M, N], the blocks' partial sums of squares of the new rows [parts, 8], parts)."""
+    (bfloat16(residual * norm_weight) [M, N], the blocks' partial sums of squares of the new rows
+    [parts, 8 or, above eight rows, 16], parts)."""
     lib = load_library("gemv_bf16")
     M, K = x.shape
     N = weight.shape[0]
     parts = lib.tb_gemv_grid(N, 0, sm_count(x.device))
-    partials = torch.empty((parts, 8), dtype=torch.float32, device=x.device)
+    partials = torch.empty((parts, gemv_partial_rows(M)), dtype=torch.float32, device=x.device)
     scaled = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     ops._check(lib.tb_gemv_add(ops._stream(), ops._ptr(x), ops._ptr(weight), ops._ptr(residual), ops._ptr(norm_weight), ops._ptr(scaled),
                                ops._ptr(partials), M, N, K, sm_count(x.device)), "gemv (added into the residual)")
@@ -193,21 +210,28 @@ ROW_CLASSES = (1, 2, 4, 8, 16, 32, 64)
 # ``python -m tandem_b200.kernels.microbench dispatch --shapes 8b|14b|32b`` prints.  Shapes that are
 # not listed follow the rule in ``choose``.  12vivi/tandem keeps such a table per GPU
 # (python/tandem/layers/triton_gemv.py:221-267).
+# The class of 9 to 16 rows names the streaming kernel for the first three products of a Qwen3-8B layer:
+# it takes them up to 14 rows (``gemv_applies``; 15 and 16 fall through to the rule), alone it is level
+# with the library there (qkv 11.7 against 12.1 us, o 9.2 against 9.9, gate_up 34.3 against 34.4 at 12
+# rows), and in a decode step it takes the add and the norm between the products along and lets decode
+# attention move in early: 3.78 against 3.99 ms at batch 9, 3.94 against 4.12 at 12, 4.15 against 4.23 at 14.
+# With K = 5120 it takes up to 11 rows, and a step gains from it for gate_up alone (Qwen3-14B at batch 10:
+# 6.34 against 6.48 ms, 6.38 with o and qkv as well; Qwen3-32B: 13.31 against 13.49 ms, 13.49 with qkv as well).
 _G, _S, _L = "gemv", "skinny", "library"
 MEASURED = {
-    (6144, 4096): {1: _G, 2: _G, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
-    (4096, 4096): {1: _G, 2: _G, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
-    (24576, 4096): {1: _G, 2: _G, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
+    (6144, 4096): {1: _G, 2: _G, 4: _G, 8: _G, 16: _G, 32: _L, 64: _L},
+    (4096, 4096): {1: _G, 2: _G, 4: _G, 8: _G, 16: _G, 32: _L, 64: _L},
+    (24576, 4096): {1: _G, 2: _G, 4: _G, 8: _G, 16: _G, 32: _L, 64: _L},
     (4096, 12288): {1: _G, 2: _G, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
     (151936, 4096): {1: _G, 2: _G, 4: _G, 8: _G, 16: _S, 32: _S, 64: _S},
     (7168, 5120): {1: _L, 2: _L, 4: _L, 8: _L, 16: _L, 32: _L, 64: _L},
     (5120, 5120): {1: _L, 2: _L, 4: _L, 8: _L, 16: _L, 32: _L, 64: _L},
-    (34816, 5120): {1: _G, 2: _G, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
+    (34816, 5120): {1: _G, 2: _G, 4: _G, 8: _G, 16: _G, 32: _L, 64: _L},
     (5120, 17408): {1: _L, 2: _L, 4: _L, 8: _L, 16: _L, 32: _L, 64: _L},
     (151936, 5120): {1: _S, 2: _S, 4: _S, 8: _G, 16: _S, 32: _S, 64: _S},
     (10240, 5120): {1: _G, 2: _L, 4: _G, 8: _G, 16: _L, 32: _L, 64: _L},
     (5120, 8192): {1: _G, 2: _L, 4: _L, 8: _L, 16: _L, 32: _L, 64: _L},
-    (51200, 5120): {1: _G, 2: _G, 4: _G, 8: _G, 16: _S, 32: _S, 64: _L},
+    (51200, 5120): {1: _G, 2: _G, 4: _G, 8: _G, 16: _G, 32: _S, 64: _L},
     (5120, 25600): {1: _S, 2: _S, 4: _S, 8: _S, 16: _S, 32: _L, 64: _L},
 }
 

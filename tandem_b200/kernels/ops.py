@@ -222,6 +222,14 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- matrix products
+def linear_streams(rows: int, weight: torch.Tensor) -> bool:
+    """Whether ``linear`` of so many rows with this weight runs this package's streaming kernel (all of
+    whose blocks are resident at once, so that a kernel behind it may move in early)."""
+    from tandem_b200.kernels import gemm_bf16
+
+    return weight.dtype == torch.bfloat16 and gemm_bf16.choose(rows, weight.shape[0], weight.shape[1], weight.is_contiguous()) == "gemv"
+
+
 def linear(x, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None, defer: bool = False):
     """x [M, K] @ weight [N, K]^T -> [M, N].  float32 operands run the CUDA-core kernel (true
     32-bit arithmetic); bfloat16 operands run on the tensor cores with float32 accumulation.

@@ -79,7 +79,8 @@ class PagedAttention(Mixer):
         kv = ctx.kv(self)
         fresh = None
         if attention_kernels.decodes_only(ctx, s.num_heads, s.num_kv_heads, s.head_dim, s.window, qkv.dtype) and \
-                attention_kernels.fresh_applies(s.head_dim, self.position.rotary_dim, kv.writable, qkv.shape[0]):
+                attention_kernels.fresh_applies(s.head_dim, self.position.rotary_dim, kv.writable, qkv.shape[0],
+                                                ops.linear_streams(qkv.shape[0], self.qkv)):
             # single tokens only: decode attention normalises, rotates and stores what it needs itself
             fresh = dict(positions=ctx.positions, slots=kv.slots, q_norm=self.q_norm, k_norm=self.k_norm,
                          cos_sin=self.position.cos_sin, eps=s.qk_norm_eps)

@@ -98,7 +98,7 @@ def test_cuda_graph_decode_matches_eager(tiny_folder):
     from tandem_b200.engine.cuda_graph import DecodeGraphs, bucket_sizes
     from tandem_b200.engine.executor import StepEntry
 
-    assert bucket_sizes(64) == [1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64] and bucket_sizes(5) == [1, 2, 4, 5]
+    assert bucket_sizes(64) == [1, 2, 4, 8, 12, 16, 24, 32, 40, 48, 56, 64] and bucket_sizes(5) == [1, 2, 4, 5]
     decoder, _ = load_model(tiny_folder("B"), "bfloat16", "cuda:0")
     eager = build_executor(decoder, page_size=16, num_pages=64, max_requests=8)
     graph = build_executor(decoder, page_size=16, num_pages=64, max_requests=8)

@@ -178,10 +178,11 @@ def test_gemm_bf16(ops, M, N, K, out_dtype):
                                    (2, 24, 8), (1, 151936, 512), (2, 130, 2056), (1, 7, 2048), (1, 3000, 25600),
                                    (3, 4096, 4096), (4, 1000, 12288), (4, 77, 200), (8, 6144, 4096), (8, 4096, 12288),
                                    (5, 2500, 1000), (8, 17, 72), (7, 24576, 4096), (6, 33, 8200), (7, 100, 20000),
-                                   (8, 300, 25600)])
+                                   (8, 300, 25600), (9, 6144, 4096), (14, 4096, 4096), (12, 1000, 96), (14, 24576, 4096), (16, 512, 2048),
+                                   (13, 77, 200), (16, 17, 72), (11, 2500, 1000), (10, 130, 2056), (11, 300, 5120)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemv_bf16(ops, M, N, K, out_dtype):
-    """Up to eight rows through the register-streaming kernel: odd N, fewer rows of the weight
+    """Up to sixteen rows through the register-streaming kernel: odd N, fewer rows of the weight
     than a block takes, K that is no multiple of a step or of the warps' shares, and the same bits every time."""
     from tandem_b200.kernels import gemm_bf16
 
@@ -197,12 +198,21 @@ def test_gemv_bf16(ops, M, N, K, out_dtype):
     assert torch.equal(first, gemm_bf16.gemv(xd, wd, out_dtype))
     if M > 1:  # a row alone gives the bits it gives beside others
         assert torch.equal(gemm_bf16.gemv(xd[M - 1:].contiguous(), wd, out_dtype)[0], first[M - 1])
-    assert not gemm_bf16.gemv_applies(9, N, K) and not gemm_bf16.gemv_applies(1, N, K + 4)
-    with pytest.raises(Exception):
-        gemm_bf16.gemv(dev(torch.zeros(9, K).bfloat16()), wd, out_dtype)
+    if M > 8:  # and so do the first eight
+        assert torch.equal(gemm_bf16.gemv(xd[:8].contiguous(), wd, out_dtype), first[:8])
+    assert not gemm_bf16.gemv_applies(17, N, K) and not gemm_bf16.gemv_applies(1, N, K + 4)
+    assert gemm_bf16.gemv_applies(8, N, 25600) and not gemm_bf16.gemv_applies(9, N, 25600)  # nine rows of that length do not fit into shared memory
+    assert gemm_bf16.gemv_applies(14, N, 4096) and not gemm_bf16.gemv_applies(15, N, 4096)
+    assert gemm_bf16.gemv_applies(11, N, 5120) and not gemm_bf16.gemv_applies(12, N, 5120)
+    lib = gemm_bf16.load_library("gemv_bf16")
+    assert all(bool(lib.tb_gemv_takes(m, k)) == gemm_bf16.gemv_applies(m, N, k) for m in range(0, 18) for k in (8, 72, 2048, 4096, 4100, 5120, 8192, 25600))
+    for rows, k in ((17, K), (9, 25600)):
+        with pytest.raises(Exception):
+            gemm_bf16.gemv(dev(torch.zeros(rows, k).bfloat16()), dev(torch.zeros(8, k).bfloat16()), out_dtype)
 
 
-@pytest.mark.parametrize("M,I,K", [(1, 16, 64), (8, 12288, 4096), (3, 104, 200), (5, 1000, 1000), (8, 40, 12288), (2, 4096, 520)])
+@pytest.mark.parametrize("M,I,K", [(1, 16, 64), (8, 12288, 4096), (3, 104, 200), (5, 1000, 1000), (8, 40, 12288), (2, 4096, 520),
+                                   (14, 12288, 4096), (9, 104, 200), (16, 1000, 1000)])
 def test_gemv_gated_gives_the_bits_of_product_then_activation(ops, M, I, K):
     """silu(x gate^T) * (x up^T) inside the streaming kernel (8 gate rows and their 8 up rows share a
     tile); bit for bit what the product followed by ops.silu_mul gives."""
@@ -222,8 +232,9 @@ def test_gemv_gated_gives_the_bits_of_product_then_activation(ops, M, I, K):
 
 
 @pytest.mark.parametrize("M,H,N2,K0", [(1, 4096, 6144, 4096), (8, 4096, 24576, 12288), (5, 1000, 136, 200), (3, 64, 64, 64),
-                                        (8, 96, 512, 256), (7, 4096, 4096, 12288)])
-def test_gemv_takes_the_residual_add_and_the_norm_along(ops, M, H, N2, K0):
+                                        (8, 96, 512, 256), (7, 4096, 4096, 12288), (14, 4096, 24576, 4096), (9, 1000, 136, 200),
+                                        (16, 96, 512, 256)])
+def test_gemv_takes_the_residual_add_and_the_norm_along(ops, M, H, N2, K0, monkeypatch):
     """A product added into the residual by its own kernel (which also writes residual * norm weight
     and partial sums of squares), and the product behind it scaling its rows by the norm's
     rsqrt(mean square + eps), against the three kernels one after the other: the residual bit for
@@ -231,6 +242,8 @@ def test_gemv_takes_the_residual_add_and_the_norm_along(ops, M, H, N2, K0):
     to within the one bfloat16 rounding that has moved; real products within the usual bounds."""
     from tandem_b200.kernels import deferred, gemm_bf16
 
+    if M > 8:  # nine to sixteen rows go to the streaming kernel only where a measurement said so
+        monkeypatch.setenv("TANDEM_GEMM", "gemv")
     g = torch.Generator().manual_seed(17 + M)
     x = dev(torch.randn(M, K0, generator=g).bfloat16())
     w1 = dev((torch.randn(H, K0, generator=g) / math.sqrt(K0)).bfloat16())
@@ -244,7 +257,7 @@ def test_gemv_takes_the_residual_add_and_the_norm_along(ops, M, H, N2, K0):
     pending = ops.add_rmsnorm(deferred.PendingLinear(x, w1), res_b, wn, 1e-5, torch.bfloat16, defer=True)
     assert isinstance(pending, deferred.PendingNorm) and pending.residual is res_b
     assert torch.equal(res_a, res_b)
-    assert pending.partials.shape == (pending.parts, 8) and (pending.partials[:, M:] == 0).all()
+    assert pending.partials.shape == (pending.parts, 8 if M <= 8 else 16) and (pending.partials[:, M:] == 0).all()
     torch.testing.assert_close(pending.partials.sum(0)[:M].double().cpu(), res_b.double().pow(2).sum(1).cpu(), rtol=1e-5, atol=0)
     assert torch.equal(pending.scaled, (res_b * wn).bfloat16())
     # the scale in the second product's epilogue
@@ -265,10 +278,10 @@ def test_gemv_takes_the_residual_add_and_the_norm_along(ops, M, H, N2, K0):
         I = N2 // 2
         torch.testing.assert_close(ops.gated_linear(pending, w2).double(), torch.nn.functional.silu(want[:, :I]) * want[:, I:], atol=3e-2, rtol=3e-2)
     # a reader that the streaming kernel does not run gets the rows from the stand-alone norm kernel
-    wide_x = deferred.PendingNorm(res_b.repeat(9, 1)[:9].contiguous(), wn, 1e-5, torch.bfloat16, pending.scaled.repeat(9, 1)[:9].contiguous(),
+    wide_x = deferred.PendingNorm(res_b.repeat(17, 1)[:17].contiguous(), wn, 1e-5, torch.bfloat16, pending.scaled.repeat(17, 1)[:17].contiguous(),
                                   pending.partials, pending.parts)
     w3 = dev((torch.randn(24, H, generator=g) / math.sqrt(H)).bfloat16())
-    assert not gemm_bf16.scale_fusable(wide_x, w3) and ops.linear(wide_x, w3).shape == (9, 24)
+    assert not gemm_bf16.scale_fusable(wide_x, w3) and ops.linear(wide_x, w3).shape == (17, 24)
     ops.check_status("cuda")
 
 
