@@ -130,6 +130,18 @@ class CacheManager:
             short += max(0, need - (g.pool.num_free + freed))
         return short
 
+    def pages_to_grow(self, request_id: str, total_tokens: int) -> list:
+        """Per group, the pages that ``grow(request_id, total_tokens)`` would take from the pool beyond
+        those it first gives back (negative: it gives back more than it takes)."""
+        live = self.live[request_id]
+        out = []
+        for g in self.groups:
+            table = g.tables[request_id]
+            first = self._first_needed_page(g, live.num_tokens)
+            freed = sum(1 for p in table[:first] if p >= 0)
+            out.append(max(0, cdiv(total_tokens, self.page_size) - len(table)) - freed)
+        return out
+
     def grow(self, request_id: str, total_tokens: int) -> bool:
         """Make room for the request to hold ``total_tokens`` tokens.  First gives back, in the
         windowed groups, the pages that the request's next query no longer reads.  Takes pages

@@ -6,10 +6,11 @@
 // unsigned integers), eight bits a pass: a pass builds a histogram of the next digit among the
 // values that share the digits found so far, counts for top-k and probability mass for top-p (in
 // 52-bit fixed point, so that the sums are integers and do not depend on the order of the atomic
-// additions), and the next pass reads off the digit.  A row is cut into chunks that many blocks
-// work on at once (a row of 150,000 logits is more than one SM should walk a dozen times), one
-// small launch per pass; sums that stay floating point (the normaliser, the kept mass per chunk)
-// are taken per chunk and added in chunk order.  Where tandem draws with torch.multinomial, the
+// additions), and the next pass reads off the digit.  A row is cut into eight chunks that the blocks
+// of a thread-block cluster work on at once (a row of 150,000 logits is more than one SM should walk
+// a dozen times); all passes run in one launch, the cluster meeting between them; sums that stay
+// floating point (the normaliser, the kept mass per chunk) are taken per chunk and added in chunk
+// order, so a row's token does not depend on how many rows the call has.  Where tandem draws with torch.multinomial, the
 // draw here is the inverse CDF in vocabulary order at u * total for a uniform number u that the
 // caller supplies per row, so a draw is a pure function of (logits, options, u).  Tokens whose
 // value equals the cut are all kept (a sort keeps as many of them as fit); the outcomes differ only
@@ -139,10 +140,11 @@ argmax_split_kernel(const float* __restrict__ logits, int* __restrict__ out, uns
 }
 
 // ------------------------------------------------------------------------------------------------
-// Temperature sampling, many blocks per row.
-constexpr int SP_THREADS = 256;
-constexpr int SP_MAX_CHUNKS = 64;
+// Temperature sampling: one cluster of blocks per row, one launch for all passes.
+constexpr int SP_THREADS = 1024;
+constexpr int SP_MAX_CHUNKS = 8;  // a row is cut into eight chunks; a cluster of 8, 4, 2 or 1 blocks shares them out
 constexpr int SP_FIXED_BITS = 52;  // probability mass as an integer multiple of 2^-52
+constexpr int SP_LANES = 64;     // private copies of the first top-p histogram (see pass_mass)
 
 struct RowScratch {
   unsigned long long best;             // argmax word: ordered key above, inverted index below
@@ -167,16 +169,24 @@ struct SampleArgs {
   const float* uniform;
   RowScratch* scratch;
   int* out;
-  int V, chunks;
+  int V, cluster;  // blocks per row (gridDim.x)
 };
 
 // What every pass needs of a row: its options, its largest logit, and the bounds of this block's chunk.
 struct RowView {
   const float* x;
   RowScratch* rs;
-  float inv_t, mx, tp, mp;
-  int k, begin, end, argmax;
+  float inv_t, mx, tp, mp, inv_z;
+  int k, begin, end, argmax;  // [begin, end): all the chunks of this block
+  int first_chunk, num_chunks, chunk_len;
   bool greedy, use_k, use_p;
+};
+
+struct SampleShared {
+  unsigned long long lanes[32][SP_LANES];  // pass_mass, first digit: private copies of the histogram's upper bins
+  unsigned long long lhist[256], lscratch[8], lshare[2], warp_best[SP_THREADS / 32];
+  int ihist[256], iscratch[8], ishare[2], chosen;
+  float fs[33], parts[SP_MAX_CHUNKS], prefix[SP_THREADS];
 };
 
 __device__ __forceinline__ RowView row_view(const SampleArgs& a) {
@@ -192,28 +202,54 @@ __device__ __forceinline__ RowView row_view(const SampleArgs& a) {
   v.mp = a.min_p[r];
   v.use_k = !v.greedy && v.k > 0 && v.k < a.V;
   v.use_p = !v.greedy && v.tp < 1.f;
-  const int len = ((a.V + a.chunks - 1) / a.chunks + 3) & ~3;
-  v.begin = min(a.V, (int)blockIdx.x * len);
-  v.end = min(a.V, v.begin + len);
+  v.chunk_len = ((a.V + SP_MAX_CHUNKS - 1) / SP_MAX_CHUNKS + 3) & ~3;
+  v.num_chunks = SP_MAX_CHUNKS / a.cluster;
+  v.first_chunk = (int)blockIdx.x * v.num_chunks;
+  v.begin = min(a.V, v.first_chunk * v.chunk_len);
+  v.end = min(a.V, v.begin + v.num_chunks * v.chunk_len);
   v.argmax = 0;
   v.mx = 0.f;
+  v.inv_z = 0.f;
   return v;
 }
 
-// f(i, x[i]) for this thread's share of the block's chunk: 16-byte loads where the row allows them
-// (a chunk starts at a multiple of four).
+// f(i, x[i]) for this thread's share of [begin, end) of the row: 16-byte loads where the row allows them
+// (begin is a multiple of four, end is V or one), four of them in flight.
 template <typename F>
-__device__ __forceinline__ void chunk_for_each(const RowView& v, int V, F f) {
+__device__ __forceinline__ void range_for_each(const RowView& v, int V, int begin, int end, F f) {
   if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(v.x) & 15) == 0) {
-#pragma unroll 2
-    for (int i = v.begin + 4 * (int)threadIdx.x; i < v.end; i += 4 * SP_THREADS) {  // v.end is V or a multiple of four
+#pragma unroll 4
+    for (int i = begin + 4 * (int)threadIdx.x; i < end; i += 4 * SP_THREADS) {
       const float4 q = *reinterpret_cast<const float4*>(v.x + i);
       f(i, q.x); f(i + 1, q.y); f(i + 2, q.z); f(i + 3, q.w);
     }
   } else {
 #pragma unroll 4
-    for (int i = v.begin + (int)threadIdx.x; i < v.end; i += SP_THREADS) f(i, v.x[i]);
+    for (int i = begin + (int)threadIdx.x; i < end; i += SP_THREADS) f(i, v.x[i]);
   }
+}
+
+// All the chunks of this block at once (for what does not depend on the order: maxima, integer sums).
+template <typename F>
+__device__ __forceinline__ void chunk_for_each(const RowView& v, int V, F f) { range_for_each(v, V, v.begin, v.end, f); }
+
+// Chunk by chunk, g(chunk, sum over the block of f's results in that chunk): sums in floating point are taken per
+// chunk by the same threads over the same elements however many chunks a block has, so that a row's
+// result does not depend on how many blocks share it (which goes with the number of rows).
+template <typename F, typename G>
+__device__ __forceinline__ void chunk_sums(const RowView& v, int V, float* scratch33, F f, G g) {
+  for (int c = v.first_chunk; c < v.first_chunk + v.num_chunks; ++c) {
+    const int begin = min(V, c * v.chunk_len), end = min(V, begin + v.chunk_len);
+    float t = 0.f;
+    range_for_each(v, V, begin, end, [&](int, float x) { t += f(x); });
+    t = block_sum(t, scratch33);
+    if (threadIdx.x == 0) g(c, t);
+  }
+}
+
+// The blocks of a row meet: what each has added to the row's scratch in global memory is seen by all behind it.
+__device__ __forceinline__ void row_meet() {  // (every thread releases what it wrote and acquires what the others did)
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // After the first pass: the index of the largest logit (lowest index among equals) and the largest scaled logit.
@@ -223,7 +259,8 @@ __device__ __forceinline__ void read_max(RowView& v) {
   v.mx = v.x[v.argmax] * v.inv_t;  // scaling by a positive number keeps the order
 }
 
-// Suffix sums over the 256 bins of a histogram (thread b = bin b, 256 threads): sum of bins >= b.
+// Suffix sums over the 256 bins of a histogram (thread b = bin b for the block's first 256 threads, the
+// others bring zero and get nothing of use back): sum of bins >= b.  Called by the whole block.
 template <typename T>
 __device__ T suffix_sum_256(T mine, T* scratch /* [8] */) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -234,7 +271,7 @@ __device__ T suffix_sum_256(T mine, T* scratch /* [8] */) {
     if (lane + o < 32) v += up;
   }
   __syncthreads();
-  if (lane == 0) scratch[warp] = v;  // the warp's total
+  if (lane == 0 && warp < 8) scratch[warp] = v;  // the warp's total
   __syncthreads();
   T above = 0;
   for (int w = warp + 1; w < 8; ++w) above += scratch[w];
@@ -244,18 +281,19 @@ __device__ T suffix_sum_256(T mine, T* scratch /* [8] */) {
 // The key of the k-th largest scaled logit after `digits` digits (the lower digits are zero), and how
 // many of the k lie among the keys that share them.  A pass knows the digits before it from the
 // record of the pass before, reads the last one off that pass's histogram (the largest digit with
-// at least k keys at or above it: one bin has suffix >= k > suffix of the next bin), and its block
-// 0 records the result for the passes behind it.
+// at least k keys at or above it: one bin has suffix >= k > suffix of the next bin), and the row's
+// first block records the result for the passes behind it.
 __device__ unsigned top_k_state(const RowView& v, int digits, int* k_left, int* iscratch, int* ishare) {
   if (digits == 0) { *k_left = v.k; return 0u; }
   const int q = digits - 1;
+  const bool bin = threadIdx.x < 256;
   const unsigned before = q ? __ldcg(&v.rs->k_prefix[q]) : 0u;
   const int k = q ? __ldcg(&v.rs->k_left[q]) : v.k;
-  const int mine = __ldcg(&v.rs->count[q][threadIdx.x]);
+  const int mine = bin ? __ldcg(&v.rs->count[q][threadIdx.x]) : 0;
   const int suffix = suffix_sum_256(mine, iscratch);
   if (threadIdx.x == 0) { ishare[0] = 0; ishare[1] = k; }
   __syncthreads();
-  if (suffix >= k && suffix - mine < k) { ishare[0] = threadIdx.x; ishare[1] = k - (suffix - mine); }
+  if (bin && suffix >= k && suffix - mine < k) { ishare[0] = threadIdx.x; ishare[1] = k - (suffix - mine); }
   __syncthreads();
   const unsigned key = before | ((unsigned)ishare[0] << (24 - 8 * q));
   *k_left = ishare[1];
@@ -271,13 +309,14 @@ __device__ unsigned top_p_state(const RowView& v, int digits, unsigned long long
                                 unsigned long long* lscratch, unsigned long long* lshare) {
   if (digits == 0) { *above_out = 0ull; return 0u; }
   const int q = digits - 1;
+  const bool bin = threadIdx.x < 256;
   const unsigned before = q ? __ldcg(&v.rs->p_prefix[q]) : 0u;
   const unsigned long long above = q ? __ldcg(&v.rs->p_above[q]) : 0ull;
-  const unsigned long long mine = __ldcg(&v.rs->mass[q][threadIdx.x]);
+  const unsigned long long mine = bin ? __ldcg(&v.rs->mass[q][threadIdx.x]) : 0ull;
   const unsigned long long suffix = suffix_sum_256(mine, lscratch);
   if (threadIdx.x == 0) { lshare[0] = 0; lshare[1] = 0; }
   __syncthreads();
-  if (above + suffix > tp_fixed && !(above + suffix - mine > tp_fixed)) { lshare[0] = threadIdx.x; lshare[1] = suffix - mine; }
+  if (bin && above + suffix > tp_fixed && !(above + suffix - mine > tp_fixed)) { lshare[0] = threadIdx.x; lshare[1] = suffix - mine; }
   __syncthreads();
   const unsigned cut = before | ((unsigned)lshare[0] << (24 - 8 * q));
   *above_out = above + lshare[1];
@@ -290,12 +329,8 @@ __device__ unsigned top_p_state(const RowView& v, int digits, unsigned long long
 __device__ __forceinline__ unsigned long long to_fixed(float p) { return __float2ull_rz(p * 4503599627370496.f); }
 static_assert(SP_FIXED_BITS == 52, "4503599627370496 = 2^52");
 
-// pass 0: the largest logit of every row and its index
-__global__ void __launch_bounds__(SP_THREADS) sample_max_kernel(const SampleArgs a) {
-  __shared__ unsigned long long warp_best[SP_THREADS / 32];
-  pdl_launch_dependents();
-  pdl_wait();
-  const RowView v = row_view(a);
+// the largest logit of the row and its index
+__device__ void pass_max(const SampleArgs& a, const RowView& v, SampleShared& sh) {
   unsigned long long mine = 0ull;
   chunk_for_each(v, a.V, [&](int i, float x) {
     const unsigned long long cand = ((unsigned long long)ordered_key(x) << 32) | (0xFFFFFFFFu - (unsigned)i);
@@ -306,88 +341,95 @@ __global__ void __launch_bounds__(SP_THREADS) sample_max_kernel(const SampleArgs
     const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
     mine = other > mine ? other : mine;
   }
-  if ((threadIdx.x & 31) == 0) warp_best[threadIdx.x >> 5] = mine;
+  if ((threadIdx.x & 31) == 0) sh.warp_best[threadIdx.x >> 5] = mine;
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int w = 1; w < SP_THREADS / 32; ++w) mine = warp_best[w] > mine ? warp_best[w] : mine;
+    for (int w = 1; w < SP_THREADS / 32; ++w) mine = sh.warp_best[w] > mine ? sh.warp_best[w] : mine;
     if (mine) atomicMax(&v.rs->best, mine);
   }
 }
 
 // top-k, digit `pass` (0: the top eight bits): how many keys that share the digits found so far have each next digit
-__global__ void __launch_bounds__(SP_THREADS) sample_count_kernel(const SampleArgs a, int pass) {
-  __shared__ int hist[256];
-  __shared__ int iscratch[8];
-  __shared__ int ishare[2];
-  pdl_launch_dependents();
-  pdl_wait();
-  RowView v = row_view(a);
-  if (!v.use_k) return;
+__device__ void pass_count(const SampleArgs& a, const RowView& v, int pass, SampleShared& sh) {
   int k_left;
-  const unsigned prefix = top_k_state(v, pass, &k_left, iscratch, ishare);
+  const unsigned prefix = top_k_state(v, pass, &k_left, sh.iscratch, sh.ishare);
   const int shift = 24 - 8 * pass;
-  hist[threadIdx.x] = 0;
+  if (threadIdx.x < 256) sh.ihist[threadIdx.x] = 0;
   __syncthreads();
   chunk_for_each(v, a.V, [&](int, float x) {
     const unsigned key = ordered_key(x * v.inv_t);
-    if (pass == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&hist[(key >> shift) & 255u], 1);
+    if (pass == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&sh.ihist[(key >> shift) & 255u], 1);
   });
   __syncthreads();
-  if (hist[threadIdx.x]) atomicAdd(&v.rs->count[pass][threadIdx.x], hist[threadIdx.x]);
+  if (threadIdx.x < 256 && sh.ihist[threadIdx.x]) atomicAdd(&v.rs->count[pass][threadIdx.x], sh.ihist[threadIdx.x]);
 }
 
 // the normaliser: sum of exp(s - max) over the tokens that top-k keeps, per chunk
-__global__ void __launch_bounds__(SP_THREADS) sample_z_kernel(const SampleArgs a) {
-  __shared__ float fs[33];
-  __shared__ int iscratch[8];
-  __shared__ int ishare[2];
-  pdl_launch_dependents();
-  pdl_wait();
-  RowView v = row_view(a);
-  if (v.greedy) return;
-  read_max(v);
+__device__ void pass_z(const SampleArgs& a, const RowView& v, SampleShared& sh) {
   int k_left;
-  const unsigned kth = v.use_k ? top_k_state(v, 4, &k_left, iscratch, ishare) : 0u;  // the last digit: found and recorded here
-  float z = 0.f;
-  chunk_for_each(v, a.V, [&](int, float x) {
-    const float s = x * v.inv_t;
-    z += ordered_key(s) >= kth ? expf(s - v.mx) : 0.f;
-  });
-  z = block_sum(z, fs);
-  if (threadIdx.x == 0) v.rs->z_part[blockIdx.x] = z;
+  const unsigned kth = v.use_k ? top_k_state(v, 4, &k_left, sh.iscratch, sh.ishare) : 0u;  // the last digit: found and recorded here
+  chunk_sums(v, a.V, sh.fs,
+             [&](float x) {
+               const float s = x * v.inv_t;
+               return ordered_key(s) >= kth ? expf(s - v.mx) : 0.f;
+             },
+             [&](int c, float z) { v.rs->z_part[c] = z; });
 }
 
-__device__ __forceinline__ float sum_parts(const float* parts, int chunks) {  // in chunk order, by every thread alike
+// The sum of a row's per-chunk parts, in chunk order, by every thread alike.  The parts come through shared
+// memory: one round trip to the L2 for all of them.
+__device__ __forceinline__ float sum_parts(const float* parts, float* staged) {
+  if (threadIdx.x < SP_MAX_CHUNKS) staged[threadIdx.x] = __ldcg(parts + threadIdx.x);
+  __syncthreads();
   float t = 0.f;
-  for (int c = 0; c < chunks; ++c) t += __ldcg(parts + c);
+#pragma unroll
+  for (int c = 0; c < SP_MAX_CHUNKS; ++c) t += staged[c];
+  __syncthreads();  // `staged` may be filled again
   return t;
 }
 
-// top-p, digit `pass`: the probability mass of every next digit among the probabilities that share the digits found
-__global__ void __launch_bounds__(SP_THREADS) sample_mass_kernel(const SampleArgs a, int pass) {
-  __shared__ unsigned long long hist[256];
-  __shared__ unsigned long long lscratch[8];
-  __shared__ unsigned long long lshare[2];
-  pdl_launch_dependents();
-  pdl_wait();
-  RowView v = row_view(a);
-  if (!v.use_p) return;
-  read_max(v);
+// top-p, digit `pass`: the probability mass of every next digit among the probabilities that share the digits found.
+// Atomics on one word of shared memory take turns, 64-bit ones by compare-and-swap, and the first digit of a
+// probability (a float's top eight bits: its sign and most of its exponent) falls into a handful of bins: with
+// one histogram per block that pass took 293 us at 64 rows where the others took 17.  So the first digit is
+// counted in SP_LANES private copies of the bins that can hold mass at all (a probability below 2^-52 is zero
+// in fixed point, which leaves the top eight bits 32 .. 63), a thread adding to the copy of its lane, where
+// it meets only threads of other warps; the copies are added up in a fixed order (the sums are integers).
+__device__ void pass_mass(const SampleArgs& a, const RowView& v, int pass, SampleShared& sh) {
   const unsigned kth = v.use_k ? __ldcg(&v.rs->k_prefix[4]) : 0u;
-  const float inv_z = 1.f / sum_parts(v.rs->z_part, a.chunks);
   unsigned long long above;
-  const unsigned prefix = top_p_state(v, pass, to_fixed(v.tp), &above, lscratch, lshare);
+  const unsigned prefix = top_p_state(v, pass, to_fixed(v.tp), &above, sh.lscratch, sh.lshare);
   const int shift = 24 - 8 * pass;
-  hist[threadIdx.x] = 0ull;
+  if (threadIdx.x < 256) sh.lhist[threadIdx.x] = 0ull;
+  if (pass == 0)
+    for (int i = threadIdx.x; i < 32 * SP_LANES; i += SP_THREADS) (&sh.lanes[0][0])[i] = 0ull;
   __syncthreads();
-  chunk_for_each(v, a.V, [&](int, float x) {
-    const float s = x * v.inv_t;
-    const float p = ordered_key(s) >= kth ? expf(s - v.mx) * inv_z : 0.f;
-    const unsigned bits = __float_as_uint(p);
-    if (p > 0.f && (pass == 0 || (bits >> (shift + 8)) == (prefix >> (shift + 8)))) atomicAdd(&hist[(bits >> shift) & 255u], to_fixed(p));
-  });
+  if (pass == 0) {
+    const int copy = threadIdx.x & (SP_LANES - 1);
+    chunk_for_each(v, a.V, [&](int, float x) {
+      const float s = x * v.inv_t;
+      const float p = ordered_key(s) >= kth ? expf(s - v.mx) * v.inv_z : 0.f;
+      const unsigned long long mass = to_fixed(p);
+      const unsigned digit = __float_as_uint(p) >> 24;  // 63 at most: p <= 1
+      if (mass) atomicAdd(&sh.lanes[digit & 31u][copy], mass);  // mass > 0: digit >= 32
+    });
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;  // warp w adds up the copies of bin 32 + w
+    unsigned long long t = sh.lanes[warp][lane] + sh.lanes[warp][lane + 32];
+    static_assert(SP_LANES == 64 && SP_THREADS == 1024, "one warp per bin, two copies per lane");
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) sh.lhist[32 + warp] = t;
+  } else {
+    chunk_for_each(v, a.V, [&](int, float x) {
+      const float s = x * v.inv_t;
+      const float p = ordered_key(s) >= kth ? expf(s - v.mx) * v.inv_z : 0.f;
+      const unsigned bits = __float_as_uint(p);
+      if (p > 0.f && (bits >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&sh.lhist[(bits >> shift) & 255u], to_fixed(p));
+    });
+  }
   __syncthreads();
-  if (hist[threadIdx.x]) atomicAdd(&v.rs->mass[pass][threadIdx.x], hist[threadIdx.x]);
+  if (threadIdx.x < 256 && sh.lhist[threadIdx.x]) atomicAdd(&v.rs->mass[pass][threadIdx.x], sh.lhist[threadIdx.x]);
 }
 
 // The probability a token keeps after all filters (0: dropped).
@@ -401,15 +443,14 @@ struct Filter {
   }
 };
 
-// `recorded`: the last digit of the top-p cut has been worked out by an earlier launch
-__device__ Filter make_filter(RowView& v, const SampleArgs& a, bool recorded, unsigned long long* lscratch, unsigned long long* lshare) {
+// `recorded`: the last digit of the top-p cut has been worked out by an earlier pass
+__device__ Filter make_filter(const RowView& v, bool recorded, SampleShared& sh) {
   Filter f;
-  read_max(v);
   f.kth = v.use_k ? __ldcg(&v.rs->k_prefix[4]) : 0u;
-  f.inv_z = 1.f / sum_parts(v.rs->z_part, a.chunks);
+  f.inv_z = v.inv_z;
   unsigned long long above;
   // keep a token iff the mass of strictly larger probabilities is <= top_p: bits >= the largest v with mass(bits >= v) > top_p
-  f.cut = !v.use_p ? 0u : recorded ? __ldcg(&v.rs->p_prefix[4]) : top_p_state(v, 4, to_fixed(v.tp), &above, lscratch, lshare);
+  f.cut = !v.use_p ? 0u : recorded ? __ldcg(&v.rs->p_prefix[4]) : top_p_state(v, 4, to_fixed(v.tp), &above, sh.lscratch, sh.lshare);
   f.floor_p = v.mp > 0.f ? v.mp * f.inv_z : 0.f;  // min-p relative to the largest probability, exp(0) / z
   f.inv_t = v.inv_t;
   f.mx = v.mx;
@@ -417,42 +458,24 @@ __device__ Filter make_filter(RowView& v, const SampleArgs& a, bool recorded, un
 }
 
 // the mass that survives all filters, per chunk
-__global__ void __launch_bounds__(SP_THREADS) sample_kept_kernel(const SampleArgs a) {
-  __shared__ float fs[33];
-  __shared__ unsigned long long lscratch[8];
-  __shared__ unsigned long long lshare[2];
-  pdl_launch_dependents();
-  pdl_wait();
-  RowView v = row_view(a);
-  if (v.greedy) return;
-  const Filter f = make_filter(v, a, false, lscratch, lshare);
-  float m = 0.f;
-  chunk_for_each(v, a.V, [&](int, float x) { m += f.kept(x); });
-  m = block_sum(m, fs);
-  if (threadIdx.x == 0) v.rs->kept_part[blockIdx.x] = m;
+__device__ void pass_kept(const SampleArgs& a, const RowView& v, SampleShared& sh) {
+  const Filter f = make_filter(v, false, sh);
+  chunk_sums(v, a.V, sh.fs, [&](float x) { return f.kept(x); }, [&](int c, float m) { v.rs->kept_part[c] = m; });
 }
 
 // the draw: inverse CDF in vocabulary order at u * total; the block whose chunk holds that point picks the token
-__global__ void __launch_bounds__(SP_THREADS) sample_pick_kernel(const SampleArgs a) {
-  __shared__ float prefix[SP_THREADS];
-  __shared__ int ishare[2];
-  __shared__ int chosen;
-  pdl_launch_dependents();
-  pdl_wait();
-  RowView v = row_view(a);
+__device__ void pass_pick(const SampleArgs& a, const RowView& v, SampleShared& sh) {
   const int r = blockIdx.y, tid = threadIdx.x;
-  if (v.greedy) {
-    if (blockIdx.x == 0 && tid == 0) { read_max(v); a.out[r] = v.argmax; }
-    return;
-  }
   // which chunk holds the target (every block finds the same answer); `last`: the last chunk with any mass
+  if (tid < SP_MAX_CHUNKS) sh.parts[tid] = __ldcg(v.rs->kept_part + tid);
+  __syncthreads();
   float total = 0.f;
-  for (int c = 0; c < a.chunks; ++c) total += __ldcg(v.rs->kept_part + c);
+  for (int c = 0; c < SP_MAX_CHUNKS; ++c) total += sh.parts[c];
   const float target = a.uniform[r] * total;
   int mine = -1, last = -1;
   float before = 0.f, run = 0.f;
-  for (int c = 0; c < a.chunks; ++c) {
-    const float m = __ldcg(v.rs->kept_part + c);
+  for (int c = 0; c < SP_MAX_CHUNKS; ++c) {
+    const float m = sh.parts[c];
     if (m > 0.f) {
       last = c;
       if (mine < 0 && target < run + m) { mine = c; before = run; }
@@ -461,13 +484,15 @@ __global__ void __launch_bounds__(SP_THREADS) sample_pick_kernel(const SampleArg
   }
   const bool past_end = mine < 0;  // rounding pushed the target past the end: the last kept token
   if (past_end) mine = last;
-  if ((int)blockIdx.x != mine) return;
-  const Filter f = make_filter(v, a, true, nullptr, nullptr);
+  if (mine < v.first_chunk || mine >= v.first_chunk + v.num_chunks) return;
+  const Filter f = make_filter(v, true, sh);
   // thread t owns the contiguous piece [b, e) of the chunk
-  const int len = v.end - v.begin, piece = (len + SP_THREADS - 1) / SP_THREADS;
-  const int b = min(v.end, v.begin + tid * piece), e = min(v.end, b + piece);
+  const int c_begin = min(a.V, mine * v.chunk_len), c_end = min(a.V, c_begin + v.chunk_len);
+  const int len = c_end - c_begin, piece = (len + SP_THREADS - 1) / SP_THREADS;
+  const int b = min(c_end, c_begin + tid * piece), e = min(c_end, b + piece);
   float sum = 0.f;
   for (int i = b; i < e; ++i) sum += f.kept(v.x[i]);
+  float* prefix = sh.prefix;
   prefix[tid] = sum;
   __syncthreads();
   for (int o = 1; o < SP_THREADS; o <<= 1) {  // inclusive scan over the thread sums
@@ -476,7 +501,7 @@ __global__ void __launch_bounds__(SP_THREADS) sample_pick_kernel(const SampleArg
     prefix[tid] += add;
     __syncthreads();
   }
-  if (tid == 0) chosen = a.V;
+  if (tid == 0) sh.chosen = a.V;
   __syncthreads();
   const float start = before + (tid > 0 ? prefix[tid - 1] : 0.f);
   if (!past_end && sum > 0.f && start <= target && target < before + prefix[tid]) {
@@ -490,20 +515,55 @@ __global__ void __launch_bounds__(SP_THREADS) sample_pick_kernel(const SampleArg
         if (c > target) { pick = i; break; }
       }
     }
-    atomicMin(&chosen, pick >= 0 ? pick : seen);
+    atomicMin(&sh.chosen, pick >= 0 ? pick : seen);
   }
   __syncthreads();
-  if (chosen == a.V) {  // no thread's interval took the target (rounding): the last kept token of the chunk
+  if (sh.chosen == a.V) {  // no thread's interval took the target (rounding): the last kept token of the chunk
     int seen = -1;
     for (int i = b; i < e; ++i) if (f.kept(v.x[i]) > 0.f) seen = i;
-    if (tid == 0) ishare[0] = -1;
+    if (tid == 0) sh.ishare[0] = -1;
     __syncthreads();
-    if (seen >= 0) atomicMax(&ishare[0], seen);
+    if (seen >= 0) atomicMax(&sh.ishare[0], seen);
     __syncthreads();
-    if (tid == 0) chosen = ishare[0] >= 0 ? ishare[0] : v.argmax;
+    if (tid == 0) sh.chosen = sh.ishare[0] >= 0 ? sh.ishare[0] : v.argmax;
     __syncthreads();
   }
-  if (tid == 0) a.out[r] = chosen;
+  if (tid == 0) a.out[r] = sh.chosen;
+}
+
+// One row per cluster: the passes follow one another in one launch, the row's blocks meeting in between
+// (as separate launches, twelve of them with every filter on, each cost 10 to 17 us of which the walk
+// over the logits was the least part).  A row skips the passes of the filters it does not use.  The
+// cluster's size is the launch's (gridDim.x: 8 blocks a row for few rows, fewer for many, so that all
+// rows are resident at once).
+__global__ void __launch_bounds__(SP_THREADS, 1) sample_kernel(const SampleArgs a) {
+  __shared__ SampleShared sh;
+  pdl_launch_dependents();
+  pdl_wait();
+  RowView v = row_view(a);
+  pass_max(a, v, sh);
+  row_meet();
+  read_max(v);
+  if (v.greedy) {  // (the whole row, and so the whole cluster)
+    if (blockIdx.x == 0 && threadIdx.x == 0) a.out[blockIdx.y] = v.argmax;
+    return;
+  }
+  if (v.use_k)
+    for (int pass = 0; pass < 4; ++pass) {
+      pass_count(a, v, pass, sh);
+      row_meet();
+    }
+  pass_z(a, v, sh);
+  row_meet();
+  v.inv_z = 1.f / sum_parts(v.rs->z_part, sh.parts);
+  if (v.use_p)
+    for (int pass = 0; pass < 4; ++pass) {
+      pass_mass(a, v, pass, sh);
+      row_meet();
+    }
+  pass_kept(a, v, sh);
+  row_meet();
+  pass_pick(a, v, sh);
 }
 
 }  // namespace tb
@@ -529,28 +589,53 @@ int tb_argmax_split(void* stream, const float* logits, int* out, void* best, int
 // Bytes of scratch a row needs; the scratch [R rows] must be zero when tb_sample is called.
 int tb_sample_scratch_bytes() { return (int)sizeof(tb::RowScratch); }
 
-// One token per row.  top_k_any / top_p_any: whether any row uses that filter (its passes are skipped otherwise).
+// One token per row.  top_k_any / top_p_any: whether any row uses that filter; kept for callers, since every
+// row skips the passes of the filters it does not use by itself.
 int tb_sample(void* stream, const float* logits, const float* temperature, const int* top_k, const float* top_p,
               const float* min_p, const float* uniform, void* scratch, int* out, int R, int V, int top_k_any, int top_p_any) {
+  (void)top_k_any; (void)top_p_any;
   if (R <= 0) return 0;
   if (V <= 0 || R > 65535) return TB_ERR_BAD_SIZE;
   tb::SampleArgs a;
   a.logits = logits; a.temperature = temperature; a.top_k = top_k; a.top_p = top_p; a.min_p = min_p; a.uniform = uniform;
   a.scratch = static_cast<tb::RowScratch*>(scratch); a.out = out; a.V = V;
-  // chunks of at least 2,048 logits, and about four blocks per SM over all rows
-  int chunks = (592 + R - 1) / R;
-  if (chunks > V / 2048) chunks = V / 2048;
-  a.chunks = chunks < 1 ? 1 : (chunks > tb::SP_MAX_CHUNKS ? tb::SP_MAX_CHUNKS : chunks);
-  const dim3 grid(a.chunks, R), block(tb::SP_THREADS);
-  int e = tb::launch(tb::sample_max_kernel, grid, block, 0, stream, a);
-  if (top_k_any)
-    for (int pass = 0; pass < 4 && !e; ++pass) e = tb::launch(tb::sample_count_kernel, grid, block, 0, stream, a, pass);
-  if (!e) e = tb::launch(tb::sample_z_kernel, grid, block, 0, stream, a);
-  if (top_p_any)
-    for (int pass = 0; pass < 4 && !e; ++pass) e = tb::launch(tb::sample_mass_kernel, grid, block, 0, stream, a, pass);
-  if (!e) e = tb::launch(tb::sample_kept_kernel, grid, block, 0, stream, a);
-  if (!e) e = tb::launch(tb::sample_pick_kernel, grid, block, 0, stream, a);
-  return e;
+  // A block of 1,024 threads has an SM to itself, and a cluster's blocks must find their SMs in one GPC: the most
+  // blocks per row with which all rows are resident at once (asked of the driver once per device and size).
+  static int resident[64][4] = {};  // clusters of 8, 4, 2, 1 blocks that can run at a time
+  int device = 0;
+  cudaError_t ce = cudaGetDevice(&device);
+  if (ce != cudaSuccess) return (int)ce;
+  if (device < 0 || device >= 64) return TB_ERR_BAD_SIZE;
+  a.cluster = 1;
+  for (int i = 0, size = tb::SP_MAX_CHUNKS; size > 1; ++i, size >>= 1) {
+    if (!resident[device][i]) {
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(size, 1024);
+      q.blockDim = dim3(tb::SP_THREADS);
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = size; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.attrs = qa;
+      q.numAttrs = 1;
+      int n = 0;
+      ce = cudaOccupancyMaxActiveClusters(&n, tb::sample_kernel, &q);
+      if (ce != cudaSuccess) return (int)ce;
+      resident[device][i] = n > 0 ? n : -1;
+    }
+    if (resident[device][i] >= R) { a.cluster = size; break; }
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a.cluster, R);
+  cfg.blockDim = dim3(tb::SP_THREADS);
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = tb::pdl_enabled() ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = a.cluster; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return (int)cudaLaunchKernelEx(&cfg, tb::sample_kernel, a);
 }
 
 // ---------------------------------------------------------------------------------------------

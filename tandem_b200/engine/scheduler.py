@@ -150,6 +150,9 @@ class Scheduler:
         return True
 
     def _preempt(self, req: Request) -> None:
+        if req.has_pending_token:  # its token would arrive for a request that has started over
+            raise RuntimeError(f"request {req.request_id!r} would be preempted with a token in flight "
+                               "(the engine reads the step in flight first when may_preempt() says so)")
         self.running.remove(req)
         self._give_back(req)
         req.num_computed_tokens = 0
@@ -177,11 +180,20 @@ class Scheduler:
         return req.has_pending_token and self._length_reached(req, req.num_output_tokens, req.num_tokens)
 
     def may_preempt(self) -> bool:
-        """Could the next ``schedule`` run short of pages for a running request?  Each may need one
-        more page, and prompt portions at most a budget's worth.  The engine then reads the step in
-        flight first, so that no request with a placeholder is ever preempted."""
-        need = len(self.running) + -(-self.max_num_batched_tokens // self.cache.page_size) + 1
-        return any(self.cache.free_pages(g) < need for g in range(len(self.cache.groups)))
+        """Could the next ``schedule`` run short of pages for a running request?  Only running
+        requests are ever given pages at another's cost (admission waits instead), so what is
+        counted is what they can ask for: each the pages for its lacking tokens, a budget's worth at
+        most, beyond the pages it holds, group by group.  The engine then reads the step in flight
+        first, so that no request with a placeholder is ever preempted.  A pool that is nearly full of
+        decoding requests, the steady state under load, says no here except on the steps in which
+        some request begins a page that the pool no longer has."""
+        want = [0] * len(self.cache.groups)
+        for req in self.running:
+            share = min(req.tokens_lacking, self.max_num_batched_tokens)
+            if share > 0:
+                for g, n in enumerate(self.cache.pages_to_grow(req.request_id, req.num_computed_tokens + share)):
+                    want[g] += max(0, n)
+        return any(n > self.cache.free_pages(g) for g, n in enumerate(want))
 
     # ------------------------------------------------------------------ a step's outcome
     def book_launch(self, plan: StepPlan) -> None:

@@ -280,6 +280,32 @@ def bench_tokenwise(args) -> None:
     print(f"argmax      R={logits.shape[0]} V=151936  {us:8.1f} us  {logits.numel() * 4 / us / 1e3:7.0f} GB/s")
 
 
+def bench_sampling(args) -> None:
+    """From logits [rows, vocabulary] to tokens: argmax and the filters of temperature sampling, one by one
+    and together, against one pass over the logits at memory speed."""
+    from tandem_b200.kernels import ops
+
+    R, V = args.rows, args.vocab
+    logits = [torch.randn(R, V, device="cuda") * 3 for _ in range(copies_for(R * V * 4))]
+    u = torch.rand(R, device="cuda")
+
+    def opts(temperature=1.0, top_k=0, top_p=1.0, min_p=0.0):
+        f = lambda v: torch.full((R,), v, device="cuda", dtype=torch.float32)
+        return f(temperature), torch.full((R,), top_k, device="cuda", dtype=torch.int32), f(top_p), f(min_p)
+
+    cases = [("argmax", None), ("temperature 0.8", opts(0.8)), ("top_k 50", opts(0.8, top_k=50)), ("top_p 0.9", opts(0.8, top_p=0.9)),
+             ("min_p 0.05", opts(0.8, min_p=0.05)), ("top_k 50, top_p 0.9, min_p 0.05", opts(0.8, 50, 0.9, 0.05))]
+    for name, o in cases:
+        if o is None:
+            us = time_calls(lambda i: ops.argmax(logits[i % len(logits)]), args.iters, args.graph)
+        else:
+            t, k, tp, mp = o
+            any_k, any_p = bool(k[0] > 0), bool(tp[0] < 1)
+            us = time_calls(lambda i: ops.sample(logits[i % len(logits)], t, k, tp, mp, u, any_top_k=any_k, any_top_p=any_p),
+                            args.iters, args.graph)
+        print(f"sampling R={R} V={V}  {name:32s} {us:8.1f} us  ({R * V * 4 / us / 1e3:6.0f} GB/s if it were one pass)")
+
+
 def main(argv=None) -> None:
     p = argparse.ArgumentParser(prog="python -m tandem_b200.kernels.microbench")
     sub = p.add_subparsers(dest="case", required=True)
@@ -319,6 +345,10 @@ def main(argv=None) -> None:
     t.add_argument("--hidden", type=int, default=4096)
     t.add_argument("--intermediate", type=int, default=12288)
     t.set_defaults(fn=bench_tokenwise)
+    sa = sub.add_parser("sampling", parents=[common])
+    sa.add_argument("--rows", type=int, default=64)
+    sa.add_argument("--vocab", type=int, default=151936)
+    sa.set_defaults(fn=bench_sampling)
     dp = sub.add_parser("dispatch", parents=[common])
     dp.add_argument("--shapes", choices=sorted(LAYER_SHAPES), default="8b")
     dp.add_argument("--many-rows", action="store_true", help="also the pair kernel against the library at 96 to 8,192 rows, every product")

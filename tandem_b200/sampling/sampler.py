@@ -4,7 +4,7 @@ The rules are 12vivi/tandem's (python/tandem/layers/sampler.py:19-64): a request
 its temperature is below 1e-5; otherwise logits / temperature, keep the top_k largest, softmax,
 keep the smallest head of the sorted distribution whose preceding mass exceeds top_p nowhere,
 drop what is below min_p times the largest probability, renormalise, draw.  All of it runs in
-a few small CUDA kernels per step, many blocks per row (``tandem_b200/csrc/sampling.cu``); the draw is the inverse CDF at a
+one CUDA kernel per step, a cluster of blocks per row (``tandem_b200/csrc/sampling.cu``); the draw is the inverse CDF at a
 uniform number that depends only on the request's seed and the index of the token, so it does
 not depend on the batch (``tandem_b200.sampling.rng``).
 """

@@ -658,6 +658,27 @@ def test_sample_matches_the_plain_sampler(ops, V):
                 assert p[got[i]] > 0 and lo - 1e-5 <= target <= float(cum[got[i]]) + 1e-5, (i, trial, got[i], want)
 
 
+@pytest.mark.parametrize("V", [151936, 1003])
+def test_sample_does_not_depend_on_the_number_of_rows(ops, V):
+    """A row's blocks share eight chunks of the vocabulary however many they are (eight blocks a row for
+    few rows, fewer for many): floating-point sums are taken per chunk, so the token of a row is the
+    same alone, among 20 rows, among 70 and among 200."""
+    g = torch.Generator().manual_seed(31)
+    R = 200
+    logits = dev(torch.randn(R, V, generator=g) * 3)
+    t = dev(0.5 + torch.rand(R, generator=g))
+    k = dev(torch.where(torch.rand(R, generator=g) < 0.5, torch.randint(1, 100, (R,), generator=g), torch.full((R,), -1)).to(torch.int32))
+    p = dev(torch.where(torch.rand(R, generator=g) < 0.5, 0.5 + 0.5 * torch.rand(R, generator=g), torch.ones(R)))
+    m = dev(torch.where(torch.rand(R, generator=g) < 0.3, 0.1 * torch.rand(R, generator=g), torch.zeros(R)))
+    u = dev(torch.rand(R, generator=g))
+    whole = ops.sample(logits, t, k, p, m, u)
+    assert torch.equal(whole, ops.sample(logits, t, k, p, m, u))
+    for n in (1, 20, 70):
+        part = ops.sample(logits[:n].contiguous(), t[:n].contiguous(), k[:n].contiguous(), p[:n].contiguous(), m[:n].contiguous(),
+                          u[:n].contiguous())
+        assert torch.equal(part, whole[:n]), n
+
+
 def test_sample_keeps_only_filtered_tokens_and_follows_u(ops):
     V = 4
     logits = torch.log(torch.tensor([[0.5, 0.3, 0.15, 0.05]])).repeat(6, 1)

@@ -204,9 +204,26 @@ def test_overlap_drops_the_token_launched_after_an_end_token():
 
 
 def test_overlap_resolves_first_when_pages_are_short():
-    s, _ = make(pages=2, page_size=4, budget=8)
-    assert s.may_preempt()  # fewer free pages than a budget's worth: the engine reads the step in flight before it schedules
+    """The step in flight is read first only when a running request may have to give way: when the
+    running requests' next shares need more pages than are free.  An empty line, a full pool whose
+    requests still have room in their last pages, and waiting requests (which wait, and take
+    nobody's pages) do not count."""
+    s, cache = make(pages=4, page_size=4, budget=16)
+    assert not s.may_preempt()  # nobody is running
+    a, b = req("a", 6, max_tokens=8), req("b", 5, max_tokens=8)
+    s.add_request(a)
+    s.add_request(b)
+    p0 = overlap_step(s, None, {})  # both prompts: 2 pages each, the pool is full
+    assert sizes(p0) == [("a", 6), ("b", 5)] and cache.free_pages(0) == 0
+    s.add_request(req("c", 3, max_tokens=2))  # waits; it can take nobody's pages
+    assert not s.may_preempt()  # tokens 7 and 6 fit into the pages held
+    p1 = overlap_step(s, p0, {"a": 11, "b": 21})
+    assert sizes(p1) == [("a", 1), ("b", 1)] and not s.may_preempt()  # a's 8th token still fits
+    p2 = overlap_step(s, p1, {"a": 12, "b": 22})
+    assert s.may_preempt()  # a's 9th token begins a page and none is free
     s2, _ = make(pages=64, page_size=4, budget=8)
+    s2.add_request(req("a", 6, max_tokens=8))
+    overlap_step(s2, None, {})
     assert not s2.may_preempt()
 
 
