@@ -45,9 +45,14 @@ SKINNY_MIN_WEIGHT_BYTES = {1: 200 << 20, 2: 200 << 20, 4: 400 << 20, 8: 400 << 2
 # block pairs (256-row tiles) is the fastest by 2 to 10 % (measured at the gate_up sizes of
 # Qwen3-8B, -14B and -32B, 192 to 8,192 rows) unless its last tile of 256 rows is less than half
 # full and the rows are few (384 rows: 75 against 67 us).  Else the single-block kernel where one
-# wave of its 128-row tiles is full (up to 128 rows) or the waves are many (from 1536 rows); in
+# wave of its 128-row tiles is full (64 to 128 rows) or the waves are many (from 1536 rows); in
 # between the library's tilings followed by the activation kernel are 5 to 10 % faster.
-WIDE_GATED_ROWS = ((65, 128), (1536, None))
+WIDE_GATED_ROWS = ((64, 128), (1536, None))
+# Below that the single-block kernel is a weight stream with the activation thrown in (one tile of 128 rows,
+# mostly empty): it beats the library's product followed by the activation kernel where the weights are
+# large (Qwen3-14B gate_up, 340 MiB: 60 against 62 to 67 us at 16 to 64 rows; Qwen3-32B, 500 MiB: 86 to 88
+# against 93 to 97) and loses where they are small (Qwen3-8B, 192 MiB: 39 against 36 to 38 us up to 56 rows).
+WIDE_GATED_FEW_ROWS_MIN_WEIGHT_BYTES = 300 << 20
 PAIR_GATED_MIN_ROWS = 192
 PAIR_MAX_PADDING = 1.08  # rows the pair kernel computes (whole tiles of 256) over those the single-block kernel does (of 128)
 _mm_out_dtype = True  # torch.mm(..., out_dtype=) is tried once
@@ -266,8 +271,10 @@ def choose_gated(M: int, N: int, K: int, aligned: bool = True) -> str:
     if N % 16:
         return "product"
     forced = os.environ.get("TANDEM_GEMM")
-    if M <= GEMV_MAX_ROWS:
-        return "gemv" if choose(M, N, K, aligned) == "gemv" else "product"
+    if M <= GEMV_MAX_ROWS and choose(M, N, K, aligned) == "gemv":
+        return "gemv"
+    if M <= GEMV_ROWS_ANY_K:
+        return "product"
     if forced in ("wide", "pair"):
         return forced if wide_applies(M, N, K) and aligned else "product"
     if forced in ("library", "skinny", "gemv"):
@@ -277,6 +284,8 @@ def choose_gated(M: int, N: int, K: int, aligned: bool = True) -> str:
     if M >= PAIR_GATED_MIN_ROWS and -(-M // 256) * 256 <= PAIR_MAX_PADDING * (-(-M // 128) * 128):
         return "pair"
     in_range = any(lo <= M and (hi is None or M <= hi) for lo, hi in WIDE_GATED_ROWS)
+    if M < WIDE_GATED_ROWS[0][0] and N * K * 2 >= WIDE_GATED_FEW_ROWS_MIN_WEIGHT_BYTES:
+        in_range = True
     return "wide" if in_range else "product"
 
 

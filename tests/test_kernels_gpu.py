@@ -770,7 +770,7 @@ def test_gemm_wide(ops, M, N, K, out, impl):
     ops.check_status("cuda")
 
 
-@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 264, 200), (2048, 1536, 4096), (3, 8, 16)])
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (300, 264, 200), (2048, 1536, 4096), (3, 8, 16), (17, 17408, 5120), (40, 1000, 520)])
 @pytest.mark.parametrize("impl", ["wide", "wide_pair"])
 def test_gemm_wide_gated(ops, M, I, K, impl):
     """Rows [gate | up] of the weight in one launch: silu(x gate^T) * (x up^T), both products rounded
