@@ -14,7 +14,6 @@ Both plans are cut on the host and travel to the device with the batch descripti
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Optional
 
 import torch
@@ -93,7 +92,7 @@ def plan_decode(rows, window: Optional[int], num_kv_heads: int, target_blocks: i
 
 
 def prefill_library(head_dim: int):
-    extra = tuple(d for d in os.environ.get("TANDEM_PREFILL_DEFS", "").split(",") if d)
+    extra = tuple(d for d in ops.env("TANDEM_PREFILL_DEFS", "").split(",") if d)
     return load_library("attention_prefill", (f"TB_HD={head_dim}",) + extra)
 
 
@@ -101,7 +100,7 @@ def tcgen05_prefill_applies(head_dim: int, page_size: int) -> bool:
     """The tcgen05 prefill kernel takes head sizes 64 and 128 and pages of 8 keys or a multiple of 16
     (``TANDEM_PREFILL=mma`` keeps the mma.sync kernel)."""
     return (head_dim in (64, 128) and (page_size == 8 or page_size % 16 == 0)
-            and os.environ.get("TANDEM_PREFILL", "tcgen05") != "mma")
+            and ops.env("TANDEM_PREFILL", "tcgen05") != "mma")
 
 
 def plan_prefill(seqs, groups: int, tile_rows: int = TILE_ROWS) -> list:
@@ -178,7 +177,7 @@ def _workspace(device, items: int, num_kv_heads: int, groups: int, head_dim: int
     """Scratch of the decode kernel, kept and grown per device: partial outputs, their (max, sum)
     and arrival counters (zero between launches).  A scratch that was outgrown is kept, not freed:
     CUDA graphs captured while it was current still write to it when they are replayed."""
-    key = str(device)
+    key = ops.device_key(device)
     rows = items * num_kv_heads * groups
     ws = _workspaces.get(key)
     if ws is None or ws["rows"] < rows or ws["hd"] < head_dim:
@@ -208,7 +207,7 @@ def fresh_applies(head_dim: int, rotary_dim: int, writable: bool, num_tokens: in
     48 and 64 tokens, and 5.99 against 5.06 ms at 32, where the kernel in front is then a library
     product whose blocks do not all fit at once and the attention blocks that move in early take their room."""
     return (writable and rotary_dim == head_dim and head_dim & (head_dim - 1) == 0 and 16 <= head_dim <= 256
-            and (num_tokens <= FRESH_MAX_TOKENS or streamed) and os.environ.get("TANDEM_FRESH_ATTENTION", "1") != "0")
+            and (num_tokens <= FRESH_MAX_TOKENS or streamed) and ops.env("TANDEM_FRESH_ATTENTION", "1") != "0")
 
 
 def paged_attention_decode(qkv: torch.Tensor, kv, items: torch.Tensor, count: torch.Tensor, num_heads: int,

@@ -25,7 +25,6 @@ prints the table's lines and what the rule would have picked.
 from __future__ import annotations
 
 import ctypes
-import os
 
 import torch
 
@@ -71,7 +70,7 @@ def _library(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> t
 
 
 def sm_count(device) -> int:
-    key = str(device)
+    key = ops.device_key(device)
     if key not in _sm_count:
         _sm_count[key] = torch.cuda.get_device_properties(device).multi_processor_count
     return _sm_count[key]
@@ -80,7 +79,7 @@ def sm_count(device) -> int:
 def skinny_scratch(device):
     """Scratch of the skinny kernel, once per device: float32 partials of tiles whose K range is
     shared between blocks, and the tiles' arrival counters (zero between launches)."""
-    key = ("scratch", str(device))
+    key = ("scratch", ops.device_key(device))
     if key not in _sm_count:
         _sm_count[key] = (torch.empty(sm_count(device) * 2 * SKINNY_MAX_ROWS * 128, dtype=torch.float32, device=device),
                           torch.zeros(1 << 16, dtype=torch.int32, device=device))
@@ -195,7 +194,7 @@ def gemv_add(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, norm
 
 def add_fusable(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """A product that the streaming kernel runs, and so may add into the residual itself."""
-    if os.environ.get("TANDEM_FUSE_NORM", "1") == "0":
+    if ops.env("TANDEM_FUSE_NORM", "1") == "0":
         return False
     return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
             and choose(x.shape[0], weight.shape[0], x.shape[1], _aligned(x, weight)) == "gemv")
@@ -251,7 +250,7 @@ def choose(M: int, N: int, K: int, aligned: bool = True) -> str:
     run.  ``aligned``: x and the weight are contiguous and start on 16-byte boundaries."""
     can_gemv = gemv_applies(M, N, K) and aligned
     can_skinny = skinny_applies(M, N, K) and aligned
-    forced = os.environ.get("TANDEM_GEMM")
+    forced = ops.env("TANDEM_GEMM")
     if forced == "library" or (forced == "gemv" and can_gemv) or (forced == "skinny" and can_skinny):
         return forced
     measured = MEASURED.get((N, K), {}).get(row_class(M))
@@ -270,7 +269,7 @@ def choose_gated(M: int, N: int, K: int, aligned: bool = True) -> str:
     or single blocks), or "product" (the product as ``choose`` says, then the activation kernel)."""
     if N % 16:
         return "product"
-    forced = os.environ.get("TANDEM_GEMM")
+    forced = ops.env("TANDEM_GEMM")
     if M <= GEMV_MAX_ROWS and choose(M, N, K, aligned) == "gemv":
         return "gemv"
     if M <= GEMV_ROWS_ANY_K:

@@ -9,6 +9,7 @@ library that cannot be built, raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -33,8 +34,45 @@ def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current CUDA stream's handle.  Through torch's C entry points where it has them: the Python
+    wrappers around the same question took a fifth of the host's time in a step that is not replayed
+    from a CUDA graph (15 us a launch)."""
+    if _raw_stream is not None and _raw_device is not None:
+        return ctypes.c_void_p(_raw_stream(_raw_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_environ_bytes = getattr(os.environ, "_data", None)  # the mapping behind os.environ, keyed by encoded names (POSIX)
+_encoded_names: dict = {}
+
+
+def env(name: str, default: Optional[str] = None) -> Optional[str]:
+    """``os.environ.get(name, default)``, read afresh at every call (tests and users change these
+    switches while a process runs) but without encoding the name each time: the switches are asked
+    for some fifteen times a layer."""
+    if type(_environ_bytes) is not dict:
+        return os.environ.get(name, default)
+    key = _encoded_names.get(name)
+    if key is None:
+        key = _encoded_names[name] = os.fsencode(name)
+    value = _environ_bytes.get(key)
+    return default if value is None else os.fsdecode(value)
+
+
+def device_key(device) -> str:
+    """A dictionary key for per-device caches; ``str(torch.device)`` costs 2 us, so it is taken once per device object."""
+    key = _device_keys.get(device)
+    if key is None:
+        key = _device_keys[device] = str(device)
+    return key
+
+
+_device_keys: dict = {}
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
@@ -63,7 +101,7 @@ _status: dict = {}
 def status_word(device) -> torch.Tensor:
     """int32 [1] on the device where kernels record a fault they survived (0: none): a bounded
     wait that gave up (1), a block table entry that should have held a page (2)."""
-    key = str(device)
+    key = device_key(device)
     if key not in _status:
         with torch.inference_mode(False):  # an ordinary tensor: it is written in and outside inference mode
             _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
@@ -324,7 +362,7 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     if chunks < 2 or R > _ARGMAX_ROWS:
         _check(lib.tb_argmax(_stream(), _ptr(logits), _ptr(out), R, V), "argmax")
         return out
-    key = str(logits.device)
+    key = device_key(logits.device)
     if key not in _argmax_scratch:  # zero before and after every call: the kernel cleans up after itself
         _argmax_scratch[key] = (torch.zeros(_ARGMAX_ROWS, dtype=torch.int64, device=logits.device),
                                 torch.zeros(_ARGMAX_ROWS, dtype=torch.int32, device=logits.device))
@@ -353,7 +391,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     lib = load_library("sampling")
     per_row = lib.tb_sample_scratch_bytes()
-    key = str(logits.device)
+    key = device_key(logits.device)
     scratch = _sample_scratch.get(key)
     if scratch is None or scratch.numel() < R * per_row:  # histograms and partial sums of the rows, kept per device
         scratch = _sample_scratch[key] = torch.empty(max(R, 64) * per_row, dtype=torch.uint8, device=logits.device)
