@@ -1,4 +1,4 @@
-"""CUDA graphs for decode-only steps.
+"""CUDA graphs for decode-only steps, and for short steps that bring prompt portions.
 
 A step in which every request brings exactly one token launches a few hundred small kernels; at
 small batches their launch cost exceeds their run time.  Such steps are captured once per batch
@@ -18,17 +18,28 @@ per-request state indexes its state tensor by ``ctx.state_slots`` on the device;
 point at the state tensor's last row, which belongs to no request.  Mixers that asked for per-step
 arrays (``step_arrays``) say how large they can get for a bucket through
 ``step_array_capacity(bucket, max_model_len, page_size, out)``.
+
+A step that is not replayed costs the host some 15 us per kernel it launches, 4.7 ms for the 36 layers
+of Qwen3-8B, while the device needs 3.3 ms for a step of up to a few hundred tokens (it streams the
+weights once): the first portion of a short prompt, or a few decoded tokens beside one, would wait for
+the host.  So steps of up to ``MIXED_MAX_TOKENS`` tokens are captured as well, per bucket of tokens
+(8, 16, 32, 64, 128, 256) for up to as many requests as the decode graphs take: token rows beyond the
+step's are padding (token 0, no cache slot, in no attention item), the attention plan keeps the layout
+of its capacity (``StepContext.static_layout``), and both attention kernels run in every replay, one of
+them perhaps with nothing to do.  This needs mixers that say how large their arrays get for such steps
+(``mixed_step_array_capacity``); a step whose plan outgrows that room runs without a graph.
 """
 
 from __future__ import annotations
 
 from typing import Sequence
 
+import numpy as np
 import torch
 
-from tandem_b200.engine.executor import Executor, StepEntry
+from tandem_b200.engine.executor import Executor, OutOfPages, StepEntry
 from tandem_b200.kernels import ops
-from tandem_b200.parts.base import StepContext
+from tandem_b200.parts.base import PlanTooLarge, StepContext
 
 
 def bucket_sizes(max_batch: int) -> list:
@@ -41,18 +52,22 @@ def bucket_sizes(max_batch: int) -> list:
 class _Captured:
     """One bucket: the static batch description, its graph and its logits."""
 
-    def __init__(self, executor: Executor, bucket: int, max_model_len: int) -> None:
-        self.executor, self.bucket = executor, bucket
+    def __init__(self, executor: Executor, bucket: int, max_model_len: int, seqs: int = 0) -> None:
+        """``bucket`` token rows; ``seqs`` = 0: as many requests, one token each; else up to ``seqs`` requests
+        that share the rows among them (prompt portions beside single tokens)."""
+        self.executor, self.bucket, self.seqs, self.mixed = executor, bucket, seqs or bucket, bool(seqs)
         m = executor.manager
         self.width = -(-max_model_len // m.page_size)
-        self.sizes = {"ids": bucket, "positions": bucket, "seq_of_token": bucket, "cu": bucket + 1, "starts": bucket,
-                      "slots": bucket, "rows": bucket, "pending": bucket}
+        self.sizes = {"ids": bucket, "positions": bucket, "seq_of_token": bucket, "cu": self.seqs + 1, "starts": self.seqs,
+                      "slots": self.seqs, "rows": self.seqs, "pending": bucket}
         for g in range(len(m.groups)):
-            self.sizes[("table", g)] = bucket * self.width
+            self.sizes[("table", g)] = self.seqs * self.width
             self.sizes[("kvslots", g)] = bucket
         capacity: dict = {}
         for mixer in executor.mixers:
-            if hasattr(mixer, "step_array_capacity"):
+            if seqs:
+                mixer.mixed_step_array_capacity(bucket, seqs, max_model_len, m.page_size, capacity)
+            elif hasattr(mixer, "step_array_capacity"):
                 mixer.step_array_capacity(bucket, max_model_len, m.page_size, capacity)
         self.extra_keys = list(capacity)
         for key, n in capacity.items():
@@ -73,6 +88,7 @@ class _Captured:
         self.graph = None
         self.logits = None
         self.launches = 0
+        self.replays = 0
 
     def view(self, k):
         return self.device[self.offsets[k]: self.offsets[k] + self.sizes[k]]
@@ -136,8 +152,87 @@ class _Captured:
             ops.take_tokens(self.view("ids"), self.view("pending"), ex.pending_tokens)
         return ctx
 
+    def fill_mixed(self, entries: Sequence[StepEntry]) -> StepContext:
+        """The same for a step whose requests bring any number of tokens, ``bucket`` at most in all.  Raises
+        ``PlanTooLarge`` (nothing has been copied then) if a mixer's plan does not fit its room."""
+        ex, m, ps, Tb, Sb = self.executor, self.executor.manager, self.executor.manager.page_size, self.bucket, self.seqs
+        starts = [m.num_tokens(e.request_id) for e in entries]
+        lens = [len(e.tokens) for e in entries]
+        slots = [m.slot(e.request_id) for e in entries]
+        T, B = sum(lens), len(entries)
+        ctx = StepContext(
+            dtype=ex.decoder.dtype, device=ex.device, num_tokens=Tb, num_seqs=Sb, token_ids=self.view("ids"),
+            positions=self.view("positions"), seq_of_token=self.view("seq_of_token"), cu_seqlens=self.view("cu"),
+            seq_starts=self.view("starts"), state_slots=self.view("slots"), host_starts=starts, host_lens=lens,
+            host_slots=slots, max_new=max(lens), max_total=max(s + n for s, n in zip(starts, lens)), storage=ex.storage,
+            page_size=ps, static_layout=True,
+        )
+        extras: dict = {}
+        for mixer in ex.mixers:  # first of all: the one thing that can fail
+            mixer.step_arrays(ctx, extras)
+        for key in self.extra_keys:
+            if len(extras.get(key, ())) > self.sizes[("extra", key)]:
+                raise PlanTooLarge(f"step array {key} has {len(extras[key])} entries, the graph has room for {self.sizes[('extra', key)]}")
+        self.turn = 1 - self.turn
+        self.host, self.host_np = self.hosts[self.turn], self.hosts_np[self.turn]
+        if self.copied[self.turn] is not None:
+            self.copied[self.turn].synchronize()  # almost always long past
+        ids = np.zeros(Tb, dtype=np.int32)
+        positions = np.zeros(Tb, dtype=np.int32)
+        seq_of = np.zeros(Tb, dtype=np.int32)
+        pending = np.full(Tb, -1, dtype=np.int32)
+        cu, rows, any_pending = [0], [], False
+        for b, (e, start, n) in enumerate(zip(entries, starts, lens)):
+            row = cu[-1]
+            ids[row: row + n] = e.tokens
+            if e.pending is not None:  # only the newest token can still be on its way
+                ids[row + n - 1] = 0
+                pending[row + n - 1] = e.pending
+                any_pending = True
+            positions[row: row + n] = np.arange(start, start + n, dtype=np.int32)
+            seq_of[row: row + n] = b
+            rows.extend(row + w for w in e.want)
+            cu.append(row + n)
+        self.num_rows = len(rows)
+        self.put("ids", ids)
+        self.put("pending", pending)
+        self.put("positions", positions)
+        self.put("seq_of_token", seq_of)
+        self.put("cu", cu + [T] * (Sb - B))
+        self.put("starts", starts + [0] * (Sb - B))
+        self.put("slots", slots + [ex.storage.scratch_slot] * (Sb - B))
+        self.put("rows", rows + [0] * (Sb - len(rows)))
+        for g in range(len(m.groups)):
+            o = self.offsets[("table", g)]
+            block = self.host_np[o: o + Sb * self.width].reshape(Sb, self.width)
+            kvslots = np.full(Tb, -1, dtype=np.int32)
+            for b, (e, start, n) in enumerate(zip(entries, starts, lens)):
+                t = m.table(g, e.request_id)
+                if len(t) * ps < start + n:
+                    raise OutOfPages(f"request {e.request_id!r} holds {len(t)} pages, {start + n} tokens need more")
+                block[b, : len(t)] = t
+                pos = np.arange(start, start + n)
+                pages = np.asarray(t, dtype=np.int64)[pos // ps]
+                if (pages < 0).any():
+                    raise RuntimeError(f"position {int(pos[pages < 0][0])} of {e.request_id!r} lies in a page that was given back")
+                kvslots[cu[b]: cu[b] + n] = pages * ps + pos % ps
+            self.put(("kvslots", g), kvslots)
+        for key in self.extra_keys:
+            self.put(("extra", key), extras.get(key, []))
+            ctx.extras[key] = self.view(("extra", key))
+        for g in range(len(m.groups)):
+            ctx.tables[g] = (self.view(("table", g)).view(Sb, self.width), self.view(("kvslots", g)))
+        self.device.copy_(self.host, non_blocking=True)
+        if self.copied[self.turn] is None:
+            self.copied[self.turn] = torch.cuda.Event()
+        self.copied[self.turn].record()
+        ex.h2d_bytes_last = self.host.numel() * 4
+        if any_pending:
+            ops.take_tokens(self.view("ids"), self.view("pending"), ex.pending_tokens)
+        return ctx
+
     def capture(self, entries: Sequence[StepEntry]) -> None:
-        ctx = self.fill(entries)
+        ctx = self.fill_mixed(entries) if self.mixed else self.fill(entries)
         rows = self.view("rows")
         torch.cuda.synchronize()
         before = ops.launches
@@ -147,11 +242,29 @@ class _Captured:
         self.launches = ops.launches - before
 
 
+MIXED_BUCKETS = (8, 16, 32, 64, 128, 256)  # token rows of the graphs for steps with prompt portions
+MIXED_MAX_TOKENS = MIXED_BUCKETS[-1]  # beyond this a step keeps the device busy longer than the host needs to launch it
+
+
 class DecodeGraphs:
     def __init__(self, executor: Executor, max_batch: int, max_model_len: int) -> None:
         self.executor, self.max_model_len = executor, max_model_len
         self.buckets = bucket_sizes(max_batch)
         self.captured: dict = {}
+        if executor.device.type == "cuda":
+            # a padded batch may be the first to reach a library product, and a library cannot be set up while a stream captures
+            a = torch.zeros((16, 16), dtype=torch.bfloat16, device=executor.device)
+            torch.mm(a, a)
+        # steps with prompt portions: only if every mixer that plans on the host can say how large such a plan gets
+        self.mixed = all(hasattr(mixer, "mixed_step_array_capacity") for mixer in executor.mixers) and self._mixed_has_room()
+        self.mixed_fallbacks = 0  # steps that were meant for a graph and ran without (their plan outgrew it)
+
+    def _mixed_has_room(self) -> bool:
+        probe: dict = {}
+        m = self.executor.manager
+        for mixer in self.executor.mixers:
+            mixer.mixed_step_array_capacity(MIXED_BUCKETS[0], min(MIXED_BUCKETS[0], self.buckets[-1]), self.max_model_len, m.page_size, probe)
+        return bool(probe) or not self.executor.mixers
 
     @classmethod
     def maybe(cls, executor: Executor, max_batch: int, max_model_len: int):
@@ -165,36 +278,66 @@ class DecodeGraphs:
                 return None
         return cls(executor, max_batch, max_model_len)
 
+    def _decodes(self, entries: Sequence[StepEntry]) -> bool:
+        return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+
     def takes(self, entries: Sequence[StepEntry]) -> bool:
-        return (0 < len(entries) <= self.buckets[-1]
-                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
-                and all(self.executor.manager.num_tokens(e.request_id) < self.max_model_len for e in entries))
+        if not (0 < len(entries) <= self.buckets[-1]
+                and all(self.executor.manager.num_tokens(e.request_id) + len(e.tokens) <= self.max_model_len for e in entries)):
+            return False
+        if self._decodes(entries):
+            return True
+        tokens = sum(len(e.tokens) for e in entries)
+        return (self.mixed and tokens <= MIXED_MAX_TOKENS and sum(len(e.want) for e in entries) <= self._mixed_seqs(tokens)
+                and len(entries) <= self._mixed_seqs(tokens))
 
     def bucket_of(self, n: int) -> int:
         return next(b for b in self.buckets if b >= n)
+
+    def _mixed_bucket(self, tokens: int) -> int:
+        return next(b for b in MIXED_BUCKETS if b >= tokens)
+
+    def _mixed_seqs(self, tokens: int) -> int:
+        return min(self._mixed_bucket(tokens), self.buckets[-1])
 
     def launches_per_replay(self, entries: Sequence[StepEntry]) -> int:
         cap = self.captured.get(self.bucket_of(len(entries)))
         return cap.launches if cap else 0
 
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Same contract as ``Executor.run`` for a step of single tokens that all want logits."""
+        """Same contract as ``Executor.run``, for the steps that ``takes`` accepts."""
         ex = self.executor
         ex.validate(entries)
-        bucket = self.bucket_of(len(entries))
-        cap = self.captured.get(bucket)
+        decodes = self._decodes(entries)
+        tokens = sum(len(e.tokens) for e in entries)
+        key = self.bucket_of(len(entries)) if decodes else ("mixed", self._mixed_bucket(tokens))
+        cap = self.captured.get(key)
         if cap is None:
             logits = ex.run(entries)  # the first step of a bucket runs eagerly (this also builds what is built lazily)
-            cap = _Captured(ex, bucket, self.max_model_len)
-            with torch.inference_mode():
-                cap.capture(entries)
-            self.captured[bucket] = cap
+            cap = _Captured(ex, key, self.max_model_len) if decodes else _Captured(ex, key[1], self.max_model_len, self._mixed_seqs(tokens))
+            try:
+                with torch.inference_mode():
+                    cap.capture(entries)
+            except PlanTooLarge:
+                self.mixed_fallbacks += 1
+                return logits
+            self.captured[key] = cap
             return logits
         for e in entries:
             if ex.manager.num_tokens(e.request_id) == 0:
                 ex.storage.reset_state(ex.manager.slot(e.request_id))
-        cap.fill(entries)
+        if decodes:
+            cap.fill(entries)
+            wanted = len(entries)
+        else:
+            try:
+                cap.fill_mixed(entries)
+            except PlanTooLarge:
+                self.mixed_fallbacks += 1
+                return ex.run(entries)
+            wanted = cap.num_rows
         cap.graph.replay()
+        cap.replays += 1
         ops.launches += cap.launches
         ex.num_steps += 1
-        return cap.logits[: len(entries)]
+        return cap.logits[:wanted]

@@ -19,6 +19,7 @@ from typing import Optional
 import torch
 
 from tandem_b200.kernels import ops
+from tandem_b200.parts.base import PlanTooLarge
 from tandem_b200.kernels.build import load_library
 
 ITEM_INTS = 6  # token row, request, key begin, key end, first item of the request, its item count
@@ -127,13 +128,14 @@ def _item_steps(p0: int, ntok: int, per_tile: int, window: Optional[int]) -> int
 
 
 def plan_prefill_queues(seqs, groups: int, num_kv_heads: int, window: Optional[int], blocks: int,
-                        tile_rows: int = TILE_ROWS) -> list:
+                        tile_rows: int = TILE_ROWS, fixed_blocks: bool = False) -> list:
     """The tcgen05 kernel's plan.  ``seqs`` as for ``plan_prefill``; an item is up to two tiles' worth
     of consecutive tokens of a request for one kv head, [first token row, request, first position,
     number of tokens, kv head].  One persistent block per SM walks a queue of items; the queues are
     balanced here (heaviest item first, each to the block with the least work so far), so that the
     kernel neither counts nor fetches anything at run time.  Returns [queue position][block][5];
-    an item without tokens ends a block's queue."""
+    an item without tokens ends a block's queue.  ``fixed_blocks``: queues for all ``blocks`` blocks
+    even where the items are fewer (a CUDA graph launches the same grid whatever the step brings)."""
     import heapq
 
     per_tile = tile_rows // groups
@@ -146,7 +148,7 @@ def plan_prefill_queues(seqs, groups: int, num_kv_heads: int, window: Optional[i
     if not items:
         return []
     items.sort(key=lambda x: -x[0])
-    blocks = max(1, min(blocks, len(items)))
+    blocks = max(1, blocks if fixed_blocks else min(blocks, len(items)))
     queues = [[] for _ in range(blocks)]
     heap = [(0.0, c) for c in range(blocks)]
     for cost, item in items:
@@ -155,6 +157,15 @@ def plan_prefill_queues(seqs, groups: int, num_kv_heads: int, window: Optional[i
         heapq.heappush(heap, (load + cost, c))
     longest = max(len(q) for q in queues)
     return [[q[k] if k < len(q) else [0] * WORK_INTS for q in queues] for k in range(longest)]
+
+
+def prefill_queue_capacity(tokens: int, seqs: int, groups: int, num_kv_heads: int, blocks: int, tile_rows: int = TILE_ROWS) -> int:
+    """Queue positions that ``plan_prefill_queues`` is given room for in a CUDA graph for steps of up to
+    ``tokens`` tokens of up to ``seqs`` requests: the items at their most (every request's last item may be
+    short) shared out evenly, and two more; a step whose balance by cost needs more runs without a graph."""
+    per_item = 2 * (tile_rows // groups)
+    items = (tokens // per_item + min(seqs, tokens)) * num_kv_heads
+    return -(-items // max(1, blocks)) + 2
 
 
 def prefill_plan(seqs, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: Optional[int],
@@ -305,10 +316,25 @@ def plan_step(ctx, window: Optional[int], num_heads: int, num_kv_heads: int, hea
     if tcgen05_prefill_applies(head_dim, ctx.page_size):
         from tandem_b200.kernels.gemm_bf16 import sm_count
 
-        queues = plan_prefill_queues(several, groups, num_kv_heads, window, sm_count(ctx.device))
-        out[key + ("tiles",)] = [x for row in queues for item in row for x in item]
+        blocks = sm_count(ctx.device)
+        queues = plan_prefill_queues(several, groups, num_kv_heads, window, blocks, fixed_blocks=ctx.static_layout)
+        if ctx.static_layout:  # every queue position of the graph's capacity, empty ones included; both kernels always run
+            import numpy as np
+
+            capacity = prefill_queue_capacity(ctx.num_tokens, ctx.num_seqs, groups, num_kv_heads, blocks)
+            if len(queues) > capacity:
+                raise PlanTooLarge(f"{len(queues)} queue positions, the graph has room for {capacity}")
+            laid_out = np.zeros((capacity, blocks, WORK_INTS), dtype=np.int32)
+            if queues:
+                laid_out[: len(queues)] = np.asarray(queues, dtype=np.int32)
+            out[key + ("tiles",)] = laid_out.reshape(-1)
+            ctx.scratch[key] = (1, capacity)
+            return
         ctx.scratch[key] = (len(items), len(queues))
+        out[key + ("tiles",)] = [x for row in queues for item in row for x in item]
     else:
+        if ctx.static_layout:
+            raise PlanTooLarge("steps with prompt portions are captured only where the tcgen05 prefill kernel applies")
         tiles = plan_prefill(several, groups)
         out[key + ("tiles",)] = [x for t in tiles for x in t]
         ctx.scratch[key] = (len(items), len(tiles))

@@ -73,6 +73,27 @@ class PagedAttention(Mixer):
         out[key + ("tiles",)] = 0
         attention_kernels._workspace(self.qkv.device, items, s.num_kv_heads, groups, s.head_dim)
 
+    def mixed_step_array_capacity(self, tokens: int, seqs: int, max_model_len: int, page_size: int, out: dict) -> None:
+        """The same for steps of up to ``tokens`` tokens of up to ``seqs`` requests, prompt portions among
+        them (``ctx.static_layout``): decode items for the requests that bring one token, and the prefill
+        kernel's queues at their full length.  Leaves ``out`` alone where such steps cannot be captured."""
+        s = self.spec
+        key = attention_kernels.plan_key(s.window, s.num_heads, s.num_kv_heads, s.head_dim, self.qkv.dtype)
+        groups = s.num_heads // s.num_kv_heads
+        if key + ("items",) in out or \
+                not attention_kernels.tensor_core_path_applies(self.qkv.dtype, s.head_dim, page_size, groups) or \
+                not attention_kernels.tcgen05_prefill_applies(s.head_dim, page_size):
+            return
+        from tandem_b200.kernels.gemm_bf16 import sm_count
+
+        blocks = sm_count(self.qkv.device)
+        items = attention_kernels.decode_items_capacity(seqs, s.num_kv_heads, max_model_len)
+        out[key + ("items",)] = items * attention_kernels.ITEM_INTS
+        out[key + ("count",)] = 1
+        out[key + ("tiles",)] = (attention_kernels.prefill_queue_capacity(tokens, seqs, groups, s.num_kv_heads, blocks)
+                                 * blocks * attention_kernels.WORK_INTS)
+        attention_kernels._workspace(self.qkv.device, items, s.num_kv_heads, groups, s.head_dim)
+
     def forward(self, x, ctx: StepContext, defer: bool = False):
         s = self.spec
         qkv = ops.linear(x, self.qkv)

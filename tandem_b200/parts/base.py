@@ -72,6 +72,10 @@ class StepContext:
     extras: dict = field(default_factory=dict)  # key -> int32 device array a mixer asked for (Mixer.step_arrays)
     tables: dict = field(default_factory=dict)  # group -> (block_table, slots)
     run: int = 0  # position in ModelPlan.order of the run in flight
+    # The step is captured into, or replayed from, a CUDA graph that also takes prompt portions: num_tokens and
+    # num_seqs are the graph's capacities (rows beyond the real tokens are padding), and the arrays of
+    # ``Mixer.step_arrays`` must keep the layout of their capacity whatever the step brings.
+    static_layout: bool = False
     scratch: dict = field(default_factory=dict)  # per-step values parts may share (keyed by them)
 
     def kv(self, mixer: Any = None) -> KVView:
@@ -83,6 +87,11 @@ class StepContext:
         """[max requests + 1, *shape] tensor of the asking mixer's per-request state in the run in
         flight; the last row belongs to no request (rows that pad a captured batch point there)."""
         return self.storage.state[self.storage.user(self.run, mixer)]
+
+
+class PlanTooLarge(RuntimeError):
+    """Raised from ``Mixer.step_arrays`` under ``ctx.static_layout``: this step's arrays do not fit the room
+    that the mixer asked for, so the step runs without a CUDA graph."""
 
 
 class Mixer:
@@ -105,6 +114,10 @@ class Mixer:
     # the host side of the batch (ctx.host_starts, ctx.host_lens, ...).  It may add integer arrays
     # to ``out`` under keys of its own (skipping keys that are already there); they travel to the
     # device with the batch description and appear as ``ctx.extras[key]`` in ``forward``.
+    # A mixer that does so tells CUDA graphs how large the arrays can get:
+    # ``step_array_capacity(self, bucket, max_model_len, page_size, out)`` for steps of up to ``bucket`` single
+    # tokens, and (optional) ``mixed_step_array_capacity(self, tokens, seqs, max_model_len, page_size, out)``
+    # for steps of up to ``tokens`` tokens of up to ``seqs`` requests (``ctx.static_layout``); out[key] = entries.
 
 
 class FeedForward:

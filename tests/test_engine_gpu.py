@@ -194,6 +194,83 @@ def test_cuda_graph_decode_follows_the_plain_implementation(tiny_folder, name, p
             assert err <= 1.5 * base + 0.02, (rid, pos, err, base)
 
 
+def test_cuda_graphs_take_short_steps_with_prompt_portions(tmp_path):
+    """Steps of up to 256 tokens that bring prompt portions are replayed from CUDA graphs too (where the
+    tcgen05 prefill kernel applies: a head size of 64 here): portions of 2 to 40 tokens of up to four
+    requests beside single tokens of others, padded to buckets of 16 to 128 token rows, on pages that
+    finished requests gave back; every row of logits against the plain implementation."""
+    import replay_cases as rc
+    from tandem_b200.engine.core import build_executor, load_model
+    from tandem_b200.engine.cuda_graph import DecodeGraphs
+    from tandem_b200.engine.executor import StepEntry
+    from tandem_b200.weights.random_init import write_random_model
+
+    config = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=3, hidden_size=136,
+                  num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=264, vocab_size=1003,
+                  rope_theta=50000.0, rms_norm_eps=2e-6, tie_word_embeddings=False, max_position_embeddings=512)
+    folder = str(tmp_path / "hd64")
+    write_random_model(config, folder, seed=11, dtype="bfloat16", std=0.05)
+    cfg, w64 = plain.read_folder(folder, torch.float64)
+    _, w16 = plain.read_folder(folder, torch.bfloat16)
+    g = torch.Generator().manual_seed(77)
+    lengths = {f"r{i}": int(n) for i, n in enumerate(torch.randint(40, 200, (9,), generator=g))}
+    toks = {rid: random_tokens(900 + i, n, 1003) for i, (rid, n) in enumerate(lengths.items())}
+    decoder, _ = load_model(folder, "bfloat16", "cuda:0")
+    ex = build_executor(decoder, page_size=16, num_pages=40, max_requests=8)
+    log = rc.PageLog(ex.manager)
+    graphs = DecodeGraphs.maybe(ex, 8, 512)
+    assert graphs is not None and graphs.mixed
+    at = {rid: 0 for rid in toks}
+    got = {rid: {} for rid in toks}
+    waiting, live, steps, replayed_before = list(toks), [], 0, 0
+    while waiting or live:
+        while waiting and len(live) < 4 and ex.manager.free_pages(0) * 16 >= lengths[waiting[0]] + 16:
+            rid = waiting.pop(0)
+            ex.manager.begin(rid)
+            live.append(rid)
+        entries = []
+        for rid in live:
+            left = lengths[rid] - at[rid]
+            # most steps cut prompts into short portions; a request near its end goes token by token
+            n = 1 if left <= 12 else min(left, int(torch.randint(2, 41, (1,), generator=g)))
+            entries.append(StepEntry(rid, toks[rid][at[rid]: at[rid] + n], [n - 1] if n > 1 or left <= 12 else []))
+        for e in entries:
+            assert ex.manager.grow(e.request_id, at[e.request_id] + len(e.tokens))
+        if graphs.takes(entries):
+            logits = graphs.run(entries).double().cpu()
+        else:
+            assert sum(len(e.tokens) for e in entries) > 256 or sum(len(e.want) for e in entries) > 8
+            logits = ex.run(entries).double().cpu()
+        row = 0
+        for e in entries:
+            ex.manager.commit(e.request_id, len(e.tokens))
+            for w in e.want:
+                got[e.request_id][at[e.request_id] + w] = logits[row]
+                row += 1
+            at[e.request_id] += len(e.tokens)
+        assert row == logits.shape[0]
+        for rid in [r for r in live if at[r] >= lengths[r]]:
+            ex.manager.end(rid)
+            live.remove(rid)
+        ex.manager.check()
+        steps += 1
+    assert ex.manager.all_free() and log.reused_beside_live >= 2
+    mixed = {k: c for k, c in graphs.captured.items() if isinstance(k, tuple)}
+    assert len(mixed) >= 3 and sum(c.replays for c in mixed.values()) >= 10, {k: c.replays for k, c in graphs.captured.items()}
+    assert graphs.mixed_fallbacks == 0
+    for rid, rows in got.items():
+        assert rows, rid
+        ref = plain.forward(cfg, w64, toks[rid], torch.float64)
+        low = plain.forward(cfg, w16, toks[rid], torch.bfloat16).double()
+        base = (low - ref).abs().max().item()
+        for pos, row in rows.items():
+            err = (row - ref[pos]).abs().max().item()
+            assert err <= 1.5 * base + 0.02, (rid, pos, err, base)
+    from tandem_b200.kernels import ops as kernel_ops
+
+    kernel_ops.check_status("cuda")
+
+
 def test_a_fault_recorded_by_a_kernel_stops_the_engine(tiny_folder):
     """Kernels that survive a fault (a bounded wait that gave up, a missing page) record it in a
     status word; the engine reads the word with the step's tokens and raises instead of handing
