@@ -25,7 +25,7 @@ class EngineConfig:
     num_kv_blocks: Optional[int] = None  # pages per cache group; overrides kv_cache_memory_gb
     kv_cache_memory_gb: float = 1.0
     seed: int = 0
-    cuda_graph: bool = True  # decode-only steps replay CUDA graphs
+    cuda_graph: bool = True  # decode-only steps, and short steps with prompt portions, replay CUDA graphs
     cuda_graph_max_bs: int = 64
     overlap_schedule: bool = True  # launch step N before step N-1's tokens reach the host (config.py:64 of the reference)
 
