@@ -26,8 +26,9 @@ the host.  So steps of up to ``MIXED_MAX_TOKENS`` tokens are captured as well, p
 (8, 16, 32, 64, 128, 256) for up to as many requests as the decode graphs take: token rows beyond the
 step's are padding (token 0, no cache slot, in no attention item), the attention plan keeps the layout
 of its capacity (``StepContext.static_layout``), and both attention kernels run in every replay, one of
-them perhaps with nothing to do.  This needs mixers that say how large their arrays get for such steps
-(``mixed_step_array_capacity``); a step whose plan outgrows that room runs without a graph.
+them perhaps with nothing to do.  This needs mixers that declare ``capturable_portions = True`` (what
+``capturable`` says, for requests that bring several tokens too) and say how large their arrays get for
+such steps (``mixed_step_array_capacity``); a step whose plan outgrows that room runs without a graph.
 """
 
 from __future__ import annotations
@@ -54,8 +55,10 @@ class _Captured:
 
     def __init__(self, executor: Executor, bucket: int, max_model_len: int, seqs: int = 0) -> None:
         """``bucket`` token rows; ``seqs`` = 0: as many requests, one token each; else up to ``seqs`` requests
-        that share the rows among them (prompt portions beside single tokens)."""
-        self.executor, self.bucket, self.seqs, self.mixed = executor, bucket, seqs or bucket, bool(seqs)
+        that share the rows among them (prompt portions beside single tokens), and one more that no request
+        ever is: the rows that pad the step are its tokens, so a mixer with state sends them to the state
+        tensor's spare row."""
+        self.executor, self.bucket, self.seqs, self.mixed = executor, bucket, (seqs + 1) if seqs else bucket, bool(seqs)
         m = executor.manager
         self.width = -(-max_model_len // m.page_size)
         self.sizes = {"ids": bucket, "positions": bucket, "seq_of_token": bucket, "cu": self.seqs + 1, "starts": self.seqs,
@@ -66,7 +69,7 @@ class _Captured:
         capacity: dict = {}
         for mixer in executor.mixers:
             if seqs:
-                mixer.mixed_step_array_capacity(bucket, seqs, max_model_len, m.page_size, capacity)
+                mixer.mixed_step_array_capacity(bucket, self.seqs, max_model_len, m.page_size, capacity)
             elif hasattr(mixer, "step_array_capacity"):
                 mixer.step_array_capacity(bucket, max_model_len, m.page_size, capacity)
         self.extra_keys = list(capacity)
@@ -179,7 +182,7 @@ class _Captured:
             self.copied[self.turn].synchronize()  # almost always long past
         ids = np.zeros(Tb, dtype=np.int32)
         positions = np.zeros(Tb, dtype=np.int32)
-        seq_of = np.zeros(Tb, dtype=np.int32)
+        seq_of = np.full(Tb, B, dtype=np.int32)  # padding rows: the tokens of a request of their own, behind the real ones
         pending = np.full(Tb, -1, dtype=np.int32)
         cu, rows, any_pending = [0], [], False
         for b, (e, start, n) in enumerate(zip(entries, starts, lens)):
@@ -198,7 +201,7 @@ class _Captured:
         self.put("pending", pending)
         self.put("positions", positions)
         self.put("seq_of_token", seq_of)
-        self.put("cu", cu + [T] * (Sb - B))
+        self.put("cu", cu + [Tb] * (Sb - B))
         self.put("starts", starts + [0] * (Sb - B))
         self.put("slots", slots + [ex.storage.scratch_slot] * (Sb - B))
         self.put("rows", rows + [0] * (Sb - len(rows)))
@@ -255,8 +258,10 @@ class DecodeGraphs:
             # a padded batch may be the first to reach a library product, and a library cannot be set up while a stream captures
             a = torch.zeros((16, 16), dtype=torch.bfloat16, device=executor.device)
             torch.mm(a, a)
-        # steps with prompt portions: only if every mixer that plans on the host can say how large such a plan gets
-        self.mixed = all(hasattr(mixer, "mixed_step_array_capacity") for mixer in executor.mixers) and self._mixed_has_room()
+        # steps with prompt portions: only if every mixer reads such a batch from the device arrays alone, and every
+        # mixer that plans on the host can say how large such a plan gets
+        self.mixed = (all(getattr(mixer, "capturable_portions", False) for mixer in executor.decoder.mixers())
+                      and all(hasattr(mixer, "mixed_step_array_capacity") for mixer in executor.mixers) and self._mixed_has_room())
         self.mixed_fallbacks = 0  # steps that were meant for a graph and ran without (their plan outgrew it)
 
     def _mixed_has_room(self) -> bool:

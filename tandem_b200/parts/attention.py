@@ -22,6 +22,7 @@ from tandem_b200.parts.shared import position_encoding
 
 class PagedAttention(Mixer):
     capturable = True  # forward only launches kernels: decode steps may be captured in CUDA graphs
+    capturable_portions = True  # and so may steps in which requests bring several tokens (it reads the batch from device arrays only)
     takes_deferred = True  # x may be a norm whose scale is pending; with ``defer`` the output projection may stay pending
 
     @staticmethod

@@ -118,6 +118,9 @@ class Mixer:
     # ``step_array_capacity(self, bucket, max_model_len, page_size, out)`` for steps of up to ``bucket`` single
     # tokens, and (optional) ``mixed_step_array_capacity(self, tokens, seqs, max_model_len, page_size, out)``
     # for steps of up to ``tokens`` tokens of up to ``seqs`` requests (``ctx.static_layout``); out[key] = entries.
+    # ``capturable = True``: ``forward`` of a step of single tokens only launches kernels and reads the batch from
+    # the context's device arrays, never from its host-side lists; ``capturable_portions = True``: the same holds
+    # for steps in which requests bring several tokens.
 
 
 class FeedForward:
