@@ -762,6 +762,48 @@ def test_overlap_scheduling_changes_no_token(tiny_folder, dtype):
     assert small == sync and eng.scheduler.num_preemptions > 0
 
 
+def test_overlap_scheduling_changes_no_token_in_captured_steps_with_prompt_portions(tmp_path):
+    """A head size with which steps that bring prompt portions are replayed from CUDA graphs: tokens that
+    are still on their way enter such a step on the device like any other.  Requests arrive while others
+    decode (a small budget cuts their prompts), greedy and seeded; the overlap loop returns what the
+    synchronous loop returns, and most steps with portions were replays."""
+    from tandem_b200 import EngineConfig, LLMEngine, SamplingParams
+    from tandem_b200.weights.random_init import write_random_model
+
+    config = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=128,
+                  num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=256, vocab_size=1000,
+                  rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=512)
+    folder = str(tmp_path / "hd64")
+    write_random_model(config, folder, seed=3, dtype="bfloat16", std=0.1)
+    prompts = [random_tokens(300 + i, n, 1000) for i, n in enumerate([33, 9, 70, 2, 48, 17, 90, 5])]
+    params = [SamplingParams(max_tokens=n, temperature=0.0, ignore_eos=True) if i % 2 == 0 else
+              SamplingParams(max_tokens=n, temperature=0.8, top_p=0.9, seed=40 + i, ignore_eos=True)
+              for i, n in enumerate((20, 7, 12, 30, 9, 25, 6, 14))]
+
+    def run(overlap):
+        eng = LLMEngine(EngineConfig(model=folder, dtype="bfloat16", block_size=16, max_num_batched_tokens=40, num_kv_blocks=64,
+                                     max_num_seqs=8, schedule_policy="decode_first", overlap_schedule=overlap), load_tokenizer=False)
+        assert eng.graphs is not None and eng.graphs.mixed
+        ids = [eng.add_request(p, sp) for p, sp in zip(prompts[:3], params[:3])]
+        final, steps = {}, 0
+        while eng.has_unfinished_requests() or len(ids) < len(prompts):
+            if steps % 4 == 3 and len(ids) < len(prompts):  # the others arrive while these decode
+                ids.append(eng.add_request(prompts[len(ids)], params[len(ids)]))
+            for out in eng.step():
+                if out.finished:
+                    final[out.request_id] = out.output_token_ids
+            steps += 1
+        eng.cache.check()
+        assert eng.cache.all_free() and eng.inflight is None
+        return [final[i] for i in ids], eng
+
+    sync, _ = run(False)
+    over, eng = run(True)
+    assert over == sync and all(len(t) == sp.max_tokens for t, sp in zip(sync, params))
+    mixed = [c for k, c in eng.graphs.captured.items() if isinstance(k, tuple)]
+    assert mixed and sum(c.replays for c in mixed) >= 5 and eng.graphs.mixed_fallbacks == 0
+
+
 @dataclass(frozen=True)
 class RoutedSpec:
     family = "feed_forward"
