@@ -3,8 +3,8 @@
 A step in which every request brings exactly one token launches a few hundred small kernels; at
 small batches their launch cost exceeds their run time.  Such steps are captured once per batch
 *bucket* (1, 2, 4, 8, 16, 24, 32, ... as python/tandem/executor/cuda_graph.py:34-38 of
-12vivi/tandem, and 12 beside them: up to 14 rows the products of a layer are this package's
-streaming kernel, which 16 rows are not) and replayed: the batch description lives in one static int32 buffer on the
+12vivi/tandem; 12 beside them, and the most rows whose products over the model's width this
+package's streaming kernel still takes, 14 for a width of 4,096: at 16 rows they are the library's) and replayed: the batch description lives in one static int32 buffer on the
 device, refilled by a single copy before each replay.  Rows that pad a batch up to its bucket
 carry token 0 at position 0 with a negative cache slot (the cache-write kernel skips them) and no
 attention item; their outputs are never read.  Logits and sampling stay outside the graph
@@ -43,8 +43,8 @@ from tandem_b200.kernels import ops
 from tandem_b200.parts.base import PlanTooLarge, StepContext
 
 
-def bucket_sizes(max_batch: int) -> list:
-    sizes = [b for b in (1, 2, 4, 8, 12, 16) if b <= max_batch] + list(range(24, max_batch + 1, 8))
+def bucket_sizes(max_batch: int, also: Sequence[int] = ()) -> list:
+    sizes = [b for b in (1, 2, 4, 8, 12, 16) + tuple(also) if 0 < b <= max_batch] + list(range(24, max_batch + 1, 8))
     if max_batch not in sizes:
         sizes.append(max_batch)
     return sorted(set(sizes))
@@ -252,7 +252,10 @@ MIXED_MAX_TOKENS = MIXED_BUCKETS[-1]  # beyond this a step keeps the device busy
 class DecodeGraphs:
     def __init__(self, executor: Executor, max_batch: int, max_model_len: int) -> None:
         self.executor, self.max_model_len = executor, max_model_len
-        self.buckets = bucket_sizes(max_batch)
+        # a bucket of its own for the largest batch whose products over the model's width are still the streaming
+        # kernel's (14 rows of 4,096, 11 of 5,120): one more row and all of them go to the library
+        width = executor.decoder.embedding.shape[1]
+        self.buckets = bucket_sizes(max_batch, (ops.streaming_row_limit(width),) if executor.decoder.dtype == torch.bfloat16 else ())
         self.captured: dict = {}
         if executor.device.type == "cuda":
             # a padded batch may be the first to reach a library product, and a library cannot be set up while a stream captures

@@ -260,6 +260,14 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- matrix products
+def streaming_row_limit(width: int) -> int:
+    """The most rows of ``width`` elements that the streaming kernel takes (bfloat16): a batch of so many
+    decoding requests still has its products of that width run by it, one more goes to the library."""
+    from tandem_b200.kernels import gemm_bf16
+
+    return max((m for m in range(1, gemm_bf16.GEMV_MAX_ROWS + 1) if gemm_bf16.gemv_applies(m, 1, width)), default=0)
+
+
 def linear_streams(rows: int, weight: torch.Tensor) -> bool:
     """Whether ``linear`` of so many rows with this weight runs this package's streaming kernel (all of
     whose blocks are resident at once, so that a kernel behind it may move in early)."""
