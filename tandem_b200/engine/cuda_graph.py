@@ -312,6 +312,37 @@ class DecodeGraphs:
         cap = self.captured.get(self.bucket_of(len(entries)))
         return cap.launches if cap else 0
 
+    def capture_all(self) -> int:
+        """Capture every bucket now instead of at its first step (12vivi/tandem captures its graphs when the
+        engine is built: python/tandem/executor/cuda_graph.py:104-112), with requests of this method's own on
+        pages that it gives back: one token each for the decode buckets, one request of as many tokens as the
+        bucket has rows for those with prompt portions.  Buckets for which the pool has no room now stay for
+        later.  Returns how many were captured."""
+        ex, m = self.executor, self.executor.manager
+        keys = list(reversed(self.buckets)) + ([("mixed", b) for b in reversed(MIXED_BUCKETS)] if self.mixed else [])
+        captured = 0
+        for key in keys:
+            if key in self.captured:
+                continue
+            lens = [min(key[1], self.max_model_len)] if isinstance(key, tuple) else [1] * key
+            rids = [f"__capture_{i}" for i in range(len(lens))]
+            begun, room = [], len(lens) <= m.slots.num_free
+            try:
+                for rid, n in zip(rids, lens):
+                    if not room:
+                        break
+                    m.begin(rid)
+                    begun.append(rid)
+                    room = m.grow(rid, n)  # False: no pages for so many now; the bucket is captured when a step first needs it
+                entries = [StepEntry(rid, [0] * n, [n - 1]) for rid, n in zip(rids, lens)]
+                if room and self.takes(entries):
+                    self.run(entries)
+                    captured += key in self.captured
+            finally:
+                for rid in begun:
+                    m.end(rid)
+        return captured
+
     def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Same contract as ``Executor.run``, for the steps that ``takes`` accepts."""
         ex = self.executor

@@ -99,6 +99,8 @@ class LLMEngine:
             from tandem_b200.engine.cuda_graph import DecodeGraphs
 
             self.graphs = DecodeGraphs.maybe(self.executor, config.cuda_graph_max_bs, self.max_model_len)
+            if self.graphs is not None and config.cuda_graph_capture_at_start:
+                self.graphs.capture_all()
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: Optional[PromptType] = None, sampling_params: Optional[SamplingParams] = None,
