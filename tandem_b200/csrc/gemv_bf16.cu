@@ -143,8 +143,13 @@ gemv_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w, void* __re
   }
   pdl_wait();  // x is the output of the kernel in front
   if (X_IN_SMEM) {
-    for (int i = threadIdx.x; i < M * pieces; i += GV_THREADS) xs[(i / pieces) * x_stride + i % pieces] = x[i];
-    __syncthreads();
+    // a warp reads only its own part of K of every row: it copies that part and meets nobody but itself
+    const int c0 = s0 * 8, width = min(pieces, s1 * 8) - c0;
+    for (int i = lane; i < M * width; i += 32) {
+      const int row = i / width, c = c0 + i % width;
+      xs[row * x_stride + c] = x[(size_t)row * pieces + c];
+    }
+    __syncwarp();
   } else if (streams) {
     load_x(s0, cur);
   }
