@@ -359,7 +359,7 @@ def test_qwen3_8b_widths_follow_the_plain_implementation_however_they_are_cut():
         ex = build_executor(decoder, page_size=16, num_pages=30, max_requests=4)
         whole = ex.step([StepEntry("w", tokens, list(range(300, 330)))], end=["w"])
         cut, at = [], 0
-        for n in [130, 2, 61, 107] + [1] * 30:
+        for n in [130, 2, 61, 9, 12, 14, 72] + [1] * 30:  # 9 to 14 rows: the streaming products' two-tile form, add and norm riding along
             out = ex.step([StepEntry("p", tokens[at: at + n], [i for i in range(n) if at + i >= 300])])
             at += n
             cut.append(out)
