@@ -227,6 +227,52 @@ def test_overlap_resolves_first_when_pages_are_short():
     assert not s2.may_preempt()
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_the_overlap_loop_under_random_requests_and_tight_pools(seed):
+    """The engine's overlap loop with fake tokens: pools of a few pages, windows, both policies, requests
+    that arrive while others run and end by length, by an end token or by a stop token.  The step in flight
+    is read first exactly when ``may_preempt`` says so; no request is ever preempted with a token on its way
+    (the scheduler raises if one would be), no page is lost, and every request ends."""
+    import random
+
+    rnd = random.Random(seed)
+    page, pages = rnd.choice([2, 4, 8]), rnd.randint(6, 14)
+    window = rnd.choice([None, None, 3 * page])
+    s, cache = make(policy=rnd.choice(["prefill_first", "decode_first"]), pages=pages, page_size=page,
+                    budget=rnd.choice([4, 8, 16]), max_seqs=rnd.randint(2, 5), max_len=pages * page, window=window)
+    todo = [req(f"r{i}", rnd.randint(1, max(1, pages * page // 3)), max_tokens=rnd.randint(1, 12),
+                **({"stop_token_ids": [5]} if i % 3 == 0 else {})) for i in range(14)]
+    inflight, steps, early_reads = None, 0, 0
+
+    def deliver(plan):
+        tokens = {rid: rnd.choice([0, 5, 7, 8, 9, 11]) if rnd.random() < 0.25 else 7 for rid in plan.promised}
+        s.deliver_tokens(plan, tokens)
+
+    while todo or s.has_unfinished() or inflight is not None:
+        if todo and (steps % 3 == 0 or not s.has_unfinished()):
+            s.add_request(todo.pop(0))
+        if inflight is not None and s.may_preempt():
+            deliver(inflight)
+            inflight = None
+            early_reads += 1
+        plan = s.schedule()  # raises if a request with a token on its way had to give way
+        plan.promised = [x.request.request_id for x in plan.scheduled
+                         if x.request.num_computed_tokens + x.num_tokens >= x.request.num_tokens]
+        launched = None
+        if not plan.is_empty:
+            s.book_launch(plan)
+            launched = plan
+        else:
+            assert inflight is not None or plan.preempted or not s.has_unfinished(), "nothing could be placed"
+        previous, inflight = inflight, launched
+        if previous is not None:
+            deliver(previous)
+        cache.check()
+        steps += 1
+        assert steps < 2000
+    assert cache.all_free() and not s.running and not s.waiting
+
+
 def test_a_prompt_that_preempts_itself_is_reported_and_not_admitted_again_in_that_step():
     """prefill_first: the prompt pass comes out empty because the only request reading its prompt
     had to give way itself (a decoding request holds the rest of the pool and is not in that
