@@ -28,6 +28,7 @@ class EngineConfig:
     cuda_graph: bool = True  # decode-only steps, and short steps with prompt portions, replay CUDA graphs
     cuda_graph_max_bs: int = 64
     cuda_graph_capture_at_start: bool = False  # capture every bucket when the engine is built (as the reference does) instead of at its first step
+    small_batch_gemv: bool = True  # False: the library runs every bfloat16 product (cli.py:35-36 of the reference; process-wide)
     overlap_schedule: bool = True  # launch step N before step N-1's tokens reach the host (config.py:64 of the reference)
 
     def __post_init__(self) -> None:

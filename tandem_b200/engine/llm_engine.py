@@ -94,6 +94,10 @@ class LLMEngine:
         self._ids = itertools.count()
         self.num_steps = 0
         self.trace = None  # engine.trace.TraceWriter: every launched step, in the replay tool's format
+        if not config.small_batch_gemv:
+            from tandem_b200.kernels import gemm_bf16
+
+            gemm_bf16.keep_library_products()
         self.graphs = None
         if config.cuda_graph:
             from tandem_b200.engine.cuda_graph import DecodeGraphs

@@ -30,6 +30,7 @@ def _engine_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--no-overlap", action="store_true", help="read every step's tokens before the next step is launched")
     p.add_argument("--cuda-graph-max-bs", type=int, default=64)
     p.add_argument("--cuda-graph-capture-at-start", action="store_true", help="capture every CUDA graph when the engine is built, not at its first use")
+    p.add_argument("--no-small-batch-gemv", action="store_true", help="keep cuBLAS for every bfloat16 product, the decoder projections at small batch too")
     p.add_argument("--engine-seed", type=int, default=0, help="seed of requests that carry none")
 
 
@@ -41,7 +42,7 @@ def _engine_config(args):
         max_num_batched_tokens=args.max_num_batched_tokens, schedule_policy=args.schedule_policy,
         max_model_len=args.max_model_len, block_size=args.block_size, kv_cache_memory_gb=args.kv_cache_gb,
         num_kv_blocks=args.num_kv_blocks, seed=args.engine_seed, cuda_graph=not args.no_cuda_graph, overlap_schedule=not args.no_overlap,
-        cuda_graph_max_bs=args.cuda_graph_max_bs, cuda_graph_capture_at_start=args.cuda_graph_capture_at_start,
+        cuda_graph_max_bs=args.cuda_graph_max_bs, cuda_graph_capture_at_start=args.cuda_graph_capture_at_start, small_batch_gemv=not args.no_small_batch_gemv,
     )
 
 

@@ -25,6 +25,7 @@ prints the table's lines and what the rule would have picked.
 from __future__ import annotations
 
 import ctypes
+from typing import Optional
 
 import torch
 
@@ -245,12 +246,26 @@ def row_class(M: int) -> int:
     return next(c for c in ROW_CLASSES if M <= c) if M <= SKINNY_MAX_ROWS else 0
 
 
+_library_only = False
+
+
+def keep_library_products(on: bool = True) -> None:
+    """Process-wide: every bfloat16 product goes to the library, as ``TANDEM_GEMM=library`` does (12vivi/tandem's
+    ``--no-small-batch-gemv``, python/tandem/entrypoints/cli.py:35-36: keep cuBLAS for the decoder projections)."""
+    global _library_only
+    _library_only = bool(on)
+
+
+def _forced() -> Optional[str]:
+    return "library" if _library_only else ops.env("TANDEM_GEMM")
+
+
 def choose(M: int, N: int, K: int, aligned: bool = True) -> str:
     """"gemv", "skinny" or "library" for a product of these sizes: a fixed rule, the same on every
     run.  ``aligned``: x and the weight are contiguous and start on 16-byte boundaries."""
     can_gemv = gemv_applies(M, N, K) and aligned
     can_skinny = skinny_applies(M, N, K) and aligned
-    forced = ops.env("TANDEM_GEMM")
+    forced = _forced()
     if forced == "library" or (forced == "gemv" and can_gemv) or (forced == "skinny" and can_skinny):
         return forced
     measured = MEASURED.get((N, K), {}).get(row_class(M))
@@ -269,7 +284,7 @@ def choose_gated(M: int, N: int, K: int, aligned: bool = True) -> str:
     or single blocks), or "product" (the product as ``choose`` says, then the activation kernel)."""
     if N % 16:
         return "product"
-    forced = ops.env("TANDEM_GEMM")
+    forced = _forced()
     if M <= GEMV_MAX_ROWS and choose(M, N, K, aligned) == "gemv":
         return "gemv"
     if M <= GEMV_ROWS_ANY_K:

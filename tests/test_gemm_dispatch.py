@@ -38,3 +38,13 @@ def test_a_kernel_can_be_forced_where_it_applies(monkeypatch, forced):
     assert G.choose(4, *QKV) == (forced if forced in ("library", "skinny") else "gemv")
     assert G.choose_gated(256, *GATE_UP) == (forced if forced in ("wide", "pair") else "product")
     assert G.choose_gated(4, *GATE_UP) == ("gemv" if forced not in ("library", "skinny") else "product")
+
+
+def test_the_library_can_be_kept_for_every_product():
+    G.keep_library_products()
+    try:
+        assert G.choose(1, *QKV) == "library" and G.choose(8, *HEAD) == "library"
+        assert G.choose_gated(4, *GATE_UP) == "product" and G.choose_gated(2048, *GATE_UP) == "product"
+    finally:
+        G.keep_library_products(False)
+    assert G.choose(1, *QKV) == "gemv"
